@@ -1,0 +1,598 @@
+// C ABI of libglq_b200: plan builder, launch sequencing, stateless wrappers.
+#include <algorithm>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <tuple>
+#include <vector>
+
+#include "glqb_kernels.cuh"
+
+namespace glqb {
+
+static thread_local std::string g_err;
+
+static int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t _e = (expr);                                                             \
+    if (_e != cudaSuccess) return fail(GLQB_E_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+static inline int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
+
+// One launch of a streaming decode kernel: a set of layers that share format / bit widths /
+// token-column blocks, contiguous in the device table.
+struct Segment {
+  int format, k1, k2, ns, nb;
+  int first, count;          // range in the device table
+  long long total_groups;
+  int per_warp;
+  int grid;
+};
+
+}  // namespace glqb
+
+using namespace glqb;
+
+struct GlqbPlan {
+  std::vector<GlqbLinearDesc> descs;   // in caller order
+  std::vector<int> order;              // device-table position -> caller index
+  std::vector<DevLinear> dev;          // host copy of the device table
+  std::vector<Segment> segs;
+  std::vector<RhtItem> items_in, items_out;
+  DevLinear* d_layers = nullptr;
+  RhtItem* d_items_in = nullptr;
+  RhtItem* d_items_out = nullptr;
+  size_t ws_bytes = 0;
+  int max_batch = 1;
+  int max_bs_in = 32, max_bs_out = 32;
+  int sm_count = 0;
+  int64_t code_bytes = 0, flops = 0;
+  bool timing = false;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  bool have_time = false;
+};
+
+namespace glqb {
+
+// ------------------------------------------------------------------------------------------
+// kernel variant tables
+// ------------------------------------------------------------------------------------------
+typedef void (*MvKernel)(const DevLinear*, int, long long, int, uint8_t*);
+
+template <int K1, int K2>
+static MvKernel trellis_kernel_nb(int nb) {
+  switch (nb) {
+    case 1: return trellis_mv_kernel<K1, K2, 1>;
+    case 2: return trellis_mv_kernel<K1, K2, 2>;
+    case 4: return trellis_mv_kernel<K1, K2, 4>;
+    case 8: if constexpr (K2 == 0) return trellis_mv_kernel<K1, K2, 8>; else return nullptr;
+  }
+  return nullptr;
+}
+
+static MvKernel trellis_kernel(int k1, int k2, int nb) {
+#define T_CASE(A, B) if (k1 == A && k2 == B) return trellis_kernel_nb<A, B>(nb);
+  T_CASE(1, 0) T_CASE(2, 0) T_CASE(3, 0) T_CASE(4, 0)
+  T_CASE(4, 1) T_CASE(4, 2) T_CASE(4, 3) T_CASE(4, 4)
+  T_CASE(2, 2) T_CASE(3, 3) T_CASE(2, 1) T_CASE(3, 1) T_CASE(3, 2)
+#undef T_CASE
+  return nullptr;
+}
+
+template <int NS>
+static MvKernel e8_kernel_nb(int nb) {
+  switch (nb) {
+    case 1: return e8_mv_kernel<NS, 1>;
+    case 2: return e8_mv_kernel<NS, 2>;
+    case 4: return e8_mv_kernel<NS, 4>;
+    case 8: if constexpr (NS <= 2) return e8_mv_kernel<NS, 8>; else return nullptr;
+  }
+  return nullptr;
+}
+
+static MvKernel e8_kernel(int ns, int nb) {
+  switch (ns) {
+    case 1: return e8_kernel_nb<1>(nb);
+    case 2: return e8_kernel_nb<2>(nb);
+    case 3: return e8_kernel_nb<3>(nb);
+    case 4: return e8_kernel_nb<4>(nb);
+  }
+  return nullptr;
+}
+
+static MvKernel pick_kernel(const Segment& s) {
+  return s.format == GLQB_FMT_TRELLIS_3INST ? trellis_kernel(s.k1, s.k2, s.nb) : e8_kernel(s.ns, s.nb);
+}
+
+static int nb_for_batch(int batch) {
+  if (batch <= 8) return 1;
+  if (batch <= 16) return 2;
+  if (batch <= 32) return 4;
+  return 8;
+}
+
+static int validate(const GlqbLinearDesc& d, int idx) {
+  if (d.format != GLQB_FMT_TRELLIS_3INST && d.format != GLQB_FMT_E8_SHELL)
+    return fail(GLQB_E_INVALID, "layer %d: unknown format %d", idx, d.format);
+  if (d.m_pad <= 0 || d.n_pad <= 0 || d.in_features <= 0 || d.out_features <= 0 ||
+      d.in_features > d.n_pad || d.out_features > d.m_pad)
+    return fail(GLQB_E_INVALID, "layer %d: bad dims m_pad=%d n_pad=%d in=%d out=%d", idx, d.m_pad, d.n_pad,
+                d.in_features, d.out_features);
+  if (d.batch < 1) return fail(GLQB_E_INVALID, "layer %d: batch %d", idx, d.batch);
+  if (d.batch > 64)
+    return fail(GLQB_E_INVALID, "layer %d: batch %d exceeds the decode-path limit of 64 tokens", idx, d.batch);
+  if (!d.su || !d.sv || !d.codes[0]) return fail(GLQB_E_INVALID, "layer %d: null su/sv/codes", idx);
+  if (d.format == GLQB_FMT_TRELLIS_3INST) {
+    if (d.m_pad % 32 || d.n_pad % 32)
+      return fail(GLQB_E_INVALID, "layer %d: trellis needs m %% 32 == 0 and n %% 32 == 0 (got %d x %d)", idx,
+                  d.m_pad, d.n_pad);
+    if (d.n_stages < 1 || d.n_stages > 2) return fail(GLQB_E_INVALID, "layer %d: trellis stages %d", idx, d.n_stages);
+    for (int s = 0; s < d.n_stages; ++s)
+      if (d.bits[s] < 1 || d.bits[s] > 4 || !d.codes[s])
+        return fail(GLQB_E_INVALID, "layer %d: trellis stage %d has K=%d (supported 1..4)", idx, s, d.bits[s]);
+    if (!trellis_kernel(d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, 1))
+      return fail(GLQB_E_INVALID, "layer %d: no kernel for trellis rates K=%d+%d", idx, d.bits[0],
+                  d.n_stages > 1 ? d.bits[1] : 0);
+    if (d.in_features != d.n_pad) return fail(GLQB_E_INVALID, "layer %d: trellis layers are never padded", idx);
+  } else {
+    if (d.n_pad % 8) return fail(GLQB_E_INVALID, "layer %d: E8 needs n_pad %% 8 == 0", idx);
+    if (d.n_stages < 1 || d.n_stages > 4) return fail(GLQB_E_INVALID, "layer %d: E8 stages %d", idx, d.n_stages);
+    for (int s = 0; s < d.n_stages; ++s) {
+      if (!d.codes[s] || !d.table[s]) return fail(GLQB_E_INVALID, "layer %d: E8 stage %d null codes/table", idx, s);
+      const int e = d.table_entries[s];
+      if (e < 1 || e > 65536 || (e & (e - 1)))
+        return fail(GLQB_E_INVALID, "layer %d: E8 table entries %d must be a power of two <= 65536", idx, e);
+    }
+  }
+  int sn = 0, sm = 0;
+  if (d.n_blocks_n < 1 || d.n_blocks_n > GLQB_MAX_BLOCKS || d.n_blocks_m < 1 || d.n_blocks_m > GLQB_MAX_BLOCKS)
+    return fail(GLQB_E_INVALID, "layer %d: block counts %d/%d", idx, d.n_blocks_n, d.n_blocks_m);
+  for (int i = 0; i < d.n_blocks_n; ++i) {
+    const int b = d.blocks_n[i];
+    if (b < 1 || (b & (b - 1)) || b > 32768) return fail(GLQB_E_INVALID, "layer %d: blocks_n[%d]=%d", idx, i, b);
+    sn += b;
+  }
+  for (int i = 0; i < d.n_blocks_m; ++i) {
+    const int b = d.blocks_m[i];
+    if (b < 1 || (b & (b - 1)) || b > 32768) return fail(GLQB_E_INVALID, "layer %d: blocks_m[%d]=%d", idx, i, b);
+    sm += b;
+  }
+  if (sn != d.n_pad || sm != d.m_pad)
+    return fail(GLQB_E_INVALID, "layer %d: Hadamard blocks sum to %d/%d, expected n_pad=%d m_pad=%d", idx, sn, sm,
+                d.n_pad, d.m_pad);
+  if (d.x_dtype < 0 || d.x_dtype > 2 || d.y_dtype < 0 || d.y_dtype > 2)
+    return fail(GLQB_E_INVALID, "layer %d: dtype", idx);
+  if (d.stop_at_yrht && d.y_dtype != GLQB_DT_F32)
+    return fail(GLQB_E_INVALID, "layer %d: rotated-domain output must be fp32", idx);
+  return GLQB_OK;
+}
+
+static int build_plan(GlqbPlan* P) {
+  const int n = (int)P->descs.size();
+  int dev_id = 0;
+  CUDA_TRY(cudaGetDevice(&dev_id));
+  CUDA_TRY(cudaDeviceGetAttribute(&P->sm_count, cudaDevAttrMultiProcessorCount, dev_id));
+
+  // ---- segments: layers with the same kernel variant, in caller order inside a segment
+  typedef std::tuple<int, int, int, int, int> Key;   // format, k1, k2, ns, nb
+  std::map<Key, std::vector<int>> groups;
+  std::vector<Key> key_order;
+  for (int i = 0; i < n; ++i) {
+    const GlqbLinearDesc& d = P->descs[i];
+    Key k;
+    if (d.format == GLQB_FMT_TRELLIS_3INST)
+      k = Key(d.format, d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, d.n_stages, nb_for_batch(d.batch));
+    else
+      k = Key(d.format, 0, 0, d.n_stages, nb_for_batch(d.batch));
+    if (!groups.count(k)) key_order.push_back(k);
+    groups[k].push_back(i);
+  }
+  P->order.clear();
+  P->segs.clear();
+  for (const Key& k : key_order) {
+    Segment s;
+    s.format = std::get<0>(k); s.k1 = std::get<1>(k); s.k2 = std::get<2>(k);
+    s.ns = std::get<3>(k); s.nb = std::get<4>(k);
+    s.first = (int)P->order.size();
+    s.count = (int)groups[k].size();
+    for (int i : groups[k]) P->order.push_back(i);
+    if (!pick_kernel(s))
+      return fail(GLQB_E_INVALID, "no kernel variant for format=%d K=%d+%d stages=%d token blocks=%d", s.format,
+                  s.k1, s.k2, s.ns, s.nb);
+    P->segs.push_back(s);
+  }
+
+  // ---- device table
+  P->dev.assign(n, DevLinear());
+  P->code_bytes = 0;
+  P->flops = 0;
+  P->max_batch = 1;
+  for (int pos = 0; pos < n; ++pos) {
+    const GlqbLinearDesc& d = P->descs[P->order[pos]];
+    DevLinear& L = P->dev[pos];
+    memset(&L, 0, sizeof L);
+    for (int s = 0; s < GLQB_MAX_STAGES; ++s) {
+      L.codes[s] = reinterpret_cast<const uint8_t*>(d.codes[s]);
+      L.table[s] = d.table[s];
+      L.table_entries[s] = d.table_entries[s];
+      L.stage_scale[s] = d.stage_scale[s];
+      L.bits[s] = d.bits[s];
+    }
+    L.su = reinterpret_cast<const __half*>(d.su);
+    L.sv = reinterpret_cast<const __half*>(d.sv);
+    L.row_scale = d.row_scale;
+    L.wscale = d.wscale;
+    L.format = d.format; L.m = d.m_pad; L.n = d.n_pad; L.in_f = d.in_features; L.out_f = d.out_features;
+    L.n_stages = d.n_stages;
+    L.batch = d.batch; L.x_dtype = d.x_dtype; L.y_dtype = d.y_dtype; L.stop_at_yrht = d.stop_at_yrht; L.x_is_rotated = d.x_is_rotated;
+    L.x_stride = d.x_stride; L.y_stride = d.y_stride; L.x_off = d.x_offset; L.y_off = d.y_offset;
+    L.nbn = d.n_blocks_n; L.nbm = d.n_blocks_m;
+    int off = 0;
+    for (int i = 0; i < d.n_blocks_n; ++i) {
+      L.bn_off[i] = off; L.bn_log[i] = ilog2(d.blocks_n[i]); off += d.blocks_n[i];
+      P->max_bs_in = std::max(P->max_bs_in, d.blocks_n[i]);
+    }
+    off = 0;
+    for (int i = 0; i < d.n_blocks_m; ++i) {
+      L.bm_off[i] = off; L.bm_log[i] = ilog2(d.blocks_m[i]); off += d.blocks_m[i];
+      P->max_bs_out = std::max(P->max_bs_out, d.blocks_m[i]);
+    }
+    if (d.format == GLQB_FMT_TRELLIS_3INST) {
+      L.groups_per_strip = d.n_pad / 32;
+      L.strips = d.m_pad / 32;
+      for (int s = 0; s < d.n_stages; ++s) P->code_bytes += (int64_t)d.m_pad * d.n_pad * d.bits[s] / 8;
+    } else {
+      L.groups_per_strip = (d.n_pad + 255) / 256;
+      L.strips = (d.m_pad + 15) / 16;
+      P->code_bytes += (int64_t)d.n_stages * d.m_pad * (d.n_pad / 8) * 2;
+    }
+    P->flops += 2ll * d.batch * d.m_pad * d.n_pad;
+    P->max_batch = std::max(P->max_batch, d.batch);
+  }
+
+  // ---- per segment: group prefix, range length per warp, grid
+  for (Segment& s : P->segs) {
+    MvKernel kern = pick_kernel(s);
+    int ctas_per_sm = 1;
+    CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, MV_THREADS, 0));
+    ctas_per_sm = std::max(1, std::min(ctas_per_sm, 4));
+    long long total = 0;
+    for (int i = 0; i < s.count; ++i) {
+      DevLinear& L = P->dev[s.first + i];
+      L.group_base = total;
+      total += (long long)L.strips * L.groups_per_strip;
+    }
+    s.total_groups = total;
+    const long long warps = (long long)P->sm_count * ctas_per_sm * MV_WARPS;
+    long long per_warp = (total + warps - 1) / warps;
+    if (per_warp < 1) per_warp = 1;
+    s.per_warp = (int)per_warp;
+    const long long used_warps = (total + per_warp - 1) / per_warp;
+    s.grid = (int)((used_warps + MV_WARPS - 1) / MV_WARPS);
+    for (int i = 0; i < s.count; ++i) {
+      DevLinear& L = P->dev[s.first + i];
+      L.per_warp = s.per_warp;
+      L.slots = (L.groups_per_strip - 1) / s.per_warp + 2;
+    }
+  }
+
+  // ---- workspace: rotated activations (shared by layers with the same input) + partial sums
+  size_t ws = 0;
+  P->items_in.clear();
+  P->items_out.clear();
+  for (int pos = 0; pos < n; ++pos) {
+    DevLinear& L = P->dev[pos];
+    const GlqbLinearDesc& d = P->descs[P->order[pos]];
+    int same = -1;
+    for (int q = 0; q < pos && same < 0; ++q) {
+      const DevLinear& Q = P->dev[q];
+      const GlqbLinearDesc& e = P->descs[P->order[q]];
+      if (Q.format == L.format && Q.n == L.n && Q.in_f == L.in_f && Q.sv == L.sv && Q.batch == L.batch &&
+          Q.x_off == L.x_off && Q.x_stride == L.x_stride && Q.x_dtype == L.x_dtype && Q.nbn == L.nbn &&
+          Q.x_is_rotated == L.x_is_rotated &&
+          memcmp(e.blocks_n, d.blocks_n, sizeof(int32_t) * d.n_blocks_n) == 0)
+        same = q;
+    }
+    if (same >= 0) {
+      L.xr_off = P->dev[same].xr_off;
+    } else {
+      L.xr_off = (long long)ws;
+      ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half), 256);
+      for (int b = 0; b < L.nbn; ++b) P->items_in.push_back(RhtItem{pos, b});
+    }
+    L.part_off = (long long)ws;
+    ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
+    for (int b = 0; b < L.nbm; ++b) P->items_out.push_back(RhtItem{pos, b});
+  }
+  P->ws_bytes = ws;
+
+  // ---- upload
+  CUDA_TRY(cudaMalloc(&P->d_layers, sizeof(DevLinear) * n));
+  CUDA_TRY(cudaMemcpy(P->d_layers, P->dev.data(), sizeof(DevLinear) * n, cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMalloc(&P->d_items_in, sizeof(RhtItem) * std::max<size_t>(1, P->items_in.size())));
+  CUDA_TRY(cudaMemcpy(P->d_items_in, P->items_in.data(), sizeof(RhtItem) * P->items_in.size(), cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMalloc(&P->d_items_out, sizeof(RhtItem) * std::max<size_t>(1, P->items_out.size())));
+  CUDA_TRY(cudaMemcpy(P->d_items_out, P->items_out.data(), sizeof(RhtItem) * P->items_out.size(), cudaMemcpyHostToDevice));
+
+  // kernels that may need more than 48 KB of dynamic shared memory
+  const int smem_in = P->max_bs_in * 4, smem_out = P->max_bs_out * 4;
+  if (smem_in > 48 * 1024)
+    CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
+  if (smem_out > 48 * 1024)
+    CUDA_TRY(cudaFuncSetAttribute(rht_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_out));
+  return GLQB_OK;
+}
+
+static int rht_threads(int max_bs) { return std::max(64, std::min(1024, max_bs / 8)); }
+
+}  // namespace glqb
+
+// =============================================================================================
+// exported C ABI
+// =============================================================================================
+extern "C" {
+
+const char* glqb_last_error(void) { return g_err.c_str(); }
+const char* glqb_version(void) { return "glq_b200 0.1 (sm_100a)"; }
+
+int glqb_trellis_kernel_supported(int32_t m, int32_t n) { return (m > 0 && n > 0 && m % 32 == 0 && n % 32 == 0) ? 1 : 0; }
+
+int glqb_plan_create(const GlqbLinearDesc* descs, int32_t count, GlqbPlan** out_plan) {
+  if (!descs || count < 1 || !out_plan) return fail(GLQB_E_INVALID, "plan_create: bad arguments");
+  for (int i = 0; i < count; ++i) {
+    int rc = validate(descs[i], i);
+    if (rc) return rc;
+  }
+  GlqbPlan* P = new GlqbPlan();
+  P->descs.assign(descs, descs + count);
+  int rc = build_plan(P);
+  if (rc) {
+    glqb_plan_destroy(P);
+    return rc;
+  }
+  *out_plan = P;
+  return GLQB_OK;
+}
+
+size_t glqb_plan_workspace_bytes(const GlqbPlan* plan) { return plan ? plan->ws_bytes : 0; }
+int64_t glqb_plan_code_bytes(const GlqbPlan* plan) { return plan ? plan->code_bytes : 0; }
+int64_t glqb_plan_flops(const GlqbPlan* plan) { return plan ? plan->flops : 0; }
+int32_t glqb_plan_launches(const GlqbPlan* plan) {
+  if (!plan) return 0;
+  return (plan->items_in.empty() ? 0 : 1) + (int)plan->segs.size() + 1;
+}
+
+int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable) {
+  if (!plan) return fail(GLQB_E_INVALID, "null plan");
+  if (enable && !plan->ev0) {
+    CUDA_TRY(cudaEventCreate(&plan->ev0));
+    CUDA_TRY(cudaEventCreate(&plan->ev1));
+  }
+  plan->timing = enable != 0;
+  plan->have_time = false;
+  return GLQB_OK;
+}
+
+int glqb_plan_last_kernel_ms(GlqbPlan* plan, float* ms_out) {
+  if (!plan || !ms_out) return fail(GLQB_E_INVALID, "null argument");
+  if (!plan->have_time) return fail(GLQB_E_INVALID, "no timed run recorded");
+  CUDA_TRY(cudaEventSynchronize(plan->ev1));
+  CUDA_TRY(cudaEventElapsedTime(ms_out, plan->ev0, plan->ev1));
+  return GLQB_OK;
+}
+
+int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace, size_t workspace_bytes,
+                  void* stream_) {
+  if (!P || !x_base || !y_base) return fail(GLQB_E_INVALID, "plan_run: null argument");
+  if (P->ws_bytes && (!workspace || workspace_bytes < P->ws_bytes))
+    return fail(GLQB_E_WORKSPACE, "workspace of %zu bytes needed, %zu given", P->ws_bytes, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255)
+    return fail(GLQB_E_WORKSPACE, "workspace must be 256-byte aligned");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  if (!P->items_in.empty()) {
+    dim3 grid((unsigned)P->items_in.size(), (unsigned)P->max_batch);
+    rht_in_kernel<false><<<grid, rht_threads(P->max_bs_in), P->max_bs_in * 4, stream>>>(
+        P->d_layers, P->d_items_in, reinterpret_cast<const uint8_t*>(x_base), ws);
+  }
+  if (P->timing) CUDA_TRY(cudaEventRecord(P->ev0, stream));
+  for (const Segment& s : P->segs) {
+    MvKernel kern = pick_kernel(s);
+    kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);
+  }
+  if (P->timing) {
+    CUDA_TRY(cudaEventRecord(P->ev1, stream));
+    P->have_time = true;
+  }
+  {
+    dim3 grid((unsigned)P->items_out.size(), (unsigned)P->max_batch);
+    rht_out_kernel<false><<<grid, rht_threads(P->max_bs_out), P->max_bs_out * 4, stream>>>(
+        P->d_layers, P->d_items_out, ws, reinterpret_cast<uint8_t*>(y_base), nullptr);
+  }
+  CUDA_TRY(cudaGetLastError());
+  return GLQB_OK;
+}
+
+void glqb_plan_destroy(GlqbPlan* plan) {
+  if (!plan) return;
+  if (plan->d_layers) cudaFree(plan->d_layers);
+  if (plan->d_items_in) cudaFree(plan->d_items_in);
+  if (plan->d_items_out) cudaFree(plan->d_items_out);
+  if (plan->ev0) cudaEventDestroy(plan->ev0);
+  if (plan->ev1) cudaEventDestroy(plan->ev1);
+  delete plan;
+}
+
+int glqb_decompress_trellis_3inst(const void* packed, int32_t bits, const void* packed2, int32_t bits2,
+                                  float inv_resid_scale2, int32_t m, int32_t n, void* out, int32_t out_dtype,
+                                  void* stream_) {
+  if (!packed || !out || m <= 0 || n <= 0 || m % 32 || n % 32)
+    return fail(GLQB_E_INVALID, "decompress_trellis_3inst: needs m %% 32 == 0 and n %% 32 == 0 (got %d x %d)", m, n);
+  if (bits < 1 || bits > 4) return fail(GLQB_E_INVALID, "decompress_trellis_3inst: K=%d unsupported (1..4)", bits);
+  const int k2 = packed2 ? bits2 : 0;
+  if (packed2 && (bits2 < 1 || bits2 > 4)) return fail(GLQB_E_INVALID, "decompress_trellis_3inst: K2=%d", bits2);
+  if (out_dtype != GLQB_DT_F16 && out_dtype != GLQB_DT_F32) return fail(GLQB_E_INVALID, "out dtype");
+  if (k2 && out_dtype != GLQB_DT_F32) return fail(GLQB_E_INVALID, "two-stage decode is written as fp32");
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const long long groups = (long long)(m / 32) * (n / 32);
+  const int grid = (int)std::min<long long>((groups + MV_WARPS - 1) / MV_WARPS, 148 * 8);
+  const uint8_t* p1 = reinterpret_cast<const uint8_t*>(packed);
+  const uint8_t* p2 = reinterpret_cast<const uint8_t*>(packed2);
+  const int f32 = out_dtype == GLQB_DT_F32;
+#define D_CASE(A, B)                                                                                      \
+  if (bits == A && k2 == B) {                                                                             \
+    trellis_dump_kernel<A, B><<<grid, MV_THREADS, 0, stream>>>(p1, p2, inv_resid_scale2, m, n, out, f32); \
+    CUDA_TRY(cudaGetLastError());                                                                         \
+    return GLQB_OK;                                                                                       \
+  }
+  D_CASE(1, 0) D_CASE(2, 0) D_CASE(3, 0) D_CASE(4, 0)
+  D_CASE(4, 1) D_CASE(4, 2) D_CASE(4, 3) D_CASE(4, 4)
+  D_CASE(2, 2) D_CASE(3, 3) D_CASE(2, 1) D_CASE(3, 1) D_CASE(3, 2)
+#undef D_CASE
+  return fail(GLQB_E_INVALID, "decompress_trellis_3inst: no kernel for K=%d+%d", bits, k2);
+}
+
+int glqb_dequant_e8(const void* const* qidxs, const uint32_t* const* tables, const int32_t* table_entries,
+                    const float* stage_scale, int32_t n_stages, int32_t m, int32_t n, float* out, void* stream_) {
+  if (!qidxs || !tables || !table_entries || !out || n_stages < 1 || n_stages > 4 || m <= 0 || n <= 0 || n % 8)
+    return fail(GLQB_E_INVALID, "dequant_e8: bad arguments");
+  E8DumpArgs A;
+  memset(&A, 0, sizeof A);
+  for (int s = 0; s < n_stages; ++s) {
+    if (!qidxs[s] || !tables[s]) return fail(GLQB_E_INVALID, "dequant_e8: stage %d null", s);
+    const int e = table_entries[s];
+    if (e < 1 || e > 65536 || (e & (e - 1))) return fail(GLQB_E_INVALID, "dequant_e8: table entries %d", e);
+    A.q[s] = reinterpret_cast<const uint16_t*>(qidxs[s]);
+    A.table[s] = tables[s];
+    A.entries[s] = e;
+    A.scale[s] = (s && stage_scale) ? stage_scale[s] : 1.0f;
+  }
+  A.n_stages = n_stages; A.m = m; A.n = n;
+  const long long total = (long long)m * (n / 8);
+  const int grid = (int)std::min<long long>((total + 255) / 256, 148 * 16);
+  e8_dump_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(A, out);
+  CUDA_TRY(cudaGetLastError());
+  return GLQB_OK;
+}
+
+int glqb_e8_pack_table(const void* codebook_f16, int32_t entries, uint32_t* out_packed, void* stream_) {
+  if (!codebook_f16 || !out_packed || entries < 1) return fail(GLQB_E_INVALID, "e8_pack_table: bad arguments");
+  e8_pack_table_kernel<<<(entries + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      reinterpret_cast<const __half*>(codebook_f16), entries, out_packed);
+  CUDA_TRY(cudaGetLastError());
+  return GLQB_OK;
+}
+
+// The two unfused transform ops build a one-layer table in kernel-argument space is not possible for
+// a pointer-typed table, so they keep a tiny per-call device table alive in a static pool keyed by
+// stream-ordered allocation.
+static int run_rht_single(bool input, const void* src, int src_dtype, int64_t src_stride, const void* signs,
+                          void* dst, int dst_dtype, int64_t dst_stride, int32_t feat, int32_t pad,
+                          const int32_t* blocks, int32_t n_blocks, int32_t batch, cudaStream_t stream) {
+  if (!src || !signs || !dst || !blocks || n_blocks < 1 || n_blocks > GLQB_MAX_BLOCKS || batch < 1 || feat < 1 ||
+      feat > pad)
+    return fail(GLQB_E_INVALID, "rht: bad arguments");
+  DevLinear L;
+  memset(&L, 0, sizeof L);
+  int off = 0, maxbs = 32;
+  for (int i = 0; i < n_blocks; ++i) {
+    const int b = blocks[i];
+    if (b < 1 || (b & (b - 1)) || b > 32768) return fail(GLQB_E_INVALID, "rht: block %d", b);
+    if (input) { L.bn_off[i] = off; L.bn_log[i] = ilog2(b); } else { L.bm_off[i] = off; L.bm_log[i] = ilog2(b); }
+    off += b;
+    maxbs = std::max(maxbs, b);
+  }
+  if (off != pad) return fail(GLQB_E_INVALID, "rht: blocks sum to %d, expected %d", off, pad);
+  L.format = GLQB_FMT_E8_SHELL;
+  L.batch = batch;
+  std::vector<RhtItem> items;
+  for (int i = 0; i < n_blocks; ++i) items.push_back(RhtItem{0, i});
+  DevLinear* d_L = nullptr;
+  RhtItem* d_items = nullptr;
+  if (input) {
+    L.n = pad; L.in_f = feat; L.sv = reinterpret_cast<const __half*>(signs);
+    L.x_dtype = src_dtype; L.x_stride = src_stride; L.nbn = n_blocks; L.xr_off = 0;
+  } else {
+    L.m = pad; L.out_f = feat; L.su = reinterpret_cast<const __half*>(signs);
+    L.y_dtype = dst_dtype; L.y_stride = dst_stride; L.nbm = n_blocks; L.wscale = 1.f;
+  }
+  CUDA_TRY(cudaMallocAsync(&d_L, sizeof L, stream));
+  CUDA_TRY(cudaMallocAsync(&d_items, sizeof(RhtItem) * items.size(), stream));
+  CUDA_TRY(cudaMemcpyAsync(d_L, &L, sizeof L, cudaMemcpyHostToDevice, stream));
+  CUDA_TRY(cudaMemcpyAsync(d_items, items.data(), sizeof(RhtItem) * items.size(), cudaMemcpyHostToDevice, stream));
+  dim3 grid((unsigned)n_blocks, (unsigned)batch);
+  const int smem = maxbs * 4;
+  if (input) {
+    if (smem > 48 * 1024)
+      CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    rht_in_kernel<true><<<grid, rht_threads(maxbs), smem, stream>>>(d_L, d_items, reinterpret_cast<const uint8_t*>(src),
+                                                                     reinterpret_cast<uint8_t*>(dst));
+  } else {
+    if (smem > 48 * 1024)
+      CUDA_TRY(cudaFuncSetAttribute(rht_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    rht_out_kernel<true><<<grid, rht_threads(maxbs), smem, stream>>>(d_L, d_items, nullptr, reinterpret_cast<uint8_t*>(dst),
+                                                                      reinterpret_cast<const float*>(src));
+  }
+  CUDA_TRY(cudaGetLastError());
+  // the host copies above were taken from pageable memory: the copy has been staged before
+  // cudaMemcpyAsync returned, so the vectors may go out of scope
+  CUDA_TRY(cudaFreeAsync(d_L, stream));
+  CUDA_TRY(cudaFreeAsync(d_items, stream));
+  return GLQB_OK;
+}
+
+int glqb_input_rht(const void* x, int32_t x_dtype, int64_t x_stride, const void* sv, void* out_f32,
+                   int32_t in_features, int32_t n_pad, const int32_t* blocks, int32_t n_blocks, int32_t batch,
+                   void* stream) {
+  return run_rht_single(true, x, x_dtype, x_stride, sv, out_f32, GLQB_DT_F32, n_pad, in_features, n_pad, blocks,
+                        n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int glqb_output_rht(const float* y_rht, const void* su, void* out, int32_t out_dtype, int64_t out_stride,
+                    int32_t out_features, int32_t m_pad, const int32_t* blocks, int32_t n_blocks, int32_t batch,
+                    void* stream) {
+  return run_rht_single(false, y_rht, GLQB_DT_F32, m_pad, su, out, out_dtype, out_stride, out_features, m_pad,
+                        blocks, n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t glqb_linear_workspace_bytes(const GlqbLinearDesc* desc) {
+  // Upper bound that does not depend on the device: activations + the largest possible number of
+  // partial-sum slots (one per work group of a strip, plus one).
+  if (!desc) return 0;
+  const size_t gps = desc->format == GLQB_FMT_TRELLIS_3INST ? desc->n_pad / 32 : (desc->n_pad + 255) / 256;
+  size_t ws = align_up((size_t)desc->batch * desc->n_pad * 2, 256);
+  ws += align_up((gps + 1) * (size_t)desc->batch * desc->m_pad * 4, 256);
+  return ws;
+}
+
+int glqb_fused_linear(const GlqbLinearDesc* desc, const void* x, void* y, void* workspace, size_t workspace_bytes,
+                      void* stream) {
+  // Stateless form: builds a one-layer plan, runs it and releases it after the stream has consumed
+  // the table.  Callers on a hot path should keep a plan instead (glqb_plan_create once).
+  GlqbPlan* P = nullptr;
+  int rc = glqb_plan_create(desc, 1, &P);
+  if (rc) return rc;
+  rc = glqb_plan_run(P, x, y, workspace, workspace_bytes, stream);
+  cudaError_t e = cudaStreamSynchronize(reinterpret_cast<cudaStream_t>(stream));
+  glqb_plan_destroy(P);
+  if (rc) return rc;
+  if (e != cudaSuccess) return fail(GLQB_E_CUDA, "fused_linear: %s", cudaGetErrorString(e));
+  return GLQB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,47 @@
+// Internal structures shared by the host-side plan builder and the kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include "../../include/glq_b200.h"
+
+namespace glqb {
+
+// Device-side description of one linear layer inside a plan.  Pointers into the caller's
+// workspace are stored as byte offsets so that the workspace may move between runs.
+struct DevLinear {
+  const uint8_t* codes[GLQB_MAX_STAGES];
+  const uint32_t* table[GLQB_MAX_STAGES];
+  const __half* su;
+  const __half* sv;
+  const float* row_scale;
+  float stage_scale[GLQB_MAX_STAGES];
+  float wscale;
+  int table_entries[GLQB_MAX_STAGES];
+  int format, m, n, in_f, out_f, n_stages;
+  int bits[GLQB_MAX_STAGES];
+  int batch, x_dtype, y_dtype, stop_at_yrht, x_is_rotated;
+  long long x_stride, y_stride, x_off, y_off;
+  long long xr_off;      // workspace bytes: rotated activations, fp16 [batch][n]
+  long long part_off;    // workspace bytes: partial sums, fp32 [slots][batch][m]
+  long long group_base;  // first work-group index of this layer inside its launch segment
+  int groups_per_strip;  // work groups along one strip of rows
+  int strips;            // strips of rows (trellis: 32 rows, E8: 16 rows)
+  int slots;             // upper bound on partial sums per strip
+  int per_warp;          // work groups handed to each warp of the segment's launch
+  int nbn, nbm;
+  int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
+  int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];
+};
+
+// One (layer, Hadamard block) pair handled by one CTA of the transform kernels.
+struct RhtItem {
+  int layer;
+  int block;
+};
+
+// Status word written by kernels that detect an internal inconsistency (never a trap).
+enum : int { ST_OK = 0, ST_BAD_RANGE = 1 };
+
+}  // namespace glqb

@@ -1,0 +1,578 @@
+// Kernels of the decode (small-batch) path: input transform, streaming decode + mma, output transform,
+// and the dump kernels used by the bit-exact gate.
+#pragma once
+#include "glqb_internal.h"
+#include "glqb_decode.cuh"
+#include "glqb_fht.cuh"
+
+namespace glqb {
+
+constexpr int MV_THREADS = 256;               // 8 warps per CTA in the streaming kernels
+constexpr int MV_WARPS = MV_THREADS / 32;
+
+// ---------------------------------------------------------------------------------------------
+// small helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float load_act(const void* base, long long idx, int dtype) {
+  if (dtype == GLQB_DT_F16) return __half2float(reinterpret_cast<const __half*>(base)[idx]);
+  if (dtype == GLQB_DT_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[idx]);
+  return reinterpret_cast<const float*>(base)[idx];
+}
+
+__device__ __forceinline__ void store_act(void* base, long long idx, int dtype, float v) {
+  if (dtype == GLQB_DT_F16) reinterpret_cast<__half*>(base)[idx] = __float2half_rn(v);
+  else if (dtype == GLQB_DT_BF16) reinterpret_cast<__nv_bfloat16*>(base)[idx] = __float2bfloat16_rn(v);
+  else reinterpret_cast<float*>(base)[idx] = v;
+}
+
+// streaming 128/64/32-bit loads of weight codes: read once, keep out of L1
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_stream_v2(const void* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+// D(16x8, f32) += A(16x16, f16, row) * B(16x8, f16, col)
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// position of column c (0..31) of a trellis group inside the fragment-ordered activation layout
+__device__ __forceinline__ int xr_pos_trellis(int c) {
+  int ni = c >> 4, h = (c >> 3) & 1, t = (c >> 1) & 3, e = c & 1;
+  return t * 8 + ni * 4 + h * 2 + e;
+}
+// position of column i (0..7) of an E8 block: (x0,x4,x1,x5,x2,x6,x3,x7)
+__device__ __forceinline__ int xr_pos_e8(int i) { return (i & 3) * 2 + (i >> 2); }
+
+// ---------------------------------------------------------------------------------------------
+// Input transform:  xr = fp16( H_blocks( SV * pad(x) ) / sqrt(bs) ), written in the layout the
+// decode kernel of the layer's format reads (reference: glq_input_rht_multiblock_kernel,
+// glq/csrc/glq_cuda.cu:2092; rounding to fp16 as glq/csrc/glq_cuda.cu:2625).
+// grid = (items, tokens); one CTA per (layer, block, token); dynamic smem = max block * 4 bytes.
+// PLAIN_F32: write fp32 in natural order instead (the unfused input_rht op).
+// ---------------------------------------------------------------------------------------------
+template <bool PLAIN_F32>
+__global__ void __launch_bounds__(1024) rht_in_kernel(const DevLinear* __restrict__ layers,
+                                                      const RhtItem* __restrict__ items,
+                                                      const uint8_t* __restrict__ x_base,
+                                                      uint8_t* __restrict__ ws) {
+  extern __shared__ float fbuf[];
+  const RhtItem it = items[blockIdx.x];
+  const DevLinear& L = layers[it.layer];
+  const int token = blockIdx.y;
+  if (token >= L.batch) return;
+  const int off = L.bn_off[it.block];
+  const int logbs = L.bn_log[it.block];
+  const int bs = 1 << logbs;
+  const long long xrow = L.x_off + (long long)token * L.x_stride;
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const int col = off + i;
+    float v = 0.f;
+    if (col < L.in_f) {
+      v = load_act(x_base, xrow + col, L.x_dtype);
+      if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
+    }
+    fbuf[i] = v;
+  }
+  float rs = 1.0f;
+  if (!L.x_is_rotated) {
+    fht_smem(fbuf, logbs);
+    rs = rsqrtf((float)bs);
+  } else {
+    __syncthreads();
+  }
+  if constexpr (PLAIN_F32) {
+    float* out = reinterpret_cast<float*>(ws + L.xr_off) + (long long)token * L.n;
+    for (int i = threadIdx.x; i < bs; i += blockDim.x) out[off + i] = fbuf[i] * rs;
+  } else {
+    __half* out = reinterpret_cast<__half*>(ws + L.xr_off) + (long long)token * L.n;
+    const bool trellis = (L.format == GLQB_FMT_TRELLIS_3INST);
+    for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+      const int col = off + i;
+      const int pos = trellis ? ((col & ~31) + xr_pos_trellis(col & 31)) : ((col & ~7) + xr_pos_e8(col & 7));
+      out[pos] = __float2half_rn(fbuf[i] * rs);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Output transform: sums the per-warp partial sums of every strip in fixed (ascending slot) order,
+// applies wscale (and the optional per-row scale), the block Hadamard, 1/sqrt(bs) and SU, and
+// writes y[:, :out_features] (reference: glq_output_rht_multiblock_kernel, glq/csrc/glq_cuda.cu:2151).
+// FROM_F32: input is a plain fp32 (batch, m) matrix at x_base (the unfused output_rht op).
+// ---------------------------------------------------------------------------------------------
+template <bool FROM_F32>
+__global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restrict__ layers,
+                                                       const RhtItem* __restrict__ items,
+                                                       const uint8_t* __restrict__ ws,
+                                                       uint8_t* __restrict__ y_base,
+                                                       const float* __restrict__ yrht_in) {
+  extern __shared__ float fbuf[];
+  const RhtItem it = items[blockIdx.x];
+  const DevLinear& L = layers[it.layer];
+  const int token = blockIdx.y;
+  if (token >= L.batch) return;
+  const int off = L.bm_off[it.block];
+  const int logbs = L.bm_log[it.block];
+  const int bs = 1 << logbs;
+  const long long yrow = L.y_off + (long long)token * L.y_stride;
+  const int rows_per_strip = (L.format == GLQB_FMT_TRELLIS_3INST) ? 32 : 16;
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const int row = off + i;
+    float s = 0.f;
+    if constexpr (FROM_F32) {
+      s = yrht_in[(long long)token * L.m + row];
+    } else if (row < L.m) {
+      const int strip = row / rows_per_strip;
+      const long long g0 = L.group_base + (long long)strip * L.groups_per_strip;
+      const int cnt = (int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1;
+      const float* p = reinterpret_cast<const float*>(ws + L.part_off) + (long long)token * L.m + row;
+      const long long slot_stride = (long long)L.batch * L.m;
+      for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];
+      s *= L.wscale;
+      if (L.row_scale) s *= L.row_scale[row];
+    }
+    if (L.stop_at_yrht) {
+      if (row < L.m) reinterpret_cast<float*>(y_base)[yrow + row] = s;
+    } else {
+      fbuf[i] = s;
+    }
+  }
+  if (L.stop_at_yrht) return;
+  fht_smem(fbuf, logbs);
+  const float rs = rsqrtf((float)bs);
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const int row = off + i;
+    if (row < L.out_f) store_act(y_base, yrow + row, L.y_dtype, fbuf[i] * rs * __half2float(L.su[row]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Trellis 3INST streaming decode + mma (batch <= 8*NB tokens ride the MMA columns).
+//
+// Work is the flattened list of 32x32 groups of every layer of the launch; warp w owns the
+// contiguous range [w*per_warp, (w+1)*per_warp).  Inside a strip of 32 rows the warp accumulates in
+// registers; at a strip boundary (or the end of its range) it writes one partial sum per
+// (token, row) to slot (w - first warp touching the strip).  No atomics: the output transform adds
+// the slots in ascending order, so results do not depend on scheduling.
+//
+// Per group and lane: one 4K-byte load of codes, K shuffles to fetch the next lane's chunks (the
+// 16 bits that follow a lane's chunk in the tile's cyclic stream), one 16-byte load of rotated
+// activations per 8 tokens, 32 state decodes, 4 MMAs per 8 tokens (two with a second stage).
+// ---------------------------------------------------------------------------------------------
+template <int K>
+__device__ __forceinline__ Words<K> load_words(const uint8_t* p) {
+  Words<K> v;
+  if constexpr (K == 4) {
+    uint4 t = ld_stream_v4(p); v.w[0] = t.x; v.w[1] = t.y; v.w[2] = t.z; v.w[3] = t.w;
+  } else if constexpr (K == 2) {
+    uint2 t = ld_stream_v2(p); v.w[0] = t.x; v.w[1] = t.y;
+  } else if constexpr (K == 1) {
+    v.w[0] = ld_stream_u32(p);
+  } else {
+    v.w[0] = ld_stream_u32(p); v.w[1] = ld_stream_u32(p + 4); v.w[2] = ld_stream_u32(p + 8);
+  }
+  return v;
+}
+
+template <int K>
+__device__ __forceinline__ Words<K> shfl_words(const Words<K>& v, int src) {
+  Words<K> r;
+#pragma unroll
+  for (int i = 0; i < K; ++i) r.w[i] = __shfl_sync(0xffffffffu, v.w[i], src);
+  return r;
+}
+
+// decode the four tiles of a group and issue their MMAs against the B fragments in xb[nb]
+template <int K, int NB>
+__device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uint4 (&xb)[NB],
+                                          float (&acc)[NB][2][4]) {
+  const Words<K> vn = shfl_words<K>(v, (lane + 1) & 31);
+  Words<K> vn2 = vn;
+  if constexpr (K == 1) vn2 = shfl_words<K>(v, (lane + 2) & 31);
+#pragma unroll
+  for (int ni = 0; ni < 2; ++ni) {
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+      const int q = ni * 2 + mi;
+      uint32_t a[4];
+      decode_tile<K>(chunk_of<K>(v, q), chunk_of<K>(vn, q), chunk_of<K>(vn2, q), a);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        const uint32_t b0 = ni ? xb[nb].z : xb[nb].x;
+        const uint32_t b1 = ni ? xb[nb].w : xb[nb].y;
+        mma16816(acc[nb][mi], a, b0, b1);
+      }
+    }
+  }
+}
+
+template <int K1, int K2, int NB>
+__global__ void __launch_bounds__(MV_THREADS)
+trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
+                  int per_warp, uint8_t* __restrict__ ws) {
+  constexpr int PF = 4;   // codes of PF groups in flight per lane
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * MV_WARPS + (threadIdx.x >> 5);
+  long long g = w * per_warp;
+  const long long gend = min(g + per_warp, total_groups);
+  if (g >= gend) return;
+  // locate the layer holding group g (layers are sorted by group_base)
+  int lo = 0, hi = n_layers - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (layers[mid].group_base <= g) lo = mid; else hi = mid - 1;
+  }
+  int li = lo;
+  const int gq = lane >> 2, tq = lane & 3;
+
+  while (g < gend) {
+    const DevLinear& L = layers[li];
+    const long long local = g - L.group_base;
+    const int gps = L.groups_per_strip;
+    const int strip = (int)(local / gps);
+    const int c0 = (int)(local - (long long)strip * gps);
+    const int c1 = (int)min((long long)gps, c0 + (gend - g));
+    const int batch = L.batch;
+
+    float acc[NB][2][4];
+    float acc2[K2 ? NB : 1][2][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { acc[nb][mi][i] = 0.f; if constexpr (K2 > 0) acc2[nb][mi][i] = 0.f; }
+
+    const uint8_t* p1 = L.codes[0] + ((long long)strip * gps + c0) * (128 * K1) + lane * (4 * K1);
+    const uint8_t* p2 = nullptr;
+    if constexpr (K2 > 0) p2 = L.codes[1] + ((long long)strip * gps + c0) * (128 * K2) + lane * (4 * K2);
+    const __half* xr = reinterpret_cast<const __half*>(ws + L.xr_off);
+    const uint4* xq[NB];
+    bool xok[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+      const int token = nb * 8 + gq;
+      xok[nb] = token < batch;
+      xq[nb] = reinterpret_cast<const uint4*>(xr + (long long)(xok[nb] ? token : 0) * L.n + c0 * 32 + tq * 8);
+    }
+
+    const int ng = c1 - c0;
+    Words<K1> cur[PF];
+    Words<(K2 > 0 ? K2 : 1)> cur2[PF];
+#pragma unroll
+    for (int i = 0; i < PF; ++i) {
+      if (i < ng) {
+        cur[i] = load_words<K1>(p1 + (long long)i * (128 * K1));
+        if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + (long long)i * (128 * K2));
+      }
+    }
+    for (int c = 0; c < ng; c += PF) {
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        if (c + i < ng) {
+          const Words<K1> v = cur[i];
+          Words<(K2 > 0 ? K2 : 1)> v2;
+          if constexpr (K2 > 0) v2 = cur2[i];
+          if (c + i + PF < ng) {
+            cur[i] = load_words<K1>(p1 + (long long)(c + i + PF) * (128 * K1));
+            if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + (long long)(c + i + PF) * (128 * K2));
+          }
+          uint4 xb[NB];
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            xb[nb] = make_uint4(0u, 0u, 0u, 0u);
+            if (xok[nb]) xb[nb] = __ldg(xq[nb] + (c + i) * 4);   // 32 halfs = 4 uint4 per group
+          }
+          group_mma<K1, NB>(v, lane, xb, acc);
+          if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
+        }
+      }
+    }
+
+    // flush: C fragment (row gq / gq+8, tokens 2tq, 2tq+1 of each column block)
+    {
+      const long long g0 = L.group_base + (long long)strip * gps;
+      const int slot = (int)(w - g0 / per_warp);
+      float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)slot * batch * L.m;
+      const float s2 = L.stage_scale[1];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int token = nb * 8 + tq * 2 + (i & 1);
+            const int row = strip * 32 + mi * 16 + gq + ((i >> 1) ? 8 : 0);
+            if (token < batch) {
+              float v = acc[nb][mi][i];
+              if constexpr (K2 > 0) v = __fadd_rn(v, __fmul_rn(s2, acc2[nb][mi][i]));
+              part[(long long)token * L.m + row] = v;
+            }
+          }
+        }
+      }
+    }
+    g += ng;
+    if (c1 == gps && strip == L.strips - 1) ++li;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// E8 shell streaming gather + mma.
+//
+// Work group = 16 rows x 256 columns (32 indices per row).  Lane (g, t) loads 8 consecutive indices
+// of row g and of row g+8 (columns 256*G + 64*t ...), gathers their nibble-packed codebook entries,
+// expands each to 8 exact fp16 values and feeds two MMAs per index pair.  The MMA's k index is a
+// dummy summation index, so a lane's 8 weights of one index may sit in any k slots as long as the
+// activations are permuted the same way: the rotated activations are stored per 8-column block in
+// the order (x0,x4,x1,x5,x2,x6,x3,x7), which lets a lane fetch the B fragments of both MMAs with
+// one 16-byte load.  Every residual stage has its own accumulator (all stage values are exact in
+// fp16); stages are combined in fp32 when a strip is flushed.
+// ---------------------------------------------------------------------------------------------
+template <int NS, int NB>
+__global__ void __launch_bounds__(MV_THREADS)
+e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
+             int per_warp, uint8_t* __restrict__ ws) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * MV_WARPS + (threadIdx.x >> 5);
+  long long g = w * per_warp;
+  const long long gend = min(g + per_warp, total_groups);
+  if (g >= gend) return;
+  int lo = 0, hi = n_layers - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (layers[mid].group_base <= g) lo = mid; else hi = mid - 1;
+  }
+  int li = lo;
+  const int gq = lane >> 2, tq = lane & 3;
+
+  while (g < gend) {
+    const DevLinear& L = layers[li];
+    const long long local = g - L.group_base;
+    const int gps = L.groups_per_strip;
+    const int strip = (int)(local / gps);
+    const int c0 = (int)(local - (long long)strip * gps);
+    const int c1 = (int)min((long long)gps, c0 + (gend - g));
+    const int batch = L.batch;
+    const int nidx = L.n >> 3;                 // indices per row
+    const bool vec_ok = (nidx & 7) == 0;       // rows start 16-byte aligned
+    const int rowA = strip * 16 + gq, rowB = rowA + 8;
+    const bool okA = rowA < L.m, okB = rowB < L.m;
+
+    float acc[NS][NB][4];
+#pragma unroll
+    for (int s = 0; s < NS; ++s)
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[s][nb][i] = 0.f;
+
+    const __half* xr = reinterpret_cast<const __half*>(ws + L.xr_off);
+
+    for (int c = c0; c < c1; ++c) {
+      const int i0 = c * 32 + tq * 8;          // first index (8-column block) of this lane
+      // ---- load 8 indices per row and stage
+      uint32_t qa[NS][4], qb[NS][4];           // 8 uint16 packed in 4 words
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]);
+        const uint16_t* pa = q + (long long)rowA * nidx + i0;
+        const uint16_t* pb = q + (long long)rowB * nidx + i0;
+        if (vec_ok && i0 + 8 <= nidx) {
+          uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
+          if (okA) va = ld_stream_v4(pa);
+          if (okB) vb = ld_stream_v4(pb);
+          qa[s][0] = va.x; qa[s][1] = va.y; qa[s][2] = va.z; qa[s][3] = va.w;
+          qb[s][0] = vb.x; qb[s][1] = vb.y; qb[s][2] = vb.z; qb[s][3] = vb.w;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint32_t a0 = 0, a1 = 0, b0 = 0, b1 = 0;
+            if (i0 + 2 * k < nidx) { if (okA) a0 = pa[2 * k]; if (okB) b0 = pb[2 * k]; }
+            if (i0 + 2 * k + 1 < nidx) { if (okA) a1 = pa[2 * k + 1]; if (okB) b1 = pb[2 * k + 1]; }
+            qa[s][k] = a0 | (a1 << 16);
+            qb[s][k] = b0 | (b1 << 16);
+          }
+        }
+      }
+      // ---- 8 index pairs
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const int blk = i0 + k;                // 8-column block of x
+        uint4 xb[NB];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          const int token = nb * 8 + gq;
+          xb[nb] = make_uint4(0u, 0u, 0u, 0u);
+          if (token < batch && blk < nidx)
+            xb[nb] = __ldg(reinterpret_cast<const uint4*>(xr + (long long)token * L.n) + blk);
+        }
+#pragma unroll
+        for (int s = 0; s < NS; ++s) {
+          const uint32_t ia = (qa[s][k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
+          const uint32_t ib = (qb[s][k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
+          const uint32_t mask = (uint32_t)L.table_entries[s] - 1u;
+          const uint32_t ea = __ldg(L.table[s] + (ia & mask));
+          const uint32_t eb = __ldg(L.table[s] + (ib & mask));
+          uint32_t ha[4], hb[4];
+          e8_entry_to_half2(ea, ha);
+          e8_entry_to_half2(eb, hb);
+          const uint32_t a1[4] = {ha[0], hb[0], ha[1], hb[1]};
+          const uint32_t a2[4] = {ha[2], hb[2], ha[3], hb[3]};
+#pragma unroll
+          for (int nb = 0; nb < NB; ++nb) {
+            mma16816(acc[s][nb], a1, xb[nb].x, xb[nb].y);
+            mma16816(acc[s][nb], a2, xb[nb].z, xb[nb].w);
+          }
+        }
+      }
+    }
+
+    {
+      const long long g0 = L.group_base + (long long)strip * gps;
+      const int slot = (int)(w - g0 / per_warp);
+      float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)slot * batch * L.m;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int token = nb * 8 + tq * 2 + (i & 1);
+          const int row = (i >> 1) ? rowB : rowA;
+          if (token < batch && row < L.m) {
+            float v = acc[0][nb][i];
+#pragma unroll
+            for (int s = 1; s < NS; ++s) v = __fadd_rn(v, __fmul_rn(L.stage_scale[s], acc[s][nb][i]));
+            part[(long long)token * L.m + row] = v;
+          }
+        }
+      }
+    }
+    g += c1 - c0;
+    if (c1 == gps && strip == L.strips - 1) ++li;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Dump kernels (bit-exact gate).  They call the same decode_tile / table expansion as the compute
+// kernels and write the reconstructed rotated-domain weights in natural (row, col) order.
+// ---------------------------------------------------------------------------------------------
+template <int K1, int K2>
+__global__ void __launch_bounds__(MV_THREADS)
+trellis_dump_kernel(const uint8_t* __restrict__ p1, const uint8_t* __restrict__ p2, float s2,
+                    int m, int n, void* __restrict__ out, int out_f32) {
+  const int lane = threadIdx.x & 31;
+  const int gps = n >> 5;
+  const long long total = (long long)(m >> 5) * gps;
+  for (long long g = (long long)blockIdx.x * MV_WARPS + (threadIdx.x >> 5); g < total;
+       g += (long long)gridDim.x * MV_WARPS) {
+    const int strip = (int)(g / gps), cp = (int)(g % gps);
+    const Words<K1> v = load_words<K1>(p1 + g * (128 * K1) + lane * (4 * K1));
+    const Words<K1> vn = shfl_words<K1>(v, (lane + 1) & 31);
+    Words<K1> vn2 = vn;
+    if constexpr (K1 == 1) vn2 = shfl_words<K1>(v, (lane + 2) & 31);
+    Words<(K2 > 0 ? K2 : 1)> u, un, un2;
+    if constexpr (K2 > 0) {
+      u = load_words<K2>(p2 + g * (128 * K2) + lane * (4 * K2));
+      un = shfl_words<K2>(u, (lane + 1) & 31);
+      un2 = un;
+      if constexpr (K2 == 1) un2 = shfl_words<K2>(u, (lane + 2) & 31);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int ni = q >> 1, mi = q & 1;
+      uint32_t a[4], b[4];
+      decode_tile<K1>(chunk_of<K1>(v, q), chunk_of<K1>(vn, q), chunk_of<K1>(vn2, q), a);
+      if constexpr (K2 > 0) decode_tile<K2>(chunk_of<K2>(u, q), chunk_of<K2>(un, q), chunk_of<K2>(un2, q), b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int row = strip * 32 + mi * 16 + tile_row(lane, j);
+        const int col = cp * 32 + ni * 16 + tile_col(lane, j);
+        const uint32_t reg = a[j >> 1];
+        const __half h = __ushort_as_half((unsigned short)((j & 1) ? (reg >> 16) : (reg & 0xFFFFu)));
+        if (out_f32) {
+          float f = __half2float(h);
+          if constexpr (K2 > 0) {
+            const uint32_t reg2 = b[j >> 1];
+            const __half h2 = __ushort_as_half((unsigned short)((j & 1) ? (reg2 >> 16) : (reg2 & 0xFFFFu)));
+            f = __fadd_rn(f, __fmul_rn(__half2float(h2), s2));
+          }
+          reinterpret_cast<float*>(out)[(long long)row * n + col] = f;
+        } else {
+          reinterpret_cast<__half*>(out)[(long long)row * n + col] = h;
+        }
+      }
+    }
+  }
+}
+
+struct E8DumpArgs {
+  const uint16_t* q[GLQB_MAX_STAGES];
+  const uint32_t* table[GLQB_MAX_STAGES];
+  int entries[GLQB_MAX_STAGES];
+  float scale[GLQB_MAX_STAGES];
+  int n_stages, m, n;
+};
+
+__global__ void __launch_bounds__(256) e8_dump_kernel(E8DumpArgs A, float* __restrict__ out) {
+  const int nidx = A.n >> 3;
+  const long long total = (long long)A.m * nidx;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+    {
+      const uint32_t e = A.table[0][A.q[0][i] & (uint32_t)(A.entries[0] - 1)];
+      uint32_t h[4];
+      e8_entry_to_half2(e, h);     // same expansion the matvec uses; unpack (c_k, c_{k+4})
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        v[k] = __half2float(__ushort_as_half((unsigned short)(h[k] & 0xFFFFu)));
+        v[k + 4] = __half2float(__ushort_as_half((unsigned short)(h[k] >> 16)));
+      }
+    }
+    for (int s = 1; s < A.n_stages; ++s) {
+      const uint32_t e = A.table[s][A.q[s][i] & (uint32_t)(A.entries[s] - 1)];
+      uint32_t h[4];
+      e8_entry_to_half2(e, h);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float lo = __half2float(__ushort_as_half((unsigned short)(h[k] & 0xFFFFu)));
+        const float hi = __half2float(__ushort_as_half((unsigned short)(h[k] >> 16)));
+        v[k] = __fadd_rn(v[k], __fmul_rn(lo, A.scale[s]));
+        v[k + 4] = __fadd_rn(v[k + 4], __fmul_rn(hi, A.scale[s]));
+      }
+    }
+    float* o = out + i * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = v[k];
+  }
+}
+
+__global__ void e8_pack_table_kernel(const __half* __restrict__ cb, int entries, uint32_t* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= entries) return;
+  uint32_t p = 0;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int code = __float2int_rn(__half2float(cb[i * 8 + k]) * 2.0f) + 6;
+    p |= (uint32_t)(code & 0xF) << (4 * k);
+  }
+  out[i] = p;
+}
+
+}  // namespace glqb

@@ -1,0 +1,139 @@
+/*
+ * glq_b200 — C ABI of the B200 (sm_100a) compressed-weight matmul library for GLQ checkpoints.
+ *
+ * Everything here is plain C: device pointers travel as void*, sizes as integers, the CUDA
+ * stream as an opaque pointer (a cudaStream_t).  No entry point allocates device memory on the
+ * per-call path: callers hand in a workspace (size reported by the plan), so every run call may be
+ * captured into a CUDA graph.  Every function returns 0 on success or a negative GLQB_E_* code
+ * and never throws; glqb_last_error() gives the message for the calling thread.
+ *
+ * Citations of the form file:line name the interface of the reference project (cnygaard/glq)
+ * that the entry point stands in for.
+ */
+#ifndef GLQ_B200_H
+#define GLQ_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GLQB_OK 0
+#define GLQB_E_INVALID (-1)     /* bad argument / unsupported shape */
+#define GLQB_E_CUDA (-2)        /* a CUDA runtime call failed */
+#define GLQB_E_WORKSPACE (-3)   /* workspace missing or too small */
+#define GLQB_E_DEVICE (-4)      /* kernel reported an internal error through its status word */
+
+#define GLQB_FMT_TRELLIS_3INST 0   /* trellis_packed{,2}: glq/quantized_linear.py:351-361 */
+#define GLQB_FMT_E8_SHELL 1        /* Qidxs{,2,3,4}:      glq/quantized_linear.py:235-247 */
+
+#define GLQB_DT_F16 0
+#define GLQB_DT_BF16 1
+#define GLQB_DT_F32 2
+
+#define GLQB_MAX_STAGES 4
+#define GLQB_MAX_BLOCKS 16
+
+/* Activation codes of the MoE ops (glq_vllm/fused_moe_method.py:671-677). */
+#define GLQB_ACT_SILU 0
+#define GLQB_ACT_GELU_TANH 1
+#define GLQB_ACT_RELU2 2
+
+/*
+ * One quantised linear layer  y = [SU * H_m( wscale * W~ * H_n(SV * pad(x)) )][:out_features]
+ * with W~ decoded on the fly from `codes`.  Mirrors the argument lists of
+ *   glq_fused_linear_cuda / glq_fused_linear_block_diag_cuda    (glq/csrc/glq_bindings.cpp:334-550,
+ *                                                                schemas glq_vllm/custom_ops.py:105-126)
+ *   glq_fused_linear_trellis_3inst{,_rvq2}_cuda                 (glq_vllm/custom_ops.py:373-407)
+ */
+typedef struct GlqbLinearDesc {
+  int32_t format;                        /* GLQB_FMT_* */
+  int32_t m_pad, n_pad;                  /* stored matrix: rows (outputs) x cols (inputs) */
+  int32_t in_features, out_features;     /* <= n_pad / <= m_pad */
+  int32_t n_stages;                      /* trellis 1..2, E8 1..4 */
+  int32_t bits[GLQB_MAX_STAGES];         /* trellis: K bits/weight of the stage (1..4); E8: unused */
+  const void* codes[GLQB_MAX_STAGES];    /* device: int16 bit-stream / int16 index matrix per stage */
+  const uint32_t* table[GLQB_MAX_STAGES];/* E8: device nibble-packed table of the stage (see glqb_e8_pack_table) */
+  int32_t table_entries[GLQB_MAX_STAGES];/* E8: rows of that table (65536, or 256 for the small second stage) */
+  float stage_scale[GLQB_MAX_STAGES];    /* [0] unused; [s] = cumulative inverse residual scale of stage s+1 */
+  float wscale;                          /* the layer's scalar Wscale */
+  const float* row_scale;                /* optional device fp32 (m_pad,) multiplied per output row of W~; NULL = none */
+  const void* su;                        /* device fp16 (m_pad,) +-1 */
+  const void* sv;                        /* device fp16 (n_pad,) +-1 */
+  int32_t n_blocks_n, n_blocks_m;        /* block-diagonal Hadamard decomposition (powers of two, descending) */
+  int32_t blocks_n[GLQB_MAX_BLOCKS];
+  int32_t blocks_m[GLQB_MAX_BLOCKS];
+  int32_t batch;                         /* tokens B (rows of x) */
+  int32_t x_dtype, y_dtype;              /* GLQB_DT_* */
+  int64_t x_stride, y_stride;            /* elements between consecutive tokens */
+  int64_t x_offset, y_offset;            /* element offsets added to the x / y base pointers given at run time */
+  int32_t stop_at_yrht;                  /* 1: write fp32 rotated-domain outputs (wscale applied, no output transform)
+                                            to y (the "_yrht" ops, glq_vllm/custom_ops.py:388-392) */
+  int32_t x_is_rotated;                  /* 1: x already holds H_n(SV * pad(x)) for n_pad columns (the unfused
+                                            dequant_matvec / dequant_matmul ops, glq_vllm/custom_ops.py:58-71) */
+} GlqbLinearDesc;
+
+typedef struct GlqbPlan GlqbPlan;
+
+/* Build a plan for `count` independent linears executed by ONE launch sequence (fused q/k/v or
+ * gate/up shards that share x, the experts of one MoE step, or a whole sweep of layers).  Copies the
+ * descriptors; uploads a small device table (the only allocation, at creation). */
+int glqb_plan_create(const GlqbLinearDesc* descs, int32_t count, GlqbPlan** out_plan);
+size_t glqb_plan_workspace_bytes(const GlqbPlan* plan);
+/* algorithmic bytes (index / bit-stream tensors read once) and flops (2*B*m*n) of one run */
+int64_t glqb_plan_code_bytes(const GlqbPlan* plan);
+int64_t glqb_plan_flops(const GlqbPlan* plan);
+/* kernels launched by one glqb_plan_run */
+int32_t glqb_plan_launches(const GlqbPlan* plan);
+/* Enqueue on `stream`; returns without synchronising.  x_base / y_base are device pointers the
+ * descriptors' offsets are applied to. */
+int glqb_plan_run(GlqbPlan* plan, const void* x_base, void* y_base,
+                  void* workspace, size_t workspace_bytes, void* stream);
+/* Time (ms) the main decode kernel took in the last run made with glqb_plan_set_timing(plan, 1);
+ * measured with CUDA events on the launching stream; synchronises on that event pair. */
+int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable);
+int glqb_plan_last_kernel_ms(GlqbPlan* plan, float* ms_out);
+void glqb_plan_destroy(GlqbPlan* plan);
+
+/* Stateless single-layer forms of the reference's fused ops.  `workspace` must hold
+ * glqb_linear_workspace_bytes(desc) bytes. */
+size_t glqb_linear_workspace_bytes(const GlqbLinearDesc* desc);
+int glqb_fused_linear(const GlqbLinearDesc* desc, const void* x, void* y,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Kernel-internal decode written out, for the bit-exact gate.
+ * Trellis: replaces glq_decompress_trellis_3inst_cuda (glq/csrc/glq_bindings.cpp:349-352) — one
+ * stage gives fp16 (m, n); with a second stage the fp32 sum dec1 + dec2*inv_resid_scale2
+ * (glq/trellis.py:923-933).  out_dtype GLQB_DT_F16 (single stage only) or GLQB_DT_F32. */
+int glqb_decompress_trellis_3inst(const void* packed, int32_t bits, const void* packed2, int32_t bits2,
+                                  float inv_resid_scale2, int32_t m, int32_t n,
+                                  void* out, int32_t out_dtype, void* stream);
+/* E8: W~ = cb[q1] + cb2[q2]*s1 + cb[q3]*s2 + cb[q4]*s3 evaluated left to right with separate fp32
+ * multiply and add (glq/quantized_linear.py:1177-1194); out fp32 (m, n). */
+int glqb_dequant_e8(const void* const* qidxs, const uint32_t* const* tables, const int32_t* table_entries,
+                    const float* stage_scale, int32_t n_stages, int32_t m, int32_t n,
+                    float* out, void* stream);
+/* fp16 (entries, 8) codebook (the tensor the reference ops take, glq/codebook.py:189) -> nibble
+ * packed uint32 (entries,) with nibble i = 2*coord_i + 6 (glq/codebook.py:102-115). */
+int glqb_e8_pack_table(const void* codebook_f16, int32_t entries, uint32_t* out_packed, void* stream);
+
+/* Unfused transforms: glq_input_rht_cuda / glq_output_rht_cuda (glq_vllm/custom_ops.py:90-99). */
+int glqb_input_rht(const void* x, int32_t x_dtype, int64_t x_stride, const void* sv, void* out_f32,
+                   int32_t in_features, int32_t n_pad, const int32_t* blocks, int32_t n_blocks,
+                   int32_t batch, void* stream);
+int glqb_output_rht(const float* y_rht, const void* su, void* out, int32_t out_dtype, int64_t out_stride,
+                    int32_t out_features, int32_t m_pad, const int32_t* blocks, int32_t n_blocks,
+                    int32_t batch, void* stream);
+
+/* glq_trellis_kernel_supported(m, k) (glq/csrc/glq_bindings.cpp:345). */
+int glqb_trellis_kernel_supported(int32_t m, int32_t n);
+
+const char* glqb_last_error(void);
+const char* glqb_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLQ_B200_H */
