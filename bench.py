@@ -1,0 +1,323 @@
+#!/usr/bin/env python
+"""Benchmark of the compressed-weight matmul hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+
+Default workload (N=1): batch-1 decode over every projection of a SmolLM3-3B-shaped model stored as
+trellis 3INST at 4 bits per weight — 36 layers x (q, k, v, o, gate, up, down), 1.406 GB of packed
+bit-streams, all distinct buffers (far larger than the 126 MB L2, so nothing is re-read from cache
+between steps).  One step = one pass over all 252 projections with seeded synthetic bit-streams,
+sign vectors, scales and bf16 activations.  The metric is compressed bytes read per second.
+
+With N > 1 every projection is split tensor-parallel (rows of q/k/v/gate/up, columns of o/down, each
+shard a GLQ layer of its own) and the o/down outputs are summed with an NCCL all-reduce; the total
+work is fixed ("strong" scaling).
+
+`--impl reference` times the CPU restatement of the reference's decode-then-matmul path
+(oracle/glq_oracle.c, all host threads) on one decoder layer per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode matvec compressed-byte HBM GB/s (bs=1)"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            try:
+                sm.append(float(s[0]))
+                mx = float(s[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, s[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        med = sm[len(sm) // 2] if sm else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------------
+# workload construction
+# --------------------------------------------------------------------------------------------------
+def build_trellis_decode(device, world, rank, bits=(4,), n_layers=None):
+    """All projections of the SmolLM3-3B shape as one sweep plan; returns plan + buffers + bookkeeping."""
+    import torch
+    from glq_b200 import synth
+    from glq_b200.plan import Plan
+
+    cfg = synth.SMOLLM3_3B
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1234 + rank)
+    layers, specs = [], []
+    x_off = y_off = 0
+    reduce_slices = []          # (offset, length) of row-parallel outputs inside y, summed across ranks
+    for li in range(n_layers or cfg["layers"]):
+        for name, m, n in cfg["proj"]:
+            ms, ns = synth.shard_shape(name, m, n, world)
+            L = synth.trellis_layer(f"L{li}.{name}", ms, ns, list(bits), gen, device)
+            layers.append(L)
+            specs.append(L.spec(batch=1, x_offset=x_off, y_offset=y_off, x_stride=ns, y_stride=ms))
+            if name in synth.ROW_PARALLEL and world > 1:
+                reduce_slices.append((y_off, ms))
+            x_off += ns
+            y_off += ms
+    plan = Plan(specs)
+    gx = torch.Generator(device=device)
+    gx.manual_seed(99)
+    x = torch.randn(x_off, generator=gx, device=device, dtype=torch.float32).to(torch.bfloat16)
+    y = torch.zeros(y_off, device=device, dtype=torch.bfloat16)
+    return dict(plan=plan, x=x, y=y, layers=layers, reduce_slices=reduce_slices,
+                code_bytes=plan.code_bytes, name="smollm3-3b trellis-3inst %dbpw decode bs=1" % sum(bits))
+
+
+def cpu_layer_sample(threads_note=True):
+    """One SmolLM3-3B decoder layer (7 projections, 39,059,456 packed bytes) for the CPU restatement."""
+    import numpy as np
+    from glq_b200 import synth
+    rng = np.random.default_rng(0)
+    out = []
+    for name, m, n in synth.SMOLLM3_3B["proj"]:
+        packed = rng.integers(0, 65536, size=((m // 16) * (n // 16), 64), dtype=np.uint16).view(np.int16)
+        su = (rng.integers(0, 2, size=m) * 2 - 1).astype(np.float16)
+        sv = (rng.integers(0, 2, size=n) * 2 - 1).astype(np.float16)
+        x = rng.standard_normal((1, n)).astype(np.float32)
+        out.append((name, m, n, packed, su, sv, x))
+    return out
+
+
+def run_cpu_layer(sample):
+    from oracle import c_oracle as CO
+    from oracle import glq_oracle as O
+    nbytes = 0
+    for name, m, n, packed, su, sv, x in sample:
+        CO.trellis_linear(x, packed, 4, None, 0, 0.0, m, n, su, sv, 0.02, O.block_decompose(n), O.block_decompose(m))
+        nbytes += packed.nbytes
+    return nbytes
+
+
+def cpu_baseline(budget_s=12.0):
+    sample = cpu_layer_sample()
+    run_cpu_layer(sample)                      # warm-up (builds the library on first use)
+    t0 = time.perf_counter()
+    reps, nbytes = 0, 0
+    while True:
+        nbytes += run_cpu_layer(sample)
+        reps += 1
+        if time.perf_counter() - t0 >= budget_s or reps >= 64:
+            break
+    dt = time.perf_counter() - t0
+    threads = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"{reps} x one SmolLM3-3B decoder layer (7 projections, {nbytes // reps} packed bytes), "
+                      "decode + fp32 matvec + Hadamard transforms, oracle/glq_oracle.c with OpenMP"}
+
+
+# --------------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", type=int, default=None,
+                    help="decoder layers to build (default: all 36); smaller values are for profiler captures only")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "trellis 3INST 4 bpw decode matvec, batch 1, SmolLM3-3B projections "
+                          "(36 layers x q/k/v/o/gate/up/down), L=16 K=4, 16x16 tiles",
+              "cache": "inputs larger than L2 (1.4 GB of distinct packed weights per step)",
+              "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        sample = cpu_layer_sample()
+        for _ in range(max(1, min(args.warmup, 3))):
+            run_cpu_layer(sample)
+        t0 = time.perf_counter()
+        nbytes = 0
+        for _ in range(args.steps):
+            nbytes += run_cpu_layer(sample)
+        dt = time.perf_counter() - t0
+        v = nbytes / dt / 1e9
+        threads = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+        line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+                "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+                "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                                 "sample": "each step = one SmolLM3-3B decoder layer (7 projections, 39,059,456 packed "
+                                           "bytes): decode + fp32 matvec + Hadamard transforms on the host cores"},
+                "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path in glq_b200)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    W = build_trellis_decode(device, world, rank, n_layers=args.layers)
+    if args.layers:
+        config["layers_built"] = args.layers
+    plan, x, y = W["plan"], W["x"], W["y"]
+    total_code_bytes = W["code_bytes"]
+    if world > 1:
+        t = torch.tensor([total_code_bytes], device=device, dtype=torch.int64)
+        dist.all_reduce(t)
+        total_code_bytes = int(t.item())
+
+    def step():
+        plan.run(x, y)
+        if world > 1:
+            # row-parallel outputs (o, down) are partial sums over ranks
+            for off, ln in W["reduce_slices"]:
+                dist.all_reduce(y[off:off + ln])
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sync()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    plan.set_timing(True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    sync()
+    ms_total = e0.elapsed_time(e1)
+    kern_ms, kern_runs = plan.kernel_ms()
+    plan.set_timing(False)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = total_code_bytes / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers in, host buffers out, through the same public call
+    hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+    hx.copy_(x)
+    hy = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+    for _ in range(3):
+        x.copy_(hx, non_blocking=True); step(); hy.copy_(y, non_blocking=True)
+    sync()
+    e0.record()
+    for _ in range(args.steps):
+        x.copy_(hx, non_blocking=True)
+        step()
+        hy.copy_(y, non_blocking=True)
+    e1.record()
+    sync()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = total_code_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        kern_ms_avg = kern_ms / max(1, kern_runs)
+        achieved = W["code_bytes"] / (kern_ms_avg * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": config,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x.numel() * x.element_size(),
+                    "d2h_bytes_per_step": y.numel() * y.element_size()},
+            "gpu_launches": plan.launches * args.steps,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "kernel": "trellis_mv_kernel<4,0,1>", "achieved": achieved, "peak": peak,
+                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
+                         "kernel_ms": kern_ms_avg, "bytes_per_launch": W["code_bytes"], "traffic": None},
+        }
+        if args.gpus == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -63,8 +63,8 @@ struct GlqbPlan {
   int sm_count = 0;
   int64_t code_bytes = 0, flops = 0;
   bool timing = false;
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
-  bool have_time = false;
+  std::vector<cudaEvent_t> ev;   // pairs (start, stop) around the decode kernels of each timed run
+  size_t ev_used = 0;
 };
 
 namespace glqb {
@@ -379,20 +379,22 @@ int32_t glqb_plan_launches(const GlqbPlan* plan) {
 
 int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable) {
   if (!plan) return fail(GLQB_E_INVALID, "null plan");
-  if (enable && !plan->ev0) {
-    CUDA_TRY(cudaEventCreate(&plan->ev0));
-    CUDA_TRY(cudaEventCreate(&plan->ev1));
-  }
   plan->timing = enable != 0;
-  plan->have_time = false;
+  plan->ev_used = 0;
   return GLQB_OK;
 }
 
-int glqb_plan_last_kernel_ms(GlqbPlan* plan, float* ms_out) {
-  if (!plan || !ms_out) return fail(GLQB_E_INVALID, "null argument");
-  if (!plan->have_time) return fail(GLQB_E_INVALID, "no timed run recorded");
-  CUDA_TRY(cudaEventSynchronize(plan->ev1));
-  CUDA_TRY(cudaEventElapsedTime(ms_out, plan->ev0, plan->ev1));
+int glqb_plan_kernel_ms(GlqbPlan* plan, double* total_ms_out, int32_t* runs_out) {
+  if (!plan || !total_ms_out || !runs_out) return fail(GLQB_E_INVALID, "null argument");
+  double total = 0.0;
+  for (size_t i = 0; i + 1 < plan->ev_used; i += 2) {
+    float ms = 0.f;
+    CUDA_TRY(cudaEventSynchronize(plan->ev[i + 1]));
+    CUDA_TRY(cudaEventElapsedTime(&ms, plan->ev[i], plan->ev[i + 1]));
+    total += ms;
+  }
+  *total_ms_out = total;
+  *runs_out = (int32_t)(plan->ev_used / 2);
   return GLQB_OK;
 }
 
@@ -410,14 +412,21 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     rht_in_kernel<false><<<grid, rht_threads(P->max_bs_in), P->max_bs_in * 4, stream>>>(
         P->d_layers, P->d_items_in, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
-  if (P->timing) CUDA_TRY(cudaEventRecord(P->ev0, stream));
+  if (P->timing) {
+    while (P->ev.size() < P->ev_used + 2) {
+      cudaEvent_t e;
+      CUDA_TRY(cudaEventCreate(&e));
+      P->ev.push_back(e);
+    }
+    CUDA_TRY(cudaEventRecord(P->ev[P->ev_used], stream));
+  }
   for (const Segment& s : P->segs) {
     MvKernel kern = pick_kernel(s);
     kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);
   }
   if (P->timing) {
-    CUDA_TRY(cudaEventRecord(P->ev1, stream));
-    P->have_time = true;
+    CUDA_TRY(cudaEventRecord(P->ev[P->ev_used + 1], stream));
+    P->ev_used += 2;
   }
   {
     dim3 grid((unsigned)P->items_out.size(), (unsigned)P->max_batch);
@@ -433,8 +442,7 @@ void glqb_plan_destroy(GlqbPlan* plan) {
   if (plan->d_layers) cudaFree(plan->d_layers);
   if (plan->d_items_in) cudaFree(plan->d_items_in);
   if (plan->d_items_out) cudaFree(plan->d_items_out);
-  if (plan->ev0) cudaEventDestroy(plan->ev0);
-  if (plan->ev1) cudaEventDestroy(plan->ev1);
+  for (cudaEvent_t e : plan->ev) cudaEventDestroy(e);
   delete plan;
 }
 

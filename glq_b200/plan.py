@@ -130,10 +130,11 @@ class Plan:
     def set_timing(self, on: bool) -> None:
         _lib.check(self.lib.glqb_plan_set_timing(self.handle, 1 if on else 0), "plan_set_timing")
 
-    def last_kernel_ms(self) -> float:
-        ms = C.c_float()
-        _lib.check(self.lib.glqb_plan_last_kernel_ms(self.handle, C.byref(ms)), "plan_last_kernel_ms")
-        return float(ms.value)
+    def kernel_ms(self) -> tuple[float, int]:
+        """(summed decode-kernel time in ms, runs recorded) since timing was enabled; synchronises."""
+        ms, runs = C.c_double(), C.c_int32()
+        _lib.check(self.lib.glqb_plan_kernel_ms(self.handle, C.byref(ms), C.byref(runs)), "plan_kernel_ms")
+        return float(ms.value), int(runs.value)
 
     def close(self) -> None:
         if getattr(self, "handle", None):

@@ -91,10 +91,11 @@ int32_t glqb_plan_launches(const GlqbPlan* plan);
  * descriptors' offsets are applied to. */
 int glqb_plan_run(GlqbPlan* plan, const void* x_base, void* y_base,
                   void* workspace, size_t workspace_bytes, void* stream);
-/* Time (ms) the main decode kernel took in the last run made with glqb_plan_set_timing(plan, 1);
- * measured with CUDA events on the launching stream; synchronises on that event pair. */
+/* With timing enabled every run brackets its decode kernels with a CUDA event pair on the launching
+ * stream.  glqb_plan_kernel_ms waits for those events and returns the summed kernel time (ms) and the
+ * number of runs recorded since timing was (re-)enabled. */
 int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable);
-int glqb_plan_last_kernel_ms(GlqbPlan* plan, float* ms_out);
+int glqb_plan_kernel_ms(GlqbPlan* plan, double* total_ms_out, int32_t* runs_out);
 void glqb_plan_destroy(GlqbPlan* plan);
 
 /* Stateless single-layer forms of the reference's fused ops.  `workspace` must hold
