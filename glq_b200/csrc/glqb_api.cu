@@ -312,7 +312,8 @@ static int build_plan(GlqbPlan* P) {
       L.xr_off = P->dev[same].xr_off;
     } else {
       L.xr_off = (long long)ws;
-      ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half), 256);
+      ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) *
+                             (L.format == GLQB_FMT_TRELLIS_3INST ? XR_TRELLIS_EXPAND : 1), 256);
       for (int b = 0; b < L.nbn; ++b) P->items_in.push_back(RhtItem{pos, b});
     }
     L.part_off = (long long)ws;
@@ -583,7 +584,7 @@ size_t glqb_linear_workspace_bytes(const GlqbLinearDesc* desc) {
   // partial-sum slots (one per work group of a strip, plus one).
   if (!desc) return 0;
   const size_t gps = desc->format == GLQB_FMT_TRELLIS_3INST ? desc->n_pad / 32 : (desc->n_pad + 255) / 256;
-  size_t ws = align_up((size_t)desc->batch * desc->n_pad * 2, 256);
+  size_t ws = align_up((size_t)desc->batch * desc->n_pad * 2 * XR_TRELLIS_EXPAND, 256);
   ws += align_up((gps + 1) * (size_t)desc->batch * desc->m_pad * 4, 256);
   return ws;
 }

@@ -15,15 +15,21 @@ constexpr uint32_t MASK3 = 0x8FFF8FFFu;
 constexpr uint32_t XOR3 = 0x3B603B60u;
 
 __device__ __forceinline__ uint32_t hash3(uint32_t state16) {
-  return ((state16 * MUL3 + ADD3) & MASK3) ^ XOR3;
+  const uint32_t h = state16 * MUL3 + ADD3;
+  uint32_t r;
+  // (h & MASK) ^ XOR as ONE three-input logic op (truth table 0x6A), both constants in registers
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(r) : "r"(h), "r"(MASK3), "r"(XOR3));
+  return r;
 }
 
-// Two hashed states -> half2 (value0, value1); each value = hi half + lo half, added in fp16.
-__device__ __forceinline__ uint32_t pair3(uint32_t r0, uint32_t r1) {
-  uint32_t lo = __byte_perm(r0, r1, 0x5410);
-  uint32_t hi = __byte_perm(r0, r1, 0x7632);
-  __half2 v = __hadd2(*reinterpret_cast<__half2*>(&hi), *reinterpret_cast<__half2*>(&lo));
-  return *reinterpret_cast<uint32_t*>(&v);
+// One hashed state -> half2 (v, v) with v = fp16(hi half) + fp16(lo half), the addition done in fp16
+// (round to nearest even) exactly as the reference does.  Both halves of the result carry v: the MMA
+// then takes the register as an A-fragment entry whose two k slots meet (x, 0) in the B fragment, so
+// no instruction is spent on packing two different weights into one register.
+__device__ __forceinline__ uint32_t sum_dup3(uint32_t r) {
+  const __half2 v = *reinterpret_cast<const __half2*>(&r);
+  const __half2 s = __hadd2(__low2half2(v), __high2half2(v));
+  return *reinterpret_cast<const uint32_t*>(&s);
 }
 
 // A lane's share of one 32x32 group is 4*K bytes = K 32-bit words, holding four chunks of 8K bits
@@ -50,29 +56,50 @@ __device__ __forceinline__ uint32_t chunk_of(const Words<K>& v, int q) {
   }
 }
 
-// Decode the 8 weights a lane owns in one 16x16 tile into the four registers of an
-// m16n8k16 A fragment.  c = this lane's chunk, cn / cn2 = the chunks of lanes +1 / +2 of the same
-// tile (cyclic).  Weight j has state = stream bits [K*j, K*j+16) counted from the top of c.
+// The 8 states a lane owns in one 16x16 tile.  c = this lane's chunk, cn / cn2 = the chunks of
+// lanes +1 / +2 of the same tile (cyclic).  Weight j has state = stream bits [K*j, K*j+16) counted
+// from the top of c.
 template <int K>
-__device__ __forceinline__ void decode_tile(uint32_t c, uint32_t cn, uint32_t cn2, uint32_t (&a)[4]) {
-  uint32_t hi, lo;
+__device__ __forceinline__ void tile_states(uint32_t c, uint32_t cn, uint32_t cn2, uint32_t (&s)[8]) {
   if constexpr (K == 4) {
-    hi = c; lo = cn;
-  } else if constexpr (K == 3) {
-    hi = (c << 8) | (cn >> 16); lo = cn << 16;
-  } else if constexpr (K == 2) {
-    hi = (c << 16) | cn; lo = 0;
+    // 64-bit window {c, cn}; states start every 4 bits.  Even states are byte aligned in the window,
+    // odd states are byte aligned in the window shifted left by 4: every state is one byte permute
+    // (zero-filled upper half) of c, c<<4, w2 = window bits [16,48) or w2<<4.
+    const uint32_t w2 = __byte_perm(cn, c, 0x5432);
+    const uint32_t t1 = c << 4;
+    const uint32_t t2 = w2 << 4;
+    s[0] = __byte_perm(c, 0u, 0x4432);
+    s[1] = __byte_perm(t1, 0u, 0x4432);
+    s[2] = __byte_perm(c, 0u, 0x4421);
+    s[3] = __byte_perm(t1, 0u, 0x4421);
+    s[4] = __byte_perm(c, 0u, 0x4410);
+    s[5] = __byte_perm(t2, 0u, 0x4432);
+    s[6] = __byte_perm(w2, 0u, 0x4421);
+    s[7] = __byte_perm(t2, 0u, 0x4421);
   } else {
-    hi = (c << 24) | (cn << 16) | (cn2 << 8); lo = 0;
-  }
-  uint32_t r[8];
+    uint32_t hi, lo;
+    if constexpr (K == 3) {
+      hi = (c << 8) | (cn >> 16); lo = cn << 16;
+    } else if constexpr (K == 2) {
+      hi = (c << 16) | cn; lo = 0;
+    } else {
+      hi = (c << 24) | (cn << 16) | (cn2 << 8); lo = 0;
+    }
 #pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    uint32_t top = (K * j == 0) ? hi : __funnelshift_l(lo, hi, K * j);
-    r[j] = hash3(top >> 16);
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t top = (K * j == 0) ? hi : ((K * j + 16 <= 32) ? (hi << (K * j)) : __funnelshift_l(lo, hi, K * j));
+      s[j] = top >> 16;
+    }
   }
+}
+
+// Decode a lane's 8 weights of a tile: a[j] = half2 (w_j, w_j).
+template <int K>
+__device__ __forceinline__ void decode_tile(uint32_t c, uint32_t cn, uint32_t cn2, uint32_t (&a)[8]) {
+  uint32_t s[8];
+  tile_states<K>(c, cn, cn2, s);
 #pragma unroll
-  for (int p = 0; p < 4; ++p) a[p] = pair3(r[2 * p], r[2 * p + 1]);
+  for (int j = 0; j < 8; ++j) a[j] = sum_dup3(hash3(s[j]));
 }
 
 // Position of weight (lane, j) inside its 16x16 tile.

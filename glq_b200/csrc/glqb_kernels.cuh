@@ -51,10 +51,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// position of column c (0..31) of a trellis group inside the fragment-ordered activation layout
+// Trellis activations are stored per 32-column group as 64 halfs: column c = 16ni + 8h + 2t + e sits at
+// half index t*16 + ni*8 + e*4 + h*2 and is followed by a zero, i.e. every B-fragment register of
+// the MMA is (x, 0).  Lane t fetches its 32 bytes of a group with two 16-byte loads (one per ni).
+constexpr int XR_TRELLIS_EXPAND = 2;   // halfs stored per activation
 __device__ __forceinline__ int xr_pos_trellis(int c) {
   int ni = c >> 4, h = (c >> 3) & 1, t = (c >> 1) & 3, e = c & 1;
-  return t * 8 + ni * 4 + h * 2 + e;
+  return t * 16 + ni * 8 + e * 4 + h * 2;
 }
 // position of column i (0..7) of an E8 block: (x0,x4,x1,x5,x2,x6,x3,x7)
 __device__ __forceinline__ int xr_pos_e8(int i) { return (i & 3) * 2 + (i >> 2); }
@@ -100,12 +103,20 @@ __global__ void __launch_bounds__(1024) rht_in_kernel(const DevLinear* __restric
     float* out = reinterpret_cast<float*>(ws + L.xr_off) + (long long)token * L.n;
     for (int i = threadIdx.x; i < bs; i += blockDim.x) out[off + i] = fbuf[i] * rs;
   } else {
-    __half* out = reinterpret_cast<__half*>(ws + L.xr_off) + (long long)token * L.n;
     const bool trellis = (L.format == GLQB_FMT_TRELLIS_3INST);
-    for (int i = threadIdx.x; i < bs; i += blockDim.x) {
-      const int col = off + i;
-      const int pos = trellis ? ((col & ~31) + xr_pos_trellis(col & 31)) : ((col & ~7) + xr_pos_e8(col & 7));
-      out[pos] = __float2half_rn(fbuf[i] * rs);
+    if (trellis) {
+      __half2* out = reinterpret_cast<__half2*>(ws + L.xr_off) + (long long)token * L.n;
+      for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+        const int col = off + i;
+        const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);   // half index, even
+        out[pos >> 1] = __halves2half2(__float2half_rn(fbuf[i] * rs), __float2half_rn(0.f));
+      }
+    } else {
+      __half* out = reinterpret_cast<__half*>(ws + L.xr_off) + (long long)token * L.n;
+      for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+        const int col = off + i;
+        out[(col & ~7) + xr_pos_e8(col & 7)] = __float2half_rn(fbuf[i] * rs);
+      }
     }
   }
 }
@@ -198,9 +209,10 @@ __device__ __forceinline__ Words<K> shfl_words(const Words<K>& v, int src) {
   return r;
 }
 
-// decode the four tiles of a group and issue their MMAs against the B fragments in xb[nb]
+// decode the four tiles of a group and issue their MMAs against the B fragments xb[nb][ni]
+// (xb[nb][ni] = {e0:(x,0) k-lo, e0 k-hi, e1 k-lo, e1 k-hi})
 template <int K, int NB>
-__device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uint4 (&xb)[NB],
+__device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uint4 (&xb)[NB][2],
                                           float (&acc)[NB][2][4]) {
   const Words<K> vn = shfl_words<K>(v, (lane + 1) & 31);
   Words<K> vn2 = vn;
@@ -210,20 +222,21 @@ __device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uin
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi) {
       const int q = ni * 2 + mi;
-      uint32_t a[4];
+      uint32_t a[8];
       decode_tile<K>(chunk_of<K>(v, q), chunk_of<K>(vn, q), chunk_of<K>(vn2, q), a);
+      const uint32_t a_even[4] = {a[0], a[2], a[4], a[6]};   // columns 2t   / 8+2t   of the tile
+      const uint32_t a_odd[4] = {a[1], a[3], a[5], a[7]};    // columns 2t+1 / 8+2t+1
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
-        const uint32_t b0 = ni ? xb[nb].z : xb[nb].x;
-        const uint32_t b1 = ni ? xb[nb].w : xb[nb].y;
-        mma16816(acc[nb][mi], a, b0, b1);
+        mma16816(acc[nb][mi], a_even, xb[nb][ni].x, xb[nb][ni].y);
+        mma16816(acc[nb][mi], a_odd, xb[nb][ni].z, xb[nb][ni].w);
       }
     }
   }
 }
 
 template <int K1, int K2, int NB>
-__global__ void __launch_bounds__(MV_THREADS)
+__global__ void __launch_bounds__(MV_THREADS, (NB == 1 && K2 == 0) ? 3 : 1)
 trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
                   int per_warp, uint8_t* __restrict__ ws) {
   constexpr int PF = 4;   // codes of PF groups in flight per lane
@@ -269,20 +282,53 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
     for (int nb = 0; nb < NB; ++nb) {
       const int token = nb * 8 + gq;
       xok[nb] = token < batch;
-      xq[nb] = reinterpret_cast<const uint4*>(xr + (long long)(xok[nb] ? token : 0) * L.n + c0 * 32 + tq * 8);
+      xq[nb] = reinterpret_cast<const uint4*>(xr + ((long long)(xok[nb] ? token : 0) * L.n + c0 * 32) * XR_TRELLIS_EXPAND +
+                                              tq * 16);
     }
 
     const int ng = c1 - c0;
+    // One group step: codes of this group are in v/v2; the codes of the group PF ahead are requested
+    // before the decode starts so that PF groups per lane are always in flight.
     Words<K1> cur[PF];
     Words<(K2 > 0 ? K2 : 1)> cur2[PF];
 #pragma unroll
     for (int i = 0; i < PF; ++i) {
       if (i < ng) {
-        cur[i] = load_words<K1>(p1 + (long long)i * (128 * K1));
-        if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + (long long)i * (128 * K2));
+        cur[i] = load_words<K1>(p1 + i * (128 * K1));
+        if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + i * (128 * K2));
       }
     }
-    for (int c = 0; c < ng; c += PF) {
+    const uint8_t* q1 = p1 + PF * (128 * K1);     // next codes to request
+    const uint8_t* q2 = p2 + PF * (128 * K2);
+    int c = 0;
+    // full chunks with every prefetch in range: no per-group bounds checks
+    for (; c + 2 * PF <= ng; c += PF) {
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        const Words<K1> v = cur[i];
+        Words<(K2 > 0 ? K2 : 1)> v2;
+        if constexpr (K2 > 0) v2 = cur2[i];
+        cur[i] = load_words<K1>(q1 + i * (128 * K1));
+        if constexpr (K2 > 0) cur2[i] = load_words<K2>(q2 + i * (128 * K2));
+        uint4 xb[NB][2];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          xb[nb][0] = xb[nb][1] = make_uint4(0u, 0u, 0u, 0u);
+          if (xok[nb]) {                                   // 64 halfs = 8 uint4 per group
+            xb[nb][0] = __ldg(xq[nb] + i * 8);
+            xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
+          }
+        }
+        group_mma<K1, NB>(v, lane, xb, acc);
+        if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
+      }
+      q1 += PF * (128 * K1);
+      q2 += PF * (128 * K2);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) xq[nb] += PF * 8;
+    }
+    // tail: up to 2*PF - 1 groups, bounds checked
+    for (; c < ng; c += PF) {
 #pragma unroll
       for (int i = 0; i < PF; ++i) {
         if (c + i < ng) {
@@ -290,19 +336,26 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
           Words<(K2 > 0 ? K2 : 1)> v2;
           if constexpr (K2 > 0) v2 = cur2[i];
           if (c + i + PF < ng) {
-            cur[i] = load_words<K1>(p1 + (long long)(c + i + PF) * (128 * K1));
-            if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + (long long)(c + i + PF) * (128 * K2));
+            cur[i] = load_words<K1>(q1 + i * (128 * K1));
+            if constexpr (K2 > 0) cur2[i] = load_words<K2>(q2 + i * (128 * K2));
           }
-          uint4 xb[NB];
+          uint4 xb[NB][2];
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb) {
-            xb[nb] = make_uint4(0u, 0u, 0u, 0u);
-            if (xok[nb]) xb[nb] = __ldg(xq[nb] + (c + i) * 4);   // 32 halfs = 4 uint4 per group
+            xb[nb][0] = xb[nb][1] = make_uint4(0u, 0u, 0u, 0u);
+            if (xok[nb]) {
+              xb[nb][0] = __ldg(xq[nb] + i * 8);
+              xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
+            }
           }
           group_mma<K1, NB>(v, lane, xb, acc);
           if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
         }
       }
+      q1 += PF * (128 * K1);
+      q2 += PF * (128 * K2);
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) xq[nb] += PF * 8;
     }
 
     // flush: C fragment (row gq / gq+8, tokens 2tq, 2tq+1 of each column block)
@@ -496,20 +549,18 @@ trellis_dump_kernel(const uint8_t* __restrict__ p1, const uint8_t* __restrict__ 
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const int ni = q >> 1, mi = q & 1;
-      uint32_t a[4], b[4];
+      uint32_t a[8], b[8];
       decode_tile<K1>(chunk_of<K1>(v, q), chunk_of<K1>(vn, q), chunk_of<K1>(vn2, q), a);
       if constexpr (K2 > 0) decode_tile<K2>(chunk_of<K2>(u, q), chunk_of<K2>(un, q), chunk_of<K2>(un2, q), b);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int row = strip * 32 + mi * 16 + tile_row(lane, j);
         const int col = cp * 32 + ni * 16 + tile_col(lane, j);
-        const uint32_t reg = a[j >> 1];
-        const __half h = __ushort_as_half((unsigned short)((j & 1) ? (reg >> 16) : (reg & 0xFFFFu)));
+        const __half h = __ushort_as_half((unsigned short)(a[j] & 0xFFFFu));
         if (out_f32) {
           float f = __half2float(h);
           if constexpr (K2 > 0) {
-            const uint32_t reg2 = b[j >> 1];
-            const __half h2 = __ushort_as_half((unsigned short)((j & 1) ? (reg2 >> 16) : (reg2 & 0xFFFFu)));
+            const __half h2 = __ushort_as_half((unsigned short)(b[j] & 0xFFFFu));
             f = __fadd_rn(f, __fmul_rn(__half2float(h2), s2));
           }
           reinterpret_cast<float*>(out)[(long long)row * n + col] = f;
