@@ -23,6 +23,7 @@ EXPORTS = [
     "glqb_plan_destroy", "glqb_linear_workspace_bytes", "glqb_fused_linear",
     "glqb_decompress_trellis_3inst", "glqb_dequant_e8", "glqb_e8_pack_table", "glqb_input_rht",
     "glqb_output_rht", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
+    "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
 ]
 
 
@@ -100,6 +101,11 @@ def load() -> C.CDLL:
     lib.glqb_output_rht.restype = C.c_int
     lib.glqb_trellis_kernel_supported.argtypes = [i32, i32]
     lib.glqb_trellis_kernel_supported.restype = C.c_int
+    lib.glqb_trellis_linear_noalloc.argtypes = [vp, i32, vp, i32, vp, i32, vp, vp, f32, i32, i32,
+                                                C.POINTER(i32), i32, C.POINTER(i32), i32, vp]
+    lib.glqb_trellis_linear_noalloc.restype = C.c_int
+    lib.glqb_noalloc_scratch_bytes.argtypes = []
+    lib.glqb_noalloc_scratch_bytes.restype = sz
     lib.glqb_last_error.argtypes = []
     lib.glqb_last_error.restype = C.c_char_p
     lib.glqb_version.argtypes = []

@@ -15,6 +15,8 @@ namespace glqb {
 
 static thread_local std::string g_err;
 
+void set_error_message(const char* msg) { g_err = msg ? msg : ""; }
+
 static int fail(int code, const char* fmt, ...) {
   char buf[512];
   va_list ap;

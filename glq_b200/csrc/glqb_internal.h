@@ -41,6 +41,9 @@ struct RhtItem {
   int block;
 };
 
+// Stores the message glqb_last_error() returns for the calling thread (defined in glqb_api.cu).
+void set_error_message(const char* msg);
+
 // Status word written by kernels that detect an internal inconsistency (never a trap).
 enum : int { ST_OK = 0, ST_BAD_RANGE = 1 };
 

@@ -580,7 +580,7 @@ struct E8DumpArgs {
   int n_stages, m, n;
 };
 
-__global__ void __launch_bounds__(256) e8_dump_kernel(E8DumpArgs A, float* __restrict__ out) {
+static __global__ void __launch_bounds__(256) e8_dump_kernel(E8DumpArgs A, float* __restrict__ out) {
   const int nidx = A.n >> 3;
   const long long total = (long long)A.m * nidx;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -614,7 +614,7 @@ __global__ void __launch_bounds__(256) e8_dump_kernel(E8DumpArgs A, float* __res
   }
 }
 
-__global__ void e8_pack_table_kernel(const __half* __restrict__ cb, int entries, uint32_t* __restrict__ out) {
+static __global__ void e8_pack_table_kernel(const __half* __restrict__ cb, int entries, uint32_t* __restrict__ out) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= entries) return;
   uint32_t p = 0;

@@ -131,6 +131,29 @@ int glqb_output_rht(const float* y_rht, const void* su, void* out, int32_t out_d
 /* glq_trellis_kernel_supported(m, k) (glq/csrc/glq_bindings.cpp:345). */
 int glqb_trellis_kernel_supported(int32_t m, int32_t n);
 
+/*
+ * Batch-1 trellis 3INST linear (same mathematics as a one-layer plan) that needs neither a plan nor a
+ * workspace: its scratch memory is a fixed array inside the library.  No counterpart in the reference.
+ * It exists for callers that cannot allocate device memory where they run a layer (a host that sized
+ * all device memory at start-up, a callback inside another allocator, a program without any
+ * allocator of its own).  It calls no cudaMalloc/cudaFree and no allocating library routine.
+ *   - limits: one token, one stage, K = 1..4, m % 32 == 0, n % 32 == 0, m and n <= 32768; larger or
+ *     batched layers are refused with GLQB_E_INVALID (use the plan entry points);
+ *   - glqb_noalloc_scratch_bytes() bytes (4 MiB) of device memory are held by every GPU that loads the
+ *     library, until the process ends;
+ *   - the first call on a device looks up the array's device address and raises two kernels'
+ *     shared-memory limits: make that first call outside of any stream capture;
+ *   - all calls on one GPU share the array (it keeps the previous call's contents; every word a
+ *     call reads it has written earlier in the same call, so nothing needs clearing): calls that may
+ *     overlap on the GPU — different streams, or different host threads — race and must be ordered
+ *     by the caller.
+ */
+int glqb_trellis_linear_noalloc(const void* x, int32_t x_dtype, void* y, int32_t y_dtype, const void* packed,
+                                int32_t bits, const void* su, const void* sv, float wscale, int32_t m, int32_t n,
+                                const int32_t* blocks_n, int32_t n_blocks_n, const int32_t* blocks_m,
+                                int32_t n_blocks_m, void* stream);
+size_t glqb_noalloc_scratch_bytes(void);
+
 const char* glqb_last_error(void);
 const char* glqb_version(void);
 
