@@ -9,7 +9,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libglq_b200.so")
+LIB_PATH = os.environ.get("GLQB_LIB_PATH") or os.path.join(_HERE, "libglq_b200.so")
 
 MAX_STAGES = 4
 MAX_BLOCKS = 16

@@ -33,20 +33,23 @@ def needs_build() -> bool:
     return os.path.exists(hdr) and os.path.getmtime(hdr) > t
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    if not force and not needs_build():
+def build(force: bool = False, verbose: bool = False, out: str = LIB, defines=()) -> str:
+    """``out`` / ``defines`` build a tuning variant beside the default library (see GLQB_LIB_PATH)."""
+    if not force and out == LIB and not needs_build():
         return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS]
+    cmd = [_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines]]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB]
+    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", out]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr)
-    return LIB
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    _defs = [a[2:] for a in sys.argv[1:] if a.startswith("-D")]
+    _out = next((a.split("=", 1)[1] for a in sys.argv[1:] if a.startswith("--out=")), LIB)
+    print(build(force="--force" in sys.argv or bool(_defs), verbose="-v" in sys.argv, out=_out, defines=_defs))

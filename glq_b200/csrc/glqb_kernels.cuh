@@ -236,10 +236,16 @@ __device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uin
 }
 
 template <int K1, int K2, int NB>
-__global__ void __launch_bounds__(MV_THREADS, (NB == 1 && K2 == 0) ? 3 : 1)
+#ifndef GLQB_MINB
+#define GLQB_MINB 3
+#endif
+__global__ void __launch_bounds__(MV_THREADS, (NB == 1 && K2 == 0) ? GLQB_MINB : 1)
 trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
                   int per_warp, uint8_t* __restrict__ ws) {
-  constexpr int PF = 4;   // codes of PF groups in flight per lane
+#ifndef GLQB_PF
+#define GLQB_PF 4
+#endif
+  constexpr int PF = GLQB_PF;   // codes of PF groups in flight per lane
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * MV_WARPS + (threadIdx.x >> 5);
   long long g = w * per_warp;
@@ -276,14 +282,14 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
     const uint8_t* p2 = nullptr;
     if constexpr (K2 > 0) p2 = L.codes[1] + ((long long)strip * gps + c0) * (128 * K2) + lane * (4 * K2);
     const __half* xr = reinterpret_cast<const __half*>(ws + L.xr_off);
+    // MMA column gq of block nb carries token 8*nb + gq.  Columns past the batch read the last
+    // token again: their products land in accumulator columns that are never stored, which saves the
+    // predicate and the zero fill on every group.
     const uint4* xq[NB];
-    bool xok[NB];
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
-      const int token = nb * 8 + gq;
-      xok[nb] = token < batch;
-      xq[nb] = reinterpret_cast<const uint4*>(xr + ((long long)(xok[nb] ? token : 0) * L.n + c0 * 32) * XR_TRELLIS_EXPAND +
-                                              tq * 16);
+      const int token = min(nb * 8 + gq, batch - 1);
+      xq[nb] = reinterpret_cast<const uint4*>(xr + ((long long)token * L.n + c0 * 32) * XR_TRELLIS_EXPAND + tq * 16);
     }
 
     const int ng = c1 - c0;
@@ -313,11 +319,8 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
         uint4 xb[NB][2];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          xb[nb][0] = xb[nb][1] = make_uint4(0u, 0u, 0u, 0u);
-          if (xok[nb]) {                                   // 64 halfs = 8 uint4 per group
-            xb[nb][0] = __ldg(xq[nb] + i * 8);
-            xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
-          }
+          xb[nb][0] = __ldg(xq[nb] + i * 8);               // 64 halfs = 8 uint4 per group
+          xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
         }
         group_mma<K1, NB>(v, lane, xb, acc);
         if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
@@ -342,11 +345,8 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
           uint4 xb[NB][2];
 #pragma unroll
           for (int nb = 0; nb < NB; ++nb) {
-            xb[nb][0] = xb[nb][1] = make_uint4(0u, 0u, 0u, 0u);
-            if (xok[nb]) {
-              xb[nb][0] = __ldg(xq[nb] + i * 8);
-              xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
-            }
+            xb[nb][0] = __ldg(xq[nb] + i * 8);
+            xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
           }
           group_mma<K1, NB>(v, lane, xb, acc);
           if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
