@@ -106,28 +106,23 @@ def build_trellis_decode(device, world, rank, bits=(4,), n_layers=None):
     from glq_b200 import synth
     from glq_b200.plan import Plan
 
+    from glq_b200 import tp
+
     cfg = synth.SMOLLM3_3B
     gen = torch.Generator(device=device)
     gen.manual_seed(1234 + rank)
+    layout = tp.build_layout(cfg["proj"], n_layers or cfg["layers"], world, rank)
     layers, specs = [], []
-    x_off = y_off = 0
-    reduce_slices = []          # (offset, length) of row-parallel outputs inside y, summed across ranks
-    for li in range(n_layers or cfg["layers"]):
-        for name, m, n in cfg["proj"]:
-            ms, ns = synth.shard_shape(name, m, n, world)
-            L = synth.trellis_layer(f"L{li}.{name}", ms, ns, list(bits), gen, device)
-            layers.append(L)
-            specs.append(L.spec(batch=1, x_offset=x_off, y_offset=y_off, x_stride=ns, y_stride=ms))
-            if name in synth.ROW_PARALLEL and world > 1:
-                reduce_slices.append((y_off, ms))
-            x_off += ns
-            y_off += ms
+    for e in layout.entries:
+        L = synth.trellis_layer(f"L{e.layer}.{e.name}", e.m, e.n, list(bits), gen, device)
+        layers.append(L)
+        specs.append(L.spec(batch=1, x_offset=e.x_offset, y_offset=e.y_offset, x_stride=e.n, y_stride=e.m))
     plan = Plan(specs)
     gx = torch.Generator(device=device)
     gx.manual_seed(99)
-    x = torch.randn(x_off, generator=gx, device=device, dtype=torch.float32).to(torch.bfloat16)
-    y = torch.zeros(y_off, device=device, dtype=torch.bfloat16)
-    return dict(plan=plan, x=x, y=y, layers=layers, reduce_slices=reduce_slices,
+    x = torch.randn(layout.x_elems, generator=gx, device=device, dtype=torch.float32).to(torch.bfloat16)
+    y = torch.zeros(layout.y_elems, device=device, dtype=torch.bfloat16)
+    return dict(plan=plan, x=x, y=y, layers=layers, layout=layout,
                 code_bytes=plan.code_bytes, name="smollm3-3b trellis-3inst %dbpw decode bs=1" % sum(bits))
 
 
@@ -235,12 +230,14 @@ def main():
         dist.all_reduce(t)
         total_code_bytes = int(t.item())
 
+    from glq_b200 import tp
+
     def step():
         plan.run(x, y)
-        if world > 1:
-            # row-parallel outputs (o, down) are partial sums over ranks
-            for off, ln in W["reduce_slices"]:
-                dist.all_reduce(y[off:off + ln])
+        # row-parallel outputs (o, down) are partial sums over ranks: one NCCL all-reduce over the
+        # contiguous tail of y (the sweep has no dependency between layers, so the per-layer
+        # reductions of a real decode step are issued as one)
+        tp.all_reduce_row_parallel(y, W["layout"])
 
     def sync():
         if world > 1:
