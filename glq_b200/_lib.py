@@ -20,7 +20,7 @@ DT_F16, DT_BF16, DT_F32 = 0, 1, 2
 EXPORTS = [
     "glqb_plan_create", "glqb_plan_workspace_bytes", "glqb_plan_code_bytes", "glqb_plan_flops",
     "glqb_plan_launches", "glqb_plan_run", "glqb_plan_set_timing", "glqb_plan_kernel_ms",
-    "glqb_plan_destroy", "glqb_linear_workspace_bytes", "glqb_fused_linear",
+    "glqb_plan_destroy", "glqb_plan_status", "glqb_linear_workspace_bytes", "glqb_fused_linear",
     "glqb_decompress_trellis_3inst", "glqb_dequant_e8", "glqb_e8_pack_table", "glqb_input_rht",
     "glqb_output_rht", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
     "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
@@ -82,6 +82,8 @@ def load() -> C.CDLL:
     lib.glqb_plan_set_timing.restype = C.c_int
     lib.glqb_plan_kernel_ms.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(i32)]
     lib.glqb_plan_kernel_ms.restype = C.c_int
+    lib.glqb_plan_status.argtypes = [vp, C.POINTER(i32)]
+    lib.glqb_plan_status.restype = C.c_int
     lib.glqb_plan_destroy.argtypes = [vp]
     lib.glqb_plan_destroy.restype = None
     lib.glqb_linear_workspace_bytes.argtypes = [C.POINTER(LinearDesc)]

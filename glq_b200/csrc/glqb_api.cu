@@ -10,6 +10,7 @@
 #include <vector>
 
 #include "glqb_kernels.cuh"
+#include "glqb_gemm.cuh"
 
 namespace glqb {
 
@@ -40,11 +41,16 @@ static inline int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; 
 // token-column blocks, contiguous in the device table.
 struct Segment {
   int format, k1, k2, ns, nb;
+  int tn;                    // 0: streaming decode kernel; 128 / 256: tensor-core GEMM with that token tile
   int first, count;          // range in the device table
   long long total_groups;
   int per_warp;
   int grid;
+  int item_first, item_count;   // GEMM work items (range in the plan's item array)
 };
+
+constexpr int GEMM_STAGES = 4;
+constexpr int DECODE_MAX_BATCH = 64;   // above this the GEMM path is used
 
 }  // namespace glqb
 
@@ -56,9 +62,15 @@ struct GlqbPlan {
   std::vector<DevLinear> dev;          // host copy of the device table
   std::vector<Segment> segs;
   std::vector<RhtItem> items_in, items_out;
+  std::vector<RhtItem> items_in_gemm;
+  std::vector<GemmItem> gemm_items;
   DevLinear* d_layers = nullptr;
   RhtItem* d_items_in = nullptr;
+  RhtItem* d_items_in_gemm = nullptr;
   RhtItem* d_items_out = nullptr;
+  GemmItem* d_gemm_items = nullptr;
+  int* d_status = nullptr;
+  int max_batch_gemm = 1;
   size_t ws_bytes = 0;
   int max_batch = 1;
   int max_bs_in = 32, max_bs_out = 32;
@@ -121,6 +133,39 @@ static MvKernel pick_kernel(const Segment& s) {
   return s.format == GLQB_FMT_TRELLIS_3INST ? trellis_kernel(s.k1, s.k2, s.nb) : e8_kernel(s.ns, s.nb);
 }
 
+typedef void (*GemmKernel)(const DevLinear*, const GemmItem*, int, uint8_t*, int*);
+
+template <int FORMAT, int K1, int K2>
+static GemmKernel gemm_kernel_tn(int tn) {
+  if (tn == 128) return glq_gemm_kernel<FORMAT, K1, K2, 128, GEMM_STAGES>;
+  if (tn == 256) return glq_gemm_kernel<FORMAT, K1, K2, 256, GEMM_STAGES>;
+  return nullptr;
+}
+
+static GemmKernel pick_gemm_kernel(const Segment& s) {
+  if (s.format == GLQB_FMT_TRELLIS_3INST) {
+#define G_CASE(A, B) if (s.k1 == A && s.k2 == B) return gemm_kernel_tn<0, A, B>(s.tn);
+    G_CASE(1, 0) G_CASE(2, 0) G_CASE(3, 0) G_CASE(4, 0)
+    G_CASE(4, 1) G_CASE(4, 2) G_CASE(4, 3) G_CASE(4, 4)
+    G_CASE(2, 2) G_CASE(3, 3) G_CASE(2, 1) G_CASE(3, 1) G_CASE(3, 2)
+#undef G_CASE
+    return nullptr;
+  }
+  switch (s.ns) {
+    case 1: return gemm_kernel_tn<1, 1, 0>(s.tn);
+    case 2: return gemm_kernel_tn<1, 2, 0>(s.tn);
+    case 3: return gemm_kernel_tn<1, 3, 0>(s.tn);
+    case 4: return gemm_kernel_tn<1, 4, 0>(s.tn);
+  }
+  return nullptr;
+}
+
+static size_t gemm_smem_bytes(int tn) {
+  return (size_t)GEMM_STAGES * (GM_A_BYTES + (size_t)tn * 128) + (3 * GEMM_STAGES + 2) * 8 + 16 + 1024;
+}
+
+static int tn_for_batch(int batch) { return batch <= DECODE_MAX_BATCH ? 0 : (batch <= 128 ? 128 : 256); }
+
 static int nb_for_batch(int batch) {
   if (batch <= 8) return 1;
   if (batch <= 16) return 2;
@@ -136,8 +181,7 @@ static int validate(const GlqbLinearDesc& d, int idx) {
     return fail(GLQB_E_INVALID, "layer %d: bad dims m_pad=%d n_pad=%d in=%d out=%d", idx, d.m_pad, d.n_pad,
                 d.in_features, d.out_features);
   if (d.batch < 1) return fail(GLQB_E_INVALID, "layer %d: batch %d", idx, d.batch);
-  if (d.batch > 64)
-    return fail(GLQB_E_INVALID, "layer %d: batch %d exceeds the decode-path limit of 64 tokens", idx, d.batch);
+  if (d.batch > 65535) return fail(GLQB_E_INVALID, "layer %d: batch %d exceeds 65535 tokens", idx, d.batch);
   if (!d.su || !d.sv || !d.codes[0]) return fail(GLQB_E_INVALID, "layer %d: null su/sv/codes", idx);
   if (d.format == GLQB_FMT_TRELLIS_3INST) {
     if (d.m_pad % 32 || d.n_pad % 32)
@@ -191,16 +235,18 @@ static int build_plan(GlqbPlan* P) {
   CUDA_TRY(cudaDeviceGetAttribute(&P->sm_count, cudaDevAttrMultiProcessorCount, dev_id));
 
   // ---- segments: layers with the same kernel variant, in caller order inside a segment
-  typedef std::tuple<int, int, int, int, int> Key;   // format, k1, k2, ns, nb
+  typedef std::tuple<int, int, int, int, int, int> Key;   // format, k1, k2, ns, nb, tn
   std::map<Key, std::vector<int>> groups;
   std::vector<Key> key_order;
   for (int i = 0; i < n; ++i) {
     const GlqbLinearDesc& d = P->descs[i];
     Key k;
+    const int tn = tn_for_batch(d.batch);
+    const int nb = tn ? 0 : nb_for_batch(d.batch);
     if (d.format == GLQB_FMT_TRELLIS_3INST)
-      k = Key(d.format, d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, d.n_stages, nb_for_batch(d.batch));
+      k = Key(d.format, d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, d.n_stages, nb, tn);
     else
-      k = Key(d.format, 0, 0, d.n_stages, nb_for_batch(d.batch));
+      k = Key(d.format, 0, 0, d.n_stages, nb, tn);
     if (!groups.count(k)) key_order.push_back(k);
     groups[k].push_back(i);
   }
@@ -209,11 +255,12 @@ static int build_plan(GlqbPlan* P) {
   for (const Key& k : key_order) {
     Segment s;
     s.format = std::get<0>(k); s.k1 = std::get<1>(k); s.k2 = std::get<2>(k);
-    s.ns = std::get<3>(k); s.nb = std::get<4>(k);
+    s.ns = std::get<3>(k); s.nb = std::get<4>(k); s.tn = std::get<5>(k);
+    s.item_first = s.item_count = 0;
     s.first = (int)P->order.size();
     s.count = (int)groups[k].size();
     for (int i : groups[k]) P->order.push_back(i);
-    if (!pick_kernel(s))
+    if (s.tn ? !pick_gemm_kernel(s) : !pick_kernel(s))
       return fail(GLQB_E_INVALID, "no kernel variant for format=%d K=%d+%d stages=%d token blocks=%d", s.format,
                   s.k1, s.k2, s.ns, s.nb);
     P->segs.push_back(s);
@@ -268,7 +315,44 @@ static int build_plan(GlqbPlan* P) {
   }
 
   // ---- per segment: group prefix, range length per warp, grid
+  P->gemm_items.clear();
   for (Segment& s : P->segs) {
+    if (s.tn) {
+      // tensor-core GEMM: work items = (layer, 128-row tile, token tile[, K split]); the K range is
+      // split only when there are too few tiles to occupy the SMs
+      long long tiles = 0;
+      for (int i = 0; i < s.count; ++i) {
+        const DevLinear& L = P->dev[s.first + i];
+        tiles += (long long)((L.m + GM_TILE_M - 1) / GM_TILE_M) * ((L.batch + s.tn - 1) / s.tn);
+      }
+      s.item_first = (int)P->gemm_items.size();
+      for (int i = 0; i < s.count; ++i) {
+        DevLinear& L = P->dev[s.first + i];
+        const int m_tiles = (L.m + GM_TILE_M - 1) / GM_TILE_M, n_tiles = (L.batch + s.tn - 1) / s.tn;
+        const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
+        int ks = 1;
+        if (tiles < P->sm_count) ks = (int)std::min<long long>(std::max(1, kchunks / 8), (P->sm_count + tiles - 1) / tiles);
+        ks = std::max(1, std::min(ks, 16));
+        const int per = (kchunks + ks - 1) / ks;
+        ks = (kchunks + per - 1) / per;
+        L.fixed_slots = ks;
+        L.slots = ks;
+        L.gemm_tn = s.tn;
+        L.per_warp = 1;
+        for (int mt = 0; mt < m_tiles; ++mt)
+          for (int nt = 0; nt < n_tiles; ++nt)
+            for (int k = 0; k < ks; ++k)
+              P->gemm_items.push_back(GemmItem{s.first + i, mt, nt, k * per, std::min(kchunks, (k + 1) * per), k});
+        P->max_batch_gemm = std::max(P->max_batch_gemm, L.batch);
+      }
+      s.item_count = (int)P->gemm_items.size() - s.item_first;
+      s.grid = std::min(s.item_count, P->sm_count);
+      s.total_groups = 0;
+      s.per_warp = 1;
+      CUDA_TRY(cudaFuncSetAttribute(pick_gemm_kernel(s), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)gemm_smem_bytes(s.tn)));
+      continue;
+    }
     MvKernel kern = pick_kernel(s);
     int ctas_per_sm = 1;
     CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, MV_THREADS, 0));
@@ -296,6 +380,7 @@ static int build_plan(GlqbPlan* P) {
   // ---- workspace: rotated activations (shared by layers with the same input) + partial sums
   size_t ws = 0;
   P->items_in.clear();
+  P->items_in_gemm.clear();
   P->items_out.clear();
   for (int pos = 0; pos < n; ++pos) {
     DevLinear& L = P->dev[pos];
@@ -304,7 +389,8 @@ static int build_plan(GlqbPlan* P) {
     for (int q = 0; q < pos && same < 0; ++q) {
       const DevLinear& Q = P->dev[q];
       const GlqbLinearDesc& e = P->descs[P->order[q]];
-      if (Q.format == L.format && Q.n == L.n && Q.in_f == L.in_f && Q.sv == L.sv && Q.batch == L.batch &&
+      if (Q.format == L.format && Q.gemm_tn == L.gemm_tn && Q.n == L.n && Q.in_f == L.in_f && Q.sv == L.sv &&
+          Q.batch == L.batch &&
           Q.x_off == L.x_off && Q.x_stride == L.x_stride && Q.x_dtype == L.x_dtype && Q.nbn == L.nbn &&
           Q.x_is_rotated == L.x_is_rotated &&
           memcmp(e.blocks_n, d.blocks_n, sizeof(int32_t) * d.n_blocks_n) == 0)
@@ -313,10 +399,17 @@ static int build_plan(GlqbPlan* P) {
     if (same >= 0) {
       L.xr_off = P->dev[same].xr_off;
     } else {
+      ws = align_up(ws, 1024);
       L.xr_off = (long long)ws;
-      ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) *
-                             (L.format == GLQB_FMT_TRELLIS_3INST ? XR_TRELLIS_EXPAND : 1), 256);
-      for (int b = 0; b < L.nbn; ++b) P->items_in.push_back(RhtItem{pos, b});
+      if (L.gemm_tn) {
+        const size_t n_tiles = (L.batch + L.gemm_tn - 1) / L.gemm_tn, kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
+        ws = align_up(ws + n_tiles * kchunks * L.gemm_tn * 128, 256);
+        for (int b = 0; b < L.nbn; ++b) P->items_in_gemm.push_back(RhtItem{pos, b});
+      } else {
+        ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) *
+                               (L.format == GLQB_FMT_TRELLIS_3INST ? XR_TRELLIS_EXPAND : 1), 256);
+        for (int b = 0; b < L.nbn; ++b) P->items_in.push_back(RhtItem{pos, b});
+      }
     }
     L.part_off = (long long)ws;
     ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
@@ -329,13 +422,23 @@ static int build_plan(GlqbPlan* P) {
   CUDA_TRY(cudaMemcpy(P->d_layers, P->dev.data(), sizeof(DevLinear) * n, cudaMemcpyHostToDevice));
   CUDA_TRY(cudaMalloc(&P->d_items_in, sizeof(RhtItem) * std::max<size_t>(1, P->items_in.size())));
   CUDA_TRY(cudaMemcpy(P->d_items_in, P->items_in.data(), sizeof(RhtItem) * P->items_in.size(), cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMalloc(&P->d_items_in_gemm, sizeof(RhtItem) * std::max<size_t>(1, P->items_in_gemm.size())));
+  CUDA_TRY(cudaMemcpy(P->d_items_in_gemm, P->items_in_gemm.data(), sizeof(RhtItem) * P->items_in_gemm.size(),
+                      cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMalloc(&P->d_gemm_items, sizeof(GemmItem) * std::max<size_t>(1, P->gemm_items.size())));
+  CUDA_TRY(cudaMemcpy(P->d_gemm_items, P->gemm_items.data(), sizeof(GemmItem) * P->gemm_items.size(),
+                      cudaMemcpyHostToDevice));
+  CUDA_TRY(cudaMalloc(&P->d_status, sizeof(int)));
+  CUDA_TRY(cudaMemset(P->d_status, 0, sizeof(int)));
   CUDA_TRY(cudaMalloc(&P->d_items_out, sizeof(RhtItem) * std::max<size_t>(1, P->items_out.size())));
   CUDA_TRY(cudaMemcpy(P->d_items_out, P->items_out.data(), sizeof(RhtItem) * P->items_out.size(), cudaMemcpyHostToDevice));
 
   // kernels that may need more than 48 KB of dynamic shared memory
   const int smem_in = P->max_bs_in * 4, smem_out = P->max_bs_out * 4;
-  if (smem_in > 48 * 1024)
+  if (smem_in > 48 * 1024) {
     CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
+    CUDA_TRY(cudaFuncSetAttribute(rht_in_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
+  }
   if (smem_out > 48 * 1024)
     CUDA_TRY(cudaFuncSetAttribute(rht_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_out));
   return GLQB_OK;
@@ -377,7 +480,7 @@ int64_t glqb_plan_code_bytes(const GlqbPlan* plan) { return plan ? plan->code_by
 int64_t glqb_plan_flops(const GlqbPlan* plan) { return plan ? plan->flops : 0; }
 int32_t glqb_plan_launches(const GlqbPlan* plan) {
   if (!plan) return 0;
-  return (plan->items_in.empty() ? 0 : 1) + (int)plan->segs.size() + 1;
+  return (plan->items_in.empty() ? 0 : 1) + (plan->items_in_gemm.empty() ? 0 : 1) + (int)plan->segs.size() + 1;
 }
 
 int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable) {
@@ -415,6 +518,11 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     rht_in_kernel<false><<<grid, rht_threads(P->max_bs_in), P->max_bs_in * 4, stream>>>(
         P->d_layers, P->d_items_in, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
+  if (!P->items_in_gemm.empty()) {
+    dim3 grid((unsigned)P->items_in_gemm.size(), (unsigned)P->max_batch_gemm);
+    rht_in_gemm_kernel<<<grid, rht_threads(P->max_bs_in), P->max_bs_in * 4, stream>>>(
+        P->d_layers, P->d_items_in_gemm, reinterpret_cast<const uint8_t*>(x_base), ws);
+  }
   if (P->timing) {
     while (P->ev.size() < P->ev_used + 2) {
       cudaEvent_t e;
@@ -424,8 +532,14 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     CUDA_TRY(cudaEventRecord(P->ev[P->ev_used], stream));
   }
   for (const Segment& s : P->segs) {
-    MvKernel kern = pick_kernel(s);
-    kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);
+    if (s.tn) {
+      GemmKernel kern = pick_gemm_kernel(s);
+      kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,
+                                                                   s.item_count, ws, P->d_status);
+    } else {
+      MvKernel kern = pick_kernel(s);
+      kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);
+    }
   }
   if (P->timing) {
     CUDA_TRY(cudaEventRecord(P->ev[P->ev_used + 1], stream));
@@ -440,11 +554,23 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   return GLQB_OK;
 }
 
+int glqb_plan_status(GlqbPlan* plan, int32_t* status_out) {
+  if (!plan || !status_out) return fail(GLQB_E_INVALID, "null argument");
+  int v = 0;
+  CUDA_TRY(cudaMemcpy(&v, plan->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  *status_out = v;
+  if (v) return fail(GLQB_E_DEVICE, "a kernel gave up waiting (status %d): results of that run are invalid", v);
+  return GLQB_OK;
+}
+
 void glqb_plan_destroy(GlqbPlan* plan) {
   if (!plan) return;
   if (plan->d_layers) cudaFree(plan->d_layers);
   if (plan->d_items_in) cudaFree(plan->d_items_in);
   if (plan->d_items_out) cudaFree(plan->d_items_out);
+  if (plan->d_items_in_gemm) cudaFree(plan->d_items_in_gemm);
+  if (plan->d_gemm_items) cudaFree(plan->d_gemm_items);
+  if (plan->d_status) cudaFree(plan->d_status);
   for (cudaEvent_t e : plan->ev) cudaEventDestroy(e);
   delete plan;
 }

@@ -1,0 +1,472 @@
+// Prefill path: decoded weight tiles -> swizzled shared memory -> tcgen05.mma with fp32 accumulators in
+// tensor memory (TMEM).  One CTA computes D[128 weight rows x TN tokens] = W~[128 x K] * X~[TN x K]^T.
+//
+// Warp roles (GM_THREADS = 320):
+//   warps 0-7  decode producers: every warp decodes one 32x32 trellis group (or 16 rows x 64 columns of
+//              E8 indices) of the current 128x64 weight chunk into the stage's A tile, K-major with the
+//              128-byte swizzle the tensor core expects; warps 0-3 also drain the accumulators
+//   warp  8    one thread issues tcgen05.mma (4 per chunk: K = 16 each) and tcgen05.commit
+//   warp  9    one thread fetches the activation tile of the chunk with a bulk async copy (TMA, no
+//              multicast); the input-transform kernel has already written the activations in the
+//              exact shared-memory image (swizzled), so one contiguous copy per chunk suffices
+// Stages hand over through mbarriers.  Every wait is bounded: on expiry the kernel records a status
+// word, stops issuing work, frees its TMEM columns and returns.
+#pragma once
+#include "glqb_kernels.cuh"
+
+namespace glqb {
+
+constexpr int GM_THREADS = 320;
+constexpr int GM_PRODUCER_WARPS = 8;
+constexpr int GM_TILE_M = 128;
+constexpr int GM_TILE_K = 64;                      // fp16 elements = 128 bytes = one swizzle row
+constexpr int GM_A_BYTES = GM_TILE_M * GM_TILE_K * 2;   // 16 KiB
+constexpr uint32_t GM_SPIN_LIMIT = 1u << 22;       // try_wait attempts before a wait gives up
+
+struct GemmItem {
+  int layer;       // index into the device table
+  int m_tile;      // 128-row tile
+  int n_tile;      // TN-token tile
+  int k_begin;     // first 64-column chunk
+  int k_end;       // one past the last chunk
+  int slot;        // partial-sum slot this item writes
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+// bounded wait; false = gave up
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < GM_SPIN_LIMIT; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void fence_mbar_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p; }" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+      "%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, 8-row atoms of 1024 bytes stacked along
+// M/N (stride byte offset 1024), descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major) = 1
+  d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+  d |= (uint64_t)1 << 46;                 // descriptor version
+  d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor: D fp32, A and B fp16, both K-major, M = 128, N = tn
+__device__ __forceinline__ uint32_t umma_idesc_f16(int tn) {
+  return (1u << 4) | ((uint32_t)(tn >> 3) << 17) | ((uint32_t)(GM_TILE_M >> 4) << 24);
+}
+// byte offset of element (row r, fp16 column e) inside a swizzled K-major tile
+__device__ __forceinline__ uint32_t sw128_offset(int r, int e) {
+  return (uint32_t)((r >> 3) * 1024 + (r & 7) * 128 + ((((e >> 3) ^ (r & 7)) & 7) << 4) + (e & 7) * 2);
+}
+
+// ---- input transform for the GEMM path: activations written as swizzled TN x 64 tiles ---------------
+// grid = (items, tokens); tiles ordered [n_tile][k_chunk], each TN*128 bytes.  Columns past n (the last
+// chunk of a layer whose n is not a multiple of 64) are written as zeros by the CTA of the last block.
+__global__ void __launch_bounds__(1024) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
+                                                           const RhtItem* __restrict__ items,
+                                                           const uint8_t* __restrict__ x_base,
+                                                           uint8_t* __restrict__ ws) {
+  extern __shared__ float fbuf[];
+  const RhtItem it = items[blockIdx.x];
+  const DevLinear& L = layers[it.layer];
+  const int token = blockIdx.y;
+  if (token >= L.batch) return;
+  const int tn = L.gemm_tn;
+  const int off = L.bn_off[it.block];
+  const int logbs = L.bn_log[it.block];
+  const int bs = 1 << logbs;
+  const long long xrow = L.x_off + (long long)token * L.x_stride;
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const int col = off + i;
+    float v = 0.f;
+    if (col < L.in_f) {
+      v = load_act(x_base, xrow + col, L.x_dtype);
+      if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
+    }
+    fbuf[i] = v;
+  }
+  float rs = 1.0f;
+  if (!L.x_is_rotated) {
+    fht_smem(fbuf, logbs);
+    rs = rsqrtf((float)bs);
+  } else {
+    __syncthreads();
+  }
+  const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
+  const int nt = token / tn, r = token - nt * tn;
+  uint8_t* base = ws + L.xr_off + (size_t)nt * kchunks * tn * 128;
+  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+    const int col = off + i;
+    const int kc = col >> 6, e = col & 63;
+    *reinterpret_cast<__half*>(base + (size_t)kc * tn * 128 + sw128_offset(r, e)) = __float2half_rn(fbuf[i] * rs);
+  }
+  if (it.block == L.nbn - 1) {
+    for (int col = L.n + threadIdx.x; col < kchunks * GM_TILE_K; col += blockDim.x) {
+      const int kc = col >> 6, e = col & 63;
+      *reinterpret_cast<__half*>(base + (size_t)kc * tn * 128 + sw128_offset(r, e)) = __float2half_rn(0.f);
+    }
+  }
+}
+
+// ---- weight producers ------------------------------------------------------------------------------
+// One trellis group (32 rows x 32 columns) -> its place in the 128 x 64 A tile.
+template <int K1, int K2>
+__device__ __forceinline__ void gemm_store_group(uint8_t* a_tile, int strip, int cg, int lane, const Words<K1>& v,
+                                                 const Words<(K2 > 0 ? K2 : 1)>& v2, __half2 s2) {
+  const Words<K1> vn = shfl_words<K1>(v, (lane + 1) & 31);
+  Words<K1> vn2 = vn;
+  if constexpr (K1 == 1) vn2 = shfl_words<K1>(v, (lane + 2) & 31);
+  Words<(K2 > 0 ? K2 : 1)> un, un2;
+  if constexpr (K2 > 0) {
+    un = shfl_words<K2>(v2, (lane + 1) & 31);
+    un2 = un;
+    if constexpr (K2 == 1) un2 = shfl_words<K2>(v2, (lane + 2) & 31);
+  }
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int ni = 0; ni < 2; ++ni) {
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+      const int q = ni * 2 + mi;
+      uint32_t a[8], b[8];
+      decode_tile<K1>(chunk_of<K1>(v, q), chunk_of<K1>(vn, q), chunk_of<K1>(vn2, q), a);
+      if constexpr (K2 > 0) decode_tile<K2>(chunk_of<K2>(v2, q), chunk_of<K2>(un, q), chunk_of<K2>(un2, q), b);
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        uint32_t w = __byte_perm(a[2 * p], a[2 * p + 1], 0x5410);        // (w_{2p}, w_{2p+1})
+        if constexpr (K2 > 0) {
+          // second stage folded into the fp16 operand: w = fp16(w1 + s2 * w2), one rounding
+          const uint32_t w2 = __byte_perm(b[2 * p], b[2 * p + 1], 0x5410);
+          const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&w2), s2, *reinterpret_cast<const __half2*>(&w));
+          w = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        const int c = p >> 1, a_ = p & 1;
+        const int row = strip * 32 + mi * 16 + 8 * a_ + g;
+        const int col = cg * 32 + ni * 16 + 8 * c + 2 * t;
+        *reinterpret_cast<uint32_t*>(a_tile + sw128_offset(row, col)) = w;
+      }
+    }
+  }
+}
+
+// ---- the GEMM kernel -------------------------------------------------------------------------------
+// FORMAT 0: trellis (K1, K2 bits); FORMAT 1: E8 (K1 = number of stages, K2 unused)
+template <int FORMAT, int K1, int K2, int TN, int STAGES>
+__global__ void __launch_bounds__(GM_THREADS, 1)
+glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict__ items, int n_items,
+                uint8_t* __restrict__ ws, int* __restrict__ status) {
+  constexpr int B_BYTES = TN * 128;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* a_base = smem;                                   // STAGES x 16 KiB
+  uint8_t* b_base = smem + STAGES * GM_A_BYTES;             // STAGES x TN*128
+  uint64_t* bars = reinterpret_cast<uint64_t*>(b_base + STAGES * B_BYTES);
+  uint64_t* full_a = bars;
+  uint64_t* full_b = bars + STAGES;
+  uint64_t* empty = bars + 2 * STAGES;
+  uint64_t* acc_full = bars + 3 * STAGES;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_a[s], GM_PRODUCER_WARPS);
+      mbar_init(&full_b[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 4);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, TN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp < GM_PRODUCER_WARPS) {
+    // ------------------------------------------------------------------ producers (+ epilogue)
+    int stage = 0;
+    uint32_t phase = 0, acc_phase = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const GemmItem it = items[item];
+      const DevLinear& L = layers[it.layer];
+      if constexpr (FORMAT == 0) {
+        const int strip = warp >> 1, cg = warp & 1;
+        const int rp = it.m_tile * 4 + strip;
+        const int gps = L.groups_per_strip;
+        const bool row_ok = rp < L.strips;
+        const uint8_t* p1 = L.codes[0] + ((long long)rp * gps) * (128 * K1) + lane * (4 * K1);
+        const uint8_t* p2 = nullptr;
+        if constexpr (K2 > 0) p2 = L.codes[1] + ((long long)rp * gps) * (128 * K2) + lane * (4 * K2);
+        const __half2 s2 = __float2half2_rn(L.stage_scale[1]);
+        Words<K1> nxt;
+        Words<(K2 > 0 ? K2 : 1)> nxt2;
+        auto fetch = [&](int kc) {
+          const int cp = kc * 2 + cg;
+          if (row_ok && cp < gps) {
+            nxt = load_words<K1>(p1 + (long long)cp * (128 * K1));
+            if constexpr (K2 > 0) nxt2 = load_words<K2>(p2 + (long long)cp * (128 * K2));
+          }
+        };
+        fetch(it.k_begin);
+        for (int kc = it.k_begin; kc < it.k_end; ++kc) {
+          const Words<K1> v = nxt;
+          const Words<(K2 > 0 ? K2 : 1)> v2 = nxt2;
+          const bool valid = row_ok && (kc * 2 + cg) < gps;
+          if (kc + 1 < it.k_end) fetch(kc + 1);
+          if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+          uint8_t* a_tile = a_base + stage * GM_A_BYTES;
+          if (valid) {
+            gemm_store_group<K1, K2>(a_tile, strip, cg, lane, v, v2, s2);
+          } else {
+            // rows or columns past the matrix: zeros (the shuffles inside the decode need all lanes, so
+            // the whole warp takes this branch together: validity is uniform per warp)
+            const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+#pragma unroll
+              for (int p = 0; p < 4; ++p) {
+                const int row = strip * 32 + (q & 1) * 16 + 8 * (p & 1) + g;
+                const int col = cg * 32 + (q >> 1) * 16 + 8 * (p >> 1) + 2 * t;
+                *reinterpret_cast<uint32_t*>(a_tile + sw128_offset(row, col)) = 0u;
+              }
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_a[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      } else {
+        // E8: 128 rows x 8 indices per chunk; thread (row = tid >> 1, half = tid & 1) expands 4 indices
+        const int tid = threadIdx.x;                      // 0..255
+        const int row_l = tid >> 1, hf = tid & 1;
+        const int row = it.m_tile * GM_TILE_M + row_l;
+        const int nidx = L.n >> 3;
+        const bool row_ok = row < L.m;
+        uint2 nq[K1];                                     // 4 indices (8 bytes) per stage
+        auto fetch = [&](int kc) {
+          const int i0 = kc * 8 + hf * 4;
+#pragma unroll
+          for (int s = 0; s < K1; ++s) {
+            nq[s] = make_uint2(0u, 0u);
+            if (row_ok && i0 + 4 <= nidx) {
+              nq[s] = ld_stream_v2(reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx + i0);
+            } else if (row_ok) {
+              const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx;
+              uint32_t v[4] = {0, 0, 0, 0};
+              for (int k = 0; k < 4; ++k) if (i0 + k < nidx) v[k] = q[i0 + k];
+              nq[s] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
+            }
+          }
+        };
+        fetch(it.k_begin);
+        for (int kc = it.k_begin; kc < it.k_end; ++kc) {
+          uint2 cq[K1];
+#pragma unroll
+          for (int s = 0; s < K1; ++s) cq[s] = nq[s];
+          if (kc + 1 < it.k_end) fetch(kc + 1);
+          // gather before waiting for the stage: the table reads overlap the wait
+          uint32_t ent[K1][4];
+          const int i0 = kc * 8 + hf * 4;
+#pragma unroll
+          for (int s = 0; s < K1; ++s) {
+            const uint32_t mask = (uint32_t)L.table_entries[s] - 1u;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const uint32_t idx = ((k < 2 ? cq[s].x : cq[s].y) >> ((k & 1) * 16)) & 0xFFFFu;
+              ent[s][k] = __ldg(L.table[s] + (idx & mask));
+            }
+          }
+          if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+          uint8_t* a_tile = a_base + stage * GM_A_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            uint4 out = make_uint4(0u, 0u, 0u, 0u);
+            if (row_ok && i0 + k < nidx) {
+              uint32_t h[4];
+              e8_entry_to_half2(ent[0][k], h);               // (c0,c4),(c1,c5),(c2,c6),(c3,c7)
+#pragma unroll
+              for (int s = 1; s < K1; ++s) {
+                uint32_t h2[4];
+                e8_entry_to_half2(ent[s][k], h2);
+                const __half2 sc = __float2half2_rn(L.stage_scale[s]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&h2[j]), sc,
+                                            *reinterpret_cast<const __half2*>(&h[j]));
+                  h[j] = *reinterpret_cast<const uint32_t*>(&r);
+                }
+              }
+              // natural column order inside the 16-byte chunk: (c0,c1),(c2,c3),(c4,c5),(c6,c7)
+              out.x = __byte_perm(h[0], h[1], 0x5410);
+              out.y = __byte_perm(h[2], h[3], 0x5410);
+              out.z = __byte_perm(h[0], h[1], 0x7632);
+              out.w = __byte_perm(h[2], h[3], 0x7632);
+            }
+            *reinterpret_cast<uint4*>(a_tile + sw128_offset(row_l, (hf * 4 + k) * 8)) = out;
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&full_a[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) break;
+      // ---------------- epilogue: warps 0-3 own TMEM lanes 32*warp .. 32*warp+31
+      if (warp < 4) {
+        if (!mbar_wait(acc_full, acc_phase)) { ok = false; break; }
+        acc_phase ^= 1;
+        tc_fence_after();
+        const int row = it.m_tile * GM_TILE_M + warp * 32 + lane;
+        float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)it.slot * L.batch * L.m;
+#pragma unroll 1
+        for (int c0 = 0; c0 < TN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
+          tmem_ld_wait();
+          if (row < L.m) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int token = it.n_tile * TN + c0 + i;
+              if (token < L.batch) part[(long long)token * L.m + row] = __uint_as_float(r[i]);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty);
+      }
+    }
+    if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(status, 2); }
+  } else if (warp == 8) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      const uint32_t idesc = umma_idesc_f16(TN);
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const GemmItem it = items[item];
+        if (!mbar_wait(acc_empty, acc_phase ^ 1)) { ok = false; break; }
+        acc_phase ^= 1;
+        tc_fence_after();
+        for (int kc = it.k_begin; kc < it.k_end; ++kc) {
+          if (!mbar_wait(&full_a[stage], phase) || !mbar_wait(&full_b[stage], phase)) { ok = false; break; }
+          tc_fence_after();
+          const uint64_t da = umma_desc_sw128(smem_u32(a_base + stage * GM_A_BYTES));
+          const uint64_t db = umma_desc_sw128(smem_u32(b_base + stage * B_BYTES));
+#pragma unroll
+          for (int k = 0; k < GM_TILE_K / 16; ++k)      // +32 bytes (2 x 16-byte units) per K step of 16
+            umma_f16(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kc > it.k_begin || k > 0) ? 1u : 0u);
+          umma_commit(&empty[stage]);                    // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(acc_full);
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(status, 3); }
+    }
+  } else {
+    // ------------------------------------------------------------------ activation loader
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+        const GemmItem it = items[item];
+        const DevLinear& L = layers[it.layer];
+        const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
+        const uint8_t* src = ws + L.xr_off + ((size_t)it.n_tile * kchunks) * B_BYTES;
+        for (int kc = it.k_begin; kc < it.k_end; ++kc) {
+          if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+          mbar_expect_tx(&full_b[stage], B_BYTES);
+          bulk_g2s(b_base + stage * B_BYTES, src + (size_t)kc * B_BYTES, B_BYTES, &full_b[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(status, 4); }
+    }
+  }
+  // ---- teardown: every thread arrives here (also after a wait gave up)
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem_acc, TN);
+}
+
+}  // namespace glqb

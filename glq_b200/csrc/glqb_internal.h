@@ -30,6 +30,8 @@ struct DevLinear {
   int strips;            // strips of rows (trellis: 32 rows, E8: 16 rows)
   int slots;             // upper bound on partial sums per strip
   int per_warp;          // work groups handed to each warp of the segment's launch
+  int fixed_slots;       // > 0: every strip has exactly this many partial sums (GEMM path: K splits)
+  int gemm_tn;           // token tile of the GEMM path (0: streaming decode path)
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];

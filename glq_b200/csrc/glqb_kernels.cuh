@@ -151,7 +151,8 @@ __global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restri
     } else if (row < L.m) {
       const int strip = row / rows_per_strip;
       const long long g0 = L.group_base + (long long)strip * L.groups_per_strip;
-      const int cnt = (int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1;
+      const int cnt = L.fixed_slots > 0 ? L.fixed_slots
+                                        : (int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1;
       const float* p = reinterpret_cast<const float*>(ws + L.part_off) + (long long)token * L.m + row;
       const long long slot_stride = (long long)L.batch * L.m;
       for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];

@@ -8,7 +8,7 @@ when this module is installed in place of the reference extension (see ``glq_b20
 
 Differences, all supersets: activations may be fp16, bf16 or fp32 (the reference casts to fp16
 first, glq/quantized_linear.py:1081) and the result comes back in the activation dtype; token
-counts above 64 are processed in slices of 64 tokens until the tensor-core GEMM path takes over.
+counts above 64 take the tensor-core (tcgen05) GEMM path.
 There is no CPU or PyTorch fallback: without a CUDA device and the built library these raise.
 """
 from __future__ import annotations
@@ -78,6 +78,12 @@ def clear_caches() -> None:
 def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_tokens=DECODE_MAX_TOKENS) -> None:
     """Run a single-layer op over x2d (B, in) -> out (B, out) in slices of <= max_tokens tokens."""
     B = x2d.shape[0]
+    if B > DECODE_MAX_TOKENS:
+        # prefill: one tensor-core GEMM plan for the whole token count
+        plan = _cached_plan(key_base + (B, x2d.dtype, out.dtype, x2d.stride(0), out.stride(0)),
+                            lambda: [make_spec(B)])
+        plan.run(x2d, out)
+        return
     done = 0
     while done < B:
         b = min(max_tokens, B - done)

@@ -136,6 +136,11 @@ class Plan:
         _lib.check(self.lib.glqb_plan_kernel_ms(self.handle, C.byref(ms), C.byref(runs)), "plan_kernel_ms")
         return float(ms.value), int(runs.value)
 
+    def check_status(self) -> None:
+        """Raise if a kernel of an earlier run gave up on a bounded wait (synchronises)."""
+        st = C.c_int32()
+        _lib.check(self.lib.glqb_plan_status(self.handle, C.byref(st)), "plan_status")
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.lib.glqb_plan_destroy(self.handle)

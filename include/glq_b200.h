@@ -96,6 +96,9 @@ int glqb_plan_run(GlqbPlan* plan, const void* x_base, void* y_base,
  * number of runs recorded since timing was (re-)enabled. */
 int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable);
 int glqb_plan_kernel_ms(GlqbPlan* plan, double* total_ms_out, int32_t* runs_out);
+/* Reads the plan's device status word (synchronising copy).  0 = every kernel of every run so far
+ * completed normally; non-zero = a bounded wait inside a kernel expired (GLQB_E_DEVICE is returned). */
+int glqb_plan_status(GlqbPlan* plan, int32_t* status_out);
 void glqb_plan_destroy(GlqbPlan* plan);
 
 /* Stateless single-layer forms of the reference's fused ops.  `workspace` must hold

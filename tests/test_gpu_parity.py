@@ -405,3 +405,59 @@ def test_errors_are_loud(ops):
         ops.glq_decompress_trellis_3inst_cuda(torch.zeros(4, 64, dtype=torch.int16, device="cuda"), 48, 64)
     with pytest.raises(RuntimeError):
         ops.glq_decompress_trellis_3inst_cuda(torch.zeros(4, 64, dtype=torch.int16), 32, 32)   # CPU tensor
+
+
+# ---------------------------------------------------------------------------------------------
+# prefill: tensor-core GEMM path (more than 64 tokens)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("K,K2", [(4, 0), (2, 0), (3, 0), (4, 2)])
+@pytest.mark.parametrize("T", [65, 128, 200, 300])
+def test_trellis_gemm_vs_oracle(ops, K, K2, T):
+    rng = np.random.default_rng(K * 1000 + K2 * 100 + T)
+    m, n = 352, 576            # partial 128-row tile, 9 K chunks, block-diagonal transforms
+    p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, K, K2)
+    x_t = cuda(rng.standard_normal((T, n)).astype(np.float32), torch.bfloat16)
+    ref = O.linear_forward(x_t.float().cpu().numpy(), W, su, sv, wscale)
+    y = _run_trellis(ops, x_t, p1, p2, su, sv, wscale, inv, m, n, out_dtype=torch.float32)
+    assert y.shape == (T, m)
+    assert relerr(y.cpu().numpy(), ref) <= TOL
+    y2 = _run_trellis(ops, x_t, p1, p2, su, sv, wscale, inv, m, n, out_dtype=torch.float32)
+    assert torch.equal(y, y2)
+
+
+def test_trellis_gemm_large(ops):
+    rng = np.random.default_rng(31)
+    m, n, T = 2048, 2048, 512
+    p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, 4)
+    x_t = cuda(rng.standard_normal((T, n)).astype(np.float32), torch.bfloat16)
+    ref = O.linear_forward(x_t.float().cpu().numpy(), W, su, sv, wscale)
+    y = _run_trellis(ops, x_t, p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
+    assert relerr(y.cpu().numpy(), ref) <= TOL
+    # rows of the GEMM result agree with the decode path on the same tokens (not bit-equal: the
+    # accumulation order differs)
+    y1 = _run_trellis(ops, x_t[:5], p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
+    assert relerr(y[:5].cpu().numpy(), y1.cpu().numpy()) <= 1e-4
+
+
+@pytest.mark.parametrize("stages", [1, 2, 4])
+@pytest.mark.parametrize("T", [100, 257])
+def test_e8_gemm_vs_oracle(ops, e8_table, e8_cb, stages, T):
+    full, small = e8_cb
+    rng = np.random.default_rng(stages * 7 + T)
+    m, n = 320, 576
+    qs = [rng.integers(0, 65536, size=(m, n // 8), dtype=np.uint16).view(np.int16) for _ in range(stages)]
+    inv = [0.1, 0.01, 0.001][:stages - 1]
+    su, sv = signs(rng, m), signs(rng, n)
+    wscale = float(rng.uniform(0.5, 1.5) * 0.02)
+    W = O.e8_decode_nstage(qs, [e8_table] * stages, inv)
+    x = cuda(rng.standard_normal((T, n)).astype(np.float32), torch.bfloat16)
+    empty_i = torch.empty(0, dtype=torch.int16, device="cuda")
+    empty_h = torch.empty(0, dtype=torch.float16, device="cuda")
+    tail = []
+    for s in range(1, 4):
+        tail += [cuda(qs[s]) if stages > s else empty_i, full if stages > s else empty_h, inv[s - 1] if stages > s else 0.0]
+    y = ops.fused_linear_block_diag(x, cuda(sv), cuda(su), cuda(qs[0]), full, wscale, n, m, n, m,
+                                    torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m)), None, None,
+                                    *tail, out_dtype=torch.float32)
+    ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, wscale)
+    assert relerr(y.cpu().numpy(), ref) <= TOL
