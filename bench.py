@@ -126,6 +126,61 @@ def build_trellis_decode(device, world, rank, bits=(4,), n_layers=None):
                 code_bytes=plan.code_bytes, name="smollm3-3b trellis-3inst %dbpw decode bs=1" % sum(bits))
 
 
+WORKLOADS = {
+    # name: (model shape, format, bits-or-stages, default tokens, default layers, metric)
+    "decode_trellis": ("SMOLLM3_3B", "trellis", (4,), 1, 36, METRIC),
+    "decode_trellis_6bpw": ("SMOLLM3_3B", "trellis", (4, 2), 1, 36, METRIC),
+    "decode_e8": ("LLAMA3_8B", "e8", 2, 1, 8, METRIC),
+    "prefill_e8": ("LLAMA3_8B", "e8", 2, 2048, 2, "prefill TFLOP/s per layer"),
+    "prefill_trellis": ("SMOLLM3_3B", "trellis", (4,), 2048, 4, "prefill TFLOP/s per layer"),
+}
+
+
+def build_workload(name, device, world, rank, tokens=None, n_layers=None):
+    """Plan over n_layers x 7 projections of the named shape; q/k/v and gate/up share their input."""
+    import torch
+    from glq_b200 import synth, tp
+    from glq_b200.plan import Plan
+
+    shape, fmt, par, d_tokens, d_layers, metric = WORKLOADS[name]
+    cfg = getattr(synth, shape)
+    T = tokens or d_tokens
+    nl = n_layers or d_layers
+    gen = torch.Generator(device=device)
+    gen.manual_seed(4321 + rank)
+    table = synth.load_e8_table(device) if fmt == "e8" else None
+    col_mult = 8 if fmt == "e8" else 32
+    specs, layers = [], []
+    x_elems = y_elems = 0
+    reduce_spans = []
+    for li in range(nl):
+        x_of = {}
+        for pname, m, n in cfg["proj"]:
+            ms, ns = tp.shard_shape(pname, m, n, world, 32 if fmt == "trellis" else 16, col_mult)
+            group = {"q": "attn_in", "k": "attn_in", "v": "attn_in", "gate": "mlp_in", "up": "mlp_in"}.get(pname, pname)
+            if group not in x_of:
+                x_of[group] = x_elems
+                x_elems += T * ns
+            L = (synth.trellis_layer(f"L{li}.{pname}", ms, ns, list(par), gen, device) if fmt == "trellis"
+                 else synth.e8_layer(f"L{li}.{pname}", ms, ns, par, table, gen, device))
+            if group == "attn_in" and pname != "q":
+                L.sv = layers[-1].sv if pname == "k" else layers[-2].sv      # fused shards share the input signs
+            if pname == "up":
+                L.sv = layers[-1].sv
+            layers.append(L)
+            specs.append(L.spec(batch=T, x_offset=x_of[group], y_offset=y_elems, x_stride=ns, y_stride=ms))
+            if pname in tp.ROW_PARALLEL and world > 1:
+                reduce_spans.append((y_elems, T * ms))
+            y_elems += T * ms
+    plan = Plan(specs)
+    gx = torch.Generator(device=device)
+    gx.manual_seed(77)
+    x = torch.randn(x_elems, generator=gx, device=device, dtype=torch.float32).to(torch.bfloat16)
+    y = torch.zeros(y_elems, device=device, dtype=torch.bfloat16)
+    return dict(plan=plan, x=x, y=y, layers=layers, layout=None, reduce_spans=reduce_spans, tokens=T, n_layers=nl,
+                code_bytes=plan.code_bytes, flops=plan.flops, metric=metric, shape=shape, fmt=fmt, par=par)
+
+
 def cpu_layer_sample(threads_note=True):
     """One SmolLM3-3B decoder layer (7 projections, 39,059,456 packed bytes) for the CPU restatement."""
     import numpy as np
@@ -176,6 +231,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="decode_trellis_sweep",
+                    help="decode_trellis_sweep (default, the headline) or one of: " + ", ".join(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None,
                     help="decoder layers to build (default: all 36); smaller values are for profiler captures only")
     args = ap.parse_args()
@@ -220,9 +278,17 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    W = build_trellis_decode(device, world, rank, n_layers=args.layers)
-    if args.layers:
-        config["layers_built"] = args.layers
+    generic = args.workload != "decode_trellis_sweep"
+    if generic:
+        W = build_workload(args.workload, device, world, rank, args.tokens, args.layers)
+        config = {"workload": f"{args.workload}: {W['shape']} projections, {W['fmt']} {W['par']}, {W['tokens']} tokens, "
+                              f"{W['n_layers']} decoder layers per step (weights {W['code_bytes'] / 1e6:.0f} MB, cycled)",
+                  "cache": "distinct weight buffers per layer; working set larger than L2",
+                  "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single"}
+    else:
+        W = build_trellis_decode(device, world, rank, n_layers=args.layers)
+        if args.layers:
+            config["layers_built"] = args.layers
     plan, x, y = W["plan"], W["x"], W["y"]
     total_code_bytes = W["code_bytes"]
     if world > 1:
@@ -237,7 +303,11 @@ def main():
         # row-parallel outputs (o, down) are partial sums over ranks: one NCCL all-reduce over the
         # contiguous tail of y (the sweep has no dependency between layers, so the per-layer
         # reductions of a real decode step are issued as one)
-        tp.all_reduce_row_parallel(y, W["layout"])
+        if W["layout"] is not None:
+            tp.all_reduce_row_parallel(y, W["layout"])
+        elif world > 1:
+            for off, ln in W["reduce_spans"]:
+                dist.all_reduce(y[off:off + ln])
 
     def sync():
         if world > 1:
@@ -307,7 +377,26 @@ def main():
                          "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
                          "kernel_ms": kern_ms_avg, "bytes_per_launch": W["code_bytes"], "traffic": None},
         }
-        if args.gpus == 1 and not args.no_cpu_baseline:
+        if generic and "prefill" in args.workload:
+            # per-layer TFLOP/s, against the bf16 tensor peak
+            flops_layer = W["flops"] / W["n_layers"]
+            tf = flops_layer / (ms_step / W["n_layers"] * 1e-3) / 1e12
+            tf_kernel = W["flops"] / (kern_ms_avg * 1e-3) / 1e12
+            try:
+                tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
+                tkind = "of measured"
+            except Exception:
+                tpeak, tkind = 1590.0, "of fallback"
+            line.update({"metric": W["metric"], "value": tf, "unit": "TFLOP/s", "dtype": "f16",
+                         "ms_per_layer": ms_step / W["n_layers"]})
+            line["e2e"]["value"] = W["flops"] / W["n_layers"] / (e2e_ms / args.steps / W["n_layers"] * 1e-3) / 1e12
+            line["e2e"]["unit"] = "TFLOP/s"
+            line["roofline"] = {"bound": "tensor", "kernel": "glq_gemm_kernel", "achieved": tf_kernel, "peak": tpeak,
+                                "peak_kind": tkind, "unit": "TFLOP/s", "frac": tf_kernel / tpeak,
+                                "kernel_ms": kern_ms_avg, "flops_per_launch": W["flops"], "traffic": None}
+        elif generic:
+            line["metric"] = W["metric"]
+        if args.gpus == 1 and not args.no_cpu_baseline and not generic:
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line))
     if world > 1:

@@ -24,7 +24,26 @@ EXPORTS = [
     "glqb_decompress_trellis_3inst", "glqb_dequant_e8", "glqb_e8_pack_table", "glqb_input_rht",
     "glqb_output_rht", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
     "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
+    "glqb_moe_plan_create", "glqb_moe_plan_workspace_bytes", "glqb_moe_plan_code_bytes", "glqb_moe_plan_run",
+    "glqb_moe_plan_destroy",
 ]
+
+
+class MoeDesc(C.Structure):
+    _fields_ = [
+        ("num_experts", C.c_int32), ("top_k", C.c_int32), ("hidden", C.c_int32), ("inter", C.c_int32),
+        ("w13_out", C.c_int32), ("max_tokens", C.c_int32), ("activation", C.c_int32),
+        ("w13_bits", C.c_int32), ("w13_bits2", C.c_int32), ("w2_bits", C.c_int32), ("w2_bits2", C.c_int32),
+        ("w13_packed", C.c_void_p), ("w13_packed2", C.c_void_p), ("w13_su", C.c_void_p), ("w13_sv", C.c_void_p),
+        ("w13_wscale", C.c_void_p), ("w13_inv_resid_scale2", C.c_void_p),
+        ("w2_packed", C.c_void_p), ("w2_packed2", C.c_void_p), ("w2_su", C.c_void_p), ("w2_sv", C.c_void_p),
+        ("w2_wscale", C.c_void_p), ("w2_inv_resid_scale2", C.c_void_p),
+        ("n_blocks_n_w13", C.c_int32), ("n_blocks_m_w13", C.c_int32),
+        ("n_blocks_n_w2", C.c_int32), ("n_blocks_m_w2", C.c_int32),
+        ("blocks_n_w13", C.c_int32 * MAX_BLOCKS), ("blocks_m_w13", C.c_int32 * MAX_BLOCKS),
+        ("blocks_n_w2", C.c_int32 * MAX_BLOCKS), ("blocks_m_w2", C.c_int32 * MAX_BLOCKS),
+        ("ids_are_int64", C.c_int32), ("x_dtype", C.c_int32), ("y_dtype", C.c_int32),
+    ]
 
 
 class LinearDesc(C.Structure):
@@ -108,6 +127,16 @@ def load() -> C.CDLL:
     lib.glqb_trellis_linear_noalloc.restype = C.c_int
     lib.glqb_noalloc_scratch_bytes.argtypes = []
     lib.glqb_noalloc_scratch_bytes.restype = sz
+    lib.glqb_moe_plan_create.argtypes = [C.POINTER(MoeDesc), C.POINTER(vp)]
+    lib.glqb_moe_plan_create.restype = C.c_int
+    lib.glqb_moe_plan_workspace_bytes.argtypes = [vp]
+    lib.glqb_moe_plan_workspace_bytes.restype = sz
+    lib.glqb_moe_plan_code_bytes.argtypes = [vp]
+    lib.glqb_moe_plan_code_bytes.restype = i64
+    lib.glqb_moe_plan_run.argtypes = [vp, vp, vp, vp, vp, i32, vp, sz, vp]
+    lib.glqb_moe_plan_run.restype = C.c_int
+    lib.glqb_moe_plan_destroy.argtypes = [vp]
+    lib.glqb_moe_plan_destroy.restype = None
     lib.glqb_last_error.argtypes = []
     lib.glqb_last_error.restype = C.c_char_p
     lib.glqb_version.argtypes = []

@@ -1,0 +1,509 @@
+// MoE grouped expert matmul for trellis 3INST experts:
+//     out[t] = sum_j w[t,j] * W2_e( act( W13_e x_t ) ),   e = topk_ids[t,j]
+// (reference: glq_fused_moe_trellis_3inst_cuda, glq/csrc/glq_cuda.cu:5042; eager loop
+// glq_vllm/fused_moe_method.py:393-440; storage glq_vllm/moe_shapes.py:56-72).
+//
+// Six launches, fixed grids, no host synchronisation (capture-safe):
+//   1 moe_group_kernel     count tokens per expert, prefix sums, place every (token, j) routing in a slot
+//   2 moe_rht_in_kernel    input transform of every TOKEN once (all experts share SV of w13)
+//   3 trellis_moe_mv_kernel  w13: experts' weights decoded once per 8*NB routed tokens, partial sums per slot
+//   4 moe_mid_kernel       per slot: sum partials, Wscale, output transform, SU, gated activation, then the
+//                          w2 input transform (SV, Hadamard) — three reference launches in one
+//   5 trellis_moe_mv_kernel  w2
+//   6 moe_out_kernel       per token: for j in fixed order  acc += w * SU * H(Wscale * partials)
+// Work units of the two matmuls are (expert, 32-row strip, K chunk) and are handed out by an atomic
+// counter, so skewed routing (a few hot experts) does not idle the warps that drew empty experts; the
+// partial-sum slot of a unit is its K-chunk number, so results do not depend on which warp ran it.
+// Integer atomics decide only WHERE a routing is stored, never a numeric value: outputs are
+// bit-identical run to run.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <vector>
+
+#include "glqb_kernels.cuh"
+
+namespace glqb {
+
+struct MoeDev {
+  // weights, expert-stacked
+  const uint8_t* w13[2];
+  const uint8_t* w2[2];
+  long long w13_stride[2], w2_stride[2];   // bytes between experts
+  const __half* w13_su; const __half* w13_sv; const float* w13_wscale; const float* w13_inv2;
+  const __half* w2_su; const __half* w2_sv; const float* w2_wscale; const float* w2_inv2;
+  int E, hidden, inter, w13_out, top_k, max_tokens, act, gated;
+  int ids_i64, x_dtype, y_dtype;
+  // Hadamard blocks: n13 (hidden), m13 (w13_out), n2 (inter), m2 (hidden)
+  int nb_n13, nb_m13, nb_n2, nb_m2;
+  int off_n13[GLQB_MAX_BLOCKS], log_n13[GLQB_MAX_BLOCKS];
+  int off_m13[GLQB_MAX_BLOCKS], log_m13[GLQB_MAX_BLOCKS];
+  int off_n2[GLQB_MAX_BLOCKS], log_n2[GLQB_MAX_BLOCKS];
+  int off_m2[GLQB_MAX_BLOCKS], log_m2[GLQB_MAX_BLOCKS];
+  // K chunking of the two matmuls
+  int kch13, gpc13, kch2, gpc2;
+  // workspace offsets (bytes)
+  long long o_count, o_base, o_cursor, o_work, o_route_tok, o_route_exp, o_slot_of, o_xr1, o_part1, o_xr2, o_part2;
+};
+
+__device__ __forceinline__ float moe_act(float g, int act) {
+  if (act == GLQB_ACT_SILU || act == 3) return g / (1.0f + __expf(-g));
+  if (act == GLQB_ACT_GELU_TANH) {
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(u));
+  }
+  if (act == 4) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));     // gelu (exact), not gated
+  const float r = fmaxf(g, 0.f);                                                 // relu^2 (codes 2 and 5)
+  return r * r;
+}
+
+// ---- 1: grouping ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__ MoeDev M, const void* __restrict__ ids,
+                                                         int T, uint8_t* __restrict__ ws) {
+  extern __shared__ int sh[];            // counts[E], cursor[E]
+  int* cnt = sh;
+  int* cur = sh + M.E;
+  int* g_count = reinterpret_cast<int*>(ws + M.o_count);
+  int* g_base = reinterpret_cast<int*>(ws + M.o_base);
+  int* g_work = reinterpret_cast<int*>(ws + M.o_work);
+  int* route_tok = reinterpret_cast<int*>(ws + M.o_route_tok);
+  int* route_exp = reinterpret_cast<int*>(ws + M.o_route_exp);
+  int* slot_of = reinterpret_cast<int*>(ws + M.o_slot_of);
+  const int R = T * M.top_k;
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) cnt[e] = 0;
+  if (threadIdx.x < 2) g_work[threadIdx.x] = 0;
+  __syncthreads();
+  auto expert_of = [&](int i) -> int {
+    long long v = M.ids_i64 ? reinterpret_cast<const long long*>(ids)[i] : (long long)reinterpret_cast<const int*>(ids)[i];
+    return (v < 0 || v >= M.E) ? -1 : (int)v;
+  };
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const int e = expert_of(i);
+    if (e >= 0) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < M.E; ++e) { cur[e] = run; g_base[e] = run; g_count[e] = cnt[e]; run += cnt[e]; }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    const int e = expert_of(i);
+    int slot = -1;
+    if (e >= 0) {
+      slot = atomicAdd(&cur[e], 1);
+      route_tok[slot] = i / M.top_k;
+      route_exp[slot] = e;
+    }
+    slot_of[i] = slot;
+  }
+}
+
+// ---- 2: input transform per token (w13 side) -----------------------------------------------------------
+__global__ void __launch_bounds__(1024) moe_rht_in_kernel(const __grid_constant__ MoeDev M, const uint8_t* __restrict__ x,
+                                                          uint8_t* __restrict__ ws) {
+  extern __shared__ float fb[];
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < M.hidden; i += blockDim.x)
+    fb[i] = load_act(x, (long long)t * M.hidden + i, M.x_dtype) * __half2float(M.w13_sv[i]);
+  for (int b = 0; b < M.nb_n13; ++b) fht_smem(fb + M.off_n13[b], M.log_n13[b]);
+  __half2* out = reinterpret_cast<__half2*>(ws + M.o_xr1) + (long long)t * M.hidden;
+  for (int b = 0; b < M.nb_n13; ++b) {
+    const float rs = rsqrtf((float)(1 << M.log_n13[b]));
+    for (int i = threadIdx.x; i < (1 << M.log_n13[b]); i += blockDim.x) {
+      const int col = M.off_n13[b] + i;
+      const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);
+      out[pos >> 1] = __halves2half2(__float2half_rn(fb[col] * rs), __float2half_rn(0.f));
+    }
+  }
+}
+
+// ---- 3 / 5: grouped decode + mma ------------------------------------------------------------------------
+struct MoeMvArgs {
+  const uint8_t* codes[2];
+  long long stride[2];
+  const float* inv2;       // (E,) cumulative inverse residual scale of stage 2, or null
+  const int* count;        // (E,)
+  const int* base;         // (E,)
+  const int* row_map;      // slot -> activation row, or null (identity)
+  const __half* xr;        // activation rows, 2*n halfs each
+  float* part;             // [kchunks][R][m]
+  int* work;               // atomic unit counter
+  int E, m, n, gps, strips, kchunks, gpc, R;
+};
+
+template <int K1, int K2, int NB>
+__global__ void __launch_bounds__(MV_THREADS) trellis_moe_mv_kernel(const __grid_constant__ MoeMvArgs A) {
+  const int lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const int units_per_expert = A.strips * A.kchunks;
+  const int total_units = A.E * units_per_expert;
+  for (;;) {
+    int u = 0;
+    if (lane == 0) u = atomicAdd(A.work, 1);
+    u = __shfl_sync(0xffffffffu, u, 0);
+    if (u >= total_units) break;
+    const int e = u / units_per_expert;
+    const int cnt = A.count[e];
+    if (cnt == 0) continue;
+    const int rem = u - e * units_per_expert;
+    const int strip = rem / A.kchunks, kc = rem - strip * A.kchunks;
+    const int c0 = kc * A.gpc, c1 = min(A.gps, c0 + A.gpc);
+    const int base = A.base[e];
+    const uint8_t* p1 = A.codes[0] + (long long)e * A.stride[0] + ((long long)strip * A.gps + c0) * (128 * K1) + lane * (4 * K1);
+    const uint8_t* p2 = nullptr;
+    float s2 = 0.f;
+    if constexpr (K2 > 0) {
+      p2 = A.codes[1] + (long long)e * A.stride[1] + ((long long)strip * A.gps + c0) * (128 * K2) + lane * (4 * K2);
+      s2 = A.inv2[e];
+    }
+    for (int t0 = 0; t0 < cnt; t0 += 8 * NB) {
+      float acc[NB][2][4];
+      float acc2[K2 ? NB : 1][2][4];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { acc[nb][mi][i] = 0.f; if constexpr (K2 > 0) acc2[nb][mi][i] = 0.f; }
+      const uint4* xq[NB];
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+        const int local = min(t0 + nb * 8 + gq, cnt - 1);
+        const int row = A.row_map ? A.row_map[base + local] : base + local;
+        xq[nb] = reinterpret_cast<const uint4*>(A.xr + ((long long)row * A.n + c0 * 32) * XR_TRELLIS_EXPAND + tq * 16);
+      }
+      Words<K1> nxt = load_words<K1>(p1);
+      Words<(K2 > 0 ? K2 : 1)> nxt2;
+      if constexpr (K2 > 0) nxt2 = load_words<K2>(p2);
+      for (int c = c0; c < c1; ++c) {
+        const Words<K1> v = nxt;
+        const Words<(K2 > 0 ? K2 : 1)> v2 = nxt2;
+        if (c + 1 < c1) {
+          nxt = load_words<K1>(p1 + (long long)(c + 1 - c0) * (128 * K1));
+          if constexpr (K2 > 0) nxt2 = load_words<K2>(p2 + (long long)(c + 1 - c0) * (128 * K2));
+        }
+        uint4 xb[NB][2];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          xb[nb][0] = __ldg(xq[nb] + (c - c0) * 8);
+          xb[nb][1] = __ldg(xq[nb] + (c - c0) * 8 + 1);
+        }
+        group_mma<K1, NB>(v, lane, xb, acc);
+        if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
+      }
+      float* part = A.part + (long long)kc * A.R * A.m;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int local = t0 + nb * 8 + tq * 2 + (i & 1);
+            const int row = strip * 32 + mi * 16 + gq + ((i >> 1) ? 8 : 0);
+            if (local < cnt) {
+              float v = acc[nb][mi][i];
+              if constexpr (K2 > 0) v = __fadd_rn(v, __fmul_rn(s2, acc2[nb][mi][i]));
+              part[(long long)(base + local) * A.m + row] = v;
+            }
+          }
+    }
+  }
+}
+
+// ---- 4: per slot  h = act(gate) * up  from w13 partials, then the w2 input transform ---------------------
+__global__ void __launch_bounds__(1024) moe_mid_kernel(const __grid_constant__ MoeDev M, int T, uint8_t* __restrict__ ws) {
+  extern __shared__ float fb[];              // w13_out floats, reused for inter floats
+  const int slot = blockIdx.x;
+  const int R = T * M.top_k;
+  const int* g_count = reinterpret_cast<const int*>(ws + M.o_count);
+  const int* g_base = reinterpret_cast<const int*>(ws + M.o_base);
+  const int used = g_base[M.E - 1] + g_count[M.E - 1];
+  if (slot >= used) return;
+  const int e = reinterpret_cast<const int*>(ws + M.o_route_exp)[slot];
+  const float* part = reinterpret_cast<const float*>(ws + M.o_part1) + (long long)slot * M.w13_out;
+  const float wsc = M.w13_wscale[e];
+  for (int i = threadIdx.x; i < M.w13_out; i += blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < M.kch13; ++k) s += part[(long long)k * R * M.w13_out + i];
+    fb[i] = s * wsc;
+  }
+  for (int b = 0; b < M.nb_m13; ++b) fht_smem(fb + M.off_m13[b], M.log_m13[b]);
+  // SU and normalisation, then the activation (values go through fp16 once, as the reference's
+  // w13 op returns fp16: glq_vllm/fused_moe_method.py:412-421)
+  const __half* su = M.w13_su + (long long)e * M.w13_out;
+  for (int b = 0; b < M.nb_m13; ++b) {
+    const float rs = rsqrtf((float)(1 << M.log_m13[b]));
+    for (int i = threadIdx.x; i < (1 << M.log_m13[b]); i += blockDim.x) {
+      const int r = M.off_m13[b] + i;
+      fb[r] = __half2float(__float2half_rn(fb[r] * rs * __half2float(su[r])));
+    }
+  }
+  __syncthreads();
+  float hv[8];                               // inter <= 8 * blockDim.x (host-checked limits)
+  int nh = 0;
+  for (int i = threadIdx.x; i < M.inter; i += blockDim.x) {
+    const float g = fb[i];
+    const float a = moe_act(g, M.act);
+    hv[nh++] = M.gated ? a * fb[M.inter + i] : a;
+  }
+  __syncthreads();
+  nh = 0;
+  for (int i = threadIdx.x; i < M.inter; i += blockDim.x)
+    fb[i] = __half2float(__float2half_rn(hv[nh++])) * __half2float(M.w2_sv[i]);
+  for (int b = 0; b < M.nb_n2; ++b) fht_smem(fb + M.off_n2[b], M.log_n2[b]);
+  __half2* out = reinterpret_cast<__half2*>(ws + M.o_xr2) + (long long)slot * M.inter;
+  for (int b = 0; b < M.nb_n2; ++b) {
+    const float rs = rsqrtf((float)(1 << M.log_n2[b]));
+    for (int i = threadIdx.x; i < (1 << M.log_n2[b]); i += blockDim.x) {
+      const int col = M.off_n2[b] + i;
+      const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);
+      out[pos >> 1] = __halves2half2(__float2half_rn(fb[col] * rs), __float2half_rn(0.f));
+    }
+  }
+}
+
+// ---- 6: per token weighted combine ------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) moe_out_kernel(const __grid_constant__ MoeDev M, int T,
+                                                       const float* __restrict__ topk_w, const uint8_t* __restrict__ ws,
+                                                       uint8_t* __restrict__ y) {
+  extern __shared__ float fb[];              // hidden floats
+  const int t = blockIdx.x;
+  const int R = T * M.top_k;
+  const int* slot_of = reinterpret_cast<const int*>(ws + M.o_slot_of);
+  const int* route_exp = reinterpret_cast<const int*>(ws + M.o_route_exp);
+  float acc[8];                              // hidden <= 8 * blockDim.x is checked on the host
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int j = 0; j < M.top_k; ++j) {
+    const int slot = slot_of[t * M.top_k + j];
+    if (slot < 0) continue;                  // uniform per CTA
+    const int e = route_exp[slot];
+    const float wsc = M.w2_wscale[e];
+    const float w = topk_w[t * M.top_k + j];
+    const float* part = reinterpret_cast<const float*>(ws + M.o_part2) + (long long)slot * M.hidden;
+    for (int i = threadIdx.x; i < M.hidden; i += blockDim.x) {
+      float s = 0.f;
+      for (int k = 0; k < M.kch2; ++k) s += part[(long long)k * R * M.hidden + i];
+      fb[i] = s * wsc;
+    }
+    for (int b = 0; b < M.nb_m2; ++b) fht_smem(fb + M.off_m2[b], M.log_m2[b]);
+    const __half* su = M.w2_su + (long long)e * M.hidden;
+    int q = 0;
+    for (int b = 0; b < M.nb_m2; ++b) {
+      const float rs = rsqrtf((float)(1 << M.log_m2[b]));
+      for (int i = threadIdx.x; i < (1 << M.log_m2[b]); i += blockDim.x) {
+        const int r = M.off_m2[b] + i;
+        // the reference's w2 op returns fp16 before the weighted sum
+        fb[r] = __half2float(__float2half_rn(fb[r] * rs * __half2float(su[r])));
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < M.hidden; i += blockDim.x) acc[q++] += w * fb[i];
+    __syncthreads();
+  }
+  int q = 0;
+  for (int i = threadIdx.x; i < M.hidden; i += blockDim.x) store_act(y, (long long)t * M.hidden + i, M.y_dtype, acc[q++]);
+}
+
+typedef void (*MoeMvKernel)(const MoeMvArgs);
+
+template <int NB>
+static MoeMvKernel moe_mv_pick(int k1, int k2) {
+#define M_CASE(A, B) if (k1 == A && k2 == B) return trellis_moe_mv_kernel<A, B, NB>;
+  M_CASE(2, 0) M_CASE(3, 0) M_CASE(4, 0) M_CASE(4, 1) M_CASE(4, 2) M_CASE(4, 3) M_CASE(4, 4)
+#undef M_CASE
+  return nullptr;
+}
+
+}  // namespace glqb
+
+using namespace glqb;
+
+struct GlqbMoePlan {
+  GlqbMoeDesc desc;
+  MoeDev dev;
+  size_t ws_bytes = 0;
+  int sm_count = 0;
+  int nb = 2;              // token-column blocks per pass (8*nb routed tokens share one decode)
+  MoeMvKernel k13 = nullptr, k2 = nullptr;
+  int grid13 = 0, grid2 = 0;
+};
+
+static int moe_fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  set_error_message(buf);
+  return code;
+}
+
+static size_t al(size_t v) { return (v + 255) / 256 * 256; }
+
+static int fill_blocks(const int32_t* blocks, int nb, int total, int* off, int* lg, const char* what) {
+  if (nb < 1 || nb > GLQB_MAX_BLOCKS) return moe_fail(GLQB_E_INVALID, "moe: %s block count %d", what, nb);
+  int o = 0;
+  for (int i = 0; i < nb; ++i) {
+    const int b = blocks[i];
+    if (b < 32 || (b & (b - 1))) return moe_fail(GLQB_E_INVALID, "moe: %s block %d", what, b);
+    off[i] = o;
+    lg[i] = 31 - __builtin_clz((unsigned)b);
+    o += b;
+  }
+  if (o != total) return moe_fail(GLQB_E_INVALID, "moe: %s blocks sum to %d, expected %d", what, o, total);
+  return GLQB_OK;
+}
+
+extern "C" {
+
+int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
+  if (!d || !out) return moe_fail(GLQB_E_INVALID, "moe_plan_create: null argument");
+  if (d->num_experts < 1 || d->num_experts > 4096 || d->top_k < 1 || d->top_k > 64 || d->max_tokens < 1)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: experts=%d top_k=%d max_tokens=%d", d->num_experts, d->top_k,
+                    d->max_tokens);
+  const bool gated = d->activation >= 0 && d->activation <= 2;
+  if (d->activation < 0 || d->activation > 5) return moe_fail(GLQB_E_INVALID, "moe_plan_create: activation %d", d->activation);
+  if (d->hidden % 32 || d->inter % 32 || d->w13_out % 32)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: hidden/inter/w13_out must be multiples of 32");
+  if (d->w13_out != (gated ? 2 : 1) * d->inter)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: w13_out=%d does not match inter=%d for activation %d", d->w13_out,
+                    d->inter, d->activation);
+  if (d->hidden > 8 * 1024 || d->inter > 4 * 1024 || d->w13_out > 16384)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: hidden <= 8192, inter <= 4096 supported");
+  if (!d->w13_packed || !d->w2_packed || !d->w13_su || !d->w13_sv || !d->w2_su || !d->w2_sv || !d->w13_wscale ||
+      !d->w2_wscale)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: null weight pointer");
+  GlqbMoePlan* P = new GlqbMoePlan();
+  P->desc = *d;
+  MoeDev& M = P->dev;
+  memset(&M, 0, sizeof M);
+  int rc;
+  if ((rc = fill_blocks(d->blocks_n_w13, d->n_blocks_n_w13, d->hidden, M.off_n13, M.log_n13, "n_w13")) ||
+      (rc = fill_blocks(d->blocks_m_w13, d->n_blocks_m_w13, d->w13_out, M.off_m13, M.log_m13, "m_w13")) ||
+      (rc = fill_blocks(d->blocks_n_w2, d->n_blocks_n_w2, d->inter, M.off_n2, M.log_n2, "n_w2")) ||
+      (rc = fill_blocks(d->blocks_m_w2, d->n_blocks_m_w2, d->hidden, M.off_m2, M.log_m2, "m_w2"))) {
+    delete P;
+    return rc;
+  }
+  M.nb_n13 = d->n_blocks_n_w13; M.nb_m13 = d->n_blocks_m_w13; M.nb_n2 = d->n_blocks_n_w2; M.nb_m2 = d->n_blocks_m_w2;
+  const int k13a = d->w13_bits, k13b = d->w13_packed2 ? d->w13_bits2 : 0;
+  const int k2a = d->w2_bits, k2b = d->w2_packed2 ? d->w2_bits2 : 0;
+  // tokens per decode pass: 16 for small steps, 32 when experts see many tokens
+  const double avg = (double)d->max_tokens * d->top_k / d->num_experts;
+  P->nb = (k13b || k2b) ? 2 : (avg > 16.0 ? 4 : 2);
+  P->k13 = P->nb == 4 ? moe_mv_pick<4>(k13a, k13b) : moe_mv_pick<2>(k13a, k13b);
+  P->k2 = P->nb == 4 ? moe_mv_pick<4>(k2a, k2b) : moe_mv_pick<2>(k2a, k2b);
+  if (!P->k13 || !P->k2) {
+    delete P;
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: no kernel for trellis rates w13 K=%d+%d, w2 K=%d+%d", k13a, k13b, k2a,
+                    k2b);
+  }
+  M.w13[0] = (const uint8_t*)d->w13_packed; M.w13[1] = (const uint8_t*)d->w13_packed2;
+  M.w2[0] = (const uint8_t*)d->w2_packed; M.w2[1] = (const uint8_t*)d->w2_packed2;
+  M.w13_stride[0] = (long long)d->w13_out * d->hidden * k13a / 8;
+  M.w13_stride[1] = (long long)d->w13_out * d->hidden * k13b / 8;
+  M.w2_stride[0] = (long long)d->hidden * d->inter * k2a / 8;
+  M.w2_stride[1] = (long long)d->hidden * d->inter * k2b / 8;
+  M.w13_su = (const __half*)d->w13_su; M.w13_sv = (const __half*)d->w13_sv;
+  M.w13_wscale = d->w13_wscale; M.w13_inv2 = d->w13_inv_resid_scale2;
+  M.w2_su = (const __half*)d->w2_su; M.w2_sv = (const __half*)d->w2_sv;
+  M.w2_wscale = d->w2_wscale; M.w2_inv2 = d->w2_inv_resid_scale2;
+  if ((k13b && !M.w13_inv2) || (k2b && !M.w2_inv2)) {
+    delete P;
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: second stage without its inverse residual scales");
+  }
+  M.E = d->num_experts; M.hidden = d->hidden; M.inter = d->inter; M.w13_out = d->w13_out; M.top_k = d->top_k;
+  M.max_tokens = d->max_tokens; M.act = d->activation; M.gated = gated ? 1 : 0;
+  M.ids_i64 = d->ids_are_int64; M.x_dtype = d->x_dtype; M.y_dtype = d->y_dtype;
+  // K chunking: 32 groups (1024 columns) per unit
+  const int gps13 = d->hidden / 32, gps2 = d->inter / 32;
+  M.gpc13 = std::min(gps13, 32); M.kch13 = (gps13 + M.gpc13 - 1) / M.gpc13;
+  M.gpc2 = std::min(gps2, 32); M.kch2 = (gps2 + M.gpc2 - 1) / M.gpc2;
+  // workspace
+  const size_t R = (size_t)d->max_tokens * d->top_k;
+  size_t o = 0;
+  M.o_count = o; o = al(o + 4 * (size_t)M.E);
+  M.o_base = o; o = al(o + 4 * (size_t)M.E);
+  M.o_cursor = o; o = al(o + 4 * (size_t)M.E);
+  M.o_work = o; o = al(o + 16);
+  M.o_route_tok = o; o = al(o + 4 * R);
+  M.o_route_exp = o; o = al(o + 4 * R);
+  M.o_slot_of = o; o = al(o + 4 * R);
+  M.o_xr1 = o; o = al(o + (size_t)d->max_tokens * d->hidden * 2 * XR_TRELLIS_EXPAND);
+  M.o_part1 = o; o = al(o + (size_t)M.kch13 * R * d->w13_out * 4);
+  M.o_xr2 = o; o = al(o + R * d->inter * 2 * XR_TRELLIS_EXPAND);
+  M.o_part2 = o; o = al(o + (size_t)M.kch2 * R * d->hidden * 4);
+  P->ws_bytes = o;
+  int dev_id = 0;
+  if (cudaGetDevice(&dev_id) != cudaSuccess ||
+      cudaDeviceGetAttribute(&P->sm_count, cudaDevAttrMultiProcessorCount, dev_id) != cudaSuccess) {
+    delete P;
+    return moe_fail(GLQB_E_CUDA, "moe_plan_create: no CUDA device");
+  }
+  const int units13 = M.E * (d->w13_out / 32) * M.kch13, units2 = M.E * (d->hidden / 32) * M.kch2;
+  const int ctas = P->sm_count * 2;
+  P->grid13 = std::max(1, std::min(ctas, (units13 + MV_WARPS - 1) / MV_WARPS));
+  P->grid2 = std::max(1, std::min(ctas, (units2 + MV_WARPS - 1) / MV_WARPS));
+  *out = P;
+  return GLQB_OK;
+}
+
+size_t glqb_moe_plan_workspace_bytes(const GlqbMoePlan* p) { return p ? p->ws_bytes : 0; }
+
+int64_t glqb_moe_plan_code_bytes(const GlqbMoePlan* p) {
+  if (!p) return 0;
+  const MoeDev& M = p->dev;
+  return (int64_t)M.E * (M.w13_stride[0] + M.w13_stride[1] + M.w2_stride[0] + M.w2_stride[1]);
+}
+
+int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const float* topk_weights, void* y,
+                      int32_t tokens, void* workspace, size_t workspace_bytes, void* stream_) {
+  if (!P || !x || !topk_ids || !topk_weights || !y) return moe_fail(GLQB_E_INVALID, "moe_plan_run: null argument");
+  if (tokens < 1 || tokens > P->desc.max_tokens)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_run: %d tokens, plan was built for at most %d", tokens, P->desc.max_tokens);
+  if (!workspace || workspace_bytes < P->ws_bytes)
+    return moe_fail(GLQB_E_WORKSPACE, "moe_plan_run: workspace of %zu bytes needed, %zu given", P->ws_bytes, workspace_bytes);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return moe_fail(GLQB_E_WORKSPACE, "workspace must be 256-byte aligned");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  const MoeDev& M = P->dev;
+  const int R = tokens * M.top_k;
+  moe_group_kernel<<<1, 1024, 2 * M.E * sizeof(int), st>>>(M, topk_ids, tokens, ws);
+  moe_rht_in_kernel<<<tokens, std::max(64, std::min(1024, M.hidden / 8)), M.hidden * 4, st>>>(
+      M, reinterpret_cast<const uint8_t*>(x), ws);
+  MoeMvArgs A;
+  memset(&A, 0, sizeof A);
+  A.codes[0] = M.w13[0]; A.codes[1] = M.w13[1]; A.stride[0] = M.w13_stride[0]; A.stride[1] = M.w13_stride[1];
+  A.inv2 = M.w13_inv2;
+  A.count = reinterpret_cast<const int*>(ws + M.o_count);
+  A.base = reinterpret_cast<const int*>(ws + M.o_base);
+  A.row_map = reinterpret_cast<const int*>(ws + M.o_route_tok);
+  A.xr = reinterpret_cast<const __half*>(ws + M.o_xr1);
+  A.part = reinterpret_cast<float*>(ws + M.o_part1);
+  A.work = reinterpret_cast<int*>(ws + M.o_work);
+  A.E = M.E; A.m = M.w13_out; A.n = M.hidden; A.gps = M.hidden / 32; A.strips = M.w13_out / 32;
+  A.kchunks = M.kch13; A.gpc = M.gpc13; A.R = R;
+  P->k13<<<P->grid13, MV_THREADS, 0, st>>>(A);
+  const int mid_threads = std::max(256, std::min(1024, M.w13_out / 8));
+  moe_mid_kernel<<<R, mid_threads, std::max(M.w13_out, M.inter) * 4, st>>>(M, tokens, ws);
+  A.codes[0] = M.w2[0]; A.codes[1] = M.w2[1]; A.stride[0] = M.w2_stride[0]; A.stride[1] = M.w2_stride[1];
+  A.inv2 = M.w2_inv2;
+  A.row_map = nullptr;
+  A.xr = reinterpret_cast<const __half*>(ws + M.o_xr2);
+  A.part = reinterpret_cast<float*>(ws + M.o_part2);
+  A.work = reinterpret_cast<int*>(ws + M.o_work) + 1;
+  A.m = M.hidden; A.n = M.inter; A.gps = M.inter / 32; A.strips = M.hidden / 32;
+  A.kchunks = M.kch2; A.gpc = M.gpc2;
+  P->k2<<<P->grid2, MV_THREADS, 0, st>>>(A);
+  moe_out_kernel<<<tokens, 1024, M.hidden * 4, st>>>(M, tokens, topk_weights, ws, reinterpret_cast<uint8_t*>(y));
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return moe_fail(GLQB_E_CUDA, "moe_plan_run: %s", cudaGetErrorString(e));
+  return GLQB_OK;
+}
+
+void glqb_moe_plan_destroy(GlqbMoePlan* p) { delete p; }
+
+}  // extern "C"

@@ -342,6 +342,101 @@ def dequant_e8(qidxs_list: Sequence[torch.Tensor], codebooks: Sequence[torch.Ten
     return out
 
 
+# ------------------------------------------------------------------------------------------------
+# MoE grouped expert matmul (glq_vllm/custom_ops.py:22-36)
+# ------------------------------------------------------------------------------------------------
+class MoePlan:
+    """Owns a GlqbMoePlan handle and its workspace."""
+
+    def __init__(self, desc: "_lib.MoeDesc", device, keep):
+        self.lib = _lib.load()
+        self.keep = keep
+        handle = C.c_void_p()
+        with torch.cuda.device(device):
+            _lib.check(self.lib.glqb_moe_plan_create(C.byref(desc), C.byref(handle)), "moe_plan_create")
+        self.handle = handle
+        self.max_tokens = desc.max_tokens
+        self.workspace = torch.empty(max(256, int(self.lib.glqb_moe_plan_workspace_bytes(handle))), dtype=torch.uint8,
+                                     device=device)
+        self.code_bytes = int(self.lib.glqb_moe_plan_code_bytes(handle))
+
+    def run(self, x, topk_ids, topk_weights, y):
+        _lib.check(self.lib.glqb_moe_plan_run(self.handle, x.data_ptr(), topk_ids.data_ptr(), topk_weights.data_ptr(),
+                                              y.data_ptr(), x.shape[0], self.workspace.data_ptr(),
+                                              self.workspace.numel(), _stream(x)), "moe_plan_run")
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.glqb_moe_plan_destroy(self.handle)
+            self.handle = None
+
+
+def _moe_capacity(tokens: int) -> int:
+    cap = 16
+    while cap < tokens:
+        cap *= 2
+    return cap
+
+
+def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
+                            w13_trellis_packed, w13_trellis_packed2, w13_SU, w13_SV, w13_Wscale, w13_inv_resid_scale2,
+                            w2_trellis_packed, w2_trellis_packed2, w2_SU, w2_SV, w2_Wscale, w2_inv_resid_scale2,
+                            hidden_size, intermediate_size, w13_out_features,
+                            n_pad_w13, m_pad_w13, n_pad_w2, m_pad_w2,
+                            blocks_n_w13, blocks_m_w13, blocks_n_w13_meta, blocks_m_w13_meta,
+                            blocks_n_w2, blocks_m_w2, blocks_n_w2_meta, blocks_m_w2_meta, activation_type):
+    """(T, hidden) -> (T, hidden): routed experts, gated activation, weighted combine; any token count,
+    no host synchronisation.  A second-stage tensor with numel() <= E is the reference's "absent" sentinel."""
+    _require_cuda(x, "x")
+    E = w13_trellis_packed.shape[0]
+    T = x.shape[0]
+    x = x.contiguous()
+    ids = topk_ids.contiguous()
+    if ids.dtype not in (torch.int32, torch.int64):
+        ids = ids.to(torch.int64)
+    tw = topk_weights.to(torch.float32).contiguous()
+    has13 = w13_trellis_packed2 is not None and w13_trellis_packed2.numel() > E
+    has2 = w2_trellis_packed2 is not None and w2_trellis_packed2.numel() > E
+    cap = _moe_capacity(T)
+    key = ("moe3", w13_trellis_packed.data_ptr(), w2_trellis_packed.data_ptr(), cap, ids.shape[1], x.dtype, ids.dtype,
+           int(activation_type), has13, has2)
+    plan = _PLAN_CACHE.get(key)
+    if plan is None:
+        d = _lib.MoeDesc()
+        d.num_experts, d.top_k, d.hidden, d.inter, d.w13_out = E, ids.shape[1], hidden_size, intermediate_size, w13_out_features
+        d.max_tokens, d.activation = cap, int(activation_type)
+        d.w13_bits, d.w2_bits = w13_trellis_packed.shape[-1] // 16, w2_trellis_packed.shape[-1] // 16
+        d.w13_bits2 = w13_trellis_packed2.shape[-1] // 16 if has13 else 0
+        d.w2_bits2 = w2_trellis_packed2.shape[-1] // 16 if has2 else 0
+        ws13 = w13_Wscale.to(torch.float32).contiguous()
+        ws2 = w2_Wscale.to(torch.float32).contiguous()
+        i13 = w13_inv_resid_scale2.to(torch.float32).contiguous() if has13 else None
+        i2 = w2_inv_resid_scale2.to(torch.float32).contiguous() if has2 else None
+        d.w13_packed, d.w13_packed2 = w13_trellis_packed.data_ptr(), (w13_trellis_packed2.data_ptr() if has13 else None)
+        d.w13_su, d.w13_sv, d.w13_wscale = w13_SU.data_ptr(), w13_SV.data_ptr(), ws13.data_ptr()
+        d.w13_inv_resid_scale2 = i13.data_ptr() if has13 else None
+        d.w2_packed, d.w2_packed2 = w2_trellis_packed.data_ptr(), (w2_trellis_packed2.data_ptr() if has2 else None)
+        d.w2_su, d.w2_sv, d.w2_wscale = w2_SU.data_ptr(), w2_SV.data_ptr(), ws2.data_ptr()
+        d.w2_inv_resid_scale2 = i2.data_ptr() if has2 else None
+        for name, blocks, total in (("n_w13", blocks_n_w13, n_pad_w13), ("m_w13", blocks_m_w13, m_pad_w13),
+                                    ("n_w2", blocks_n_w2, n_pad_w2), ("m_w2", blocks_m_w2, m_pad_w2)):
+            bl = _blocks(blocks, total)
+            setattr(d, "n_blocks_" + name, len(bl))
+            arr = getattr(d, "blocks_" + name)
+            for i, b in enumerate(bl):
+                arr[i] = b
+        d.ids_are_int64 = 1 if ids.dtype == torch.int64 else 0
+        d.x_dtype = d.y_dtype = _dt(x.dtype)
+        plan = MoePlan(d, x.device, [w13_trellis_packed, w13_trellis_packed2, w13_SU, w13_SV, ws13, i13,
+                                     w2_trellis_packed, w2_trellis_packed2, w2_SU, w2_SV, ws2, i2])
+        _PLAN_CACHE[key] = plan
+    y = torch.empty(T, hidden_size, dtype=x.dtype, device=x.device)
+    plan.run(x, ids, tw, y)
+    return y
+
+
+glq_fused_moe_trellis_3inst_cuda = fused_moe_trellis_3inst
+
 # names under which the reference's extension module exposes the same entry points
 glq_fused_linear_cuda = fused_linear
 glq_fused_linear_block_diag_cuda = fused_linear_block_diag

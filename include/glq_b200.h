@@ -101,6 +101,48 @@ int glqb_plan_kernel_ms(GlqbPlan* plan, double* total_ms_out, int32_t* runs_out)
 int glqb_plan_status(GlqbPlan* plan, int32_t* status_out);
 void glqb_plan_destroy(GlqbPlan* plan);
 
+/*
+ * MoE grouped expert matmul over trellis 3INST experts:
+ *     out[t] = sum_j topk_weights[t,j] * W2_e( act( W13_e x_t ) ),  e = topk_ids[t,j]
+ * Replaces glq_fused_moe_trellis_3inst_cuda (glq/csrc/glq_cuda.cu:5042; schema
+ * glq_vllm/custom_ops.py:22-36) with the expert-stacked storage of glq_vllm/moe_shapes.py:56-72:
+ * w13 = [gate; up] rows per expert, one SV per projection shared by all experts, SU / Wscale /
+ * inv_resid_scale2 per expert.  Works for any token count (no 256-token cap, no host synchronisation).
+ */
+typedef struct GlqbMoeDesc {
+  int32_t num_experts, top_k, hidden, inter, w13_out;
+  int32_t max_tokens;                    /* capacity the workspace is sized for */
+  int32_t activation;                    /* GLQB_ACT_* gated (0..2) or 3..5 = silu / gelu / relu^2 without gate */
+  int32_t w13_bits, w13_bits2, w2_bits, w2_bits2;   /* K of stage 1 / stage 2 (bits2 ignored when packed2 is NULL) */
+  const void* w13_packed;                /* (E, (w13_out/16)(hidden/16), 16K) int16 */
+  const void* w13_packed2;               /* NULL when there is no second stage */
+  const void* w13_su;                    /* (E, w13_out) fp16 */
+  const void* w13_sv;                    /* (hidden,) fp16 */
+  const float* w13_wscale;               /* (E,) fp32 device */
+  const float* w13_inv_resid_scale2;     /* (E,) fp32 device, NULL without a second stage */
+  const void* w2_packed;                 /* (E, (hidden/16)(inter/16), 16K) int16 */
+  const void* w2_packed2;
+  const void* w2_su;                     /* (E, hidden) fp16 */
+  const void* w2_sv;                     /* (inter,) fp16 */
+  const float* w2_wscale;
+  const float* w2_inv_resid_scale2;
+  int32_t n_blocks_n_w13, n_blocks_m_w13, n_blocks_n_w2, n_blocks_m_w2;
+  int32_t blocks_n_w13[GLQB_MAX_BLOCKS], blocks_m_w13[GLQB_MAX_BLOCKS];
+  int32_t blocks_n_w2[GLQB_MAX_BLOCKS], blocks_m_w2[GLQB_MAX_BLOCKS];
+  int32_t ids_are_int64;                 /* topk_ids dtype: 1 = int64, 0 = int32 */
+  int32_t x_dtype, y_dtype;              /* GLQB_DT_* */
+} GlqbMoeDesc;
+
+typedef struct GlqbMoePlan GlqbMoePlan;
+int glqb_moe_plan_create(const GlqbMoeDesc* desc, GlqbMoePlan** out_plan);
+size_t glqb_moe_plan_workspace_bytes(const GlqbMoePlan* plan);
+int64_t glqb_moe_plan_code_bytes(const GlqbMoePlan* plan);
+/* x (tokens, hidden), topk_ids (tokens, top_k), topk_weights (tokens, top_k) fp32, y (tokens, hidden);
+ * six launches on `stream`, returns without synchronising. */
+int glqb_moe_plan_run(GlqbMoePlan* plan, const void* x, const void* topk_ids, const float* topk_weights, void* y,
+                      int32_t tokens, void* workspace, size_t workspace_bytes, void* stream);
+void glqb_moe_plan_destroy(GlqbMoePlan* plan);
+
 /* Stateless single-layer forms of the reference's fused ops.  `workspace` must hold
  * glqb_linear_workspace_bytes(desc) bytes. */
 size_t glqb_linear_workspace_bytes(const GlqbLinearDesc* desc);
