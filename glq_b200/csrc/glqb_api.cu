@@ -74,6 +74,7 @@ struct GlqbPlan {
   size_t ws_bytes = 0;
   int max_batch = 1;
   int max_bs_in = 32, max_bs_out = 32;
+  int max_elems_in = 32, max_elems_out = 32;    // floats of shared memory the transform CTAs need
   int sm_count = 0;
   int64_t code_bytes = 0, flops = 0;
   bool timing = false;
@@ -226,6 +227,20 @@ static int validate(const GlqbLinearDesc& d, int idx) {
   if (d.stop_at_yrht && d.y_dtype != GLQB_DT_F32)
     return fail(GLQB_E_INVALID, "layer %d: rotated-domain output must be fp32", idx);
   return GLQB_OK;
+}
+
+// one item per (layer, block, tile of tokens); tracks the largest tile (floats) for the launch's smem
+static void add_rht_items(std::vector<RhtItem>& items, int layer, int nblocks, const int* logs, int batch,
+                          int& max_elems) {
+  for (int b = 0; b < nblocks; ++b) {
+    const int bs = 1 << logs[b];
+    const int tt = rht_tile_tokens(bs, batch);
+    for (int t0 = 0; t0 < batch; t0 += tt) {
+      const int nt = std::min(tt, batch - t0);
+      items.push_back(RhtItem{layer, b, t0, nt});
+      max_elems = std::max(max_elems, nt * bs);
+    }
+  }
 }
 
 static int build_plan(GlqbPlan* P) {
@@ -404,16 +419,16 @@ static int build_plan(GlqbPlan* P) {
       if (L.gemm_tn) {
         const size_t n_tiles = (L.batch + L.gemm_tn - 1) / L.gemm_tn, kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
         ws = align_up(ws + n_tiles * kchunks * L.gemm_tn * 128, 256);
-        for (int b = 0; b < L.nbn; ++b) P->items_in_gemm.push_back(RhtItem{pos, b});
+        add_rht_items(P->items_in_gemm, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
       } else {
         ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) *
                                (L.format == GLQB_FMT_TRELLIS_3INST ? XR_TRELLIS_EXPAND : 1), 256);
-        for (int b = 0; b < L.nbn; ++b) P->items_in.push_back(RhtItem{pos, b});
+        add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
       }
     }
     L.part_off = (long long)ws;
     ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
-    for (int b = 0; b < L.nbm; ++b) P->items_out.push_back(RhtItem{pos, b});
+    add_rht_items(P->items_out, pos, L.nbm, L.bm_log, L.batch, P->max_elems_out);
   }
   P->ws_bytes = ws;
 
@@ -434,7 +449,7 @@ static int build_plan(GlqbPlan* P) {
   CUDA_TRY(cudaMemcpy(P->d_items_out, P->items_out.data(), sizeof(RhtItem) * P->items_out.size(), cudaMemcpyHostToDevice));
 
   // kernels that may need more than 48 KB of dynamic shared memory
-  const int smem_in = P->max_bs_in * 4, smem_out = P->max_bs_out * 4;
+  const int smem_in = P->max_elems_in * 4, smem_out = P->max_elems_out * 4;
   if (smem_in > 48 * 1024) {
     CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
     CUDA_TRY(cudaFuncSetAttribute(rht_in_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
@@ -514,13 +529,11 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   if (!P->items_in.empty()) {
-    dim3 grid((unsigned)P->items_in.size(), (unsigned)P->max_batch);
-    rht_in_kernel<false><<<grid, rht_threads(P->max_bs_in), P->max_bs_in * 4, stream>>>(
+    rht_in_kernel<false><<<(unsigned)P->items_in.size(), rht_threads(P->max_elems_in), P->max_elems_in * 4, stream>>>(
         P->d_layers, P->d_items_in, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
   if (!P->items_in_gemm.empty()) {
-    dim3 grid((unsigned)P->items_in_gemm.size(), (unsigned)P->max_batch_gemm);
-    rht_in_gemm_kernel<<<grid, rht_threads(P->max_bs_in), P->max_bs_in * 4, stream>>>(
+    rht_in_gemm_kernel<<<(unsigned)P->items_in_gemm.size(), rht_threads(P->max_elems_in), P->max_elems_in * 4, stream>>>(
         P->d_layers, P->d_items_in_gemm, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
   if (P->timing) {
@@ -546,8 +559,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     P->ev_used += 2;
   }
   {
-    dim3 grid((unsigned)P->items_out.size(), (unsigned)P->max_batch);
-    rht_out_kernel<false><<<grid, rht_threads(P->max_bs_out), P->max_bs_out * 4, stream>>>(
+    rht_out_kernel<false><<<(unsigned)P->items_out.size(), rht_threads(P->max_elems_out), P->max_elems_out * 4, stream>>>(
         P->d_layers, P->d_items_out, ws, reinterpret_cast<uint8_t*>(y_base), nullptr);
   }
   CUDA_TRY(cudaGetLastError());
@@ -658,7 +670,8 @@ static int run_rht_single(bool input, const void* src, int src_dtype, int64_t sr
   L.format = GLQB_FMT_E8_SHELL;
   L.batch = batch;
   std::vector<RhtItem> items;
-  for (int i = 0; i < n_blocks; ++i) items.push_back(RhtItem{0, i});
+  int max_elems = 32;
+  add_rht_items(items, 0, n_blocks, input ? L.bn_log : L.bm_log, batch, max_elems);
   DevLinear* d_L = nullptr;
   RhtItem* d_items = nullptr;
   if (input) {
@@ -672,8 +685,9 @@ static int run_rht_single(bool input, const void* src, int src_dtype, int64_t sr
   CUDA_TRY(cudaMallocAsync(&d_items, sizeof(RhtItem) * items.size(), stream));
   CUDA_TRY(cudaMemcpyAsync(d_L, &L, sizeof L, cudaMemcpyHostToDevice, stream));
   CUDA_TRY(cudaMemcpyAsync(d_items, items.data(), sizeof(RhtItem) * items.size(), cudaMemcpyHostToDevice, stream));
-  dim3 grid((unsigned)n_blocks, (unsigned)batch);
-  const int smem = maxbs * 4;
+  const unsigned grid = (unsigned)items.size();
+  const int smem = max_elems * 4;
+  maxbs = max_elems;
   if (input) {
     if (smem > 48 * 1024)
       CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));

@@ -41,7 +41,17 @@ struct DevLinear {
 struct RhtItem {
   int layer;
   int block;
+  int tok0;    // first token of the tile this CTA transforms
+  int ntok;    // tokens in the tile (the CTA's shared memory holds ntok * block floats)
 };
+
+// tokens per CTA of the transform kernels: about 16K floats of shared memory per CTA
+static inline int rht_tile_tokens(int block_size, int batch) {
+  int t = 16384 / block_size;
+  if (t < 1) t = 1;
+  if (t > 64) t = 64;
+  return t < batch ? t : batch;
+}
 
 // Stores the message glqb_last_error() returns for the calling thread (defined in glqb_api.cu).
 void set_error_message(const char* msg);

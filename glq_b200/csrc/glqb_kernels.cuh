@@ -25,6 +25,42 @@ __device__ __forceinline__ void store_act(void* base, long long idx, int dtype, 
   else reinterpret_cast<float*>(base)[idx] = v;
 }
 
+// four consecutive activations; idx must be a multiple of 4 and the row 8/16-byte aligned (the callers
+// check) — one 8- or 16-byte access instead of four
+__device__ __forceinline__ void load_act4(const void* base, long long idx, int dtype, float (&v)[4]) {
+  if (dtype == GLQB_DT_F32) {
+    const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+    const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(base) + idx);
+    if (dtype == GLQB_DT_F16) {
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+      v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else {
+      v[0] = __uint_as_float(t.x << 16); v[1] = __uint_as_float(t.x & 0xFFFF0000u);
+      v[2] = __uint_as_float(t.y << 16); v[3] = __uint_as_float(t.y & 0xFFFF0000u);
+    }
+  }
+}
+__device__ __forceinline__ void store_act4(void* base, long long idx, int dtype, const float (&v)[4]) {
+  if (dtype == GLQB_DT_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + idx) = make_float4(v[0], v[1], v[2], v[3]);
+  } else if (dtype == GLQB_DT_F16) {
+    const __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(base) + idx) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  } else {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(base) + idx) =
+        make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+  }
+}
+__device__ __forceinline__ bool act_rows_aligned4(const void* base, long long off, long long stride, int dtype) {
+  const int es = dtype == GLQB_DT_F32 ? 4 : 2;
+  return ((off | stride) & 3) == 0 && (reinterpret_cast<uintptr_t>(base) & (4 * es - 1)) == 0;
+}
+
 // streaming 128/64/32-bit loads of weight codes: read once, keep out of L1
 __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
   uint4 v;
@@ -66,7 +102,7 @@ __device__ __forceinline__ int xr_pos_e8(int i) { return (i & 3) * 2 + (i >> 2);
 // Input transform:  xr = fp16( H_blocks( SV * pad(x) ) / sqrt(bs) ), written in the layout the
 // decode kernel of the layer's format reads (reference: glq_input_rht_multiblock_kernel,
 // glq/csrc/glq_cuda.cu:2092; rounding to fp16 as glq/csrc/glq_cuda.cu:2625).
-// grid = (items, tokens); one CTA per (layer, block, token); dynamic smem = max block * 4 bytes.
+// One CTA per (layer, Hadamard block, tile of tokens); dynamic smem = tile tokens * block * 4 bytes.
 // PLAIN_F32: write fp32 in natural order instead (the unfused input_rht op).
 // ---------------------------------------------------------------------------------------------
 template <bool PLAIN_F32>
@@ -77,55 +113,50 @@ __global__ void __launch_bounds__(1024) rht_in_kernel(const DevLinear* __restric
   extern __shared__ float fbuf[];
   const RhtItem it = items[blockIdx.x];
   const DevLinear& L = layers[it.layer];
-  const int token = blockIdx.y;
-  if (token >= L.batch) return;
   const int off = L.bn_off[it.block];
   const int logbs = L.bn_log[it.block];
   const int bs = 1 << logbs;
-  const long long xrow = L.x_off + (long long)token * L.x_stride;
-  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+  const int total = it.ntok << logbs;
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int tk = o >> logbs, i = o & (bs - 1);
     const int col = off + i;
     float v = 0.f;
     if (col < L.in_f) {
-      v = load_act(x_base, xrow + col, L.x_dtype);
+      v = load_act(x_base, L.x_off + (long long)(it.tok0 + tk) * L.x_stride + col, L.x_dtype);
       if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
     }
-    fbuf[i] = v;
+    fbuf[o] = v;
   }
   float rs = 1.0f;
   if (!L.x_is_rotated) {
-    fht_smem(fbuf, logbs);
+    fht_smem_rows(fbuf, logbs, it.ntok);
     rs = rsqrtf((float)bs);
   } else {
     __syncthreads();
   }
-  if constexpr (PLAIN_F32) {
-    float* out = reinterpret_cast<float*>(ws + L.xr_off) + (long long)token * L.n;
-    for (int i = threadIdx.x; i < bs; i += blockDim.x) out[off + i] = fbuf[i] * rs;
-  } else {
-    const bool trellis = (L.format == GLQB_FMT_TRELLIS_3INST);
-    if (trellis) {
-      __half2* out = reinterpret_cast<__half2*>(ws + L.xr_off) + (long long)token * L.n;
-      for (int i = threadIdx.x; i < bs; i += blockDim.x) {
-        const int col = off + i;
-        const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);   // half index, even
-        out[pos >> 1] = __halves2half2(__float2half_rn(fbuf[i] * rs), __float2half_rn(0.f));
-      }
+  const bool trellis = (L.format == GLQB_FMT_TRELLIS_3INST);
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int tk = o >> logbs, i = o & (bs - 1);
+    const int col = off + i;
+    const long long token = it.tok0 + tk;
+    const float v = fbuf[o] * rs;
+    if constexpr (PLAIN_F32) {
+      reinterpret_cast<float*>(ws + L.xr_off)[token * L.n + col] = v;
+    } else if (trellis) {
+      const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);   // half index, even
+      (reinterpret_cast<__half2*>(ws + L.xr_off) + token * L.n)[pos >> 1] =
+          __halves2half2(__float2half_rn(v), __float2half_rn(0.f));
     } else {
-      __half* out = reinterpret_cast<__half*>(ws + L.xr_off) + (long long)token * L.n;
-      for (int i = threadIdx.x; i < bs; i += blockDim.x) {
-        const int col = off + i;
-        out[(col & ~7) + xr_pos_e8(col & 7)] = __float2half_rn(fbuf[i] * rs);
-      }
+      (reinterpret_cast<__half*>(ws + L.xr_off) + token * L.n)[(col & ~7) + xr_pos_e8(col & 7)] = __float2half_rn(v);
     }
   }
 }
 
 // ---------------------------------------------------------------------------------------------
-// Output transform: sums the per-warp partial sums of every strip in fixed (ascending slot) order,
-// applies wscale (and the optional per-row scale), the block Hadamard, 1/sqrt(bs) and SU, and
-// writes y[:, :out_features] (reference: glq_output_rht_multiblock_kernel, glq/csrc/glq_cuda.cu:2151).
-// FROM_F32: input is a plain fp32 (batch, m) matrix at x_base (the unfused output_rht op).
+// Output transform: sums the partial sums of every strip in fixed (ascending slot) order, applies
+// wscale (and the optional per-row scale), the block Hadamard, 1/sqrt(bs) and SU, and writes
+// y[:, :out_features] (reference: glq_output_rht_multiblock_kernel, glq/csrc/glq_cuda.cu:2151).
+// FROM_F32: input is a plain fp32 (batch, m) matrix (the unfused output_rht op).
 // ---------------------------------------------------------------------------------------------
 template <bool FROM_F32>
 __global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restrict__ layers,
@@ -136,41 +167,94 @@ __global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restri
   extern __shared__ float fbuf[];
   const RhtItem it = items[blockIdx.x];
   const DevLinear& L = layers[it.layer];
-  const int token = blockIdx.y;
-  if (token >= L.batch) return;
   const int off = L.bm_off[it.block];
   const int logbs = L.bm_log[it.block];
   const int bs = 1 << logbs;
-  const long long yrow = L.y_off + (long long)token * L.y_stride;
+  const int total = it.ntok << logbs;
   const int rows_per_strip = (L.format == GLQB_FMT_TRELLIS_3INST) ? 32 : 16;
-  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+  const int m = L.m, fixed_slots = L.fixed_slots, gps = L.groups_per_strip, per_warp = L.per_warp;
+  const long long slot_stride = (long long)L.batch * m;
+  const float wscale = L.wscale;
+  const float* row_scale = L.row_scale;
+  const bool vec_in = !FROM_F32 && !L.stop_at_yrht && (m & 3) == 0 && bs >= 4;
+  if (vec_in) {
+    // four consecutive rows at a time: they lie in one strip, so they share the slot count
+    const float* part = reinterpret_cast<const float*>(ws + L.part_off);
+    for (int o = threadIdx.x * 4; o < total; o += blockDim.x * 4) {
+      const int tk = o >> logbs, i = o & (bs - 1);
+      const int row = off + i;
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < m) {
+        int cnt = fixed_slots;
+        if (cnt <= 0) {
+          const long long g0 = L.group_base + (long long)(row / rows_per_strip) * gps;
+          cnt = (int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1;
+        }
+        const float* p = part + (long long)(it.tok0 + tk) * m + row;
+        for (int k = 0; k < cnt; ++k) {
+          const float4 t = *reinterpret_cast<const float4*>(p + k * slot_stride);
+          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+        }
+        s.x *= wscale; s.y *= wscale; s.z *= wscale; s.w *= wscale;
+        if (row_scale) { s.x *= row_scale[row]; s.y *= row_scale[row + 1]; s.z *= row_scale[row + 2]; s.w *= row_scale[row + 3]; }
+      }
+      *reinterpret_cast<float4*>(fbuf + o) = s;
+    }
+  } else
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int tk = o >> logbs, i = o & (bs - 1);
     const int row = off + i;
+    const long long token = it.tok0 + tk;
     float s = 0.f;
     if constexpr (FROM_F32) {
-      s = yrht_in[(long long)token * L.m + row];
+      s = yrht_in[token * L.m + row];
     } else if (row < L.m) {
       const int strip = row / rows_per_strip;
       const long long g0 = L.group_base + (long long)strip * L.groups_per_strip;
       const int cnt = L.fixed_slots > 0 ? L.fixed_slots
                                         : (int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1;
-      const float* p = reinterpret_cast<const float*>(ws + L.part_off) + (long long)token * L.m + row;
+      const float* p = reinterpret_cast<const float*>(ws + L.part_off) + token * L.m + row;
       const long long slot_stride = (long long)L.batch * L.m;
       for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];
       s *= L.wscale;
       if (L.row_scale) s *= L.row_scale[row];
     }
     if (L.stop_at_yrht) {
-      if (row < L.m) reinterpret_cast<float*>(y_base)[yrow + row] = s;
+      if (row < L.m) reinterpret_cast<float*>(y_base)[L.y_off + token * L.y_stride + row] = s;
     } else {
-      fbuf[i] = s;
+      fbuf[o] = s;
     }
   }
   if (L.stop_at_yrht) return;
-  fht_smem(fbuf, logbs);
+  fht_smem_rows(fbuf, logbs, it.ntok);
   const float rs = rsqrtf((float)bs);
-  for (int i = threadIdx.x; i < bs; i += blockDim.x) {
+  const int out_f = L.out_f, y_dtype = L.y_dtype;
+  if (bs >= 4 && act_rows_aligned4(y_base, L.y_off, L.y_stride, y_dtype)) {
+    for (int o = threadIdx.x * 4; o < total; o += blockDim.x * 4) {
+      const int tk = o >> logbs, i = o & (bs - 1);
+      const int row = off + i;
+      const long long yidx = L.y_off + (long long)(it.tok0 + tk) * L.y_stride + row;
+      const float4 t = *reinterpret_cast<const float4*>(fbuf + o);
+      if (row + 3 < out_f) {
+        const uint2 su4 = *reinterpret_cast<const uint2*>(L.su + row);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&su4.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&su4.y));
+        const float v[4] = {t.x * rs * a.x, t.y * rs * a.y, t.z * rs * b.x, t.w * rs * b.y};
+        store_act4(y_base, yidx, y_dtype, v);
+      } else {
+        const float v[4] = {t.x, t.y, t.z, t.w};
+        for (int k = 0; k < 4; ++k)
+          if (row + k < out_f) store_act(y_base, yidx + k, y_dtype, v[k] * rs * __half2float(L.su[row + k]));
+      }
+    }
+    return;
+  }
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int tk = o >> logbs, i = o & (bs - 1);
     const int row = off + i;
-    if (row < L.out_f) store_act(y_base, yrow + row, L.y_dtype, fbuf[i] * rs * __half2float(L.su[row]));
+    if (row < out_f)
+      store_act(y_base, L.y_off + (long long)(it.tok0 + tk) * L.y_stride + row, y_dtype,
+                fbuf[o] * rs * __half2float(L.su[row]));
   }
 }
 
