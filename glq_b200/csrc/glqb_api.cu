@@ -47,6 +47,11 @@ struct Segment {
   int per_warp;
   int grid;
   int item_first, item_count;   // GEMM work items (range in the plan's item array)
+  // E8 only: codebook held in shared memory across a 2-CTA cluster
+  bool cluster = false;
+  const uint32_t* big_table = nullptr;
+  const uint32_t* small_table = nullptr;
+  int small_entries = 0;
 };
 
 constexpr int GEMM_STAGES = 4;
@@ -130,6 +135,35 @@ static MvKernel e8_kernel(int ns, int nb) {
   return nullptr;
 }
 
+typedef void (*E8ClusterKernel)(const DevLinear*, int, long long, int, uint8_t*, const uint32_t*, const uint32_t*, int);
+
+template <int NS>
+static E8ClusterKernel e8_cluster_kernel_nb(int nb) {
+  switch (nb) {
+    case 1: return e8_mv_cluster_kernel<NS, 1>;
+    case 2: return e8_mv_cluster_kernel<NS, 2>;
+    case 4: if constexpr (NS <= 2) return e8_mv_cluster_kernel<NS, 4>; else return nullptr;
+  }
+  return nullptr;
+}
+
+static E8ClusterKernel pick_e8_cluster_kernel(const Segment& s) {
+  switch (s.ns) {
+    case 1: return e8_cluster_kernel_nb<1>(s.nb);
+    case 2: return e8_cluster_kernel_nb<2>(s.nb);
+    case 3: return e8_cluster_kernel_nb<3>(s.nb);
+    case 4: return e8_cluster_kernel_nb<4>(s.nb);
+  }
+  return nullptr;
+}
+
+static long long e8_cluster_min_bytes() {
+  const char* e = getenv("GLQB_E8_SMEM_MIN_BYTES");
+  // Off unless asked for: on B200 the split-table form measured slower than the L1/L2 gathers (each
+  // CTA of the pair expands every index, and the expansion, not the gather, is the limit).
+  return e ? atoll(e) : (1ll << 62);
+}
+
 static MvKernel pick_kernel(const Segment& s) {
   return s.format == GLQB_FMT_TRELLIS_3INST ? trellis_kernel(s.k1, s.k2, s.nb) : e8_kernel(s.ns, s.nb);
 }
@@ -162,7 +196,7 @@ static GemmKernel pick_gemm_kernel(const Segment& s) {
 }
 
 static size_t gemm_smem_bytes(int tn) {
-  return (size_t)GEMM_STAGES * (GM_A_BYTES + (size_t)tn * 128) + (3 * GEMM_STAGES + 2) * 8 + 16 + 1024;
+  return (size_t)GEMM_STAGES * (GM_A_BYTES + (size_t)tn * 128) + (3 * GEMM_STAGES + 4) * 8 + 16 + 1024;
 }
 
 static int tn_for_batch(int batch) { return batch <= DECODE_MAX_BATCH ? 0 : (batch <= 128 ? 128 : 256); }
@@ -352,6 +386,7 @@ static int build_plan(GlqbPlan* P) {
         ks = (kchunks + per - 1) / per;
         L.fixed_slots = ks;
         L.slots = ks;
+        L.slot_mult = 1;
         L.gemm_tn = s.tn;
         L.per_warp = 1;
         for (int mt = 0; mt < m_tiles; ++mt)
@@ -372,6 +407,58 @@ static int build_plan(GlqbPlan* P) {
     int ctas_per_sm = 1;
     CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&ctas_per_sm, kern, MV_THREADS, 0));
     ctas_per_sm = std::max(1, std::min(ctas_per_sm, 4));
+    long long warps_avail = (long long)P->sm_count * ctas_per_sm * MV_WARPS;
+    int warps_per_cta = MV_WARPS;
+    // E8: keep the codebook in shared memory (2-CTA cluster) when the launch is large enough to pay
+    // for filling it and every stage reads either one shared 65,536-entry table or one small table
+    if (s.format == GLQB_FMT_E8_SHELL && pick_e8_cluster_kernel(s)) {
+      long long bytes = 0;
+      bool ok = true;
+      const uint32_t* big = nullptr;
+      const uint32_t* small = nullptr;
+      int small_n = 0;
+      for (int i = 0; i < s.count && ok; ++i) {
+        const DevLinear& L = P->dev[s.first + i];
+        bytes += (long long)L.n_stages * L.m * (L.n / 8) * 2;
+        for (int st = 0; st < L.n_stages && ok; ++st) {
+          if (L.table_entries[st] == 65536) {
+            if (big && big != L.table[st]) ok = false;
+            big = L.table[st];
+          } else if (L.table_entries[st] <= 256) {
+            if (small && (small != L.table[st] || small_n != L.table_entries[st])) ok = false;
+            small = L.table[st];
+            small_n = L.table_entries[st];
+          } else {
+            ok = false;
+          }
+        }
+      }
+      if (ok && big && bytes >= e8_cluster_min_bytes()) {
+        E8ClusterKernel ck = pick_e8_cluster_kernel(s);
+        CUDA_TRY(cudaFuncSetAttribute(ck, cudaFuncAttributeMaxDynamicSharedMemorySize, E8S_SMEM_BYTES));
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.gridDim = dim3(2 * P->sm_count, 1, 1);
+        cfg.blockDim = dim3(E8S_THREADS, 1, 1);
+        cfg.dynamicSmemBytes = E8S_SMEM_BYTES;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        int clusters = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, ck, &cfg) == cudaSuccess && clusters > 0) {
+          s.cluster = true;
+          s.big_table = big;
+          s.small_table = small ? small : big;
+          s.small_entries = small_n;
+          warps_per_cta = E8S_THREADS / 32;
+          warps_avail = (long long)clusters * warps_per_cta;     // both CTAs of a cluster walk the same ranges
+        } else {
+          cudaGetLastError();
+        }
+      }
+    }
     long long total = 0;
     for (int i = 0; i < s.count; ++i) {
       DevLinear& L = P->dev[s.first + i];
@@ -379,16 +466,18 @@ static int build_plan(GlqbPlan* P) {
       total += (long long)L.strips * L.groups_per_strip;
     }
     s.total_groups = total;
-    const long long warps = (long long)P->sm_count * ctas_per_sm * MV_WARPS;
+    const long long warps = warps_avail;
     long long per_warp = (total + warps - 1) / warps;
     if (per_warp < 1) per_warp = 1;
     s.per_warp = (int)per_warp;
     const long long used_warps = (total + per_warp - 1) / per_warp;
-    s.grid = (int)((used_warps + MV_WARPS - 1) / MV_WARPS);
+    s.grid = (int)((used_warps + warps_per_cta - 1) / warps_per_cta);
+    if (s.cluster) s.grid *= 2;
     for (int i = 0; i < s.count; ++i) {
       DevLinear& L = P->dev[s.first + i];
       L.per_warp = s.per_warp;
-      L.slots = (L.groups_per_strip - 1) / s.per_warp + 2;
+      L.slot_mult = s.cluster ? 2 : 1;
+      L.slots = ((L.groups_per_strip - 1) / s.per_warp + 2) * L.slot_mult;
     }
   }
 
@@ -549,6 +638,20 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
       GemmKernel kern = pick_gemm_kernel(s);
       kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,
                                                                    s.item_count, ws, P->d_status);
+    } else if (s.cluster) {
+      cudaLaunchConfig_t cfg;
+      memset(&cfg, 0, sizeof cfg);
+      cfg.gridDim = dim3(s.grid, 1, 1);
+      cfg.blockDim = dim3(E8S_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = E8S_SMEM_BYTES;
+      cfg.stream = stream;
+      cudaLaunchAttribute at;
+      at.id = cudaLaunchAttributeClusterDimension;
+      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+      cfg.attrs = &at;
+      cfg.numAttrs = 1;
+      CUDA_TRY(cudaLaunchKernelEx(&cfg, pick_e8_cluster_kernel(s), (const DevLinear*)(P->d_layers + s.first), s.count,
+                                  s.total_groups, s.per_warp, ws, s.big_table, s.small_table, s.small_entries));
     } else {
       MvKernel kern = pick_kernel(s);
       kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);

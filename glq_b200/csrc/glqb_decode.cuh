@@ -110,17 +110,28 @@ __device__ __forceinline__ int tile_col(int lane, int j) { return 8 * ((j >> 2) 
 // E8 shell entries: one uint32 per codebook row, nibble i = 2*coord_i + 6
 // (reference: glq/codebook.py:102-115).  Values are multiples of 1/2 in [-3, 3], exact in fp16.
 // ------------------------------------------------------------------------------------------
-// nibbles (i, i+4) -> half2 (coord_i, coord_{i+4}) via the 1024+n mantissa trick:
-// (0x6400 | n) is the fp16 number 1024 + n;  (1024 + n) * 0.5 - 515 = n/2 - 3.
+// nibbles (i, i+4) -> half2 (coord_i, coord_{i+4}) via the mantissa trick: (0x6400 | n) is the fp16
+// number 1024 + n, so (1024 + n) * 0.5 - 515 = n/2 - 3; a nibble sitting four bits higher gives
+// 1024 + 16 n, and (1024 + 16 n) / 32 - 35 = n/2 - 3 as well (all steps exact in fp16).  Odd nibbles
+// therefore need no shift: one shift (by 8) serves nibbles 2 and 3.
 __device__ __forceinline__ void e8_entry_to_half2(uint32_t e, uint32_t (&h)[4]) {
   const __half2 half = __floats2half2_rn(0.5f, 0.5f);
   const __half2 bias = __floats2half2_rn(-515.0f, -515.0f);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t v = ((e >> (4 * i)) & 0x000F000Fu) | 0x64006400u;   // (n_i, n_{i+4})
-    __half2 r = __hfma2(*reinterpret_cast<__half2*>(&v), half, bias);
-    h[i] = *reinterpret_cast<uint32_t*>(&r);
-  }
+  const __half2 half16 = __floats2half2_rn(0.03125f, 0.03125f);
+  const __half2 bias16 = __floats2half2_rn(-35.0f, -35.0f);
+  const uint32_t e8 = e >> 8;
+  uint32_t v0 = (e & 0x000F000Fu) | 0x64006400u;    // (n0, n4)
+  uint32_t v1 = (e & 0x00F000F0u) | 0x64006400u;    // 16 * (n1, n5)
+  uint32_t v2 = (e8 & 0x000F000Fu) | 0x64006400u;   // (n2, n6)
+  uint32_t v3 = (e8 & 0x00F000F0u) | 0x64006400u;   // 16 * (n3, n7)
+  __half2 r0 = __hfma2(*reinterpret_cast<__half2*>(&v0), half, bias);
+  __half2 r1 = __hfma2(*reinterpret_cast<__half2*>(&v1), half16, bias16);
+  __half2 r2 = __hfma2(*reinterpret_cast<__half2*>(&v2), half, bias);
+  __half2 r3 = __hfma2(*reinterpret_cast<__half2*>(&v3), half16, bias16);
+  h[0] = *reinterpret_cast<uint32_t*>(&r0);
+  h[1] = *reinterpret_cast<uint32_t*>(&r1);
+  h[2] = *reinterpret_cast<uint32_t*>(&r2);
+  h[3] = *reinterpret_cast<uint32_t*>(&r3);
 }
 
 __device__ __forceinline__ float e8_coord(uint32_t e, int i) {

@@ -1,12 +1,15 @@
 // Prefill path: decoded weight tiles -> swizzled shared memory -> tcgen05.mma with fp32 accumulators in
 // tensor memory (TMEM).  One CTA computes D[128 weight rows x TN tokens] = W~[128 x K] * X~[TN x K]^T.
 //
-// Warp roles (GM_THREADS = 320):
-//   warps 0-7  decode producers: every warp decodes one 32x32 trellis group (or 16 rows x 64 columns of
-//              E8 indices) of the current 128x64 weight chunk into the stage's A tile, K-major with the
-//              128-byte swizzle the tensor core expects; warps 0-3 also drain the accumulators
-//   warp  8    one thread issues tcgen05.mma (4 per chunk: K = 16 each) and tcgen05.commit
-//   warp  9    one thread fetches the activation tile of the chunk with a bulk async copy (TMA, no
+// Warp roles (GM_THREADS = 704):
+//   warps 0-15 decode producers in two groups of eight; group 0 produces the even 128x64 weight chunks,
+//              group 1 the odd ones (two stages are always being filled).  Inside a group every warp
+//              decodes one 32x32 trellis group (or 16 rows x 64 columns of E8 indices) into the stage's
+//              A tile, K-major with the 128-byte swizzle the tensor core expects
+//   warps 18-21 epilogue: tcgen05.ld of the finished accumulator (two accumulators alternate, so the
+//              next tile's MMAs run while these warps write the previous tile's partial sums)
+//   warp  16   one thread issues tcgen05.mma (4 per chunk: K = 16 each) and tcgen05.commit
+//   warp  17   one thread fetches the activation tile of the chunk with a bulk async copy (TMA, no
 //              multicast); the input-transform kernel has already written the activations in the
 //              exact shared-memory image (swizzled), so one contiguous copy per chunk suffices
 // Stages hand over through mbarriers.  Every wait is bounded: on expiry the kernel records a status
@@ -16,8 +19,12 @@
 
 namespace glqb {
 
-constexpr int GM_THREADS = 320;
-constexpr int GM_PRODUCER_WARPS = 8;
+constexpr int GM_THREADS = 704;
+constexpr int GM_PRODUCER_WARPS = 16;     // two groups of 8
+constexpr int GM_GROUP_WARPS = 8;
+constexpr int GM_MMA_WARP = 16;
+constexpr int GM_LOAD_WARP = 17;
+constexpr int GM_EPI_WARP0 = 18;          // warps 18..21 drain the accumulators (TMEM lane quarter = warp % 4)
 constexpr int GM_TILE_M = 128;
 constexpr int GM_TILE_K = 64;                      // fp16 elements = 128 bytes = one swizzle row
 constexpr int GM_A_BYTES = GM_TILE_M * GM_TILE_K * 2;   // 16 KiB
@@ -279,25 +286,27 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
   uint64_t* full_a = bars;
   uint64_t* full_b = bars + STAGES;
   uint64_t* empty = bars + 2 * STAGES;
-  uint64_t* acc_full = bars + 3 * STAGES;
-  uint64_t* acc_empty = acc_full + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint64_t* acc_full = bars + 3 * STAGES;          // [2]
+  uint64_t* acc_empty = acc_full + 2;              // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&full_a[s], GM_PRODUCER_WARPS);
+      mbar_init(&full_a[s], GM_GROUP_WARPS);
       mbar_init(&full_b[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 4);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 8) {
-    tmem_alloc(tmem_slot, TN);
+  if (warp == GM_MMA_WARP) {
+    tmem_alloc(tmem_slot, 2 * TN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -307,14 +316,17 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
 
   if (warp < GM_PRODUCER_WARPS) {
     // ------------------------------------------------------------------ producers (+ epilogue)
-    int stage = 0;
-    uint32_t phase = 0, acc_phase = 0;
+    // q numbers the chunks of this CTA over all its items; chunk q lives in stage q % STAGES and is
+    // produced by group (q & 1).  Every role derives stage and phase from q in the same way.
+    const int grp = warp >> 3, wl = warp & 7;
+    uint32_t q0 = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const GemmItem it = items[item];
       const DevLinear& L = layers[it.layer];
+      const int first = it.k_begin + (int)((grp - q0) & 1u);       // this group's first chunk of the item
       if constexpr (FORMAT == 0) {
-        const int strip = warp >> 1, cg = warp & 1;
+        const int strip = wl >> 1, cg = wl & 1;
         const int rp = it.m_tile * 4 + strip;
         const int gps = L.groups_per_strip;
         const bool row_ok = rp < L.strips;
@@ -331,37 +343,39 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
             if constexpr (K2 > 0) nxt2 = load_words<K2>(p2 + (long long)cp * (128 * K2));
           }
         };
-        fetch(it.k_begin);
-        for (int kc = it.k_begin; kc < it.k_end; ++kc) {
+        if (first < it.k_end) fetch(first);
+        for (int kc = first; kc < it.k_end; kc += 2) {
+          const uint32_t q = q0 + (uint32_t)(kc - it.k_begin);
+          const int stage = (int)(q % STAGES);
+          const uint32_t phase = (q / STAGES) & 1u;
           const Words<K1> v = nxt;
           const Words<(K2 > 0 ? K2 : 1)> v2 = nxt2;
           const bool valid = row_ok && (kc * 2 + cg) < gps;
-          if (kc + 1 < it.k_end) fetch(kc + 1);
+          if (kc + 2 < it.k_end) fetch(kc + 2);
           if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
           uint8_t* a_tile = a_base + stage * GM_A_BYTES;
           if (valid) {
             gemm_store_group<K1, K2>(a_tile, strip, cg, lane, v, v2, s2);
           } else {
-            // rows or columns past the matrix: zeros (the shuffles inside the decode need all lanes, so
-            // the whole warp takes this branch together: validity is uniform per warp)
+            // rows or columns past the matrix: zeros (validity is uniform per warp, so the shuffles
+            // inside the decode always see all 32 lanes)
             const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
+            for (int qq = 0; qq < 4; ++qq)
 #pragma unroll
               for (int p = 0; p < 4; ++p) {
-                const int row = strip * 32 + (q & 1) * 16 + 8 * (p & 1) + g;
-                const int col = cg * 32 + (q >> 1) * 16 + 8 * (p >> 1) + 2 * t;
+                const int row = strip * 32 + (qq & 1) * 16 + 8 * (p & 1) + g;
+                const int col = cg * 32 + (qq >> 1) * 16 + 8 * (p >> 1) + 2 * t;
                 *reinterpret_cast<uint32_t*>(a_tile + sw128_offset(row, col)) = 0u;
               }
           }
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&full_a[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       } else {
         // E8: 128 rows x 8 indices per chunk; thread (row = tid >> 1, half = tid & 1) expands 4 indices
-        const int tid = threadIdx.x;                      // 0..255
+        const int tid = threadIdx.x & 255;                // thread inside the producer group
         const int row_l = tid >> 1, hf = tid & 1;
         const int row = it.m_tile * GM_TILE_M + row_l;
         const int nidx = L.n >> 3;
@@ -375,19 +389,22 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
             if (row_ok && i0 + 4 <= nidx) {
               nq[s] = ld_stream_v2(reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx + i0);
             } else if (row_ok) {
-              const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx;
+              const uint16_t* qd = reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx;
               uint32_t v[4] = {0, 0, 0, 0};
-              for (int k = 0; k < 4; ++k) if (i0 + k < nidx) v[k] = q[i0 + k];
+              for (int k = 0; k < 4; ++k) if (i0 + k < nidx) v[k] = qd[i0 + k];
               nq[s] = make_uint2(v[0] | (v[1] << 16), v[2] | (v[3] << 16));
             }
           }
         };
-        fetch(it.k_begin);
-        for (int kc = it.k_begin; kc < it.k_end; ++kc) {
+        if (first < it.k_end) fetch(first);
+        for (int kc = first; kc < it.k_end; kc += 2) {
+          const uint32_t q = q0 + (uint32_t)(kc - it.k_begin);
+          const int stage = (int)(q % STAGES);
+          const uint32_t phase = (q / STAGES) & 1u;
           uint2 cq[K1];
 #pragma unroll
           for (int s = 0; s < K1; ++s) cq[s] = nq[s];
-          if (kc + 1 < it.k_end) fetch(kc + 1);
+          if (kc + 2 < it.k_end) fetch(kc + 2);
           // gather before waiting for the stage: the table reads overlap the wait
           uint32_t ent[K1][4];
           const int i0 = kc * 8 + hf * 4;
@@ -431,47 +448,24 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(&full_a[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
+      q0 += (uint32_t)(it.k_end - it.k_begin);
       if (!ok) break;
-      // ---------------- epilogue: warps 0-3 own TMEM lanes 32*warp .. 32*warp+31
-      if (warp < 4) {
-        if (!mbar_wait(acc_full, acc_phase)) { ok = false; break; }
-        acc_phase ^= 1;
-        tc_fence_after();
-        const int row = it.m_tile * GM_TILE_M + warp * 32 + lane;
-        float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)it.slot * L.batch * L.m;
-#pragma unroll 1
-        for (int c0 = 0; c0 < TN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, r);
-          tmem_ld_wait();
-          if (row < L.m) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int token = it.n_tile * TN + c0 + i;
-              if (token < L.batch) part[(long long)token * L.m + row] = __uint_as_float(r[i]);
-            }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty);
-      }
     }
     if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(status, 2); }
-  } else if (warp == 8) {
+  } else if (warp == GM_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       int stage = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t phase = 0, seq = 0;
       const uint32_t idesc = umma_idesc_f16(TN);
       bool ok = true;
-      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++seq) {
         const GemmItem it = items[item];
-        if (!mbar_wait(acc_empty, acc_phase ^ 1)) { ok = false; break; }
-        acc_phase ^= 1;
+        const uint32_t a = seq & 1u, a_phase = (seq >> 1) & 1u;     // accumulator and its use count parity
+        const uint32_t d_tmem = tmem_acc + a * TN;
+        if (!mbar_wait(&acc_empty[a], a_phase ^ 1)) { ok = false; break; }
         tc_fence_after();
         for (int kc = it.k_begin; kc < it.k_end; ++kc) {
           if (!mbar_wait(&full_a[stage], phase) || !mbar_wait(&full_b[stage], phase)) { ok = false; break; }
@@ -480,16 +474,16 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
           const uint64_t db = umma_desc_sw128(smem_u32(b_base + stage * B_BYTES));
 #pragma unroll
           for (int k = 0; k < GM_TILE_K / 16; ++k)      // +32 bytes (2 x 16-byte units) per K step of 16
-            umma_f16(tmem_acc, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kc > it.k_begin || k > 0) ? 1u : 0u);
+            umma_f16(d_tmem, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kc > it.k_begin || k > 0) ? 1u : 0u);
           umma_commit(&empty[stage]);                    // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(acc_full);
+        umma_commit(&acc_full[a]);
       }
       if (!ok) { *abort_flag = 1; atomicExch(status, 3); }
     }
-  } else {
+  } else if (warp == GM_LOAD_WARP) {
     // ------------------------------------------------------------------ activation loader
     if (lane == 0) {
       int stage = 0;
@@ -510,10 +504,42 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
       if (!ok) { *abort_flag = 1; atomicExch(status, 4); }
     }
   }
+  else {
+    // ------------------------------------------------------------------ epilogue warps
+    const int quarter = warp & 3;                          // TMEM lanes 32*quarter .. 32*quarter + 31
+    uint32_t seq = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++seq) {
+      const GemmItem it = items[item];
+      const DevLinear& L = layers[it.layer];
+      const uint32_t a = seq & 1u, a_phase = (seq >> 1) & 1u;
+      if (!mbar_wait(&acc_full[a], a_phase)) { ok = false; break; }
+      tc_fence_after();
+      const int row = it.m_tile * GM_TILE_M + quarter * 32 + lane;
+      float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)it.slot * L.batch * L.m;
+#pragma unroll 1
+      for (int c0 = 0; c0 < TN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(quarter * 32) << 16) + a * TN + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (row < L.m) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int token = it.n_tile * TN + c0 + i;
+            if (token < L.batch) part[(long long)token * L.m + row] = __uint_as_float(r[i]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[a]);
+    }
+    if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(status, 5); }
+  }
   // ---- teardown: every thread arrives here (also after a wait gave up)
   tc_fence_before();
   __syncthreads();
-  if (warp == 8) tmem_dealloc(tmem_acc, TN);
+  if (warp == GM_MMA_WARP) tmem_dealloc(tmem_acc, 2 * TN);
 }
 
 }  // namespace glqb

@@ -32,6 +32,7 @@ struct DevLinear {
   int per_warp;          // work groups handed to each warp of the segment's launch
   int fixed_slots;       // > 0: every strip has exactly this many partial sums (GEMM path: K splits)
   int gemm_tn;           // token tile of the GEMM path (0: streaming decode path)
+  int slot_mult;         // partial sums written per warp range (2 when two CTAs of a cluster split a table)
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];

@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restri
         int cnt = fixed_slots;
         if (cnt <= 0) {
           const long long g0 = L.group_base + (long long)(row / rows_per_strip) * gps;
-          cnt = (int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1;
+          cnt = ((int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1) * L.slot_mult;
         }
         const float* p = part + (long long)(it.tok0 + tk) * m + row;
         for (int k = 0; k < cnt; ++k) {
@@ -212,7 +212,8 @@ __global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restri
       const int strip = row / rows_per_strip;
       const long long g0 = L.group_base + (long long)strip * L.groups_per_strip;
       const int cnt = L.fixed_slots > 0 ? L.fixed_slots
-                                        : (int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1;
+                                        : ((int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1) *
+                                              L.slot_mult;
       const float* p = reinterpret_cast<const float*>(ws + L.part_off) + token * L.m + row;
       const long long slot_stride = (long long)L.batch * L.m;
       for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];
@@ -483,12 +484,45 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
 // one 16-byte load.  Every residual stage has its own accumulator (all stage values are exact in
 // fp16); stages are combined in fp32 when a strip is flushed.
 // ---------------------------------------------------------------------------------------------
-template <int NS, int NB>
-__global__ void __launch_bounds__(MV_THREADS)
-e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
-             int per_warp, uint8_t* __restrict__ ws) {
+// Where the codebook entries come from.  TM = 0: the packed tables stay in global memory (L1/L2
+// gathers).  TM = 1: the 65,536-entry table lives in shared memory, split over the two CTAs of a
+// thread-block cluster (128 KiB each).  Both CTAs of a cluster walk the SAME index stream (the second
+// read is an L2 hit) and each expands only the indices whose entry it holds; every other index is
+// replaced by a zero entry, so it contributes nothing.  The two CTAs write separate partial sums
+// (slot 2k + rank) which the output transform adds in fixed order.  All gathers are plain local
+// shared-memory loads.  Tables of up to 256 entries (the small second-stage codebook) are held by
+// CTA 0 alone.
+struct E8Tables {
+  uint32_t table_base;     // shared-window address of this CTA's half of the big table
+  uint32_t small_base;     // shared-window address of the small table (rank 0) 
+  uint32_t zero_addr;      // shared-window address of a zero entry
+  uint32_t rank;           // CTA rank inside the cluster
+};
+
+template <int TM>
+__device__ __forceinline__ uint32_t e8_gather(const DevLinear& L, int s, uint32_t idx, const E8Tables& T) {
+  if constexpr (TM == 0) {
+    return __ldg(L.table[s] + (idx & ((uint32_t)L.table_entries[s] - 1u)));
+  } else {
+    uint32_t addr;
+    if (L.table_entries[s] == 65536) {
+      addr = ((idx >> 15) == T.rank) ? T.table_base + ((idx & 0x7FFFu) << 2) : T.zero_addr;
+    } else {
+      addr = (T.rank == 0) ? T.small_base + ((idx & ((uint32_t)L.table_entries[s] - 1u)) << 2) : T.zero_addr;
+    }
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+  }
+}
+
+template <int NS, int NB, int TM>
+__device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
+                                           int per_warp, uint8_t* __restrict__ ws, const E8Tables& T,
+                                           int warps_per_cta) {
   const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * MV_WARPS + (threadIdx.x >> 5);
+  // TM = 1: the two CTAs of a cluster share one warp numbering (they walk the same ranges)
+  const long long w = (long long)(TM == 1 ? (blockIdx.x >> 1) : blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
   long long g = w * per_warp;
   const long long gend = min(g + per_warp, total_groups);
   if (g >= gend) return;
@@ -523,10 +557,10 @@ e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total
 
     const __half* xr = reinterpret_cast<const __half*>(ws + L.xr_off);
 
-    for (int c = c0; c < c1; ++c) {
-      const int i0 = c * 32 + tq * 8;          // first index (8-column block) of this lane
-      // ---- load 8 indices per row and stage
-      uint32_t qa[NS][4], qb[NS][4];           // 8 uint16 packed in 4 words
+    // indices of one group: 8 per row and stage, packed two per word; requested one group ahead so
+    // that the HBM latency of the index stream overlaps the gathers and MMAs of the current group
+    auto load_indices = [&](int c, uint32_t (&qa)[NS][4], uint32_t (&qb)[NS][4]) {
+      const int i0 = c * 32 + tq * 8;
 #pragma unroll
       for (int s = 0; s < NS; ++s) {
         const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]);
@@ -549,25 +583,38 @@ e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total
           }
         }
       }
+    };
+    uint32_t nqa[NS][4], nqb[NS][4];
+    load_indices(c0, nqa, nqb);
+    // columns past the batch read the last token again (their accumulator columns are never stored)
+    const __half* xrow[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) xrow[nb] = xr + (long long)min(nb * 8 + gq, batch - 1) * L.n;
+
+    for (int c = c0; c < c1; ++c) {
+      const int i0 = c * 32 + tq * 8;          // first index (8-column block) of this lane
+      uint32_t qa[NS][4], qb[NS][4];
+#pragma unroll
+      for (int s = 0; s < NS; ++s)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { qa[s][k] = nqa[s][k]; qb[s][k] = nqb[s][k]; }
+      if (c + 1 < c1) load_indices(c + 1, nqa, nqb);
       // ---- 8 index pairs
 #pragma unroll
       for (int k = 0; k < 8; ++k) {
-        const int blk = i0 + k;                // 8-column block of x
+        const int blk = min(i0 + k, nidx - 1);
         uint4 xb[NB];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          const int token = nb * 8 + gq;
-          xb[nb] = make_uint4(0u, 0u, 0u, 0u);
-          if (token < batch && blk < nidx)
-            xb[nb] = __ldg(reinterpret_cast<const uint4*>(xr + (long long)token * L.n) + blk);
+          xb[nb] = __ldg(reinterpret_cast<const uint4*>(xrow[nb]) + blk);
+          if (i0 + k >= nidx) xb[nb] = make_uint4(0u, 0u, 0u, 0u);   // past the row end: contributes nothing
         }
 #pragma unroll
         for (int s = 0; s < NS; ++s) {
           const uint32_t ia = (qa[s][k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
           const uint32_t ib = (qb[s][k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
-          const uint32_t mask = (uint32_t)L.table_entries[s] - 1u;
-          const uint32_t ea = __ldg(L.table[s] + (ia & mask));
-          const uint32_t eb = __ldg(L.table[s] + (ib & mask));
+          const uint32_t ea = e8_gather<TM>(L, s, ia, T);
+          const uint32_t eb = e8_gather<TM>(L, s, ib, T);
           uint32_t ha[4], hb[4];
           e8_entry_to_half2(ea, ha);
           e8_entry_to_half2(eb, hb);
@@ -584,7 +631,7 @@ e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total
 
     {
       const long long g0 = L.group_base + (long long)strip * gps;
-      const int slot = (int)(w - g0 / per_warp);
+      const int slot = (TM == 1) ? 2 * (int)(w - g0 / per_warp) + (int)T.rank : (int)(w - g0 / per_warp);
       float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)slot * batch * L.m;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
@@ -604,6 +651,46 @@ e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total
     g += c1 - c0;
     if (c1 == gps && strip == L.strips - 1) ++li;
   }
+}
+
+template <int NS, int NB>
+__global__ void __launch_bounds__(MV_THREADS)
+e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
+             int per_warp, uint8_t* __restrict__ ws) {
+  const E8Tables T = {0u, 0u, 0u, 0u};
+  e8_mv_body<NS, NB, 0>(layers, n_layers, total_groups, per_warp, ws, T, MV_WARPS);
+}
+
+// Cluster form: each of the two CTAs holds half of the 65,536-entry table in its shared memory.
+constexpr int E8S_THREADS = 512;
+constexpr int E8S_SMEM_BYTES = 32768 * 4 + 256 * 4 + 16;
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+template <int NS, int NB>
+__global__ void __launch_bounds__(E8S_THREADS, 1)
+e8_mv_cluster_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups, int per_warp,
+                     uint8_t* __restrict__ ws, const uint32_t* __restrict__ big_table,
+                     const uint32_t* __restrict__ small_table, int small_entries) {
+  extern __shared__ __align__(16) uint32_t e8_smem[];
+  uint32_t rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+  const uint4* src = reinterpret_cast<const uint4*>(big_table + (size_t)rank * 32768);
+  uint4* dst = reinterpret_cast<uint4*>(e8_smem);
+  for (int i = threadIdx.x; i < 32768 / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+  for (int i = threadIdx.x; i < small_entries && i < 256; i += blockDim.x) e8_smem[32768 + i] = __ldg(small_table + i);
+  if (threadIdx.x == 0) e8_smem[32768 + 256] = 0x66666666u;   // nibble 6 = coordinate 0: the zero entry
+  E8Tables T;
+  const uint32_t local = (uint32_t)__cvta_generic_to_shared(e8_smem);
+  T.table_base = local;
+  T.small_base = local + 32768 * 4;
+  T.zero_addr = local + (32768 + 256) * 4;
+  T.rank = rank;
+  __syncthreads();
+  e8_mv_body<NS, NB, 1>(layers, n_layers, total_groups, per_warp, ws, T, E8S_THREADS / 32);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -461,3 +461,41 @@ def test_e8_gemm_vs_oracle(ops, e8_table, e8_cb, stages, T):
                                     *tail, out_dtype=torch.float32)
     ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, wscale)
     assert relerr(y.cpu().numpy(), ref) <= TOL
+
+
+# ---------------------------------------------------------------------------------------------
+# E8 decode with the codebook resident in shared memory (2-CTA cluster, distributed shared memory)
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("stages,small2", [(1, False), (2, False), (2, True), (4, False)])
+@pytest.mark.parametrize("B", [1, 9])
+def test_e8_cluster_table_path_matches_oracle_and_global_path(ops, e8_table, e8_cb, monkeypatch, stages, small2, B):
+    full, small = e8_cb
+    rng = np.random.default_rng(stages * 31 + B + int(small2))
+    m, n = 320, 832
+    qs = [rng.integers(0, 65536, size=(m, n // 8), dtype=np.uint16).view(np.int16) for _ in range(stages)]
+    tabs = [e8_table] * stages
+    if small2:
+        qs[1] = rng.integers(0, 256, size=(m, n // 8), dtype=np.uint16).view(np.int16)
+        tabs[1] = e8_table[:256]
+    inv = [0.3, 0.09, 0.027][:stages - 1]
+    su, sv = signs(rng, m), signs(rng, n)
+    W = O.e8_decode_nstage(qs, tabs, inv)
+    x = cuda(rng.standard_normal((B, n)).astype(np.float32), torch.float16)
+    empty_i = torch.empty(0, dtype=torch.int16, device="cuda")
+    empty_h = torch.empty(0, dtype=torch.float16, device="cuda")
+    tail = []
+    for s in range(1, 4):
+        cb = small if (s == 1 and small2) else full
+        tail += [cuda(qs[s]) if stages > s else empty_i, cb if stages > s else empty_h, inv[s - 1] if stages > s else 0.0]
+    args = (x, cuda(sv), cuda(su), cuda(qs[0]), full, 0.02, n, m, n, m,
+            torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m)), None, None, *tail)
+    ops.clear_caches()
+    monkeypatch.setenv("GLQB_E8_SMEM_MIN_BYTES", "0")          # force the shared-memory table path
+    y_smem = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
+    ops.clear_caches()
+    monkeypatch.setenv("GLQB_E8_SMEM_MIN_BYTES", str(1 << 40))  # force the global-memory gathers
+    y_glob = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
+    ops.clear_caches()
+    ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02)
+    assert relerr(y_smem.cpu().numpy(), ref) <= TOL
+    assert relerr(y_smem.cpu().numpy(), y_glob.cpu().numpy()) <= 1e-5
