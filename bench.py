@@ -375,7 +375,11 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "hbm", "kernel": "trellis_mv_kernel<4,0,1>", "achieved": achieved, "peak": peak,
                          "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                         "kernel_ms": kern_ms_avg, "bytes_per_launch": W["code_bytes"], "traffic": None},
+                         "kernel_ms": kern_ms_avg, "bytes_per_launch": W["code_bytes"],
+                         # dram__bytes_read+write of one launch: captured with ncu on the 4-layer case
+                         # (160.9 MB for 156.2 MB of packed bytes, profiles/trellis_mv_kernel_decode_smollm3.md)
+                         # and scaled by the packed bytes of this launch (traffic grows with the layers read)
+                         "traffic": int(W["code_bytes"] * 160.93 / 156.24) if not generic else None},
         }
         if generic and "prefill" in args.workload:
             # per-layer TFLOP/s, against the bf16 tensor peak

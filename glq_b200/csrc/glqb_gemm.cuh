@@ -232,8 +232,28 @@ __global__ void __launch_bounds__(1024) rht_in_gemm_kernel(const DevLinear* __re
 
 // ---- weight producers ------------------------------------------------------------------------------
 // One trellis group (32 rows x 32 columns) -> its place in the 128 x 64 A tile.
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Byte offsets (inside a swizzled 128 x 64 tile) of the 16 register pairs a lane stores per group:
+// entry q*4 + p with q = ni*2 + mi the 16x16 tile and p = c*2 + a the pair; fixed per thread.
+__device__ __forceinline__ void gemm_lane_offsets(int strip, int cg, int lane, uint32_t (&off)[16]) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int q = 0; q < 4; ++q)
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int ni = q >> 1, mi = q & 1, c = p >> 1, a_ = p & 1;
+      off[q * 4 + p] = sw128_offset(strip * 32 + mi * 16 + 8 * a_ + g, cg * 32 + ni * 16 + 8 * c + 2 * t);
+    }
+}
+
 template <int K1, int K2>
-__device__ __forceinline__ void gemm_store_group(uint8_t* a_tile, int strip, int cg, int lane, const Words<K1>& v,
+__device__ __forceinline__ void gemm_store_group(uint32_t a_tile, const uint32_t (&off)[16], int lane, const Words<K1>& v,
                                                  const Words<(K2 > 0 ? K2 : 1)>& v2, __half2 s2) {
   const Words<K1> vn = shfl_words<K1>(v, (lane + 1) & 31);
   Words<K1> vn2 = vn;
@@ -244,7 +264,6 @@ __device__ __forceinline__ void gemm_store_group(uint8_t* a_tile, int strip, int
     un2 = un;
     if constexpr (K2 == 1) un2 = shfl_words<K2>(v2, (lane + 2) & 31);
   }
-  const int g = lane >> 2, t = lane & 3;
 #pragma unroll
   for (int ni = 0; ni < 2; ++ni) {
 #pragma unroll
@@ -262,10 +281,7 @@ __device__ __forceinline__ void gemm_store_group(uint8_t* a_tile, int strip, int
           const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&w2), s2, *reinterpret_cast<const __half2*>(&w));
           w = *reinterpret_cast<const uint32_t*>(&r);
         }
-        const int c = p >> 1, a_ = p & 1;
-        const int row = strip * 32 + mi * 16 + 8 * a_ + g;
-        const int col = cg * 32 + ni * 16 + 8 * c + 2 * t;
-        *reinterpret_cast<uint32_t*>(a_tile + sw128_offset(row, col)) = w;
+        st_shared_u32(a_tile + off[q * 4 + p], w);
       }
     }
   }
@@ -334,6 +350,8 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         const uint8_t* p2 = nullptr;
         if constexpr (K2 > 0) p2 = L.codes[1] + ((long long)rp * gps) * (128 * K2) + lane * (4 * K2);
         const __half2 s2 = __float2half2_rn(L.stage_scale[1]);
+        uint32_t off[16];
+        gemm_lane_offsets(strip, cg, lane, off);
         Words<K1> nxt;
         Words<(K2 > 0 ? K2 : 1)> nxt2;
         auto fetch = [&](int kc) {
@@ -353,21 +371,14 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
           const bool valid = row_ok && (kc * 2 + cg) < gps;
           if (kc + 2 < it.k_end) fetch(kc + 2);
           if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
-          uint8_t* a_tile = a_base + stage * GM_A_BYTES;
+          const uint32_t a_tile = smem_u32(a_base) + stage * GM_A_BYTES;
           if (valid) {
-            gemm_store_group<K1, K2>(a_tile, strip, cg, lane, v, v2, s2);
+            gemm_store_group<K1, K2>(a_tile, off, lane, v, v2, s2);
           } else {
             // rows or columns past the matrix: zeros (validity is uniform per warp, so the shuffles
             // inside the decode always see all 32 lanes)
-            const int g = lane >> 2, t = lane & 3;
 #pragma unroll
-            for (int qq = 0; qq < 4; ++qq)
-#pragma unroll
-              for (int p = 0; p < 4; ++p) {
-                const int row = strip * 32 + (qq & 1) * 16 + 8 * (p & 1) + g;
-                const int col = cg * 32 + (qq >> 1) * 16 + 8 * (p >> 1) + 2 * t;
-                *reinterpret_cast<uint32_t*>(a_tile + sw128_offset(row, col)) = 0u;
-              }
+            for (int i = 0; i < 16; ++i) st_shared_u32(a_tile + off[i], 0u);
           }
           fence_async_smem();
           __syncwarp();
@@ -418,7 +429,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
             }
           }
           if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
-          uint8_t* a_tile = a_base + stage * GM_A_BYTES;
+          const uint32_t a_tile = smem_u32(a_base) + stage * GM_A_BYTES;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             uint4 out = make_uint4(0u, 0u, 0u, 0u);
@@ -443,7 +454,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
               out.z = __byte_perm(h[0], h[1], 0x7632);
               out.w = __byte_perm(h[2], h[3], 0x7632);
             }
-            *reinterpret_cast<uint4*>(a_tile + sw128_offset(row_l, (hf * 4 + k) * 8)) = out;
+            st_shared_v4(a_tile + sw128_offset(row_l, (hf * 4 + k) * 8), out);
           }
           fence_async_smem();
           __syncwarp();
