@@ -263,6 +263,10 @@ static int validate(const GlqbLinearDesc& d, int idx) {
   return GLQB_OK;
 }
 
+// one thread per 32-value segment of the largest tile, between 64 and RHT_THREADS
+static int rht_threads(int max_elems) { return std::max(64, std::min(RHT_THREADS, (max_elems / 32 + 31) / 32 * 32)); }
+static int rht_smem(int max_elems) { return (max_elems + max_elems / 32) * 4 + 64; }
+
 // one item per (layer, block, tile of tokens); tracks the largest tile (floats) for the launch's smem
 static void add_rht_items(std::vector<RhtItem>& items, int layer, int nblocks, const int* logs, int batch,
                           int& max_elems) {
@@ -538,7 +542,7 @@ static int build_plan(GlqbPlan* P) {
   CUDA_TRY(cudaMemcpy(P->d_items_out, P->items_out.data(), sizeof(RhtItem) * P->items_out.size(), cudaMemcpyHostToDevice));
 
   // kernels that may need more than 48 KB of dynamic shared memory
-  const int smem_in = P->max_elems_in * 4, smem_out = P->max_elems_out * 4;
+  const int smem_in = rht_smem(P->max_elems_in), smem_out = rht_smem(P->max_elems_out);
   if (smem_in > 48 * 1024) {
     CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
     CUDA_TRY(cudaFuncSetAttribute(rht_in_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
@@ -548,7 +552,6 @@ static int build_plan(GlqbPlan* P) {
   return GLQB_OK;
 }
 
-static int rht_threads(int max_bs) { return std::max(64, std::min(1024, max_bs / 8)); }
 
 }  // namespace glqb
 
@@ -618,11 +621,11 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   if (!P->items_in.empty()) {
-    rht_in_kernel<false><<<(unsigned)P->items_in.size(), rht_threads(P->max_elems_in), P->max_elems_in * 4, stream>>>(
+    rht_in_kernel<false><<<(unsigned)P->items_in.size(), rht_threads(P->max_elems_in), rht_smem(P->max_elems_in), stream>>>(
         P->d_layers, P->d_items_in, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
   if (!P->items_in_gemm.empty()) {
-    rht_in_gemm_kernel<<<(unsigned)P->items_in_gemm.size(), rht_threads(P->max_elems_in), P->max_elems_in * 4, stream>>>(
+    rht_in_gemm_kernel<<<(unsigned)P->items_in_gemm.size(), rht_threads(P->max_elems_in), rht_smem(P->max_elems_in), stream>>>(
         P->d_layers, P->d_items_in_gemm, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
   if (P->timing) {
@@ -662,7 +665,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     P->ev_used += 2;
   }
   {
-    rht_out_kernel<false><<<(unsigned)P->items_out.size(), rht_threads(P->max_elems_out), P->max_elems_out * 4, stream>>>(
+    rht_out_kernel<false><<<(unsigned)P->items_out.size(), rht_threads(P->max_elems_out), rht_smem(P->max_elems_out), stream>>>(
         P->d_layers, P->d_items_out, ws, reinterpret_cast<uint8_t*>(y_base), nullptr);
   }
   CUDA_TRY(cudaGetLastError());
@@ -789,7 +792,7 @@ static int run_rht_single(bool input, const void* src, int src_dtype, int64_t sr
   CUDA_TRY(cudaMemcpyAsync(d_L, &L, sizeof L, cudaMemcpyHostToDevice, stream));
   CUDA_TRY(cudaMemcpyAsync(d_items, items.data(), sizeof(RhtItem) * items.size(), cudaMemcpyHostToDevice, stream));
   const unsigned grid = (unsigned)items.size();
-  const int smem = max_elems * 4;
+  const int smem = rht_smem(max_elems);
   maxbs = max_elems;
   if (input) {
     if (smem > 48 * 1024)

@@ -98,3 +98,122 @@ __device__ __forceinline__ void fht_smem_rows(float* buf, int logbs, int rows) {
 }
 
 }  // namespace glqb
+
+// ---------------------------------------------------------------------------------------------------
+// Tiled transform with radix-32 register passes.
+//
+// A tile is `rows` independent arrays of 2^logbs values.  Pass 1 is fused with the load: a thread pulls
+// 32 consecutive values straight from global memory (the caller's `load32`), does butterfly stages 0-4 in
+// registers and parks them in shared memory; the last pass is fused with the store (`store1` receives
+// every finished value).  Arrays of up to 32 values never touch shared memory, up to 1024 values make one
+// round trip, up to 32768 two.  Shared memory is padded by one word per 32 (index i lives at i + i/32), which
+// makes the 32-consecutive accesses of pass 1 and the strided accesses of the later passes conflict-free.
+// Butterfly order is the reference's: ascending distance, lower index gets a+b.
+// ---------------------------------------------------------------------------------------------------
+namespace glqb {
+
+__device__ __forceinline__ int fht_pad(int i) { return i + (i >> 5); }
+__host__ __device__ __forceinline__ int fht_tile_words(int logbs, int rows) {
+  const int bs = 1 << logbs;
+  return rows * (bs + (bs >> 5));
+}
+
+template <int R>
+__device__ __forceinline__ void fht_regs(float (&v)[1 << R]) {
+#pragma unroll
+  for (int s = 0; s < R; ++s) {
+#pragma unroll
+    for (int k = 0; k < (1 << R); ++k) {
+      if (!(k & (1 << s))) {
+        const float a = v[k], b = v[k | (1 << s)];
+        v[k] = a + b;
+        v[k | (1 << s)] = a - b;
+      }
+    }
+  }
+}
+
+// last pass: R remaining stages at distance 2^done; every finished value goes to store1(row, index, value)
+template <int R, class Store1>
+__device__ __forceinline__ void fht_last_pass(const float* smem, int logbs, int done, int rows, int row_words,
+                                              Store1& store1) {
+  const int S = 1 << done;                     // R == logbs - done: one group spans the whole array
+  const int total = rows << done;
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int row = o >> done, low = o & (S - 1);
+    const float* p = smem + row * row_words;
+    float v[1 << R];
+#pragma unroll
+    for (int k = 0; k < (1 << R); ++k) v[k] = p[fht_pad(low + k * S)];
+    fht_regs<R>(v);
+#pragma unroll
+    for (int k = 0; k < (1 << R); ++k) store1(row, low + k * S, v[k]);
+  }
+}
+
+template <class Load32, class Load1, class Store1>
+__device__ __forceinline__ void fht_tile(float* smem, int logbs, int rows, Load32 load32, Load1 load1, Store1 store1) {
+  const int bs = 1 << logbs;
+  if (logbs < 5) {
+    // tiny arrays (E8 layers whose width is not a multiple of 32): one thread per array, all in registers
+    for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+      float v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) v[k] = k < bs ? load1(row, k) : 0.f;
+      for (int h = 1; h < bs; h <<= 1)
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (!(k & h) && (k | h) < bs) { const float a = v[k], b = v[k | h]; v[k] = a + b; v[k | h] = a - b; }
+#pragma unroll
+      for (int k = 0; k < 16; ++k) if (k < bs) store1(row, k, v[k]);
+    }
+    return;
+  }
+  const int row_words = bs + (bs >> 5);
+  const int slog = logbs - 5;                  // log2(32-value segments per array)
+  const int nseg = rows << slog;
+  for (int s = threadIdx.x; s < nseg; s += blockDim.x) {
+    const int row = s >> slog, i0 = (s & ((1 << slog) - 1)) << 5;
+    float v[32];
+    load32(row, i0, v);
+    fht_regs<5>(v);
+    if (logbs == 5) {
+#pragma unroll
+      for (int k = 0; k < 32; ++k) store1(row, k, v[k]);
+    } else {
+      float* p = smem + row * row_words + fht_pad(i0);
+#pragma unroll
+      for (int k = 0; k < 32; ++k) p[k] = v[k];
+    }
+  }
+  if (logbs == 5) return;
+  __syncthreads();
+  int done = 5;
+  if (logbs > 10) {
+    // middle pass: stages 5..9 (distance 32..512), in place
+    const int total = rows << slog;
+    for (int o = threadIdx.x; o < total; o += blockDim.x) {
+      const int row = o >> slog, oo = o & ((1 << slog) - 1);
+      const int low = oo & 31, high = oo >> 5;
+      float* p = smem + row * row_words;
+      const int base = (high << 10) | low;
+      float v[32];
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = p[fht_pad(base + (k << 5))];
+      fht_regs<5>(v);
+#pragma unroll
+      for (int k = 0; k < 32; ++k) p[fht_pad(base + (k << 5))] = v[k];
+    }
+    __syncthreads();
+    done = 10;
+  }
+  switch (logbs - done) {
+    case 1: fht_last_pass<1>(smem, logbs, done, rows, row_words, store1); break;
+    case 2: fht_last_pass<2>(smem, logbs, done, rows, row_words, store1); break;
+    case 3: fht_last_pass<3>(smem, logbs, done, rows, row_words, store1); break;
+    case 4: fht_last_pass<4>(smem, logbs, done, rows, row_words, store1); break;
+    default: fht_last_pass<5>(smem, logbs, done, rows, row_words, store1); break;
+  }
+}
+
+}  // namespace glqb

@@ -138,10 +138,10 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int e) {
 // One CTA per (layer, Hadamard block, tile of tokens); tiles ordered [n_tile][k_chunk], each TN*128
 // bytes.  Columns past n (the last chunk of a layer whose n is not a multiple of 64) are written as
 // zeros by the CTAs of the last block.
-__global__ void __launch_bounds__(1024) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
-                                                           const RhtItem* __restrict__ items,
-                                                           const uint8_t* __restrict__ x_base,
-                                                           uint8_t* __restrict__ ws) {
+__global__ void __launch_bounds__(RHT_THREADS) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
+                                                                  const RhtItem* __restrict__ items,
+                                                                  const uint8_t* __restrict__ x_base,
+                                                                  uint8_t* __restrict__ ws) {
   extern __shared__ float fbuf[];
   const RhtItem it = items[blockIdx.x];
   const DevLinear& L = layers[it.layer];
@@ -149,73 +149,30 @@ __global__ void __launch_bounds__(1024) rht_in_gemm_kernel(const DevLinear* __re
   const int off = L.bn_off[it.block];
   const int logbs = L.bn_log[it.block];
   const int bs = 1 << logbs;
-  const int total = it.ntok << logbs;
-  const int in_f = L.in_f, x_dtype = L.x_dtype;
-  const bool rotated = L.x_is_rotated != 0;
-  if (bs >= 4 && (in_f & 3) == 0 && act_rows_aligned4(x_base, L.x_off, L.x_stride, x_dtype)) {
-    for (int o = threadIdx.x * 4; o < total; o += blockDim.x * 4) {
-      const int tk = o >> logbs, i = o & (bs - 1);
-      const int col = off + i;
-      float v[4] = {0.f, 0.f, 0.f, 0.f};
-      if (col < in_f) {
-        load_act4(x_base, L.x_off + (long long)(it.tok0 + tk) * L.x_stride + col, x_dtype, v);
-        if (!rotated) {
-          const uint2 s4 = *reinterpret_cast<const uint2*>(L.sv + col);
-          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
-          const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
-          v[0] *= a.x; v[1] *= a.y; v[2] *= b.x; v[3] *= b.y;
-        }
-      }
-      *reinterpret_cast<float4*>(fbuf + o) = make_float4(v[0], v[1], v[2], v[3]);
-    }
-  } else {
-    for (int o = threadIdx.x; o < total; o += blockDim.x) {
-      const int tk = o >> logbs, i = o & (bs - 1);
-      const int col = off + i;
-      float v = 0.f;
-      if (col < in_f) {
-        v = load_act(x_base, L.x_off + (long long)(it.tok0 + tk) * L.x_stride + col, x_dtype);
-        if (!rotated) v *= __half2float(L.sv[col]);
-      }
-      fbuf[o] = v;
-    }
-  }
-  float rs = 1.0f;
-  if (!rotated) {
-    fht_smem_rows(fbuf, logbs, it.ntok);
-    rs = rsqrtf((float)bs);
-  } else {
-    __syncthreads();
-  }
   const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
-  // eight consecutive columns = one 16-byte chunk of the swizzled tile
-  if (bs >= 8) {
-    const int octs = total >> 3;
-    for (int o = threadIdx.x; o < octs; o += blockDim.x) {
-      const int tk = o >> (logbs - 3), i = (o & ((bs >> 3) - 1)) * 8;
-      const int token = it.tok0 + tk;
-      const int nt = token / tn, r = token - nt * tn;
-      const int col = off + i;
-      const int kc = col >> 6, e = col & 63;
-      const float* f = fbuf + (tk << logbs) + i;
-      const float4 f0 = *reinterpret_cast<const float4*>(f), f1 = *reinterpret_cast<const float4*>(f + 4);
-      const __half2 h0 = __floats2half2_rn(f0.x * rs, f0.y * rs), h1 = __floats2half2_rn(f0.z * rs, f0.w * rs);
-      const __half2 h2 = __floats2half2_rn(f1.x * rs, f1.y * rs), h3 = __floats2half2_rn(f1.z * rs, f1.w * rs);
-      uint8_t* base = ws + L.xr_off + ((size_t)nt * kchunks + kc) * tn * 128;
-      *reinterpret_cast<uint4*>(base + sw128_offset(r, e)) =
-          make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
-                     *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
-    }
+  const bool vec_ok = (off & 3) == 0 && act_rows_aligned4(x_base, L.x_off, L.x_stride, L.x_dtype);
+  const float rs = L.x_is_rotated ? 1.0f : rsqrtf((float)bs);
+  auto store1 = [&](int row, int i, float val) {
+    const int token = it.tok0 + row;
+    const int nt = token / tn, r = token - nt * tn;
+    const int col = off + i;
+    const int kc = col >> 6, e = col & 63;
+    *reinterpret_cast<__half*>(ws + L.xr_off + ((size_t)nt * kchunks + kc) * tn * 128 + sw128_offset(r, e)) =
+        __float2half_rn(val * rs);
+  };
+  auto load1 = [&](int row, int i) -> float {
+    const int col = off + i;
+    if (col >= L.in_f) return 0.f;
+    float v = load_act(x_base, L.x_off + (long long)(it.tok0 + row) * L.x_stride + col, L.x_dtype);
+    if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
+    return v;
+  };
+  if (L.x_is_rotated) {
+    const int total = it.ntok << logbs;
+    for (int o = threadIdx.x; o < total; o += blockDim.x) store1(o >> logbs, o & (bs - 1), load1(o >> logbs, o & (bs - 1)));
   } else {
-    for (int o = threadIdx.x; o < total; o += blockDim.x) {
-      const int tk = o >> logbs, i = o & (bs - 1);
-      const int token = it.tok0 + tk;
-      const int nt = token / tn, r = token - nt * tn;
-      const int col = off + i;
-      const int kc = col >> 6, e = col & 63;
-      *reinterpret_cast<__half*>(ws + L.xr_off + ((size_t)nt * kchunks + kc) * tn * 128 + sw128_offset(r, e)) =
-          __float2half_rn(fbuf[o] * rs);
-    }
+    auto load32 = [&](int row, int i0, float (&v)[32]) { rht_load_x32(L, x_base, it.tok0 + row, off + i0, vec_ok, v); };
+    fht_tile(fbuf, logbs, it.ntok, load32, load1, store1);
   }
   if (it.block == L.nbn - 1) {
     const int padc = kchunks * GM_TILE_K - L.n;

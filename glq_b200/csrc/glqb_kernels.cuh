@@ -102,44 +102,59 @@ __device__ __forceinline__ int xr_pos_e8(int i) { return (i & 3) * 2 + (i >> 2);
 // Input transform:  xr = fp16( H_blocks( SV * pad(x) ) / sqrt(bs) ), written in the layout the
 // decode kernel of the layer's format reads (reference: glq_input_rht_multiblock_kernel,
 // glq/csrc/glq_cuda.cu:2092; rounding to fp16 as glq/csrc/glq_cuda.cu:2625).
-// One CTA per (layer, Hadamard block, tile of tokens); dynamic smem = tile tokens * block * 4 bytes.
+// One CTA per (layer, Hadamard block, tile of tokens); the transform itself is fht_tile (first pass
+// fused with the global loads, last pass with the stores).
 // PLAIN_F32: write fp32 in natural order instead (the unfused input_rht op).
 // ---------------------------------------------------------------------------------------------
+constexpr int RHT_THREADS = 512;
+
+// 32 consecutive activations of one token, times SV, zero past in_features
+__device__ __forceinline__ void rht_load_x32(const DevLinear& L, const uint8_t* x_base, long long token, int col0,
+                                             bool vec_ok, float (&v)[32]) {
+  const long long base = L.x_off + token * L.x_stride;
+  const bool rotated = L.x_is_rotated != 0;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int col = col0 + 4 * j;
+    float t[4] = {0.f, 0.f, 0.f, 0.f};
+    if (vec_ok && col + 3 < L.in_f) {
+      load_act4(x_base, base + col, L.x_dtype, t);
+      if (!rotated) {
+        const uint2 s4 = *reinterpret_cast<const uint2*>(L.sv + col);
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+        t[0] *= a.x; t[1] *= a.y; t[2] *= b.x; t[3] *= b.y;
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        if (col + k < L.in_f) {
+          t[k] = load_act(x_base, base + col + k, L.x_dtype);
+          if (!rotated) t[k] *= __half2float(L.sv[col + k]);
+        }
+    }
+    v[4 * j] = t[0]; v[4 * j + 1] = t[1]; v[4 * j + 2] = t[2]; v[4 * j + 3] = t[3];
+  }
+}
+
 template <bool PLAIN_F32>
-__global__ void __launch_bounds__(1024) rht_in_kernel(const DevLinear* __restrict__ layers,
-                                                      const RhtItem* __restrict__ items,
-                                                      const uint8_t* __restrict__ x_base,
-                                                      uint8_t* __restrict__ ws) {
+__global__ void __launch_bounds__(RHT_THREADS) rht_in_kernel(const DevLinear* __restrict__ layers,
+                                                             const RhtItem* __restrict__ items,
+                                                             const uint8_t* __restrict__ x_base,
+                                                             uint8_t* __restrict__ ws) {
   extern __shared__ float fbuf[];
   const RhtItem it = items[blockIdx.x];
   const DevLinear& L = layers[it.layer];
   const int off = L.bn_off[it.block];
   const int logbs = L.bn_log[it.block];
   const int bs = 1 << logbs;
-  const int total = it.ntok << logbs;
-  for (int o = threadIdx.x; o < total; o += blockDim.x) {
-    const int tk = o >> logbs, i = o & (bs - 1);
-    const int col = off + i;
-    float v = 0.f;
-    if (col < L.in_f) {
-      v = load_act(x_base, L.x_off + (long long)(it.tok0 + tk) * L.x_stride + col, L.x_dtype);
-      if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
-    }
-    fbuf[o] = v;
-  }
-  float rs = 1.0f;
-  if (!L.x_is_rotated) {
-    fht_smem_rows(fbuf, logbs, it.ntok);
-    rs = rsqrtf((float)bs);
-  } else {
-    __syncthreads();
-  }
   const bool trellis = (L.format == GLQB_FMT_TRELLIS_3INST);
-  for (int o = threadIdx.x; o < total; o += blockDim.x) {
-    const int tk = o >> logbs, i = o & (bs - 1);
+  const bool vec_ok = (off & 3) == 0 && act_rows_aligned4(x_base, L.x_off, L.x_stride, L.x_dtype);
+  const float rs = L.x_is_rotated ? 1.0f : rsqrtf((float)bs);
+  auto store1 = [&](int row, int i, float val) {
     const int col = off + i;
-    const long long token = it.tok0 + tk;
-    const float v = fbuf[o] * rs;
+    const long long token = it.tok0 + row;
+    const float v = val * rs;
     if constexpr (PLAIN_F32) {
       reinterpret_cast<float*>(ws + L.xr_off)[token * L.n + col] = v;
     } else if (trellis) {
@@ -149,7 +164,21 @@ __global__ void __launch_bounds__(1024) rht_in_kernel(const DevLinear* __restric
     } else {
       (reinterpret_cast<__half*>(ws + L.xr_off) + token * L.n)[(col & ~7) + xr_pos_e8(col & 7)] = __float2half_rn(v);
     }
+  };
+  auto load1 = [&](int row, int i) -> float {
+    const int col = off + i;
+    if (col >= L.in_f) return 0.f;
+    float v = load_act(x_base, L.x_off + (long long)(it.tok0 + row) * L.x_stride + col, L.x_dtype);
+    if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
+    return v;
+  };
+  if (L.x_is_rotated) {            // already transformed by the caller: convert and lay out only
+    const int total = it.ntok << logbs;
+    for (int o = threadIdx.x; o < total; o += blockDim.x) store1(o >> logbs, o & (bs - 1), load1(o >> logbs, o & (bs - 1)));
+    return;
   }
+  auto load32 = [&](int row, int i0, float (&v)[32]) { rht_load_x32(L, x_base, it.tok0 + row, off + i0, vec_ok, v); };
+  fht_tile(fbuf, logbs, it.ntok, load32, load1, store1);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -159,104 +188,88 @@ __global__ void __launch_bounds__(1024) rht_in_kernel(const DevLinear* __restric
 // FROM_F32: input is a plain fp32 (batch, m) matrix (the unfused output_rht op).
 // ---------------------------------------------------------------------------------------------
 template <bool FROM_F32>
-__global__ void __launch_bounds__(1024) rht_out_kernel(const DevLinear* __restrict__ layers,
-                                                       const RhtItem* __restrict__ items,
-                                                       const uint8_t* __restrict__ ws,
-                                                       uint8_t* __restrict__ y_base,
-                                                       const float* __restrict__ yrht_in) {
+__global__ void __launch_bounds__(RHT_THREADS) rht_out_kernel(const DevLinear* __restrict__ layers,
+                                                              const RhtItem* __restrict__ items,
+                                                              const uint8_t* __restrict__ ws,
+                                                              uint8_t* __restrict__ y_base,
+                                                              const float* __restrict__ yrht_in) {
   extern __shared__ float fbuf[];
   const RhtItem it = items[blockIdx.x];
   const DevLinear& L = layers[it.layer];
   const int off = L.bm_off[it.block];
   const int logbs = L.bm_log[it.block];
   const int bs = 1 << logbs;
-  const int total = it.ntok << logbs;
   const int rows_per_strip = (L.format == GLQB_FMT_TRELLIS_3INST) ? 32 : 16;
   const int m = L.m, fixed_slots = L.fixed_slots, gps = L.groups_per_strip, per_warp = L.per_warp;
   const long long slot_stride = (long long)L.batch * m;
   const float wscale = L.wscale;
   const float* row_scale = L.row_scale;
-  const bool vec_in = !FROM_F32 && !L.stop_at_yrht && (m & 3) == 0 && bs >= 4;
-  if (vec_in) {
-    // four consecutive rows at a time: they lie in one strip, so they share the slot count
-    const float* part = reinterpret_cast<const float*>(ws + L.part_off);
-    for (int o = threadIdx.x * 4; o < total; o += blockDim.x * 4) {
-      const int tk = o >> logbs, i = o & (bs - 1);
-      const int row = off + i;
-      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (row < m) {
-        int cnt = fixed_slots;
-        if (cnt <= 0) {
-          const long long g0 = L.group_base + (long long)(row / rows_per_strip) * gps;
-          cnt = ((int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1) * L.slot_mult;
-        }
-        const float* p = part + (long long)(it.tok0 + tk) * m + row;
-        for (int k = 0; k < cnt; ++k) {
-          const float4 t = *reinterpret_cast<const float4*>(p + k * slot_stride);
-          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-        }
-        s.x *= wscale; s.y *= wscale; s.z *= wscale; s.w *= wscale;
-        if (row_scale) { s.x *= row_scale[row]; s.y *= row_scale[row + 1]; s.z *= row_scale[row + 2]; s.w *= row_scale[row + 3]; }
-      }
-      *reinterpret_cast<float4*>(fbuf + o) = s;
-    }
-  } else
-  for (int o = threadIdx.x; o < total; o += blockDim.x) {
-    const int tk = o >> logbs, i = o & (bs - 1);
+  const float* part = reinterpret_cast<const float*>(ws + L.part_off);
+  auto slots_of = [&](int row) -> int {
+    if (fixed_slots > 0) return fixed_slots;
+    const long long g0 = L.group_base + (long long)(row / rows_per_strip) * gps;
+    return ((int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1) * L.slot_mult;
+  };
+  auto load1 = [&](int trow, int i) -> float {
     const int row = off + i;
-    const long long token = it.tok0 + tk;
+    const long long token = it.tok0 + trow;
+    if constexpr (FROM_F32) return yrht_in[token * m + row];
+    if (row >= m) return 0.f;
+    const int cnt = slots_of(row);
+    const float* p = part + token * m + row;
     float s = 0.f;
-    if constexpr (FROM_F32) {
-      s = yrht_in[token * L.m + row];
-    } else if (row < L.m) {
-      const int strip = row / rows_per_strip;
-      const long long g0 = L.group_base + (long long)strip * L.groups_per_strip;
-      const int cnt = L.fixed_slots > 0 ? L.fixed_slots
-                                        : ((int)((g0 + L.groups_per_strip - 1) / L.per_warp - g0 / L.per_warp) + 1) *
-                                              L.slot_mult;
-      const float* p = reinterpret_cast<const float*>(ws + L.part_off) + token * L.m + row;
-      const long long slot_stride = (long long)L.batch * L.m;
-      for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];
-      s *= L.wscale;
-      if (L.row_scale) s *= L.row_scale[row];
-    }
-    if (L.stop_at_yrht) {
-      if (row < L.m) reinterpret_cast<float*>(y_base)[L.y_off + token * L.y_stride + row] = s;
-    } else {
-      fbuf[o] = s;
-    }
-  }
-  if (L.stop_at_yrht) return;
-  fht_smem_rows(fbuf, logbs, it.ntok);
-  const float rs = rsqrtf((float)bs);
-  const int out_f = L.out_f, y_dtype = L.y_dtype;
-  if (bs >= 4 && act_rows_aligned4(y_base, L.y_off, L.y_stride, y_dtype)) {
-    for (int o = threadIdx.x * 4; o < total; o += blockDim.x * 4) {
+    for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];
+    s *= wscale;
+    if (row_scale) s *= row_scale[row];
+    return s;
+  };
+  if (L.stop_at_yrht) {            // rotated-domain result wanted: reduce and scale only
+    const int total = it.ntok << logbs;
+    for (int o = threadIdx.x; o < total; o += blockDim.x) {
       const int tk = o >> logbs, i = o & (bs - 1);
-      const int row = off + i;
-      const long long yidx = L.y_off + (long long)(it.tok0 + tk) * L.y_stride + row;
-      const float4 t = *reinterpret_cast<const float4*>(fbuf + o);
-      if (row + 3 < out_f) {
-        const uint2 su4 = *reinterpret_cast<const uint2*>(L.su + row);
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&su4.x));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&su4.y));
-        const float v[4] = {t.x * rs * a.x, t.y * rs * a.y, t.z * rs * b.x, t.w * rs * b.y};
-        store_act4(y_base, yidx, y_dtype, v);
-      } else {
-        const float v[4] = {t.x, t.y, t.z, t.w};
-        for (int k = 0; k < 4; ++k)
-          if (row + k < out_f) store_act(y_base, yidx + k, y_dtype, v[k] * rs * __half2float(L.su[row + k]));
-      }
+      if (off + i < m) reinterpret_cast<float*>(y_base)[L.y_off + (long long)(it.tok0 + tk) * L.y_stride + off + i] = load1(tk, i);
     }
     return;
   }
-  for (int o = threadIdx.x; o < total; o += blockDim.x) {
-    const int tk = o >> logbs, i = o & (bs - 1);
+  const bool vec_ok = (m & 3) == 0 && (off & 3) == 0;
+  auto load32 = [&](int trow, int i0, float (&v)[32]) {
+    const int row0 = off + i0;
+    const long long token = it.tok0 + trow;
+    if (!vec_ok || row0 + 32 > m) {
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = load1(trow, i0 + k);
+      return;
+    }
+    const float* src = FROM_F32 ? (yrht_in + token * m + row0) : (part + token * m + row0);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+      if constexpr (FROM_F32) {
+        s = *reinterpret_cast<const float4*>(src + 4 * j);
+      } else {
+        const int cnt = slots_of(row0 + 4 * j);
+        for (int k = 0; k < cnt; ++k) {
+          const float4 t = *reinterpret_cast<const float4*>(src + 4 * j + k * slot_stride);
+          s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+        }
+        s.x *= wscale; s.y *= wscale; s.z *= wscale; s.w *= wscale;
+        if (row_scale) {
+          const int r = row0 + 4 * j;
+          s.x *= row_scale[r]; s.y *= row_scale[r + 1]; s.z *= row_scale[r + 2]; s.w *= row_scale[r + 3];
+        }
+      }
+      v[4 * j] = s.x; v[4 * j + 1] = s.y; v[4 * j + 2] = s.z; v[4 * j + 3] = s.w;
+    }
+  };
+  const float rs = rsqrtf((float)bs);
+  const int out_f = L.out_f, y_dtype = L.y_dtype;
+  auto store1 = [&](int trow, int i, float val) {
     const int row = off + i;
     if (row < out_f)
-      store_act(y_base, L.y_off + (long long)(it.tok0 + tk) * L.y_stride + row, y_dtype,
-                fbuf[o] * rs * __half2float(L.su[row]));
-  }
+      store_act(y_base, L.y_off + (long long)(it.tok0 + trow) * L.y_stride + row, y_dtype,
+                val * rs * __half2float(L.su[row]));
+  };
+  fht_tile(fbuf, logbs, it.ntok, load32, load1, store1);
 }
 
 // ---------------------------------------------------------------------------------------------
