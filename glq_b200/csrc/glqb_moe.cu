@@ -133,12 +133,86 @@ struct MoeMvArgs {
   int E, m, n, gps, strips, kchunks, gpc, R;
 };
 
+// One pass of a unit: the unit's groups are decoded once and multiplied with up to 8*NB routed tokens
+// starting at t0.  Codes of MOE_PF groups are in flight per lane.
+constexpr int MOE_PF = 4;
+
 template <int K1, int K2, int NB>
-__global__ void __launch_bounds__(MV_THREADS) trellis_moe_mv_kernel(const __grid_constant__ MoeMvArgs A) {
-  const int lane = threadIdx.x & 31;
+__device__ __forceinline__ void moe_unit_pass(const MoeMvArgs& A, const uint8_t* p1, const uint8_t* p2, float s2, int ng,
+                                              int c0, int strip, int kc, int base, int cnt, int t0, int lane) {
   const int gq = lane >> 2, tq = lane & 3;
+  float acc[NB][2][4];
+  float acc2[K2 ? NB : 1][2][4];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { acc[nb][mi][i] = 0.f; if constexpr (K2 > 0) acc2[nb][mi][i] = 0.f; }
+  const uint4* xq[NB];
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb) {
+    const int local = min(t0 + nb * 8 + gq, cnt - 1);     // columns past the count repeat the last token
+    const int row = A.row_map ? A.row_map[base + local] : base + local;
+    xq[nb] = reinterpret_cast<const uint4*>(A.xr + ((long long)row * A.n + c0 * 32) * XR_TRELLIS_EXPAND + tq * 16);
+  }
+  Words<K1> cur[MOE_PF];
+  Words<(K2 > 0 ? K2 : 1)> cur2[MOE_PF];
+#pragma unroll
+  for (int i = 0; i < MOE_PF; ++i)
+    if (i < ng) {
+      cur[i] = load_words<K1>(p1 + i * (128 * K1));
+      if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + i * (128 * K2));
+    }
+  for (int c = 0; c < ng; c += MOE_PF) {
+#pragma unroll
+    for (int i = 0; i < MOE_PF; ++i) {
+      if (c + i < ng) {
+        const Words<K1> v = cur[i];
+        Words<(K2 > 0 ? K2 : 1)> v2;
+        if constexpr (K2 > 0) v2 = cur2[i];
+        if (c + i + MOE_PF < ng) {
+          cur[i] = load_words<K1>(p1 + (long long)(c + i + MOE_PF) * (128 * K1));
+          if constexpr (K2 > 0) cur2[i] = load_words<K2>(p2 + (long long)(c + i + MOE_PF) * (128 * K2));
+        }
+        uint4 xb[NB][2];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+          xb[nb][0] = __ldg(xq[nb] + (c + i) * 8);
+          xb[nb][1] = __ldg(xq[nb] + (c + i) * 8 + 1);
+        }
+        group_mma<K1, NB>(v, lane, xb, acc);
+        if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
+      }
+    }
+  }
+  float* part = A.part + (long long)kc * A.R * A.m;
+#pragma unroll
+  for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int local = t0 + nb * 8 + tq * 2 + (i & 1);
+        const int row = strip * 32 + mi * 16 + gq + ((i >> 1) ? 8 : 0);
+        if (local < cnt) {
+          float v = acc[nb][mi][i];
+          if constexpr (K2 > 0) v = __fadd_rn(v, __fmul_rn(s2, acc2[nb][mi][i]));
+          part[(long long)(base + local) * A.m + row] = v;
+        }
+      }
+}
+
+// NBMAX = largest number of token-column blocks per pass (4 = 32 tokens; 2 with a second stage).  Every unit
+// picks the smallest block count that covers its expert's tokens, so lightly loaded experts do not pay
+// for MMAs on empty columns and heavily loaded ones are decoded once per 8*NBMAX tokens.
+template <int K1, int K2, int NBMAX>
+__global__ void __launch_bounds__(MV_THREADS, 2) trellis_moe_mv_kernel(const __grid_constant__ MoeMvArgs A) {
+  const int lane = threadIdx.x & 31;
   const int units_per_expert = A.strips * A.kchunks;
   const int total_units = A.E * units_per_expert;
+  // Every warp draws one unit at a time from an atomic counter (units of experts without tokens are
+  // skipped at once, so skewed routing does not idle warps).
   for (;;) {
     int u = 0;
     if (lane == 0) u = atomicAdd(A.work, 1);
@@ -148,7 +222,7 @@ __global__ void __launch_bounds__(MV_THREADS) trellis_moe_mv_kernel(const __grid
     const int cnt = A.count[e];
     if (cnt == 0) continue;
     const int rem = u - e * units_per_expert;
-    const int strip = rem / A.kchunks, kc = rem - strip * A.kchunks;
+    const int kc = rem / A.strips, strip = rem - kc * A.strips;
     const int c0 = kc * A.gpc, c1 = min(A.gps, c0 + A.gpc);
     const int base = A.base[e];
     const uint8_t* p1 = A.codes[0] + (long long)e * A.stride[0] + ((long long)strip * A.gps + c0) * (128 * K1) + lane * (4 * K1);
@@ -158,56 +232,13 @@ __global__ void __launch_bounds__(MV_THREADS) trellis_moe_mv_kernel(const __grid
       p2 = A.codes[1] + (long long)e * A.stride[1] + ((long long)strip * A.gps + c0) * (128 * K2) + lane * (4 * K2);
       s2 = A.inv2[e];
     }
-    for (int t0 = 0; t0 < cnt; t0 += 8 * NB) {
-      float acc[NB][2][4];
-      float acc2[K2 ? NB : 1][2][4];
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { acc[nb][mi][i] = 0.f; if constexpr (K2 > 0) acc2[nb][mi][i] = 0.f; }
-      const uint4* xq[NB];
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb) {
-        const int local = min(t0 + nb * 8 + gq, cnt - 1);
-        const int row = A.row_map ? A.row_map[base + local] : base + local;
-        xq[nb] = reinterpret_cast<const uint4*>(A.xr + ((long long)row * A.n + c0 * 32) * XR_TRELLIS_EXPAND + tq * 16);
-      }
-      Words<K1> nxt = load_words<K1>(p1);
-      Words<(K2 > 0 ? K2 : 1)> nxt2;
-      if constexpr (K2 > 0) nxt2 = load_words<K2>(p2);
-      for (int c = c0; c < c1; ++c) {
-        const Words<K1> v = nxt;
-        const Words<(K2 > 0 ? K2 : 1)> v2 = nxt2;
-        if (c + 1 < c1) {
-          nxt = load_words<K1>(p1 + (long long)(c + 1 - c0) * (128 * K1));
-          if constexpr (K2 > 0) nxt2 = load_words<K2>(p2 + (long long)(c + 1 - c0) * (128 * K2));
-        }
-        uint4 xb[NB][2];
-#pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-          xb[nb][0] = __ldg(xq[nb] + (c - c0) * 8);
-          xb[nb][1] = __ldg(xq[nb] + (c - c0) * 8 + 1);
-        }
-        group_mma<K1, NB>(v, lane, xb, acc);
-        if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
-      }
-      float* part = A.part + (long long)kc * A.R * A.m;
-#pragma unroll
-      for (int nb = 0; nb < NB; ++nb)
-#pragma unroll
-        for (int mi = 0; mi < 2; ++mi)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int local = t0 + nb * 8 + tq * 2 + (i & 1);
-            const int row = strip * 32 + mi * 16 + gq + ((i >> 1) ? 8 : 0);
-            if (local < cnt) {
-              float v = acc[nb][mi][i];
-              if constexpr (K2 > 0) v = __fadd_rn(v, __fmul_rn(s2, acc2[nb][mi][i]));
-              part[(long long)(base + local) * A.m + row] = v;
-            }
-          }
+    const int ng = c1 - c0;
+    int t0 = 0;
+    for (; cnt - t0 > 8 * (NBMAX / 2); t0 += 8 * NBMAX)
+      moe_unit_pass<K1, K2, NBMAX>(A, p1, p2, s2, ng, c0, strip, kc, base, cnt, t0, lane);
+    if (cnt - t0 > 0) {
+      if (NBMAX >= 4 && cnt - t0 > 8) moe_unit_pass<K1, K2, (NBMAX >= 4 ? 2 : 1)>(A, p1, p2, s2, ng, c0, strip, kc, base, cnt, t0, lane);
+      else moe_unit_pass<K1, K2, 1>(A, p1, p2, s2, ng, c0, strip, kc, base, cnt, t0, lane);
     }
   }
 }
@@ -393,7 +424,8 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   const int k2a = d->w2_bits, k2b = d->w2_packed2 ? d->w2_bits2 : 0;
   // tokens per decode pass: 16 for small steps, 32 when experts see many tokens
   const double avg = (double)d->max_tokens * d->top_k / d->num_experts;
-  P->nb = (k13b || k2b) ? 2 : (avg > 16.0 ? 4 : 2);
+  (void)avg;
+  P->nb = (k13b || k2b) ? 2 : 4;
   P->k13 = P->nb == 4 ? moe_mv_pick<4>(k13a, k13b) : moe_mv_pick<2>(k13a, k13b);
   P->k2 = P->nb == 4 ? moe_mv_pick<4>(k2a, k2b) : moe_mv_pick<2>(k2a, k2b);
   if (!P->k13 || !P->k2) {
