@@ -133,6 +133,10 @@ WORKLOADS = {
     "decode_e8": ("LLAMA3_8B", "e8", 2, 1, 8, METRIC),
     "prefill_e8": ("LLAMA3_8B", "e8", 2, 2048, 2, "prefill TFLOP/s per layer"),
     "prefill_trellis": ("SMOLLM3_3B", "trellis", (4,), 2048, 4, "prefill TFLOP/s per layer"),
+    # 62-layer dense decoder (hidden 5376, intermediate 21504): E8 stages cycle 2/3/3 per layer (nominal
+    # 4/5/6 bpw; every stage is stored as int16, so the stored rate is 4/6/6 bits per weight)
+    "decode_e8_62l": ("DENSE_62L", "e8", [2, 3, 3], 1, 6, METRIC),
+    "prefill_e8_62l": ("DENSE_62L", "e8", [2, 3, 3], 2048, 3, "prefill TFLOP/s per layer"),
 }
 
 
@@ -161,8 +165,9 @@ def build_workload(name, device, world, rank, tokens=None, n_layers=None):
             if group not in x_of:
                 x_of[group] = x_elems
                 x_elems += T * ns
+            stages = par[li % len(par)] if isinstance(par, list) else par
             L = (synth.trellis_layer(f"L{li}.{pname}", ms, ns, list(par), gen, device) if fmt == "trellis"
-                 else synth.e8_layer(f"L{li}.{pname}", ms, ns, par, table, gen, device))
+                 else synth.e8_layer(f"L{li}.{pname}", ms, ns, stages, table, gen, device))
             if group == "attn_in" and pname != "q":
                 L.sv = layers[-1].sv if pname == "k" else layers[-2].sv      # fused shards share the input signs
             if pname == "up":
