@@ -42,6 +42,7 @@ static inline int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; 
 struct Segment {
   int format, k1, k2, ns, nb;
   int tn;                    // 0: streaming decode kernel; 128 / 256: tensor-core GEMM with that token tile
+  int two_phase = 0;         // E8 GEMM with many tokens: weight tiles decoded once beforehand
   int first, count;          // range in the device table
   long long total_groups;
   int per_warp;
@@ -177,7 +178,25 @@ static GemmKernel gemm_kernel_tn(int tn) {
   return nullptr;
 }
 
+typedef void (*TilesKernel)(const DevLinear*, int, int, uint8_t*);
+static TilesKernel pick_tiles_kernel(int ns) {
+  switch (ns) {
+    case 1: return e8_tiles_kernel<1>;
+    case 2: return e8_tiles_kernel<2>;
+    case 3: return e8_tiles_kernel<3>;
+    case 4: return e8_tiles_kernel<4>;
+  }
+  return nullptr;
+}
+
+// token count from which E8 prefill decodes the weight tiles once instead of once per token tile
+static int e8_two_phase_min_tokens() {
+  const char* e = getenv("GLQB_E8_TWO_PHASE_MIN_TOKENS");
+  return e ? atoi(e) : 512;
+}
+
 static GemmKernel pick_gemm_kernel(const Segment& s) {
+  if (s.two_phase) return gemm_kernel_tn<2, 0, 0>(s.tn);
   if (s.format == GLQB_FMT_TRELLIS_3INST) {
 #define G_CASE(A, B) if (s.k1 == A && s.k2 == B) return gemm_kernel_tn<0, A, B>(s.tn);
     G_CASE(1, 0) G_CASE(2, 0) G_CASE(3, 0) G_CASE(4, 0)
@@ -288,7 +307,7 @@ static int build_plan(GlqbPlan* P) {
   CUDA_TRY(cudaDeviceGetAttribute(&P->sm_count, cudaDevAttrMultiProcessorCount, dev_id));
 
   // ---- segments: layers with the same kernel variant, in caller order inside a segment
-  typedef std::tuple<int, int, int, int, int, int> Key;   // format, k1, k2, ns, nb, tn
+  typedef std::tuple<int, int, int, int, int, int, int> Key;   // format, k1, k2, ns, nb, tn, two-phase
   std::map<Key, std::vector<int>> groups;
   std::vector<Key> key_order;
   for (int i = 0; i < n; ++i) {
@@ -297,9 +316,9 @@ static int build_plan(GlqbPlan* P) {
     const int tn = tn_for_batch(d.batch);
     const int nb = tn ? 0 : nb_for_batch(d.batch);
     if (d.format == GLQB_FMT_TRELLIS_3INST)
-      k = Key(d.format, d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, d.n_stages, nb, tn);
+      k = Key(d.format, d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, d.n_stages, nb, tn, 0);
     else
-      k = Key(d.format, 0, 0, d.n_stages, nb, tn);
+      k = Key(d.format, 0, 0, d.n_stages, nb, tn, (tn && d.batch >= e8_two_phase_min_tokens()) ? 1 : 0);
     if (!groups.count(k)) key_order.push_back(k);
     groups[k].push_back(i);
   }
@@ -308,7 +327,7 @@ static int build_plan(GlqbPlan* P) {
   for (const Key& k : key_order) {
     Segment s;
     s.format = std::get<0>(k); s.k1 = std::get<1>(k); s.k2 = std::get<2>(k);
-    s.ns = std::get<3>(k); s.nb = std::get<4>(k); s.tn = std::get<5>(k);
+    s.ns = std::get<3>(k); s.nb = std::get<4>(k); s.tn = std::get<5>(k); s.two_phase = std::get<6>(k);
     s.item_first = s.item_count = 0;
     s.first = (int)P->order.size();
     s.count = (int)groups[k].size();
@@ -393,6 +412,7 @@ static int build_plan(GlqbPlan* P) {
         L.slot_mult = 1;
         L.gemm_tn = s.tn;
         L.per_warp = 1;
+        L.atile_off = s.two_phase ? -1 : 0;      // -1: allocate below
         for (int mt = 0; mt < m_tiles; ++mt)
           for (int nt = 0; nt < n_tiles; ++nt)
             for (int k = 0; k < ks; ++k)
@@ -521,6 +541,11 @@ static int build_plan(GlqbPlan* P) {
     }
     L.part_off = (long long)ws;
     ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
+    if (L.atile_off < 0) {
+      ws = align_up(ws, 1024);
+      L.atile_off = (long long)ws;
+      ws += (size_t)((L.m + GM_TILE_M - 1) / GM_TILE_M) * ((L.n + GM_TILE_K - 1) / GM_TILE_K) * GM_A_BYTES;
+    }
     add_rht_items(P->items_out, pos, L.nbm, L.bm_log, L.batch, P->max_elems_out);
   }
   P->ws_bytes = ws;
@@ -587,7 +612,9 @@ int64_t glqb_plan_code_bytes(const GlqbPlan* plan) { return plan ? plan->code_by
 int64_t glqb_plan_flops(const GlqbPlan* plan) { return plan ? plan->flops : 0; }
 int32_t glqb_plan_launches(const GlqbPlan* plan) {
   if (!plan) return 0;
-  return (plan->items_in.empty() ? 0 : 1) + (plan->items_in_gemm.empty() ? 0 : 1) + (int)plan->segs.size() + 1;
+  int n = (plan->items_in.empty() ? 0 : 1) + (plan->items_in_gemm.empty() ? 0 : 1) + (int)plan->segs.size() + 1;
+  for (const Segment& s : plan->segs) n += s.two_phase;
+  return n;
 }
 
 int glqb_plan_set_timing(GlqbPlan* plan, int32_t enable) {
@@ -638,6 +665,8 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   }
   for (const Segment& s : P->segs) {
     if (s.tn) {
+      if (s.two_phase)
+        pick_tiles_kernel(s.ns)<<<P->sm_count * 8, 256, 0, stream>>>(P->d_layers, s.first, s.count, ws);
       GemmKernel kern = pick_gemm_kernel(s);
       kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,
                                                                    s.item_count, ws, P->d_status);

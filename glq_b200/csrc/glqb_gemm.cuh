@@ -245,7 +245,9 @@ __device__ __forceinline__ void gemm_store_group(uint32_t a_tile, const uint32_t
 }
 
 // ---- the GEMM kernel -------------------------------------------------------------------------------
-// FORMAT 0: trellis (K1, K2 bits); FORMAT 1: E8 (K1 = number of stages, K2 unused)
+// FORMAT 0: trellis (K1, K2 bits); FORMAT 1: E8 (K1 = number of stages, K2 unused);
+// FORMAT 2: the weight tiles were decoded beforehand (e8_tiles_kernel) and are fetched like the
+//           activation tiles, one bulk copy per stage; the producer warps have nothing to do
 template <int FORMAT, int K1, int K2, int TN, int STAGES>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict__ items, int n_items,
@@ -298,7 +300,9 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
       const GemmItem it = items[item];
       const DevLinear& L = layers[it.layer];
       const int first = it.k_begin + (int)((grp - q0) & 1u);       // this group's first chunk of the item
-      if constexpr (FORMAT == 0) {
+      if constexpr (FORMAT == 2) {
+        (void)first; (void)wl; (void)L;
+      } else if constexpr (FORMAT == 0) {
         const int strip = wl >> 1, cg = wl & 1;
         const int rp = it.m_tile * 4 + strip;
         const int gps = L.groups_per_strip;
@@ -436,7 +440,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         if (!mbar_wait(&acc_empty[a], a_phase ^ 1)) { ok = false; break; }
         tc_fence_after();
         for (int kc = it.k_begin; kc < it.k_end; ++kc) {
-          if (!mbar_wait(&full_a[stage], phase) || !mbar_wait(&full_b[stage], phase)) { ok = false; break; }
+          if ((FORMAT != 2 && !mbar_wait(&full_a[stage], phase)) || !mbar_wait(&full_b[stage], phase)) { ok = false; break; }
           tc_fence_after();
           const uint64_t da = umma_desc_sw128(smem_u32(a_base + stage * GM_A_BYTES));
           const uint64_t db = umma_desc_sw128(smem_u32(b_base + stage * B_BYTES));
@@ -464,7 +468,13 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         const uint8_t* src = ws + L.xr_off + ((size_t)it.n_tile * kchunks) * B_BYTES;
         for (int kc = it.k_begin; kc < it.k_end; ++kc) {
           if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
-          mbar_expect_tx(&full_b[stage], B_BYTES);
+          if constexpr (FORMAT == 2) {
+            mbar_expect_tx(&full_b[stage], B_BYTES + GM_A_BYTES);
+            bulk_g2s(a_base + stage * GM_A_BYTES,
+                     ws + L.atile_off + ((size_t)it.m_tile * kchunks + kc) * GM_A_BYTES, GM_A_BYTES, &full_b[stage]);
+          } else {
+            mbar_expect_tx(&full_b[stage], B_BYTES);
+          }
           bulk_g2s(b_base + stage * B_BYTES, src + (size_t)kc * B_BYTES, B_BYTES, &full_b[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -508,6 +518,65 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
   tc_fence_before();
   __syncthreads();
   if (warp == GM_MMA_WARP) tmem_dealloc(tmem_acc, 2 * TN);
+}
+
+// ---- decode once: E8 indices -> swizzled fp16 weight tiles in global memory ----------------------------
+// For large token counts the fused kernel would decode every weight tile once per token tile; this
+// kernel decodes each 128 x 64 tile ONCE into the exact shared-memory image (K-major, 128-byte swizzle),
+// [m_tile][k_chunk] x 16 KiB, which glq_gemm_kernel<2,...> then fetches with one bulk copy per stage.
+// Thread (row = tid >> 1, half = tid & 1) expands 4 indices; two threads write one full 128-byte line.
+template <int NS>
+__global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restrict__ layers, int first, int count,
+                                                       uint8_t* __restrict__ ws) {
+  const int tid = threadIdx.x, row_l = tid >> 1, hf = tid & 1;
+  for (int li = first; li < first + count; ++li) {
+    const DevLinear& L = layers[li];
+    const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
+    const int m_tiles = (L.m + GM_TILE_M - 1) / GM_TILE_M;
+    const int nidx = L.n >> 3;
+    for (int t = blockIdx.x; t < m_tiles * kchunks; t += gridDim.x) {
+      const int mt = t / kchunks, kc = t - mt * kchunks;
+      const int row = mt * GM_TILE_M + row_l;
+      const bool row_ok = row < L.m;
+      const int i0 = kc * 8 + hf * 4;
+      uint32_t ent[NS][4];
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx;
+        const uint32_t mask = (uint32_t)L.table_entries[s] - 1u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t idx = (row_ok && i0 + k < nidx) ? q[i0 + k] : 0u;
+          ent[s][k] = __ldg(L.table[s] + (idx & mask));
+        }
+      }
+      uint8_t* tile = ws + L.atile_off + (size_t)t * GM_A_BYTES;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        uint4 out = make_uint4(0u, 0u, 0u, 0u);
+        if (row_ok && i0 + k < nidx) {
+          uint32_t h[4];
+          e8_entry_to_half2(ent[0][k], h);
+#pragma unroll
+          for (int s = 1; s < NS; ++s) {
+            uint32_t h2[4];
+            e8_entry_to_half2(ent[s][k], h2);
+            const __half2 sc = __float2half2_rn(L.stage_scale[s]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&h2[j]), sc, *reinterpret_cast<const __half2*>(&h[j]));
+              h[j] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+          }
+          out.x = __byte_perm(h[0], h[1], 0x5410);
+          out.y = __byte_perm(h[2], h[3], 0x5410);
+          out.z = __byte_perm(h[0], h[1], 0x7632);
+          out.w = __byte_perm(h[2], h[3], 0x7632);
+        }
+        *reinterpret_cast<uint4*>(tile + sw128_offset(row_l, (hf * 4 + k) * 8)) = out;
+      }
+    }
+  }
 }
 
 }  // namespace glqb

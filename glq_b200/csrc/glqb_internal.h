@@ -25,6 +25,7 @@ struct DevLinear {
   long long x_stride, y_stride, x_off, y_off;
   long long xr_off;      // workspace bytes: rotated activations, fp16 [batch][n]
   long long part_off;    // workspace bytes: partial sums, fp32 [slots][batch][m]
+  long long atile_off;   // workspace bytes: pre-decoded fp16 weight tiles (two-phase E8 prefill), else unused
   long long group_base;  // first work-group index of this layer inside its launch segment
   int groups_per_strip;  // work groups along one strip of rows
   int strips;            // strips of rows (trellis: 32 rows, E8: 16 rows)

@@ -440,7 +440,7 @@ def test_trellis_gemm_large(ops):
 
 
 @pytest.mark.parametrize("stages", [1, 2, 4])
-@pytest.mark.parametrize("T", [100, 257])
+@pytest.mark.parametrize("T", [100, 257, 600])       # 600 tokens: weight tiles decoded once, then a bulk-copy-fed GEMM
 def test_e8_gemm_vs_oracle(ops, e8_table, e8_cb, stages, T):
     full, small = e8_cb
     rng = np.random.default_rng(stages * 7 + T)
