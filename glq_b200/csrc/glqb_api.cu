@@ -192,7 +192,7 @@ static TilesKernel pick_tiles_kernel(int ns) {
 // token count from which E8 prefill decodes the weight tiles once instead of once per token tile
 static int e8_two_phase_min_tokens() {
   const char* e = getenv("GLQB_E8_TWO_PHASE_MIN_TOKENS");
-  return e ? atoi(e) : 512;
+  return e ? atoi(e) : 257;     // more than one token tile: the fused kernel would decode every tile twice or more
 }
 
 static GemmKernel pick_gemm_kernel(const Segment& s) {

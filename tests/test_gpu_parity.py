@@ -499,3 +499,37 @@ def test_e8_cluster_table_path_matches_oracle_and_global_path(ops, e8_table, e8_
     ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02)
     assert relerr(y_smem.cpu().numpy(), ref) <= TOL
     assert relerr(y_smem.cpu().numpy(), y_glob.cpu().numpy()) <= 1e-5
+
+
+def test_glq_linear_module_matches_oracle(e8_table, e8_cb):
+    """The E8RHTLinear mirror: load reference-named buffers, forward on the GPU, compare with the oracle."""
+    from glq_b200.linear import GLQLinear
+    full, small = e8_cb
+    rng = np.random.default_rng(12)
+    lin = GLQLinear(200, 100, bias=True)                       # power-of-two padded: 256 x 128
+    q1 = rng.integers(0, 65536, size=(128, 32), dtype=np.uint16).view(np.int16)
+    q2 = rng.integers(0, 256, size=(128, 32), dtype=np.uint16).view(np.int16)
+    su, sv = signs(rng, 128), signs(rng, 256)
+    sd = {"Qidxs": torch.from_numpy(q1.copy()), "Qidxs2": torch.from_numpy(q2.copy()), "SU": torch.from_numpy(su),
+          "SV": torch.from_numpy(sv), "Wscale": torch.tensor(0.04), "inv_resid_scale": torch.tensor(0.3),
+          "bias": torch.from_numpy(rng.standard_normal(100).astype(np.float16))}
+    lin.load_state_dict(sd, strict=False)
+    lin = lin.cuda()
+    lin.set_codebook(full, codebook2=small)
+    x = cuda(rng.standard_normal((2, 3, 200)).astype(np.float32))
+    y = lin(x)
+    assert y.shape == (2, 3, 100)
+    W = O.e8_decode_nstage([q1, q2], [e8_table, e8_table[:256]], [np.float32(0.3)])
+    ref = O.linear_forward(x.cpu().numpy().reshape(6, 200), W, su, sv, 0.04, [256], [128], 100) + sd["bias"].float().numpy()
+    assert relerr(y.cpu().numpy().reshape(6, 100), ref) <= TOL
+    assert np.array_equal(lin.dequantize_rotated().cpu().numpy().view(np.uint32), W.view(np.uint32))
+
+    tl = GLQLinear(576, 352, codebook_type="trellis")
+    p1 = rand_packed(rng, 352, 576, 4)
+    tsu, tsv = signs(rng, 352), signs(rng, 576)
+    tl.load_state_dict({"trellis_packed": torch.from_numpy(p1.copy()), "SU": torch.from_numpy(tsu),
+                        "SV": torch.from_numpy(tsv), "Wscale": torch.tensor(0.02)}, strict=False)
+    tl = tl.cuda()
+    xt = cuda(rng.standard_normal((4, 576)).astype(np.float32))
+    Wt = O.trellis_decode_layer(p1, 352, 576, 4).astype(np.float32)
+    assert relerr(tl(xt).cpu().numpy(), O.linear_forward(xt.cpu().numpy(), Wt, tsu, tsv, 0.02)) <= TOL
