@@ -385,10 +385,11 @@ def main():
             config["layers_built"] = args.layers
     plan, x, y = W["plan"], W["x"], W["y"]
     total_code_bytes = W["code_bytes"]
+    total_flops = W.get("flops", 0)
     if world > 1:
-        t = torch.tensor([total_code_bytes], device=device, dtype=torch.int64)
+        t = torch.tensor([total_code_bytes, total_flops], device=device, dtype=torch.int64)
         dist.all_reduce(t)
-        total_code_bytes = int(t.item())
+        total_code_bytes, total_flops = int(t[0].item()), int(t[1].item())
 
     from glq_b200 import tp
 
@@ -477,7 +478,7 @@ def main():
         }
         if generic and "prefill" in args.workload:
             # per-layer TFLOP/s, against the bf16 tensor peak
-            flops_layer = W["flops"] / W["n_layers"]
+            flops_layer = total_flops / W["n_layers"]          # all ranks
             tf = flops_layer / (ms_step / W["n_layers"] * 1e-3) / 1e12
             tf_kernel = W["flops"] / (kern_ms_avg * 1e-3) / 1e12
             try:
@@ -487,7 +488,7 @@ def main():
                 tpeak, tkind = 1590.0, "of fallback"
             line.update({"metric": W["metric"], "value": tf, "unit": "TFLOP/s", "dtype": "f16",
                          "ms_per_layer": ms_step / W["n_layers"]})
-            line["e2e"]["value"] = W["flops"] / W["n_layers"] / (e2e_ms / args.steps / W["n_layers"] * 1e-3) / 1e12
+            line["e2e"]["value"] = flops_layer / (e2e_ms / args.steps / W["n_layers"] * 1e-3) / 1e12
             line["e2e"]["unit"] = "TFLOP/s"
             line["roofline"] = {"bound": "tensor", "kernel": "glq_gemm_kernel", "achieved": tf_kernel, "peak": tpeak,
                                 "peak_kind": tkind, "unit": "TFLOP/s", "frac": tf_kernel / tpeak,
