@@ -48,8 +48,8 @@ struct Segment {
   int per_warp;
   int grid;
   int item_first, item_count;   // GEMM work items (range in the plan's item array)
-  // E8 only: codebook held in shared memory across a 2-CTA cluster
-  bool cluster = false;
+  // E8 only: most of the codebook resident in shared memory (one CTA per SM)
+  bool smem_table = false;
   const uint32_t* big_table = nullptr;
   const uint32_t* small_table = nullptr;
   int small_entries = 0;
@@ -136,33 +136,33 @@ static MvKernel e8_kernel(int ns, int nb) {
   return nullptr;
 }
 
-typedef void (*E8ClusterKernel)(const DevLinear*, int, long long, int, uint8_t*, const uint32_t*, const uint32_t*, int);
+typedef void (*E8SmemKernel)(const DevLinear*, int, long long, int, uint8_t*, const uint32_t*, const uint32_t*, int);
 
 template <int NS>
-static E8ClusterKernel e8_cluster_kernel_nb(int nb) {
+static E8SmemKernel e8_smem_kernel_nb(int nb) {
   switch (nb) {
-    case 1: return e8_mv_cluster_kernel<NS, 1>;
-    case 2: return e8_mv_cluster_kernel<NS, 2>;
-    case 4: if constexpr (NS <= 2) return e8_mv_cluster_kernel<NS, 4>; else return nullptr;
+    case 1: return e8_mv_smem_kernel<NS, 1>;
+    case 2: return e8_mv_smem_kernel<NS, 2>;
+    case 4: if constexpr (NS <= 2) return e8_mv_smem_kernel<NS, 4>; else return nullptr;
   }
   return nullptr;
 }
 
-static E8ClusterKernel pick_e8_cluster_kernel(const Segment& s) {
+static E8SmemKernel pick_e8_smem_kernel(const Segment& s) {
   switch (s.ns) {
-    case 1: return e8_cluster_kernel_nb<1>(s.nb);
-    case 2: return e8_cluster_kernel_nb<2>(s.nb);
-    case 3: return e8_cluster_kernel_nb<3>(s.nb);
-    case 4: return e8_cluster_kernel_nb<4>(s.nb);
+    case 1: return e8_smem_kernel_nb<1>(s.nb);
+    case 2: return e8_smem_kernel_nb<2>(s.nb);
+    case 3: return e8_smem_kernel_nb<3>(s.nb);
+    case 4: return e8_smem_kernel_nb<4>(s.nb);
   }
   return nullptr;
 }
 
-static long long e8_cluster_min_bytes() {
+static long long e8_smem_min_bytes() {
   const char* e = getenv("GLQB_E8_SMEM_MIN_BYTES");
-  // Off unless asked for: on B200 the split-table form measured slower than the L1/L2 gathers (each
-  // CTA of the pair expands every index, and the expansion, not the gather, is the limit).
-  return e ? atoll(e) : (1ll << 62);
+  // Filling the table costs every CTA about 224 KiB of L2 reads per launch (a few microseconds), so small
+  // launches keep the global-memory gathers.
+  return e ? atoll(e) : (48ll << 20);
 }
 
 static MvKernel pick_kernel(const Segment& s) {
@@ -433,9 +433,9 @@ static int build_plan(GlqbPlan* P) {
     ctas_per_sm = std::max(1, std::min(ctas_per_sm, 4));
     long long warps_avail = (long long)P->sm_count * ctas_per_sm * MV_WARPS;
     int warps_per_cta = MV_WARPS;
-    // E8: keep the codebook in shared memory (2-CTA cluster) when the launch is large enough to pay
+    // E8: keep the codebook in shared memory when the launch is large enough to pay
     // for filling it and every stage reads either one shared 65,536-entry table or one small table
-    if (s.format == GLQB_FMT_E8_SHELL && pick_e8_cluster_kernel(s)) {
+    if (s.format == GLQB_FMT_E8_SHELL && s.nb == 1 && pick_e8_smem_kernel(s)) {
       long long bytes = 0;
       bool ok = true;
       const uint32_t* big = nullptr;
@@ -457,27 +457,18 @@ static int build_plan(GlqbPlan* P) {
           }
         }
       }
-      if (ok && big && bytes >= e8_cluster_min_bytes()) {
-        E8ClusterKernel ck = pick_e8_cluster_kernel(s);
+      if (ok && big && bytes >= e8_smem_min_bytes()) {
+        E8SmemKernel ck = pick_e8_smem_kernel(s);
         CUDA_TRY(cudaFuncSetAttribute(ck, cudaFuncAttributeMaxDynamicSharedMemorySize, E8S_SMEM_BYTES));
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof cfg);
-        cfg.gridDim = dim3(2 * P->sm_count, 1, 1);
-        cfg.blockDim = dim3(E8S_THREADS, 1, 1);
-        cfg.dynamicSmemBytes = E8S_SMEM_BYTES;
-        cudaLaunchAttribute at;
-        at.id = cudaLaunchAttributeClusterDimension;
-        at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-        cfg.attrs = &at;
-        cfg.numAttrs = 1;
-        int clusters = 0;
-        if (cudaOccupancyMaxActiveClusters(&clusters, ck, &cfg) == cudaSuccess && clusters > 0) {
-          s.cluster = true;
+        int resident = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, ck, E8S_THREADS, E8S_SMEM_BYTES) == cudaSuccess &&
+            resident > 0) {
+          s.smem_table = true;
           s.big_table = big;
           s.small_table = small ? small : big;
           s.small_entries = small_n;
           warps_per_cta = E8S_THREADS / 32;
-          warps_avail = (long long)clusters * warps_per_cta;     // both CTAs of a cluster walk the same ranges
+          warps_avail = (long long)P->sm_count * warps_per_cta;
         } else {
           cudaGetLastError();
         }
@@ -496,11 +487,10 @@ static int build_plan(GlqbPlan* P) {
     s.per_warp = (int)per_warp;
     const long long used_warps = (total + per_warp - 1) / per_warp;
     s.grid = (int)((used_warps + warps_per_cta - 1) / warps_per_cta);
-    if (s.cluster) s.grid *= 2;
     for (int i = 0; i < s.count; ++i) {
       DevLinear& L = P->dev[s.first + i];
       L.per_warp = s.per_warp;
-      L.slot_mult = s.cluster ? 2 : 1;
+      L.slot_mult = 1;
       L.slots = ((L.groups_per_strip - 1) / s.per_warp + 2) * L.slot_mult;
     }
   }
@@ -534,7 +524,9 @@ static int build_plan(GlqbPlan* P) {
         ws = align_up(ws + n_tiles * kchunks * L.gemm_tn * 128, 256);
         add_rht_items(P->items_in_gemm, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
       } else {
-        ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) *
+        // E8 with several tokens interleaves groups of 8 tokens: round the token count up
+        const size_t xr_tokens = (L.format == GLQB_FMT_E8_SHELL && L.batch > 1) ? (size_t)((L.batch + 7) / 8 * 8) : (size_t)L.batch;
+        ws = align_up(ws + xr_tokens * L.n * sizeof(__half) *
                                (L.format == GLQB_FMT_TRELLIS_3INST ? XR_TRELLIS_EXPAND : 1), 256);
         add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
       }
@@ -670,20 +662,9 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
       GemmKernel kern = pick_gemm_kernel(s);
       kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,
                                                                    s.item_count, ws, P->d_status);
-    } else if (s.cluster) {
-      cudaLaunchConfig_t cfg;
-      memset(&cfg, 0, sizeof cfg);
-      cfg.gridDim = dim3(s.grid, 1, 1);
-      cfg.blockDim = dim3(E8S_THREADS, 1, 1);
-      cfg.dynamicSmemBytes = E8S_SMEM_BYTES;
-      cfg.stream = stream;
-      cudaLaunchAttribute at;
-      at.id = cudaLaunchAttributeClusterDimension;
-      at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
-      cfg.attrs = &at;
-      cfg.numAttrs = 1;
-      CUDA_TRY(cudaLaunchKernelEx(&cfg, pick_e8_cluster_kernel(s), (const DevLinear*)(P->d_layers + s.first), s.count,
-                                  s.total_groups, s.per_warp, ws, s.big_table, s.small_table, s.small_entries));
+    } else if (s.smem_table) {
+      pick_e8_smem_kernel(s)<<<s.grid, E8S_THREADS, E8S_SMEM_BYTES, stream>>>(
+          P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws, s.big_table, s.small_table, s.small_entries);
     } else {
       MvKernel kern = pick_kernel(s);
       kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);

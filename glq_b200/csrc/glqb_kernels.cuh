@@ -97,6 +97,14 @@ __device__ __forceinline__ int xr_pos_trellis(int c) {
 }
 // position of column i (0..7) of an E8 block: (x0,x4,x1,x5,x2,x6,x3,x7)
 __device__ __forceinline__ int xr_pos_e8(int i) { return (i & 3) * 2 + (i >> 2); }
+// E8 activations for the streaming kernel.  One token: 8-column blocks in order.  Several tokens: the
+// blocks of 8 consecutive tokens are interleaved (token group, block, token in group, 8 halfs), so that
+// the 8 tokens a warp multiplies against one block sit in one 128-byte line instead of eight.
+__device__ __forceinline__ long long xr_index_e8(long long token, int col, int n, int batch) {
+  const int j = xr_pos_e8(col & 7);
+  if (batch == 1) return (col & ~7) + j;
+  return ((((token >> 3) * (n >> 3) + (col >> 3)) << 3) + (token & 7)) * 8 + j;
+}
 
 // ---------------------------------------------------------------------------------------------
 // Input transform:  xr = fp16( H_blocks( SV * pad(x) ) / sqrt(bs) ), written in the layout the
@@ -162,7 +170,7 @@ __global__ void __launch_bounds__(RHT_THREADS) rht_in_kernel(const DevLinear* __
       (reinterpret_cast<__half2*>(ws + L.xr_off) + token * L.n)[pos >> 1] =
           __halves2half2(__float2half_rn(v), __float2half_rn(0.f));
     } else {
-      (reinterpret_cast<__half*>(ws + L.xr_off) + token * L.n)[(col & ~7) + xr_pos_e8(col & 7)] = __float2half_rn(v);
+      reinterpret_cast<__half*>(ws + L.xr_off)[xr_index_e8(token, col, L.n, L.batch)] = __float2half_rn(v);
     }
   };
   auto load1 = [&](int row, int i) -> float {
@@ -498,44 +506,55 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
 // fp16); stages are combined in fp32 when a strip is flushed.
 // ---------------------------------------------------------------------------------------------
 // Where the codebook entries come from.  TM = 0: the packed tables stay in global memory (L1/L2
-// gathers).  TM = 1: the 65,536-entry table lives in shared memory, split over the two CTAs of a
-// thread-block cluster (128 KiB each).  Both CTAs of a cluster walk the SAME index stream (the second
-// read is an L2 hit) and each expands only the indices whose entry it holds; every other index is
-// replaced by a zero entry, so it contributes nothing.  The two CTAs write separate partial sums
-// (slot 2k + rank) which the output transform adds in fixed order.  All gathers are plain local
-// shared-memory loads.  Tables of up to 256 entries (the small second-stage codebook) are held by
-// CTA 0 alone.
+// gathers).  TM = 1: the first E8S_RESIDENT entries of the 65,536-entry table live in the CTA's shared
+// memory (one CTA per SM) and are fetched with plain shared loads, bank conflicts and all; the few
+// indices past the resident part still go to global memory.  Tables of up to 256 entries (the small
+// second-stage codebook) are fully resident.
+constexpr int E8S_RESIDENT = 56 * 1024;
 struct E8Tables {
-  uint32_t table_base;     // shared-window address of this CTA's half of the big table
-  uint32_t small_base;     // shared-window address of the small table (rank 0) 
-  uint32_t zero_addr;      // shared-window address of a zero entry
-  uint32_t rank;           // CTA rank inside the cluster
+  uint32_t table_base;     // shared-window address of the resident part of the big table
+  uint32_t small_base;     // shared-window address of the small table
 };
 
+// One stage's gather parameters, fixed per layer.
+struct E8Stage {
+  const uint32_t* table;   // global table
+  uint32_t mask;           // entries - 1
+  uint32_t base;           // TM = 1: shared-window address of the resident copy this stage indexes
+};
+
+// The gathers are volatile so that they keep their place ahead of the (volatile) MMAs of the chunk being
+// consumed: that ordering is what keeps a whole chunk of gathers in flight.
 template <int TM>
-__device__ __forceinline__ uint32_t e8_gather(const DevLinear& L, int s, uint32_t idx, const E8Tables& T) {
+__device__ __forceinline__ uint32_t e8_gather(const E8Stage& S, uint32_t idx) {
+  uint32_t v;
+  const uint32_t* gp = S.table + idx;
   if constexpr (TM == 0) {
-    return __ldg(L.table[s] + (idx & ((uint32_t)L.table_entries[s] - 1u)));
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(gp));
   } else {
-    uint32_t addr;
-    if (L.table_entries[s] == 65536) {
-      addr = ((idx >> 15) == T.rank) ? T.table_base + ((idx & 0x7FFFu) << 2) : T.zero_addr;
-    } else {
-      addr = (T.rank == 0) ? T.small_base + ((idx & ((uint32_t)L.table_entries[s] - 1u)) << 2) : T.zero_addr;
-    }
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
+    // branch-free: lanes whose index is resident read shared memory, the others global memory
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ge.u32 p, %1, %2;\n\t"
+                 "@!p ld.shared.u32 %0, [%3];\n\t"
+                 "@p ld.global.nc.u32 %0, [%4];\n\t}"
+                 : "=r"(v)
+                 : "r"(idx), "r"((uint32_t)E8S_RESIDENT), "r"(S.base + (idx << 2)), "l"(gp));
   }
+  return v;
 }
 
+#ifndef GLQB_E8_KC
+#define GLQB_E8_KC 8
+#endif
+#ifndef GLQB_E8_MINB
+#define GLQB_E8_MINB 2
+#endif
 template <int NS, int NB, int TM>
 __device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
                                            int per_warp, uint8_t* __restrict__ ws, const E8Tables& T,
                                            int warps_per_cta) {
   const int lane = threadIdx.x & 31;
-  // TM = 1: the two CTAs of a cluster share one warp numbering (they walk the same ranges)
-  const long long w = (long long)(TM == 1 ? (blockIdx.x >> 1) : blockIdx.x) * warps_per_cta + (threadIdx.x >> 5);
+  const long long w = (long long)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
   long long g = w * per_warp;
   const long long gend = min(g + per_warp, total_groups);
   if (g >= gend) return;
@@ -570,24 +589,36 @@ __device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers,
 
     const __half* xr = reinterpret_cast<const __half*>(ws + L.xr_off);
 
-    // indices of one group: 8 per row and stage, packed two per word; requested one group ahead so
-    // that the HBM latency of the index stream overlaps the gathers and MMAs of the current group
-    auto load_indices = [&](int c, uint32_t (&qa)[NS][4], uint32_t (&qb)[NS][4]) {
-      const int i0 = c * 32 + tq * 8;
+    // Software pipeline over chunks of KC index pairs (a group is 8 / KC chunks).  While chunk cc is
+    // expanded and multiplied, the codebook gathers of chunk cc+1 are in flight (KC * 2 * NS per lane)
+    // and the index words of chunk cc+2 are on their way from HBM, so neither latency is exposed.
+    constexpr int KC = (NS <= 2 && NB <= 2) ? GLQB_E8_KC : 4;
+    constexpr int CPG = 8 / KC;
+    constexpr int W = KC / 2;
+    auto load_indices = [&](int cc, uint32_t (&qa)[NS][W], uint32_t (&qb)[NS][W]) {
+      const int i0 = (cc / CPG) * 32 + tq * 8 + (cc % CPG) * KC;
 #pragma unroll
       for (int s = 0; s < NS; ++s) {
         const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]);
         const uint16_t* pa = q + (long long)rowA * nidx + i0;
         const uint16_t* pb = q + (long long)rowB * nidx + i0;
-        if (vec_ok && i0 + 8 <= nidx) {
-          uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
-          if (okA) va = ld_stream_v4(pa);
-          if (okB) vb = ld_stream_v4(pb);
-          qa[s][0] = va.x; qa[s][1] = va.y; qa[s][2] = va.z; qa[s][3] = va.w;
-          qb[s][0] = vb.x; qb[s][1] = vb.y; qb[s][2] = vb.z; qb[s][3] = vb.w;
+        if (vec_ok && i0 + KC <= nidx) {
+          if constexpr (KC == 8) {
+            uint4 va = make_uint4(0, 0, 0, 0), vb = make_uint4(0, 0, 0, 0);
+            if (okA) va = ld_stream_v4(pa);
+            if (okB) vb = ld_stream_v4(pb);
+            qa[s][0] = va.x; qa[s][1] = va.y; qa[s][2] = va.z; qa[s][3] = va.w;
+            qb[s][0] = vb.x; qb[s][1] = vb.y; qb[s][2] = vb.z; qb[s][3] = vb.w;
+          } else {
+            uint2 va = make_uint2(0, 0), vb = make_uint2(0, 0);
+            if (okA) va = ld_stream_v2(pa);
+            if (okB) vb = ld_stream_v2(pb);
+            qa[s][0] = va.x; qa[s][1] = va.y;
+            qb[s][0] = vb.x; qb[s][1] = vb.y;
+          }
         } else {
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
+          for (int k = 0; k < W; ++k) {
             uint32_t a0 = 0, a1 = 0, b0 = 0, b1 = 0;
             if (i0 + 2 * k < nidx) { if (okA) a0 = pa[2 * k]; if (okB) b0 = pb[2 * k]; }
             if (i0 + 2 * k + 1 < nidx) { if (okA) a1 = pa[2 * k + 1]; if (okB) b1 = pb[2 * k + 1]; }
@@ -597,40 +628,47 @@ __device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers,
         }
       }
     };
-    uint32_t nqa[NS][4], nqb[NS][4];
-    load_indices(c0, nqa, nqb);
-    // columns past the batch read the last token again (their accumulator columns are never stored)
-    const __half* xrow[NB];
+    E8Stage stg[NS];
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) xrow[nb] = xr + (long long)min(nb * 8 + gq, batch - 1) * L.n;
-
-    for (int c = c0; c < c1; ++c) {
-      const int i0 = c * 32 + tq * 8;          // first index (8-column block) of this lane
-      uint32_t qa[NS][4], qb[NS][4];
+    for (int s = 0; s < NS; ++s) {
+      stg[s].table = L.table[s];
+      stg[s].mask = (uint32_t)L.table_entries[s] - 1u;
+      stg[s].base = L.table_entries[s] == 65536 ? T.table_base : T.small_base;
+    }
+    auto gather = [&](const uint32_t (&qa)[NS][W], const uint32_t (&qb)[NS][W], uint32_t (&ea)[NS][KC],
+                      uint32_t (&eb)[NS][KC]) {
 #pragma unroll
       for (int s = 0; s < NS; ++s)
 #pragma unroll
-        for (int k = 0; k < 4; ++k) { qa[s][k] = nqa[s][k]; qb[s][k] = nqb[s][k]; }
-      if (c + 1 < c1) load_indices(c + 1, nqa, nqb);
-      // ---- 8 index pairs
+        for (int k = 0; k < KC; ++k) {
+          ea[s][k] = e8_gather<TM>(stg[s], (qa[s][k >> 1] >> ((k & 1) * 16)) & stg[s].mask);
+          eb[s][k] = e8_gather<TM>(stg[s], (qb[s][k >> 1] >> ((k & 1) * 16)) & stg[s].mask);
+        }
+    };
+    // columns past the batch read the last token again (their accumulator columns are never stored)
+    const uint4* xrow[NB];
+    const int xstep = batch == 1 ? 1 : 8;      // 16-byte units between consecutive 8-column blocks
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
+    for (int nb = 0; nb < NB; ++nb) {
+      const int tok = min(nb * 8 + gq, batch - 1);
+      xrow[nb] = reinterpret_cast<const uint4*>(xr) + (batch == 1 ? 0 : (long long)(tok >> 3) * nidx * 8 + (tok & 7));
+    }
+    auto consume = [&](int cc, const uint32_t (&ea)[NS][KC], const uint32_t (&eb)[NS][KC]) {
+      const int i0 = (cc / CPG) * 32 + tq * 8 + (cc % CPG) * KC;   // first index (8-column block) of this lane
+#pragma unroll
+      for (int k = 0; k < KC; ++k) {
         const int blk = min(i0 + k, nidx - 1);
         uint4 xb[NB];
 #pragma unroll
         for (int nb = 0; nb < NB; ++nb) {
-          xb[nb] = __ldg(reinterpret_cast<const uint4*>(xrow[nb]) + blk);
+          xb[nb] = __ldg(xrow[nb] + blk * xstep);
           if (i0 + k >= nidx) xb[nb] = make_uint4(0u, 0u, 0u, 0u);   // past the row end: contributes nothing
         }
 #pragma unroll
         for (int s = 0; s < NS; ++s) {
-          const uint32_t ia = (qa[s][k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
-          const uint32_t ib = (qb[s][k >> 1] >> ((k & 1) * 16)) & 0xFFFFu;
-          const uint32_t ea = e8_gather<TM>(L, s, ia, T);
-          const uint32_t eb = e8_gather<TM>(L, s, ib, T);
           uint32_t ha[4], hb[4];
-          e8_entry_to_half2(ea, ha);
-          e8_entry_to_half2(eb, hb);
+          e8_entry_to_half2(ea[s][k], ha);
+          e8_entry_to_half2(eb[s][k], hb);
           const uint32_t a1[4] = {ha[0], hb[0], ha[1], hb[1]};
           const uint32_t a2[4] = {ha[2], hb[2], ha[3], hb[3]};
 #pragma unroll
@@ -640,11 +678,32 @@ __device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers,
           }
         }
       }
+    };
+
+    const int cc0 = c0 * CPG, cc1 = c1 * CPG;
+    uint32_t qa[NS][W], qb[NS][W];
+    uint32_t eA[NS][KC], eB[NS][KC], fA[NS][KC], fB[NS][KC];
+    load_indices(cc0, qa, qb);
+    gather(qa, qb, eA, eB);
+    if (cc0 + 1 < cc1) load_indices(cc0 + 1, qa, qb);
+    for (int cc = cc0; cc < cc1; cc += 2) {
+      if (cc + 1 < cc1) {
+        gather(qa, qb, fA, fB);
+        if (cc + 2 < cc1) load_indices(cc + 2, qa, qb);
+      }
+      consume(cc, eA, eB);
+      if (cc + 1 < cc1) {
+        if (cc + 2 < cc1) {
+          gather(qa, qb, eA, eB);
+          if (cc + 3 < cc1) load_indices(cc + 3, qa, qb);
+        }
+        consume(cc + 1, fA, fB);
+      }
     }
 
     {
       const long long g0 = L.group_base + (long long)strip * gps;
-      const int slot = (TM == 1) ? 2 * (int)(w - g0 / per_warp) + (int)T.rank : (int)(w - g0 / per_warp);
+      const int slot = (int)(w - g0 / per_warp);
       float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)slot * batch * L.m;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
@@ -667,41 +726,34 @@ __device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers,
 }
 
 template <int NS, int NB>
-__global__ void __launch_bounds__(MV_THREADS)
+__global__ void __launch_bounds__(MV_THREADS, (NB <= 2 ? GLQB_E8_MINB : 1))
 e8_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
              int per_warp, uint8_t* __restrict__ ws) {
-  const E8Tables T = {0u, 0u, 0u, 0u};
+  const E8Tables T = {0u, 0u};
   e8_mv_body<NS, NB, 0>(layers, n_layers, total_groups, per_warp, ws, T, MV_WARPS);
 }
 
-// Cluster form: each of the two CTAs holds half of the 65,536-entry table in its shared memory.
-constexpr int E8S_THREADS = 512;
-constexpr int E8S_SMEM_BYTES = 32768 * 4 + 256 * 4 + 16;
-
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
+// Resident-table form: one CTA per SM keeps most of the 65,536-entry table in shared memory.
+#ifndef GLQB_E8S_THREADS
+#define GLQB_E8S_THREADS 384
+#endif
+constexpr int E8S_THREADS = GLQB_E8S_THREADS;
+constexpr int E8S_SMEM_BYTES = E8S_RESIDENT * 4 + 256 * 4;
 
 template <int NS, int NB>
 __global__ void __launch_bounds__(E8S_THREADS, 1)
-e8_mv_cluster_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups, int per_warp,
-                     uint8_t* __restrict__ ws, const uint32_t* __restrict__ big_table,
-                     const uint32_t* __restrict__ small_table, int small_entries) {
+e8_mv_smem_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups, int per_warp,
+                  uint8_t* __restrict__ ws, const uint32_t* __restrict__ big_table,
+                  const uint32_t* __restrict__ small_table, int small_entries) {
   extern __shared__ __align__(16) uint32_t e8_smem[];
-  uint32_t rank;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-  const uint4* src = reinterpret_cast<const uint4*>(big_table + (size_t)rank * 32768);
+  const uint4* src = reinterpret_cast<const uint4*>(big_table);
   uint4* dst = reinterpret_cast<uint4*>(e8_smem);
-  for (int i = threadIdx.x; i < 32768 / 4; i += blockDim.x) dst[i] = __ldg(src + i);
-  for (int i = threadIdx.x; i < small_entries && i < 256; i += blockDim.x) e8_smem[32768 + i] = __ldg(small_table + i);
-  if (threadIdx.x == 0) e8_smem[32768 + 256] = 0x66666666u;   // nibble 6 = coordinate 0: the zero entry
+  for (int i = threadIdx.x; i < E8S_RESIDENT / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+  for (int i = threadIdx.x; i < small_entries && i < 256; i += blockDim.x) e8_smem[E8S_RESIDENT + i] = __ldg(small_table + i);
   E8Tables T;
   const uint32_t local = (uint32_t)__cvta_generic_to_shared(e8_smem);
   T.table_base = local;
-  T.small_base = local + 32768 * 4;
-  T.zero_addr = local + (32768 + 256) * 4;
-  T.rank = rank;
+  T.small_base = local + E8S_RESIDENT * 4;
   __syncthreads();
   e8_mv_body<NS, NB, 1>(layers, n_layers, total_groups, per_warp, ws, T, E8S_THREADS / 32);
 }
