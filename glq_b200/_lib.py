@@ -25,7 +25,7 @@ EXPORTS = [
     "glqb_output_rht", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
     "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
     "glqb_moe_plan_create", "glqb_moe_plan_workspace_bytes", "glqb_moe_plan_code_bytes", "glqb_moe_plan_run",
-    "glqb_moe_plan_destroy",
+    "glqb_moe_plan_status", "glqb_moe_plan_destroy",
 ]
 
 
@@ -135,6 +135,8 @@ def load() -> C.CDLL:
     lib.glqb_moe_plan_code_bytes.restype = i64
     lib.glqb_moe_plan_run.argtypes = [vp, vp, vp, vp, vp, i32, vp, sz, vp]
     lib.glqb_moe_plan_run.restype = C.c_int
+    lib.glqb_moe_plan_status.argtypes = [vp, vp, vp]
+    lib.glqb_moe_plan_status.restype = C.c_int
     lib.glqb_moe_plan_destroy.argtypes = [vp]
     lib.glqb_moe_plan_destroy.restype = None
     lib.glqb_last_error.argtypes = []

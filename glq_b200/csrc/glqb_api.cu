@@ -169,7 +169,7 @@ static MvKernel pick_kernel(const Segment& s) {
   return s.format == GLQB_FMT_TRELLIS_3INST ? trellis_kernel(s.k1, s.k2, s.nb) : e8_kernel(s.ns, s.nb);
 }
 
-typedef void (*GemmKernel)(const DevLinear*, const GemmItem*, int, uint8_t*, int*);
+typedef void (*GemmKernel)(const DevLinear*, const GemmItem*, int, uint8_t*, int*, const int*);
 
 template <int FORMAT, int K1, int K2>
 static GemmKernel gemm_kernel_tn(int tn) {
@@ -661,7 +661,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
         pick_tiles_kernel(s.ns)<<<P->sm_count * 8, 256, 0, stream>>>(P->d_layers, s.first, s.count, ws);
       GemmKernel kern = pick_gemm_kernel(s);
       kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,
-                                                                   s.item_count, ws, P->d_status);
+                                                                   s.item_count, ws, P->d_status, nullptr);
     } else if (s.smem_table) {
       pick_e8_smem_kernel(s)<<<s.grid, E8S_THREADS, E8S_SMEM_BYTES, stream>>>(
           P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws, s.big_table, s.small_table, s.small_entries);

@@ -138,7 +138,7 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int e) {
 // One CTA per (layer, Hadamard block, tile of tokens); tiles ordered [n_tile][k_chunk], each TN*128
 // bytes.  Columns past n (the last chunk of a layer whose n is not a multiple of 64) are written as
 // zeros by the CTAs of the last block.
-__global__ void __launch_bounds__(RHT_THREADS) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
+static __global__ void __launch_bounds__(RHT_THREADS) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
                                                                   const RhtItem* __restrict__ items,
                                                                   const uint8_t* __restrict__ x_base,
                                                                   uint8_t* __restrict__ ws) {
@@ -251,7 +251,9 @@ __device__ __forceinline__ void gemm_store_group(uint32_t a_tile, const uint32_t
 template <int FORMAT, int K1, int K2, int TN, int STAGES>
 __global__ void __launch_bounds__(GM_THREADS, 1)
 glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict__ items, int n_items,
-                uint8_t* __restrict__ ws, int* __restrict__ status) {
+                uint8_t* __restrict__ ws, int* __restrict__ status, const int* __restrict__ n_items_dev) {
+  // work lists built on the device (grouped expert matmul) pass their length through memory
+  if (n_items_dev) n_items = min(n_items, *n_items_dev);
   constexpr int B_BYTES = TN * 128;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);

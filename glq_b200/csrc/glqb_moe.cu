@@ -16,6 +16,12 @@
 // partial-sum slot of a unit is its K-chunk number, so results do not depend on which warp ran it.
 // Integer atomics decide only WHERE a routing is stored, never a numeric value: outputs are
 // bit-identical run to run.
+//
+// Steps with many routed tokens per expert take the tensor-core form instead: launches 3 and 5 become the
+// tcgen05 GEMM kernel (glq_gemm_kernel, trellis producers) over a work list that a setup kernel builds on
+// the device from the expert counts — every expert is a "layer" whose token count, activation tiles and
+// partial-sum rows are patched in each run; experts' routings are padded to whole 128-token tiles.  The
+// transforms write the activations straight into the swizzled tile images the GEMM's bulk copies fetch.
 #include <algorithm>
 #include <cstdarg>
 #include <cstdio>
@@ -23,6 +29,7 @@
 #include <vector>
 
 #include "glqb_kernels.cuh"
+#include "glqb_gemm.cuh"
 
 namespace glqb {
 
@@ -45,7 +52,13 @@ struct MoeDev {
   int kch13, gpc13, kch2, gpc2;
   // workspace offsets (bytes)
   long long o_count, o_base, o_cursor, o_work, o_route_tok, o_route_exp, o_slot_of, o_xr1, o_part1, o_xr2, o_part2;
+  // tensor-core form (gemm != 0): tile rows, device-built layer tables and work lists
+  int gemm, k13a, k13b, k2a, k2b, max_items13, max_items2;
+  long long o_trow, o_tile0, o_layers13, o_layers2, o_items13, o_items2, o_nitems, o_status;
 };
+
+constexpr int MOE_TN = 128;                    // routed tokens per GEMM tile
+constexpr int MOE_B_BYTES = MOE_TN * 128;      // one 64-column chunk of a token tile
 
 __device__ __forceinline__ float moe_act(float g, int act) {
   if (act == GLQB_ACT_SILU || act == 3) return g / (1.0f + __expf(-g));
@@ -78,9 +91,13 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
     long long v = M.ids_i64 ? reinterpret_cast<const long long*>(ids)[i] : (long long)reinterpret_cast<const int*>(ids)[i];
     return (v < 0 || v >= M.E) ? -1 : (int)v;
   };
-  for (int i = threadIdx.x; i < R; i += blockDim.x) {
-    const int e = expert_of(i);
-    if (e >= 0) atomicAdd(&cnt[e], 1);
+  // 8 routings per thread and round: the id loads of a round are issued together
+  for (int i0 = threadIdx.x; i0 < R; i0 += 8 * blockDim.x) {
+    int ev[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { const int i = i0 + u * blockDim.x; ev[u] = i < R ? expert_of(i) : -1; }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) if (ev[u] >= 0) atomicAdd(&cnt[ev[u]], 1);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -88,15 +105,23 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
     for (int e = 0; e < M.E; ++e) { cur[e] = run; g_base[e] = run; g_count[e] = cnt[e]; run += cnt[e]; }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < R; i += blockDim.x) {
-    const int e = expert_of(i);
-    int slot = -1;
-    if (e >= 0) {
-      slot = atomicAdd(&cur[e], 1);
-      route_tok[slot] = i / M.top_k;
-      route_exp[slot] = e;
+  for (int i0 = threadIdx.x; i0 < R; i0 += 8 * blockDim.x) {
+    int ev[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) { const int i = i0 + u * blockDim.x; ev[u] = i < R ? expert_of(i) : -1; }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = i0 + u * blockDim.x;
+      if (i < R) {
+        int slot = -1;
+        if (ev[u] >= 0) {
+          slot = atomicAdd(&cur[ev[u]], 1);
+          route_tok[slot] = i / M.top_k;
+          route_exp[slot] = ev[u];
+        }
+        slot_of[i] = slot;
+      }
     }
-    slot_of[i] = slot;
   }
 }
 
@@ -115,6 +140,113 @@ __global__ void __launch_bounds__(1024) moe_rht_in_kernel(const __grid_constant_
       const int col = M.off_n13[b] + i;
       const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);
       out[pos >> 1] = __halves2half2(__float2half_rn(fb[col] * rs), __float2half_rn(0.f));
+    }
+  }
+}
+
+// ---- tensor-core form: tile rows, per-expert layer entries and work lists, built on the device -------------
+// One CTA.  Expert e with c routings owns ceil(c / 128) token tiles; routing number i of the expert sits in
+// row (tile0[e] * 128 + i) of the padded row space.  Items are ordered (expert, token tile, row tile) so that
+// the CTAs working at one moment share an activation tile through L2.
+__global__ void __launch_bounds__(1024) moe_gemm_setup_kernel(const __grid_constant__ MoeDev M, int T,
+                                                              uint8_t* __restrict__ ws) {
+  __shared__ int s_tile0[4097];
+  const int* g_count = reinterpret_cast<const int*>(ws + M.o_count);
+  const int* g_base = reinterpret_cast<const int*>(ws + M.o_base);
+  const int* route_exp = reinterpret_cast<const int*>(ws + M.o_route_exp);
+  int* trow = reinterpret_cast<int*>(ws + M.o_trow);
+  int* nitems = reinterpret_cast<int*>(ws + M.o_nitems);
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) s_tile0[e + 1] = (g_count[e] + MOE_TN - 1) / MOE_TN;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < M.E; ++e) { const int nt = s_tile0[e + 1]; s_tile0[e] = run; run += nt; }
+    s_tile0[M.E] = run;
+    const int mt13 = (M.w13_out + GM_TILE_M - 1) / GM_TILE_M, mt2 = (M.hidden + GM_TILE_M - 1) / GM_TILE_M;
+    nitems[0] = min(run * mt13, M.max_items13);
+    nitems[1] = min(run * mt2, M.max_items2);
+    reinterpret_cast<int*>(ws + M.o_status)[0] = 0;
+  }
+  __syncthreads();
+  const int used = g_base[M.E - 1] + g_count[M.E - 1];
+  for (int slot = threadIdx.x; slot < used; slot += blockDim.x) {
+    const int e = route_exp[slot];
+    trow[slot] = s_tile0[e] * MOE_TN + (slot - g_base[e]);
+  }
+  const int kc13 = M.hidden / GM_TILE_K, kc2 = M.inter / GM_TILE_K;
+  DevLinear* L13 = reinterpret_cast<DevLinear*>(ws + M.o_layers13);
+  DevLinear* L2 = reinterpret_cast<DevLinear*>(ws + M.o_layers2);
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) {
+    DevLinear a;
+    memset(&a, 0, sizeof a);
+    a.format = GLQB_FMT_TRELLIS_3INST;
+    a.batch = g_count[e];
+    DevLinear b = a;
+    a.codes[0] = M.w13[0] + (long long)e * M.w13_stride[0];
+    a.codes[1] = M.w13[1] ? M.w13[1] + (long long)e * M.w13_stride[1] : nullptr;
+    a.stage_scale[0] = 1.f; a.stage_scale[1] = M.w13_inv2 ? M.w13_inv2[e] : 0.f;
+    a.m = M.w13_out; a.n = M.hidden; a.strips = M.w13_out / 32; a.groups_per_strip = M.hidden / 32;
+    a.xr_off = M.o_xr1 + (long long)s_tile0[e] * kc13 * MOE_B_BYTES;
+    a.part_off = M.o_part1 + (long long)g_base[e] * M.w13_out * 4;
+    b.codes[0] = M.w2[0] + (long long)e * M.w2_stride[0];
+    b.codes[1] = M.w2[1] ? M.w2[1] + (long long)e * M.w2_stride[1] : nullptr;
+    b.stage_scale[0] = 1.f; b.stage_scale[1] = M.w2_inv2 ? M.w2_inv2[e] : 0.f;
+    b.m = M.hidden; b.n = M.inter; b.strips = M.hidden / 32; b.groups_per_strip = M.inter / 32;
+    b.xr_off = M.o_xr2 + (long long)s_tile0[e] * kc2 * MOE_B_BYTES;
+    b.part_off = M.o_part2 + (long long)g_base[e] * M.hidden * 4;
+    L13[e] = a;
+    L2[e] = b;
+  }
+  GemmItem* I13 = reinterpret_cast<GemmItem*>(ws + M.o_items13);
+  GemmItem* I2 = reinterpret_cast<GemmItem*>(ws + M.o_items2);
+  const int mt13 = (M.w13_out + GM_TILE_M - 1) / GM_TILE_M, mt2 = (M.hidden + GM_TILE_M - 1) / GM_TILE_M;
+  for (int e = 0; e < M.E; ++e) {
+    const int nt = s_tile0[e + 1] - s_tile0[e];
+    for (int i = threadIdx.x; i < nt * mt13; i += blockDim.x) {
+      const int idx = s_tile0[e] * mt13 + i;
+      if (idx < M.max_items13) I13[idx] = GemmItem{e, i % mt13, i / mt13, 0, kc13, 0};
+    }
+    for (int i = threadIdx.x; i < nt * mt2; i += blockDim.x) {
+      const int idx = s_tile0[e] * mt2 + i;
+      if (idx < M.max_items2) I2[idx] = GemmItem{e, i % mt2, i / mt2, 0, kc2, 0};
+    }
+  }
+}
+
+// 16 bytes (8 consecutive columns starting at col8 * 8) of padded row `trow` in a [tile][chunk] x (128 x 64) image
+__device__ __forceinline__ void moe_store_tile16(uint8_t* base, int trow, int kchunks, int col8, uint4 v) {
+  const int tile = trow / MOE_TN, r = trow % MOE_TN;
+  const int kc = col8 >> 3, e0 = (col8 & 7) * 8;
+  *reinterpret_cast<uint4*>(base + ((size_t)tile * kchunks + kc) * MOE_B_BYTES + sw128_offset(r, e0)) = v;
+}
+
+__device__ __forceinline__ uint4 pack8_half(const float* f, float rs) {
+  __half2 h0 = __floats2half2_rn(f[0] * rs, f[1] * rs), h1 = __floats2half2_rn(f[2] * rs, f[3] * rs);
+  __half2 h2 = __floats2half2_rn(f[4] * rs, f[5] * rs), h3 = __floats2half2_rn(f[6] * rs, f[7] * rs);
+  return make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                    *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+}
+
+// Input transform of one token, stored once per routing into the token tiles of the routed experts.
+__global__ void __launch_bounds__(1024) moe_rht_in_gemm_kernel(const __grid_constant__ MoeDev M, const uint8_t* __restrict__ x,
+                                                               uint8_t* __restrict__ ws) {
+  extern __shared__ float fb[];
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < M.hidden; i += blockDim.x)
+    fb[i] = load_act(x, (long long)t * M.hidden + i, M.x_dtype) * __half2float(M.w13_sv[i]);
+  for (int b = 0; b < M.nb_n13; ++b) fht_smem(fb + M.off_n13[b], M.log_n13[b]);
+  const int* slot_of = reinterpret_cast<const int*>(ws + M.o_slot_of);
+  const int* trow = reinterpret_cast<const int*>(ws + M.o_trow);
+  const int kchunks = M.hidden / GM_TILE_K;
+  for (int b = 0; b < M.nb_n13; ++b) {
+    const float rs = rsqrtf((float)(1 << M.log_n13[b]));
+    for (int i = threadIdx.x * 8; i < (1 << M.log_n13[b]); i += blockDim.x * 8) {
+      const int col = M.off_n13[b] + i;
+      const uint4 v = pack8_half(fb + col, rs);
+      for (int j = 0; j < M.top_k; ++j) {
+        const int slot = slot_of[t * M.top_k + j];
+        if (slot >= 0) moe_store_tile16(ws + M.o_xr1, trow[slot], kchunks, col >> 3, v);
+      }
     }
   }
 }
@@ -243,99 +375,204 @@ __global__ void __launch_bounds__(MV_THREADS, 2) trellis_moe_mv_kernel(const __g
   }
 }
 
+// Shared-memory words of `rows` arrays laid out block after block, each array padded by one word per 32
+// (the layout fht_tile works in): block b of row r starts at rows * pad_off[b] + r * row_words(b).
+__device__ __forceinline__ int moe_pad_words(int n) { return n + (n >> 5); }
+
+constexpr int MOE_XF_THREADS = 384;
+
 // ---- 4: per slot  h = act(gate) * up  from w13 partials, then the w2 input transform ---------------------
-__global__ void __launch_bounds__(1024) moe_mid_kernel(const __grid_constant__ MoeDev M, int T, uint8_t* __restrict__ ws) {
-  extern __shared__ float fb[];              // w13_out floats, reused for inter floats
-  const int slot = blockIdx.x;
+// One CTA handles `sg` consecutive slots (rows of the radix-32 tile transform).
+__global__ void __launch_bounds__(MOE_XF_THREADS, 2) moe_mid_kernel(const __grid_constant__ MoeDev M, int T, int sg,
+                                                                 uint8_t* __restrict__ ws) {
+  extern __shared__ float fb[];              // sg x padded(max(w13_out, inter)) transform area, then sg x inter
   const int R = T * M.top_k;
   const int* g_count = reinterpret_cast<const int*>(ws + M.o_count);
   const int* g_base = reinterpret_cast<const int*>(ws + M.o_base);
   const int used = g_base[M.E - 1] + g_count[M.E - 1];
-  if (slot >= used) return;
-  const int e = reinterpret_cast<const int*>(ws + M.o_route_exp)[slot];
-  const float* part = reinterpret_cast<const float*>(ws + M.o_part1) + (long long)slot * M.w13_out;
-  const float wsc = M.w13_wscale[e];
-  for (int i = threadIdx.x; i < M.w13_out; i += blockDim.x) {
-    float s = 0.f;
-    for (int k = 0; k < M.kch13; ++k) s += part[(long long)k * R * M.w13_out + i];
-    fb[i] = s * wsc;
+  const int slot0 = blockIdx.x * sg;
+  if (slot0 >= used) return;
+  const int nrow = min(sg, used - slot0);
+  __shared__ int row_e[8];                   // expert of each row (sg <= 8)
+  __shared__ float row_wsc[8];
+  if (threadIdx.x < nrow) {
+    const int e = reinterpret_cast<const int*>(ws + M.o_route_exp)[slot0 + threadIdx.x];
+    row_e[threadIdx.x] = e;
+    row_wsc[threadIdx.x] = M.w13_wscale[e];
   }
-  for (int b = 0; b < M.nb_m13; ++b) fht_smem(fb + M.off_m13[b], M.log_m13[b]);
-  // SU and normalisation, then the activation (values go through fp16 once, as the reference's
-  // w13 op returns fp16: glq_vllm/fused_moe_method.py:412-421)
-  const __half* su = M.w13_su + (long long)e * M.w13_out;
+  __syncthreads();
+  float* hbuf = fb + sg * moe_pad_words(max(M.w13_out, M.inter));
+  const float* part1 = reinterpret_cast<const float*>(ws + M.o_part1);
+  auto none1 = [](int, int) -> float { return 0.f; };
+
+  // -- output transform of w13: partial sums -> SU * H(Wscale * y~), rounded through fp16 (the reference's
+  //    w13 op returns fp16: glq_vllm/fused_moe_method.py:412-421); results stay in shared memory
+  int poff = 0;
   for (int b = 0; b < M.nb_m13; ++b) {
-    const float rs = rsqrtf((float)(1 << M.log_m13[b]));
-    for (int i = threadIdx.x; i < (1 << M.log_m13[b]); i += blockDim.x) {
-      const int r = M.off_m13[b] + i;
-      fb[r] = __half2float(__float2half_rn(fb[r] * rs * __half2float(su[r])));
+    const int logbs = M.log_m13[b], off = M.off_m13[b], rw = moe_pad_words(1 << logbs);
+    float* reg = fb + sg * poff;
+    const float rs = rsqrtf((float)(1 << logbs));
+    auto load32 = [&](int row, int i0, float (&v)[32]) {
+      const int slot = slot0 + row;
+      const float wsc = row_wsc[row];
+      const float* src = part1 + (long long)slot * M.w13_out + off + i0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < M.kch13; ++k) {
+          const float4 t4 = *reinterpret_cast<const float4*>(src + 4 * j + (long long)k * R * M.w13_out);
+          a.x += t4.x; a.y += t4.y; a.z += t4.z; a.w += t4.w;
+        }
+        v[4 * j] = a.x * wsc; v[4 * j + 1] = a.y * wsc; v[4 * j + 2] = a.z * wsc; v[4 * j + 3] = a.w * wsc;
+      }
+    };
+    auto store1 = [&](int row, int i, float val) {
+      const __half su = M.w13_su[(long long)row_e[row] * M.w13_out + off + i];
+      reg[row * rw + fht_pad(i)] = __half2float(__float2half_rn(val * rs * __half2float(su)));
+    };
+    fht_tile(reg, logbs, nrow, load32, none1, store1);
+    poff += rw;
+  }
+  __syncthreads();
+  // -- activation: column c of the w13 output sits in block b(c) at padded offset
+  auto y13 = [&](int row, int c) -> float {
+    int po = 0;
+    for (int b = 0; b < M.nb_m13; ++b) {
+      const int bs = 1 << M.log_m13[b];
+      if (c < M.off_m13[b] + bs) return fb[sg * po + row * moe_pad_words(bs) + fht_pad(c - M.off_m13[b])];
+      po += moe_pad_words(bs);
     }
+    return 0.f;
+  };
+  const int hrw = moe_pad_words(M.inter);
+  for (int o = threadIdx.x; o < nrow * M.inter; o += blockDim.x) {
+    const int row = o / M.inter, i = o - row * M.inter;
+    const float a = moe_act(y13(row, i), M.act);
+    const float h = M.gated ? a * y13(row, M.inter + i) : a;
+    hbuf[row * hrw + fht_pad(i)] = __half2float(__float2half_rn(h)) * __half2float(M.w2_sv[i]);
   }
   __syncthreads();
-  float hv[8];                               // inter <= 8 * blockDim.x (host-checked limits)
-  int nh = 0;
-  for (int i = threadIdx.x; i < M.inter; i += blockDim.x) {
-    const float g = fb[i];
-    const float a = moe_act(g, M.act);
-    hv[nh++] = M.gated ? a * fb[M.inter + i] : a;
-  }
-  __syncthreads();
-  nh = 0;
-  for (int i = threadIdx.x; i < M.inter; i += blockDim.x)
-    fb[i] = __half2float(__float2half_rn(hv[nh++])) * __half2float(M.w2_sv[i]);
-  for (int b = 0; b < M.nb_n2; ++b) fht_smem(fb + M.off_n2[b], M.log_n2[b]);
-  __half2* out = reinterpret_cast<__half2*>(ws + M.o_xr2) + (long long)slot * M.inter;
+  // -- input transform of w2, results back into the transform area
+  poff = 0;
   for (int b = 0; b < M.nb_n2; ++b) {
-    const float rs = rsqrtf((float)(1 << M.log_n2[b]));
-    for (int i = threadIdx.x; i < (1 << M.log_n2[b]); i += blockDim.x) {
-      const int col = M.off_n2[b] + i;
-      const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);
-      out[pos >> 1] = __halves2half2(__float2half_rn(fb[col] * rs), __float2half_rn(0.f));
+    const int logbs = M.log_n2[b], off = M.off_n2[b], rw = moe_pad_words(1 << logbs);
+    float* reg = fb + sg * poff;
+    const float rs = rsqrtf((float)(1 << logbs));
+    auto load32 = [&](int row, int i0, float (&v)[32]) {
+      const float* src = hbuf + row * hrw + fht_pad(off + i0);    // off and i0 are multiples of 32
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = src[k];
+    };
+    auto store1 = [&](int row, int i, float val) { reg[row * rw + fht_pad(i)] = val * rs; };
+    fht_tile(reg, logbs, nrow, load32, none1, store1);
+    poff += rw;
+  }
+  __syncthreads();
+  // -- store: 8 consecutive columns per thread
+  poff = 0;
+  const int* trow = reinterpret_cast<const int*>(ws + M.o_trow);
+  for (int b = 0; b < M.nb_n2; ++b) {
+    const int bs = 1 << M.log_n2[b], off = M.off_n2[b], rw = moe_pad_words(bs);
+    const float* reg = fb + sg * poff;
+    const int per_row = bs >> 3;
+    for (int o = threadIdx.x; o < nrow * per_row; o += blockDim.x) {
+      const int row = o / per_row, i = (o - row * per_row) * 8;
+      const float* src = reg + row * rw + fht_pad(i);
+      const int slot = slot0 + row, col = off + i;
+      if (M.gemm) {
+        moe_store_tile16(ws + M.o_xr2, trow[slot], M.inter / GM_TILE_K, col >> 3, pack8_half(src, 1.0f));
+      } else {
+        __half2* out = reinterpret_cast<__half2*>(ws + M.o_xr2) + (long long)slot * M.inter;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const int c = col + k;
+          const int pos = (c & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(c & 31);
+          out[pos >> 1] = __halves2half2(__float2half_rn(src[k]), __float2half_rn(0.f));
+        }
+      }
     }
+    poff += rw;
   }
 }
 
 // ---- 6: per token weighted combine ------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) moe_out_kernel(const __grid_constant__ MoeDev M, int T,
-                                                       const float* __restrict__ topk_w, const uint8_t* __restrict__ ws,
-                                                       uint8_t* __restrict__ y) {
-  extern __shared__ float fb[];              // hidden floats
+// The routings of a token are the rows of one tile transform (`rg` at a time); their results are summed
+// in fixed j order.
+__global__ void __launch_bounds__(MOE_XF_THREADS, 2) moe_out_kernel(const __grid_constant__ MoeDev M, int T, int rg,
+                                                                 const float* __restrict__ topk_w,
+                                                                 const uint8_t* __restrict__ ws, uint8_t* __restrict__ y) {
+  extern __shared__ float fb[];              // rg x padded(hidden)
   const int t = blockIdx.x;
   const int R = T * M.top_k;
   const int* slot_of = reinterpret_cast<const int*>(ws + M.o_slot_of);
   const int* route_exp = reinterpret_cast<const int*>(ws + M.o_route_exp);
-  float acc[8];                              // hidden <= 8 * blockDim.x is checked on the host
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-  for (int j = 0; j < M.top_k; ++j) {
-    const int slot = slot_of[t * M.top_k + j];
-    if (slot < 0) continue;                  // uniform per CTA
-    const int e = route_exp[slot];
-    const float wsc = M.w2_wscale[e];
-    const float w = topk_w[t * M.top_k + j];
-    const float* part = reinterpret_cast<const float*>(ws + M.o_part2) + (long long)slot * M.hidden;
-    for (int i = threadIdx.x; i < M.hidden; i += blockDim.x) {
-      float s = 0.f;
-      for (int k = 0; k < M.kch2; ++k) s += part[(long long)k * R * M.hidden + i];
-      fb[i] = s * wsc;
-    }
-    for (int b = 0; b < M.nb_m2; ++b) fht_smem(fb + M.off_m2[b], M.log_m2[b]);
-    const __half* su = M.w2_su + (long long)e * M.hidden;
-    int q = 0;
+  const float* part2 = reinterpret_cast<const float*>(ws + M.o_part2);
+  auto none1 = [](int, int) -> float { return 0.f; };
+  __shared__ int row_slot[64], row_e[64];    // per routing j of this token (top_k <= 64)
+  __shared__ float row_wsc[64], row_w[64];
+  if (threadIdx.x < M.top_k) {
+    const int slot = slot_of[t * M.top_k + threadIdx.x];
+    const int e = slot >= 0 ? route_exp[slot] : 0;
+    row_slot[threadIdx.x] = slot;
+    row_e[threadIdx.x] = e;
+    row_wsc[threadIdx.x] = M.w2_wscale[e];
+    row_w[threadIdx.x] = topk_w[t * M.top_k + threadIdx.x];
+  }
+  __syncthreads();
+  float* accs = fb + rg * moe_pad_words(M.hidden);   // running sums over the passes, hidden floats
+  for (int j0 = 0; j0 < M.top_k; j0 += rg) {
+    const int nrow = min(rg, M.top_k - j0);
+    int poff = 0;
     for (int b = 0; b < M.nb_m2; ++b) {
-      const float rs = rsqrtf((float)(1 << M.log_m2[b]));
-      for (int i = threadIdx.x; i < (1 << M.log_m2[b]); i += blockDim.x) {
-        const int r = M.off_m2[b] + i;
-        // the reference's w2 op returns fp16 before the weighted sum
-        fb[r] = __half2float(__float2half_rn(fb[r] * rs * __half2float(su[r])));
-      }
+      const int logbs = M.log_m2[b], off = M.off_m2[b], rw = moe_pad_words(1 << logbs);
+      float* reg = fb + rg * poff;
+      const float rs = rsqrtf((float)(1 << logbs));
+      auto load32 = [&](int row, int i0, float (&v)[32]) {
+        const int slot = row_slot[j0 + row];
+        if (slot < 0) {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = 0.f;
+          return;
+        }
+        const float wsc = row_wsc[j0 + row];
+        const float* src = part2 + (long long)slot * M.hidden + off + i0;
+#pragma unroll
+        for (int jj = 0; jj < 8; ++jj) {
+          float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int k = 0; k < M.kch2; ++k) {
+            const float4 t4 = *reinterpret_cast<const float4*>(src + 4 * jj + (long long)k * R * M.hidden);
+            a.x += t4.x; a.y += t4.y; a.z += t4.z; a.w += t4.w;
+          }
+          v[4 * jj] = a.x * wsc; v[4 * jj + 1] = a.y * wsc; v[4 * jj + 2] = a.z * wsc; v[4 * jj + 3] = a.w * wsc;
+        }
+      };
+      auto store1 = [&](int row, int i, float val) {
+        float r = 0.f;
+        if (row_slot[j0 + row] >= 0) {
+          // the reference's w2 op returns fp16 before the weighted sum
+          const __half su = M.w2_su[(long long)row_e[j0 + row] * M.hidden + off + i];
+          r = __half2float(__float2half_rn(val * rs * __half2float(su)));
+        }
+        reg[row * rw + fht_pad(i)] = r;
+      };
+      fht_tile(reg, logbs, nrow, load32, none1, store1);
+      poff += rw;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < M.hidden; i += blockDim.x) acc[q++] += w * fb[i];
+    const bool last = j0 + rg >= M.top_k;
+    for (int col = threadIdx.x; col < M.hidden; col += blockDim.x) {
+      int po = 0, b = 0;
+      while (b + 1 < M.nb_m2 && col >= M.off_m2[b] + (1 << M.log_m2[b])) { po += moe_pad_words(1 << M.log_m2[b]); ++b; }
+      const int rw = moe_pad_words(1 << M.log_m2[b]);
+      const float* reg = fb + rg * po + fht_pad(col - M.off_m2[b]);
+      float a = j0 ? accs[col] : 0.f;
+      for (int row = 0; row < nrow; ++row)
+        if (row_slot[j0 + row] >= 0) a += row_w[j0 + row] * reg[row * rw];
+      if (last) store_act(y, (long long)t * M.hidden + col, M.y_dtype, a);
+      else accs[col] = a;
+    }
     __syncthreads();
   }
-  int q = 0;
-  for (int i = threadIdx.x; i < M.hidden; i += blockDim.x) store_act(y, (long long)t * M.hidden + i, M.y_dtype, acc[q++]);
 }
 
 typedef void (*MoeMvKernel)(const MoeMvArgs);
@@ -346,6 +583,23 @@ static MoeMvKernel moe_mv_pick(int k1, int k2) {
   M_CASE(2, 0) M_CASE(3, 0) M_CASE(4, 0) M_CASE(4, 1) M_CASE(4, 2) M_CASE(4, 3) M_CASE(4, 4)
 #undef M_CASE
   return nullptr;
+}
+
+typedef void (*MoeGemmKernel)(const DevLinear*, const GemmItem*, int, uint8_t*, int*, const int*);
+constexpr int MOE_GEMM_STAGES = 4;
+static MoeGemmKernel moe_gemm_pick(int k1, int k2) {
+#define M_CASE(A, B) if (k1 == A && k2 == B) return glq_gemm_kernel<0, A, B, MOE_TN, MOE_GEMM_STAGES>;
+  M_CASE(2, 0) M_CASE(3, 0) M_CASE(4, 0) M_CASE(4, 1) M_CASE(4, 2) M_CASE(4, 3) M_CASE(4, 4)
+#undef M_CASE
+  return nullptr;
+}
+static size_t moe_gemm_smem_bytes() {
+  return (size_t)MOE_GEMM_STAGES * (GM_A_BYTES + (size_t)MOE_B_BYTES) + (3 * MOE_GEMM_STAGES + 4) * 8 + 16 + 1024;
+}
+// routed tokens per expert (average) from which the tensor-core form is used
+static int moe_gemm_min_avg() {
+  const char* e = getenv("GLQB_MOE_GEMM_MIN_AVG");
+  return e ? atoi(e) : 64;
 }
 
 }  // namespace glqb
@@ -360,6 +614,12 @@ struct GlqbMoePlan {
   int nb = 2;              // token-column blocks per pass (8*nb routed tokens share one decode)
   MoeMvKernel k13 = nullptr, k2 = nullptr;
   int grid13 = 0, grid2 = 0;
+  int mid_sg = 1, out_rg = 1;          // slots per CTA of the mid kernel, routings per pass of the combine
+  size_t mid_smem = 0, out_smem = 0;
+  // tensor-core form
+  bool gemm_ok = false;
+  MoeDev devg;             // same weights, workspace laid out for the GEMM kernels
+  MoeGemmKernel g13 = nullptr, g2 = nullptr;
 };
 
 static int moe_fail(int code, const char* fmt, ...) {
@@ -469,6 +729,55 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   M.o_xr2 = o; o = al(o + R * d->inter * 2 * XR_TRELLIS_EXPAND);
   M.o_part2 = o; o = al(o + (size_t)M.kch2 * R * d->hidden * 4);
   P->ws_bytes = o;
+  // tensor-core form: its buffers overlay the decode form's (a step runs one or the other)
+  P->g13 = moe_gemm_pick(k13a, k13b);
+  P->g2 = moe_gemm_pick(k2a, k2b);
+  P->gemm_ok = P->g13 && P->g2 && d->hidden % GM_TILE_K == 0 && d->inter % GM_TILE_K == 0 && M.E <= 4096 &&
+               R >= (size_t)M.E * moe_gemm_min_avg();
+  if (P->gemm_ok) {
+    MoeDev& G = P->devg;
+    G = M;
+    G.gemm = 1; G.kch13 = 1; G.kch2 = 1;
+    G.k13a = k13a; G.k13b = k13b; G.k2a = k2a; G.k2b = k2b;
+    const size_t tiles = R / MOE_TN + M.E;
+    const size_t mt13 = (d->w13_out + GM_TILE_M - 1) / GM_TILE_M, mt2 = (d->hidden + GM_TILE_M - 1) / GM_TILE_M;
+    G.max_items13 = (int)(tiles * mt13);
+    G.max_items2 = (int)(tiles * mt2);
+    auto al1k = [](size_t v) { return (v + 1023) / 1024 * 1024; };
+    size_t g = al1k((size_t)M.o_xr1);
+    G.o_xr1 = g; g = al1k(g + tiles * (d->hidden / GM_TILE_K) * MOE_B_BYTES);
+    G.o_part1 = g; g = al1k(g + R * d->w13_out * 4);
+    G.o_xr2 = g; g = al1k(g + tiles * (d->inter / GM_TILE_K) * MOE_B_BYTES);
+    G.o_part2 = g; g = al1k(g + R * d->hidden * 4);
+    G.o_trow = g; g = al1k(g + 4 * R);
+    G.o_layers13 = g; g = al1k(g + sizeof(DevLinear) * M.E);
+    G.o_layers2 = g; g = al1k(g + sizeof(DevLinear) * M.E);
+    G.o_items13 = g; g = al1k(g + sizeof(GemmItem) * G.max_items13);
+    G.o_items2 = g; g = al1k(g + sizeof(GemmItem) * G.max_items2);
+    G.o_nitems = g; g = al1k(g + 16);
+    G.o_status = g; g = al1k(g + 16);
+    P->ws_bytes = std::max(P->ws_bytes, g);
+    if (cudaFuncSetAttribute(P->g13, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_gemm_smem_bytes()) != cudaSuccess ||
+        cudaFuncSetAttribute(P->g2, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)moe_gemm_smem_bytes()) != cudaSuccess) {
+      cudaGetLastError();
+      P->gemm_ok = false;
+    }
+  }
+  {
+    auto padw = [](size_t n) { return n + n / 32; };
+    const size_t budget = 100 * 1024;     // two CTAs per SM
+    const size_t mid_row = 4 * (padw(std::max(d->w13_out, d->inter)) + padw(d->inter)), out_row = 4 * padw(d->hidden);
+    const size_t out_fixed = 4 * (size_t)d->hidden;
+    P->mid_sg = (int)std::max<size_t>(1, std::min<size_t>(8, budget / mid_row));
+    P->out_rg = (int)std::max<size_t>(1, std::min<size_t>(std::min(8, d->top_k), (budget - out_fixed) / out_row));
+    P->mid_smem = P->mid_sg * mid_row;
+    P->out_smem = P->out_rg * out_row + out_fixed;
+    if (cudaFuncSetAttribute(moe_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P->mid_smem) != cudaSuccess ||
+        cudaFuncSetAttribute(moe_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P->out_smem) != cudaSuccess) {
+      delete P;
+      return moe_fail(GLQB_E_CUDA, "moe_plan_create: %s", cudaGetErrorString(cudaGetLastError()));
+    }
+  }
   int dev_id = 0;
   if (cudaGetDevice(&dev_id) != cudaSuccess ||
       cudaDeviceGetAttribute(&P->sm_count, cudaDevAttrMultiProcessorCount, dev_id) != cudaSuccess) {
@@ -501,6 +810,28 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return moe_fail(GLQB_E_WORKSPACE, "workspace must be 256-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  if (P->gemm_ok && (long long)tokens * P->dev.top_k >= (long long)P->dev.E * moe_gemm_min_avg()) {
+    const MoeDev& G = P->devg;
+    const int R = tokens * G.top_k;
+    moe_group_kernel<<<1, 1024, 2 * G.E * sizeof(int), st>>>(G, topk_ids, tokens, ws);
+    moe_gemm_setup_kernel<<<1, 1024, 0, st>>>(G, tokens, ws);
+    moe_rht_in_gemm_kernel<<<tokens, std::max(64, std::min(1024, G.hidden / 8)), G.hidden * 4, st>>>(
+        G, reinterpret_cast<const uint8_t*>(x), ws);
+    int* status = reinterpret_cast<int*>(ws + G.o_status);
+    const int* nitems = reinterpret_cast<const int*>(ws + G.o_nitems);
+    P->g13<<<std::min(P->sm_count, G.max_items13), GM_THREADS, moe_gemm_smem_bytes(), st>>>(
+        reinterpret_cast<const DevLinear*>(ws + G.o_layers13), reinterpret_cast<const GemmItem*>(ws + G.o_items13),
+        G.max_items13, ws, status, nitems);
+    moe_mid_kernel<<<(R + P->mid_sg - 1) / P->mid_sg, MOE_XF_THREADS, P->mid_smem, st>>>(G, tokens, P->mid_sg, ws);
+    P->g2<<<std::min(P->sm_count, G.max_items2), GM_THREADS, moe_gemm_smem_bytes(), st>>>(
+        reinterpret_cast<const DevLinear*>(ws + G.o_layers2), reinterpret_cast<const GemmItem*>(ws + G.o_items2),
+        G.max_items2, ws, status, nitems + 1);
+    moe_out_kernel<<<tokens, MOE_XF_THREADS, P->out_smem, st>>>(G, tokens, P->out_rg, topk_weights, ws,
+                                                               reinterpret_cast<uint8_t*>(y));
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return moe_fail(GLQB_E_CUDA, "moe_plan_run: %s", cudaGetErrorString(e));
+    return GLQB_OK;
+  }
   const MoeDev& M = P->dev;
   const int R = tokens * M.top_k;
   moe_group_kernel<<<1, 1024, 2 * M.E * sizeof(int), st>>>(M, topk_ids, tokens, ws);
@@ -519,8 +850,7 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   A.E = M.E; A.m = M.w13_out; A.n = M.hidden; A.gps = M.hidden / 32; A.strips = M.w13_out / 32;
   A.kchunks = M.kch13; A.gpc = M.gpc13; A.R = R;
   P->k13<<<P->grid13, MV_THREADS, 0, st>>>(A);
-  const int mid_threads = std::max(256, std::min(1024, M.w13_out / 8));
-  moe_mid_kernel<<<R, mid_threads, std::max(M.w13_out, M.inter) * 4, st>>>(M, tokens, ws);
+  moe_mid_kernel<<<(R + P->mid_sg - 1) / P->mid_sg, MOE_XF_THREADS, P->mid_smem, st>>>(M, tokens, P->mid_sg, ws);
   A.codes[0] = M.w2[0]; A.codes[1] = M.w2[1]; A.stride[0] = M.w2_stride[0]; A.stride[1] = M.w2_stride[1];
   A.inv2 = M.w2_inv2;
   A.row_map = nullptr;
@@ -530,9 +860,23 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   A.m = M.hidden; A.n = M.inter; A.gps = M.inter / 32; A.strips = M.hidden / 32;
   A.kchunks = M.kch2; A.gpc = M.gpc2;
   P->k2<<<P->grid2, MV_THREADS, 0, st>>>(A);
-  moe_out_kernel<<<tokens, 1024, M.hidden * 4, st>>>(M, tokens, topk_weights, ws, reinterpret_cast<uint8_t*>(y));
+  moe_out_kernel<<<tokens, MOE_XF_THREADS, P->out_smem, st>>>(M, tokens, P->out_rg, topk_weights, ws,
+                                                             reinterpret_cast<uint8_t*>(y));
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return moe_fail(GLQB_E_CUDA, "moe_plan_run: %s", cudaGetErrorString(e));
+  return GLQB_OK;
+}
+
+int glqb_moe_plan_status(const GlqbMoePlan* P, const void* workspace, void* stream_) {
+  if (!P || !workspace) return moe_fail(GLQB_E_INVALID, "moe_plan_status: null argument");
+  if (!P->gemm_ok) return GLQB_OK;
+  int st = 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  if (cudaMemcpyAsync(&st, reinterpret_cast<const uint8_t*>(workspace) + P->devg.o_status, sizeof st, cudaMemcpyDeviceToHost, s) !=
+          cudaSuccess ||
+      cudaStreamSynchronize(s) != cudaSuccess)
+    return moe_fail(GLQB_E_CUDA, "moe_plan_status: %s", cudaGetErrorString(cudaGetLastError()));
+  if (st != 0) return moe_fail(GLQB_E_CUDA, "moe: a bounded wait inside the GEMM kernel gave up (role %d); results are invalid", st);
   return GLQB_OK;
 }
 

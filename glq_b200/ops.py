@@ -365,6 +365,10 @@ class MoePlan:
                                               y.data_ptr(), x.shape[0], self.workspace.data_ptr(),
                                               self.workspace.numel(), _stream(x)), "moe_plan_run")
 
+    def check_status(self, x):
+        """Synchronises the stream of ``x`` and raises if a bounded wait inside the GEMM kernels gave up."""
+        _lib.check(self.lib.glqb_moe_plan_status(self.handle, self.workspace.data_ptr(), _stream(x)), "moe_plan_status")
+
     def close(self):
         if getattr(self, "handle", None):
             self.lib.glqb_moe_plan_destroy(self.handle)

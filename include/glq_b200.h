@@ -138,9 +138,13 @@ int glqb_moe_plan_create(const GlqbMoeDesc* desc, GlqbMoePlan** out_plan);
 size_t glqb_moe_plan_workspace_bytes(const GlqbMoePlan* plan);
 int64_t glqb_moe_plan_code_bytes(const GlqbMoePlan* plan);
 /* x (tokens, hidden), topk_ids (tokens, top_k), topk_weights (tokens, top_k) fp32, y (tokens, hidden);
- * six launches on `stream`, returns without synchronising. */
+ * six or seven launches on `stream`, returns without synchronising.  Steps with at least 64 routed tokens
+ * per expert on average (GLQB_MOE_GEMM_MIN_AVG) run the two matmuls on the tensor-core GEMM kernel. */
 int glqb_moe_plan_run(GlqbMoePlan* plan, const void* x, const void* topk_ids, const float* topk_weights, void* y,
                       int32_t tokens, void* workspace, size_t workspace_bytes, void* stream);
+/* Synchronises `stream` and reports whether a bounded wait inside the GEMM kernels of the last run gave up
+ * (GLQB_E_CUDA, results invalid); GLQB_OK otherwise.  No counterpart in the reference. */
+int glqb_moe_plan_status(const GlqbMoePlan* plan, const void* workspace, void* stream);
 void glqb_moe_plan_destroy(GlqbMoePlan* plan);
 
 /* Stateless single-layer forms of the reference's fused ops.  `workspace` must hold
