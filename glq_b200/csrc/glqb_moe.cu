@@ -5,12 +5,14 @@
 //
 // Six launches, fixed grids, no host synchronisation (capture-safe):
 //   1 moe_group_kernel     count tokens per expert, prefix sums, place every (token, j) routing in a slot
+//                          (tensor-core form: also the per-expert layer entries and the GEMM work lists)
 //   2 moe_rht_in_kernel    input transform of every TOKEN once (all experts share SV of w13)
 //   3 trellis_moe_mv_kernel  w13: experts' weights decoded once per 8*NB routed tokens, partial sums per slot
-//   4 moe_mid_kernel       per slot: sum partials, Wscale, output transform, SU, gated activation, then the
-//                          w2 input transform (SV, Hadamard) — three reference launches in one
+//   4 moe_mid_kernel       a few slots per CTA: sum partials, Wscale, output transform, SU, gated activation,
+//                          then the w2 input transform (SV, Hadamard) — three reference launches in one
 //   5 trellis_moe_mv_kernel  w2
-//   6 moe_out_kernel       per token: for j in fixed order  acc += w * SU * H(Wscale * partials)
+//   6 moe_out_kernel       per token: its routings are the rows of one tile transform; then, for j in fixed
+//                          order, acc += w * SU * H(Wscale * partials)
 // Work units of the two matmuls are (expert, 32-row strip, K chunk) and are handed out by an atomic
 // counter, so skewed routing (a few hot experts) does not idle the warps that drew empty experts; the
 // partial-sum slot of a unit is its K-chunk number, so results do not depend on which warp ran it.
@@ -18,8 +20,8 @@
 // bit-identical run to run.
 //
 // Steps with many routed tokens per expert take the tensor-core form instead: launches 3 and 5 become the
-// tcgen05 GEMM kernel (glq_gemm_kernel, trellis producers) over a work list that a setup kernel builds on
-// the device from the expert counts — every expert is a "layer" whose token count, activation tiles and
+// tcgen05 GEMM kernel (glq_gemm_kernel, trellis producers) over a work list that the grouping kernel builds
+// on the device from the expert counts — every expert is a "layer" whose token count, activation tiles and
 // partial-sum rows are patched in each run; experts' routings are padded to whole 128-token tiles.  The
 // transforms write the activations straight into the swizzled tile images the GEMM's bulk copies fetch.
 #include <algorithm>
@@ -74,9 +76,11 @@ __device__ __forceinline__ float moe_act(float g, int act) {
 // ---- 1: grouping ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__ MoeDev M, const void* __restrict__ ids,
                                                          int T, uint8_t* __restrict__ ws) {
-  extern __shared__ int sh[];            // counts[E], cursor[E]
+  extern __shared__ int sh[];            // counts[E], cursor[E], first slot[E], first token tile[E + 1]
   int* cnt = sh;
   int* cur = sh + M.E;
+  int* base_s = sh + 2 * M.E;
+  int* tile0 = sh + 3 * M.E;
   int* g_count = reinterpret_cast<int*>(ws + M.o_count);
   int* g_base = reinterpret_cast<int*>(ws + M.o_base);
   int* g_work = reinterpret_cast<int*>(ws + M.o_work);
@@ -101,10 +105,71 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < M.E; ++e) { cur[e] = run; g_base[e] = run; g_count[e] = cnt[e]; run += cnt[e]; }
+    int run = 0, tiles = 0;
+    for (int e = 0; e < M.E; ++e) {
+      cur[e] = run; base_s[e] = run; g_base[e] = run; g_count[e] = cnt[e]; run += cnt[e];
+      tile0[e] = tiles; tiles += (cnt[e] + MOE_TN - 1) / MOE_TN;
+    }
+    tile0[M.E] = tiles;
   }
   __syncthreads();
+  int* trow = reinterpret_cast<int*>(ws + M.o_trow);
+  if (M.gemm) {
+    // Tensor-core form.  Expert e with c routings owns ceil(c / 128) token tiles; routing number i of the
+    // expert sits in row tile0[e] * 128 + i of the padded row space.  Every expert becomes a "layer" of the
+    // GEMM kernel (token count, activation tiles and partial-sum rows of this step), and the work list is
+    // ordered (token tile, row tile) so that the CTAs working at one moment share an activation tile in L2.
+    const int kc13 = M.hidden / GM_TILE_K, kc2 = M.inter / GM_TILE_K;
+    const int mt13 = (M.w13_out + GM_TILE_M - 1) / GM_TILE_M, mt2 = (M.hidden + GM_TILE_M - 1) / GM_TILE_M;
+    const int tiles = tile0[M.E];
+    if (threadIdx.x == 0) {
+      int* nitems = reinterpret_cast<int*>(ws + M.o_nitems);
+      nitems[0] = min(tiles * mt13, M.max_items13);
+      nitems[1] = min(tiles * mt2, M.max_items2);
+      reinterpret_cast<int*>(ws + M.o_status)[0] = 0;
+    }
+    DevLinear* L13 = reinterpret_cast<DevLinear*>(ws + M.o_layers13);
+    DevLinear* L2 = reinterpret_cast<DevLinear*>(ws + M.o_layers2);
+    for (int e = threadIdx.x; e < M.E; e += blockDim.x) {
+      DevLinear a;
+      memset(&a, 0, sizeof a);
+      a.format = GLQB_FMT_TRELLIS_3INST;
+      a.batch = cnt[e];
+      DevLinear b = a;
+      a.codes[0] = M.w13[0] + (long long)e * M.w13_stride[0];
+      a.codes[1] = M.w13[1] ? M.w13[1] + (long long)e * M.w13_stride[1] : nullptr;
+      a.stage_scale[0] = 1.f; a.stage_scale[1] = M.w13_inv2 ? M.w13_inv2[e] : 0.f;
+      a.m = M.w13_out; a.n = M.hidden; a.strips = M.w13_out / 32; a.groups_per_strip = M.hidden / 32;
+      a.xr_off = M.o_xr1 + (long long)tile0[e] * kc13 * MOE_B_BYTES;
+      a.part_off = M.o_part1 + (long long)base_s[e] * M.w13_out * 4;
+      b.codes[0] = M.w2[0] + (long long)e * M.w2_stride[0];
+      b.codes[1] = M.w2[1] ? M.w2[1] + (long long)e * M.w2_stride[1] : nullptr;
+      b.stage_scale[0] = 1.f; b.stage_scale[1] = M.w2_inv2 ? M.w2_inv2[e] : 0.f;
+      b.m = M.hidden; b.n = M.inter; b.strips = M.hidden / 32; b.groups_per_strip = M.inter / 32;
+      b.xr_off = M.o_xr2 + (long long)tile0[e] * kc2 * MOE_B_BYTES;
+      b.part_off = M.o_part2 + (long long)base_s[e] * M.hidden * 4;
+      L13[e] = a;
+      L2[e] = b;
+    }
+    auto expert_of_tile = [&](int tile) -> int {       // last e with tile0[e] <= tile
+      int lo = 0, hi = M.E - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tile0[mid] <= tile) lo = mid; else hi = mid - 1;
+      }
+      return lo;
+    };
+    GemmItem* I13 = reinterpret_cast<GemmItem*>(ws + M.o_items13);
+    GemmItem* I2 = reinterpret_cast<GemmItem*>(ws + M.o_items2);
+    for (int idx = threadIdx.x; idx < min(tiles * mt13, M.max_items13); idx += blockDim.x) {
+      const int tile = idx / mt13, e = expert_of_tile(tile);
+      I13[idx] = GemmItem{e, idx - tile * mt13, tile - tile0[e], 0, kc13, 0};
+    }
+    for (int idx = threadIdx.x; idx < min(tiles * mt2, M.max_items2); idx += blockDim.x) {
+      const int tile = idx / mt2, e = expert_of_tile(tile);
+      I2[idx] = GemmItem{e, idx - tile * mt2, tile - tile0[e], 0, kc2, 0};
+    }
+  }
   for (int i0 = threadIdx.x; i0 < R; i0 += 8 * blockDim.x) {
     int ev[8];
 #pragma unroll
@@ -118,6 +183,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
           slot = atomicAdd(&cur[ev[u]], 1);
           route_tok[slot] = i / M.top_k;
           route_exp[slot] = ev[u];
+          if (M.gemm) trow[slot] = tile0[ev[u]] * MOE_TN + (slot - base_s[ev[u]]);
         }
         slot_of[i] = slot;
       }
@@ -140,75 +206,6 @@ __global__ void __launch_bounds__(1024) moe_rht_in_kernel(const __grid_constant_
       const int col = M.off_n13[b] + i;
       const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);
       out[pos >> 1] = __halves2half2(__float2half_rn(fb[col] * rs), __float2half_rn(0.f));
-    }
-  }
-}
-
-// ---- tensor-core form: tile rows, per-expert layer entries and work lists, built on the device -------------
-// One CTA.  Expert e with c routings owns ceil(c / 128) token tiles; routing number i of the expert sits in
-// row (tile0[e] * 128 + i) of the padded row space.  Items are ordered (expert, token tile, row tile) so that
-// the CTAs working at one moment share an activation tile through L2.
-__global__ void __launch_bounds__(1024) moe_gemm_setup_kernel(const __grid_constant__ MoeDev M, int T,
-                                                              uint8_t* __restrict__ ws) {
-  __shared__ int s_tile0[4097];
-  const int* g_count = reinterpret_cast<const int*>(ws + M.o_count);
-  const int* g_base = reinterpret_cast<const int*>(ws + M.o_base);
-  const int* route_exp = reinterpret_cast<const int*>(ws + M.o_route_exp);
-  int* trow = reinterpret_cast<int*>(ws + M.o_trow);
-  int* nitems = reinterpret_cast<int*>(ws + M.o_nitems);
-  for (int e = threadIdx.x; e < M.E; e += blockDim.x) s_tile0[e + 1] = (g_count[e] + MOE_TN - 1) / MOE_TN;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int run = 0;
-    for (int e = 0; e < M.E; ++e) { const int nt = s_tile0[e + 1]; s_tile0[e] = run; run += nt; }
-    s_tile0[M.E] = run;
-    const int mt13 = (M.w13_out + GM_TILE_M - 1) / GM_TILE_M, mt2 = (M.hidden + GM_TILE_M - 1) / GM_TILE_M;
-    nitems[0] = min(run * mt13, M.max_items13);
-    nitems[1] = min(run * mt2, M.max_items2);
-    reinterpret_cast<int*>(ws + M.o_status)[0] = 0;
-  }
-  __syncthreads();
-  const int used = g_base[M.E - 1] + g_count[M.E - 1];
-  for (int slot = threadIdx.x; slot < used; slot += blockDim.x) {
-    const int e = route_exp[slot];
-    trow[slot] = s_tile0[e] * MOE_TN + (slot - g_base[e]);
-  }
-  const int kc13 = M.hidden / GM_TILE_K, kc2 = M.inter / GM_TILE_K;
-  DevLinear* L13 = reinterpret_cast<DevLinear*>(ws + M.o_layers13);
-  DevLinear* L2 = reinterpret_cast<DevLinear*>(ws + M.o_layers2);
-  for (int e = threadIdx.x; e < M.E; e += blockDim.x) {
-    DevLinear a;
-    memset(&a, 0, sizeof a);
-    a.format = GLQB_FMT_TRELLIS_3INST;
-    a.batch = g_count[e];
-    DevLinear b = a;
-    a.codes[0] = M.w13[0] + (long long)e * M.w13_stride[0];
-    a.codes[1] = M.w13[1] ? M.w13[1] + (long long)e * M.w13_stride[1] : nullptr;
-    a.stage_scale[0] = 1.f; a.stage_scale[1] = M.w13_inv2 ? M.w13_inv2[e] : 0.f;
-    a.m = M.w13_out; a.n = M.hidden; a.strips = M.w13_out / 32; a.groups_per_strip = M.hidden / 32;
-    a.xr_off = M.o_xr1 + (long long)s_tile0[e] * kc13 * MOE_B_BYTES;
-    a.part_off = M.o_part1 + (long long)g_base[e] * M.w13_out * 4;
-    b.codes[0] = M.w2[0] + (long long)e * M.w2_stride[0];
-    b.codes[1] = M.w2[1] ? M.w2[1] + (long long)e * M.w2_stride[1] : nullptr;
-    b.stage_scale[0] = 1.f; b.stage_scale[1] = M.w2_inv2 ? M.w2_inv2[e] : 0.f;
-    b.m = M.hidden; b.n = M.inter; b.strips = M.hidden / 32; b.groups_per_strip = M.inter / 32;
-    b.xr_off = M.o_xr2 + (long long)s_tile0[e] * kc2 * MOE_B_BYTES;
-    b.part_off = M.o_part2 + (long long)g_base[e] * M.hidden * 4;
-    L13[e] = a;
-    L2[e] = b;
-  }
-  GemmItem* I13 = reinterpret_cast<GemmItem*>(ws + M.o_items13);
-  GemmItem* I2 = reinterpret_cast<GemmItem*>(ws + M.o_items2);
-  const int mt13 = (M.w13_out + GM_TILE_M - 1) / GM_TILE_M, mt2 = (M.hidden + GM_TILE_M - 1) / GM_TILE_M;
-  for (int e = 0; e < M.E; ++e) {
-    const int nt = s_tile0[e + 1] - s_tile0[e];
-    for (int i = threadIdx.x; i < nt * mt13; i += blockDim.x) {
-      const int idx = s_tile0[e] * mt13 + i;
-      if (idx < M.max_items13) I13[idx] = GemmItem{e, i % mt13, i / mt13, 0, kc13, 0};
-    }
-    for (int i = threadIdx.x; i < nt * mt2; i += blockDim.x) {
-      const int idx = s_tile0[e] * mt2 + i;
-      if (idx < M.max_items2) I2[idx] = GemmItem{e, i % mt2, i / mt2, 0, kc2, 0};
     }
   }
 }
@@ -379,11 +376,11 @@ __global__ void __launch_bounds__(MV_THREADS, 2) trellis_moe_mv_kernel(const __g
 // (the layout fht_tile works in): block b of row r starts at rows * pad_off[b] + r * row_words(b).
 __device__ __forceinline__ int moe_pad_words(int n) { return n + (n >> 5); }
 
-constexpr int MOE_XF_THREADS = 384;
+constexpr int MOE_XF_THREADS = 256;
 
 // ---- 4: per slot  h = act(gate) * up  from w13 partials, then the w2 input transform ---------------------
 // One CTA handles `sg` consecutive slots (rows of the radix-32 tile transform).
-__global__ void __launch_bounds__(MOE_XF_THREADS, 2) moe_mid_kernel(const __grid_constant__ MoeDev M, int T, int sg,
+__global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_mid_kernel(const __grid_constant__ MoeDev M, int T, int sg,
                                                                  uint8_t* __restrict__ ws) {
   extern __shared__ float fb[];              // sg x padded(max(w13_out, inter)) transform area, then sg x inter
   const int R = T * M.top_k;
@@ -498,7 +495,7 @@ __global__ void __launch_bounds__(MOE_XF_THREADS, 2) moe_mid_kernel(const __grid
 // ---- 6: per token weighted combine ------------------------------------------------------------------------
 // The routings of a token are the rows of one tile transform (`rg` at a time); their results are summed
 // in fixed j order.
-__global__ void __launch_bounds__(MOE_XF_THREADS, 2) moe_out_kernel(const __grid_constant__ MoeDev M, int T, int rg,
+__global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_out_kernel(const __grid_constant__ MoeDev M, int T, int rg,
                                                                  const float* __restrict__ topk_w,
                                                                  const uint8_t* __restrict__ ws, uint8_t* __restrict__ y) {
   extern __shared__ float fb[];              // rg x padded(hidden)
@@ -765,14 +762,17 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   }
   {
     auto padw = [](size_t n) { return n + n / 32; };
-    const size_t budget = 100 * 1024;     // two CTAs per SM
+    const size_t budget = 74 * 1024;      // three CTAs per SM
     const size_t mid_row = 4 * (padw(std::max(d->w13_out, d->inter)) + padw(d->inter)), out_row = 4 * padw(d->hidden);
-    const size_t out_fixed = 4 * (size_t)d->hidden;
     P->mid_sg = (int)std::max<size_t>(1, std::min<size_t>(8, budget / mid_row));
-    P->out_rg = (int)std::max<size_t>(1, std::min<size_t>(std::min(8, d->top_k), (budget - out_fixed) / out_row));
+    P->out_rg = (int)std::max<size_t>(1, std::min<size_t>(std::min(8, d->top_k), budget / out_row));
+    // running sums between passes are only needed when one pass cannot hold all routings of a token
+    const size_t out_fixed = P->out_rg < d->top_k ? 4 * (size_t)d->hidden : 0;
     P->mid_smem = P->mid_sg * mid_row;
     P->out_smem = P->out_rg * out_row + out_fixed;
-    if (cudaFuncSetAttribute(moe_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P->mid_smem) != cudaSuccess ||
+    if (cudaFuncSetAttribute(moe_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)((4 * d->num_experts + 1) * sizeof(int))) != cudaSuccess ||
+        cudaFuncSetAttribute(moe_mid_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P->mid_smem) != cudaSuccess ||
         cudaFuncSetAttribute(moe_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)P->out_smem) != cudaSuccess) {
       delete P;
       return moe_fail(GLQB_E_CUDA, "moe_plan_create: %s", cudaGetErrorString(cudaGetLastError()));
@@ -813,8 +813,7 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   if (P->gemm_ok && (long long)tokens * P->dev.top_k >= (long long)P->dev.E * moe_gemm_min_avg()) {
     const MoeDev& G = P->devg;
     const int R = tokens * G.top_k;
-    moe_group_kernel<<<1, 1024, 2 * G.E * sizeof(int), st>>>(G, topk_ids, tokens, ws);
-    moe_gemm_setup_kernel<<<1, 1024, 0, st>>>(G, tokens, ws);
+    moe_group_kernel<<<1, 1024, (4 * G.E + 1) * sizeof(int), st>>>(G, topk_ids, tokens, ws);
     moe_rht_in_gemm_kernel<<<tokens, std::max(64, std::min(1024, G.hidden / 8)), G.hidden * 4, st>>>(
         G, reinterpret_cast<const uint8_t*>(x), ws);
     int* status = reinterpret_cast<int*>(ws + G.o_status);
@@ -834,7 +833,7 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   }
   const MoeDev& M = P->dev;
   const int R = tokens * M.top_k;
-  moe_group_kernel<<<1, 1024, 2 * M.E * sizeof(int), st>>>(M, topk_ids, tokens, ws);
+  moe_group_kernel<<<1, 1024, (4 * M.E + 1) * sizeof(int), st>>>(M, topk_ids, tokens, ws);
   moe_rht_in_kernel<<<tokens, std::max(64, std::min(1024, M.hidden / 8)), M.hidden * 4, st>>>(
       M, reinterpret_cast<const uint8_t*>(x), ws);
   MoeMvArgs A;
