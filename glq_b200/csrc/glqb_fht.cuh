@@ -216,4 +216,94 @@ __device__ __forceinline__ void fht_tile(float* smem, int logbs, int rows, Load3
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Same transform with vector output: after the last butterfly pass the finished values go back to shared
+// memory and every thread hands 8 consecutive values of one array to `store8(row, i0, v, count)` (count < 8
+// only for arrays shorter than 8), so the caller can scale, convert and store them with one 16-byte access.
+// The stages after the first five are split evenly over one or two strided in-place passes
+// (2048 values: 5 + 3 + 3, 8192: 5 + 4 + 4), which keeps every pass at 8 or more values per thread.
+// ---------------------------------------------------------------------------------------------------
+template <int R>
+__device__ __forceinline__ void fht_strided_pass(float* smem, int logbs, int done, int rows, int row_words) {
+  const int S = 1 << done;
+  const int glog = logbs - R;
+  const int total = rows << glog;
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int row = o >> glog, oo = o & ((1 << glog) - 1);
+    const int low = oo & (S - 1), high = oo >> done;
+    float* p = smem + row * row_words + fht_pad(((high << (done + R)) | low));
+    const int step = S + (S >> 5);             // S is a multiple of 32: the padding grows linearly with k
+    float v[1 << R];
+#pragma unroll
+    for (int k = 0; k < (1 << R); ++k) v[k] = p[k * step];
+    fht_regs<R>(v);
+#pragma unroll
+    for (int k = 0; k < (1 << R); ++k) p[k * step] = v[k];
+  }
+}
+
+__device__ __forceinline__ void fht_strided_dispatch(float* smem, int logbs, int done, int r, int rows, int row_words) {
+  switch (r) {
+    case 1: fht_strided_pass<1>(smem, logbs, done, rows, row_words); break;
+    case 2: fht_strided_pass<2>(smem, logbs, done, rows, row_words); break;
+    case 3: fht_strided_pass<3>(smem, logbs, done, rows, row_words); break;
+    case 4: fht_strided_pass<4>(smem, logbs, done, rows, row_words); break;
+    default: fht_strided_pass<5>(smem, logbs, done, rows, row_words); break;
+  }
+}
+
+template <class Load32, class Load1, class Store8>
+__device__ __forceinline__ void fht_tile8(float* smem, int logbs, int rows, Load32 load32, Load1 load1, Store8 store8) {
+  const int bs = 1 << logbs;
+  if (logbs < 5) {
+    for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+      float v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) v[k] = k < bs ? load1(row, k) : 0.f;
+      for (int h = 1; h < bs; h <<= 1)
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (!(k & h) && (k | h) < bs) { const float a = v[k], b = v[k | h]; v[k] = a + b; v[k | h] = a - b; }
+      const float lo[8] = {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]};
+      const float hi[8] = {v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15]};
+      store8(row, 0, lo, bs < 8 ? bs : 8);
+      if (bs > 8) store8(row, 8, hi, bs - 8);
+    }
+    return;
+  }
+  const int row_words = bs + (bs >> 5);
+  const int slog = logbs - 5;
+  const int nseg = rows << slog;
+  for (int s = threadIdx.x; s < nseg; s += blockDim.x) {
+    const int row = s >> slog, i0 = (s & ((1 << slog) - 1)) << 5;
+    float v[32];
+    load32(row, i0, v);
+    fht_regs<5>(v);
+    float* p = smem + row * row_words + fht_pad(i0);
+#pragma unroll
+    for (int k = 0; k < 32; ++k) p[k] = v[k];
+  }
+  __syncthreads();
+  const int rem = logbs - 5;
+  if (rem > 0) {
+    const int r1 = rem <= 5 ? rem : (rem + 1) >> 1;
+    fht_strided_dispatch(smem, logbs, 5, r1, rows, row_words);
+    __syncthreads();
+    if (rem > r1) {
+      fht_strided_dispatch(smem, logbs, 5 + r1, rem - r1, rows, row_words);
+      __syncthreads();
+    }
+  }
+  const int plog = logbs - 3;                  // log2(8-value pieces per array)
+  const int total = rows << plog;
+  for (int o = threadIdx.x; o < total; o += blockDim.x) {
+    const int row = o >> plog, i0 = (o & ((1 << plog) - 1)) << 3;
+    const float* p = smem + row * row_words + fht_pad(i0);
+    float v[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] = p[k];
+    store8(row, i0, v, 8);
+  }
+}
+
 }  // namespace glqb

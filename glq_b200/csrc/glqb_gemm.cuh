@@ -138,7 +138,7 @@ __device__ __forceinline__ uint32_t sw128_offset(int r, int e) {
 // One CTA per (layer, Hadamard block, tile of tokens); tiles ordered [n_tile][k_chunk], each TN*128
 // bytes.  Columns past n (the last chunk of a layer whose n is not a multiple of 64) are written as
 // zeros by the CTAs of the last block.
-static __global__ void __launch_bounds__(RHT_THREADS) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
+static __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_gemm_kernel(const DevLinear* __restrict__ layers,
                                                                   const RhtItem* __restrict__ items,
                                                                   const uint8_t* __restrict__ x_base,
                                                                   uint8_t* __restrict__ ws) {
@@ -172,7 +172,24 @@ static __global__ void __launch_bounds__(RHT_THREADS) rht_in_gemm_kernel(const D
     for (int o = threadIdx.x; o < total; o += blockDim.x) store1(o >> logbs, o & (bs - 1), load1(o >> logbs, o & (bs - 1)));
   } else {
     auto load32 = [&](int row, int i0, float (&v)[32]) { rht_load_x32(L, x_base, it.tok0 + row, off + i0, vec_ok, v); };
-    fht_tile(fbuf, logbs, it.ntok, load32, load1, store1);
+    uint8_t* xr = ws + L.xr_off;
+    const int tok0 = it.tok0;
+    // 8 consecutive columns are one 16-byte unit of a swizzled 128-byte row
+    auto store8 = [&](int row, int i0, const float (&v)[8], int count) {
+      const int col0 = off + i0;
+      if (count == 8 && (col0 & 7) == 0) {
+        const int token = tok0 + row;
+        const int nt = token / tn, r = token - nt * tn;
+        const __half2 a = __floats2half2_rn(v[0] * rs, v[1] * rs), b = __floats2half2_rn(v[2] * rs, v[3] * rs);
+        const __half2 c = __floats2half2_rn(v[4] * rs, v[5] * rs), d = __floats2half2_rn(v[6] * rs, v[7] * rs);
+        *reinterpret_cast<uint4*>(xr + ((size_t)nt * kchunks + (col0 >> 6)) * tn * 128 + sw128_offset(r, col0 & 63)) =
+            make_uint4(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b),
+                       *reinterpret_cast<const uint32_t*>(&c), *reinterpret_cast<const uint32_t*>(&d));
+      } else {
+        for (int k = 0; k < count; ++k) store1(row, i0 + k, v[k]);
+      }
+    };
+    fht_tile8(fbuf, logbs, it.ntok, load32, load1, store8);
   }
   if (it.block == L.nbn - 1) {
     const int padc = kchunks * GM_TILE_K - L.n;

@@ -114,7 +114,13 @@ __device__ __forceinline__ long long xr_index_e8(long long token, int col, int n
 // fused with the global loads, last pass with the stores).
 // PLAIN_F32: write fp32 in natural order instead (the unfused input_rht op).
 // ---------------------------------------------------------------------------------------------
-constexpr int RHT_THREADS = 512;
+#ifndef GLQB_RHT_THREADS
+#define GLQB_RHT_THREADS 512
+#endif
+#ifndef GLQB_RHT_MINB
+#define GLQB_RHT_MINB 2
+#endif
+constexpr int RHT_THREADS = GLQB_RHT_THREADS;
 
 // 32 consecutive activations of one token, times SV, zero past in_features
 __device__ __forceinline__ void rht_load_x32(const DevLinear& L, const uint8_t* x_base, long long token, int col0,
@@ -146,7 +152,7 @@ __device__ __forceinline__ void rht_load_x32(const DevLinear& L, const uint8_t* 
 }
 
 template <bool PLAIN_F32>
-__global__ void __launch_bounds__(RHT_THREADS) rht_in_kernel(const DevLinear* __restrict__ layers,
+__global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_kernel(const DevLinear* __restrict__ layers,
                                                              const RhtItem* __restrict__ items,
                                                              const uint8_t* __restrict__ x_base,
                                                              uint8_t* __restrict__ ws) {
@@ -196,7 +202,7 @@ __global__ void __launch_bounds__(RHT_THREADS) rht_in_kernel(const DevLinear* __
 // FROM_F32: input is a plain fp32 (batch, m) matrix (the unfused output_rht op).
 // ---------------------------------------------------------------------------------------------
 template <bool FROM_F32>
-__global__ void __launch_bounds__(RHT_THREADS) rht_out_kernel(const DevLinear* __restrict__ layers,
+__global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_kernel(const DevLinear* __restrict__ layers,
                                                               const RhtItem* __restrict__ items,
                                                               const uint8_t* __restrict__ ws,
                                                               uint8_t* __restrict__ y_base,
@@ -240,22 +246,26 @@ __global__ void __launch_bounds__(RHT_THREADS) rht_out_kernel(const DevLinear* _
     return;
   }
   const bool vec_ok = (m & 3) == 0 && (off & 3) == 0;
+  const int tok0 = it.tok0;
   auto load32 = [&](int trow, int i0, float (&v)[32]) {
     const int row0 = off + i0;
-    const long long token = it.tok0 + trow;
+    const long long token = tok0 + trow;
     if (!vec_ok || row0 + 32 > m) {
 #pragma unroll
       for (int k = 0; k < 32; ++k) v[k] = load1(trow, i0 + k);
       return;
     }
     const float* src = FROM_F32 ? (yrht_in + token * m + row0) : (part + token * m + row0);
+    // the partial-sum count is a property of the strip (16 or 32 rows): two lookups cover the segment
+    int cnt_lo = 1, cnt_hi = 1;
+    if constexpr (!FROM_F32) { cnt_lo = slots_of(row0); cnt_hi = slots_of(row0 + 16); }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
       if constexpr (FROM_F32) {
         s = *reinterpret_cast<const float4*>(src + 4 * j);
       } else {
-        const int cnt = slots_of(row0 + 4 * j);
+        const int cnt = j < 4 ? cnt_lo : cnt_hi;
         for (int k = 0; k < cnt; ++k) {
           const float4 t = *reinterpret_cast<const float4*>(src + 4 * j + k * slot_stride);
           s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
@@ -271,13 +281,46 @@ __global__ void __launch_bounds__(RHT_THREADS) rht_out_kernel(const DevLinear* _
   };
   const float rs = rsqrtf((float)bs);
   const int out_f = L.out_f, y_dtype = L.y_dtype;
-  auto store1 = [&](int trow, int i, float val) {
-    const int row = off + i;
-    if (row < out_f)
-      store_act(y_base, L.y_off + (long long)(it.tok0 + trow) * L.y_stride + row, y_dtype,
-                val * rs * __half2float(L.su[row]));
+  const long long y_off = L.y_off, y_stride = L.y_stride;
+  const __half* su = L.su;
+  // 8 outputs per call: one 16-byte SU load and one 16-byte (32-byte for fp32) store when aligned
+  const bool su_vec = (off & 7) == 0 && (reinterpret_cast<uintptr_t>(su) & 15) == 0;
+  const bool y_vec = (reinterpret_cast<uintptr_t>(y_base) & 15) == 0;
+  auto store8 = [&](int trow, int i0, const float (&v)[8], int count) {
+    const int row0 = off + i0;
+    const long long o = y_off + (long long)(tok0 + trow) * y_stride + row0;
+    if (count == 8 && row0 + 8 <= out_f && su_vec && y_vec && (o & 7) == 0) {
+      const uint4 s4 = *reinterpret_cast<const uint4*>(su + row0);
+      const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+      const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+      const float2 s2 = __half22float2(*reinterpret_cast<const __half2*>(&s4.z));
+      const float2 s3 = __half22float2(*reinterpret_cast<const __half2*>(&s4.w));
+      const float r[8] = {v[0] * rs * s0.x, v[1] * rs * s0.y, v[2] * rs * s1.x, v[3] * rs * s1.y,
+                          v[4] * rs * s2.x, v[5] * rs * s2.y, v[6] * rs * s3.x, v[7] * rs * s3.y};
+      if (y_dtype == GLQB_DT_F32) {
+        float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(y_base) + o);
+        dst[0] = make_float4(r[0], r[1], r[2], r[3]);
+        dst[1] = make_float4(r[4], r[5], r[6], r[7]);
+      } else if (y_dtype == GLQB_DT_F16) {
+        const __half2 a = __floats2half2_rn(r[0], r[1]), b = __floats2half2_rn(r[2], r[3]);
+        const __half2 c = __floats2half2_rn(r[4], r[5]), d = __floats2half2_rn(r[6], r[7]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y_base) + o) =
+            make_uint4(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b),
+                       *reinterpret_cast<const uint32_t*>(&c), *reinterpret_cast<const uint32_t*>(&d));
+      } else {
+        const __nv_bfloat162 a = __floats2bfloat162_rn(r[0], r[1]), b = __floats2bfloat162_rn(r[2], r[3]);
+        const __nv_bfloat162 c = __floats2bfloat162_rn(r[4], r[5]), d = __floats2bfloat162_rn(r[6], r[7]);
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y_base) + o) =
+            make_uint4(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b),
+                       *reinterpret_cast<const uint32_t*>(&c), *reinterpret_cast<const uint32_t*>(&d));
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k < count && row0 + k < out_f) store_act(y_base, o + k, y_dtype, v[k] * rs * __half2float(su[row0 + k]));
+    }
   };
-  fht_tile(fbuf, logbs, it.ntok, load32, load1, store1);
+  fht_tile8(fbuf, logbs, it.ntok, load32, load1, store8);
 }
 
 // ---------------------------------------------------------------------------------------------
