@@ -252,25 +252,11 @@ __device__ __forceinline__ void fht_strided_dispatch(float* smem, int logbs, int
   }
 }
 
-template <class Load32, class Load1, class Store8>
-__device__ __forceinline__ void fht_tile8(float* smem, int logbs, int rows, Load32 load32, Load1 load1, Store8 store8) {
+// The passes alone, for arrays of 32 values or more: on return (after a __syncthreads) value i of array `row`
+// sits at smem[row * (bs + bs / 32) + fht_pad(i)].
+template <class Load32>
+__device__ __forceinline__ void fht_tile_core(float* smem, int logbs, int rows, Load32 load32) {
   const int bs = 1 << logbs;
-  if (logbs < 5) {
-    for (int row = threadIdx.x; row < rows; row += blockDim.x) {
-      float v[16];
-#pragma unroll
-      for (int k = 0; k < 16; ++k) v[k] = k < bs ? load1(row, k) : 0.f;
-      for (int h = 1; h < bs; h <<= 1)
-#pragma unroll
-        for (int k = 0; k < 16; ++k)
-          if (!(k & h) && (k | h) < bs) { const float a = v[k], b = v[k | h]; v[k] = a + b; v[k | h] = a - b; }
-      const float lo[8] = {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]};
-      const float hi[8] = {v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15]};
-      store8(row, 0, lo, bs < 8 ? bs : 8);
-      if (bs > 8) store8(row, 8, hi, bs - 8);
-    }
-    return;
-  }
   const int row_words = bs + (bs >> 5);
   const int slog = logbs - 5;
   const int nseg = rows << slog;
@@ -294,6 +280,29 @@ __device__ __forceinline__ void fht_tile8(float* smem, int logbs, int rows, Load
       __syncthreads();
     }
   }
+}
+
+template <class Load32, class Load1, class Store8>
+__device__ __forceinline__ void fht_tile8(float* smem, int logbs, int rows, Load32 load32, Load1 load1, Store8 store8) {
+  const int bs = 1 << logbs;
+  if (logbs < 5) {
+    for (int row = threadIdx.x; row < rows; row += blockDim.x) {
+      float v[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) v[k] = k < bs ? load1(row, k) : 0.f;
+      for (int h = 1; h < bs; h <<= 1)
+#pragma unroll
+        for (int k = 0; k < 16; ++k)
+          if (!(k & h) && (k | h) < bs) { const float a = v[k], b = v[k | h]; v[k] = a + b; v[k | h] = a - b; }
+      const float lo[8] = {v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]};
+      const float hi[8] = {v[8], v[9], v[10], v[11], v[12], v[13], v[14], v[15]};
+      store8(row, 0, lo, bs < 8 ? bs : 8);
+      if (bs > 8) store8(row, 8, hi, bs - 8);
+    }
+    return;
+  }
+  const int row_words = bs + (bs >> 5);
+  fht_tile_core(smem, logbs, rows, load32);
   const int plog = logbs - 3;                  // log2(8-value pieces per array)
   const int total = rows << plog;
   for (int o = threadIdx.x; o < total; o += blockDim.x) {

@@ -378,11 +378,22 @@ __device__ __forceinline__ int moe_pad_words(int n) { return n + (n >> 5); }
 
 constexpr int MOE_XF_THREADS = 256;
 
+// 8 fp16 values (16-byte aligned) as floats
+__device__ __forceinline__ void load8_half(const __half* p, float (&f)[8]) {
+  const uint4 t = *reinterpret_cast<const uint4*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&t.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&t.y));
+  const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&t.z));
+  const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&t.w));
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+__device__ __forceinline__ float round_half(float v) { return __half2float(__float2half_rn(v)); }
+
 // ---- 4: per slot  h = act(gate) * up  from w13 partials, then the w2 input transform ---------------------
 // One CTA handles `sg` consecutive slots (rows of the radix-32 tile transform).
 __global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_mid_kernel(const __grid_constant__ MoeDev M, int T, int sg,
-                                                                 uint8_t* __restrict__ ws) {
-  extern __shared__ float fb[];              // sg x padded(max(w13_out, inter)) transform area, then sg x inter
+                                                                    uint8_t* __restrict__ ws) {
+  extern __shared__ float fb[];              // sg x padded(max(w13_out, inter)) transform area, then sg x padded(inter)
   const int R = T * M.top_k;
   const int* g_count = reinterpret_cast<const int*>(ws + M.o_count);
   const int* g_base = reinterpret_cast<const int*>(ws + M.o_base);
@@ -398,93 +409,92 @@ __global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_mid_kernel(const __grid
     row_wsc[threadIdx.x] = M.w13_wscale[e];
   }
   __syncthreads();
+  const int hrw = moe_pad_words(M.inter);
   float* hbuf = fb + sg * moe_pad_words(max(M.w13_out, M.inter));
   const float* part1 = reinterpret_cast<const float*>(ws + M.o_part1);
-  auto none1 = [](int, int) -> float { return 0.f; };
+  const long long kstride = (long long)R * M.w13_out;
+  const int kch = M.kch13, w13_out = M.w13_out, inter = M.inter;
 
-  // -- output transform of w13: partial sums -> SU * H(Wscale * y~), rounded through fp16 (the reference's
-  //    w13 op returns fp16: glq_vllm/fused_moe_method.py:412-421); results stay in shared memory
+  // -- output transform of w13 (Wscale applied on the way in); results stay in shared memory
   int poff = 0;
   for (int b = 0; b < M.nb_m13; ++b) {
-    const int logbs = M.log_m13[b], off = M.off_m13[b], rw = moe_pad_words(1 << logbs);
-    float* reg = fb + sg * poff;
-    const float rs = rsqrtf((float)(1 << logbs));
+    const int logbs = M.log_m13[b], off = M.off_m13[b];
     auto load32 = [&](int row, int i0, float (&v)[32]) {
-      const int slot = slot0 + row;
       const float wsc = row_wsc[row];
-      const float* src = part1 + (long long)slot * M.w13_out + off + i0;
+      const float* src = part1 + (long long)(slot0 + row) * w13_out + off + i0;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int k = 0; k < M.kch13; ++k) {
-          const float4 t4 = *reinterpret_cast<const float4*>(src + 4 * j + (long long)k * R * M.w13_out);
+        for (int k = 0; k < kch; ++k) {
+          const float4 t4 = *reinterpret_cast<const float4*>(src + 4 * j + k * kstride);
           a.x += t4.x; a.y += t4.y; a.z += t4.z; a.w += t4.w;
         }
         v[4 * j] = a.x * wsc; v[4 * j + 1] = a.y * wsc; v[4 * j + 2] = a.z * wsc; v[4 * j + 3] = a.w * wsc;
       }
     };
-    auto store1 = [&](int row, int i, float val) {
-      const __half su = M.w13_su[(long long)row_e[row] * M.w13_out + off + i];
-      reg[row * rw + fht_pad(i)] = __half2float(__float2half_rn(val * rs * __half2float(su)));
-    };
-    fht_tile(reg, logbs, nrow, load32, none1, store1);
-    poff += rw;
+    fht_tile_core(fb + sg * poff, logbs, nrow, load32);
+    poff += moe_pad_words(1 << logbs);
   }
-  __syncthreads();
-  // -- activation: column c of the w13 output sits in block b(c) at padded offset
-  auto y13 = [&](int row, int c) -> float {
-    int po = 0;
-    for (int b = 0; b < M.nb_m13; ++b) {
-      const int bs = 1 << M.log_m13[b];
-      if (c < M.off_m13[b] + bs) return fb[sg * po + row * moe_pad_words(bs) + fht_pad(c - M.off_m13[b])];
-      po += moe_pad_words(bs);
-    }
-    return 0.f;
+  // -- 8 columns at a time: SU and 1/sqrt(bs), fp16 rounding (the reference's w13 op returns fp16:
+  //    glq_vllm/fused_moe_method.py:412-421), gated activation, fp16 rounding, SV of w2
+  auto y13_8 = [&](int row, int c, float (&f)[8]) {     // columns c .. c+7 of the w13 output (c % 8 == 0)
+    int po = 0, b = 0;
+    while (b + 1 < M.nb_m13 && c >= M.off_m13[b] + (1 << M.log_m13[b])) { po += moe_pad_words(1 << M.log_m13[b]); ++b; }
+    const int bs = 1 << M.log_m13[b];
+    const float rs = rsqrtf((float)bs);
+    const float* p = fb + sg * po + row * moe_pad_words(bs) + fht_pad(c - M.off_m13[b]);
+    float su[8];
+    load8_half(M.w13_su + (long long)row_e[row] * w13_out + c, su);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = round_half(p[k] * rs * su[k]);
   };
-  const int hrw = moe_pad_words(M.inter);
-  for (int o = threadIdx.x; o < nrow * M.inter; o += blockDim.x) {
-    const int row = o / M.inter, i = o - row * M.inter;
-    const float a = moe_act(y13(row, i), M.act);
-    const float h = M.gated ? a * y13(row, M.inter + i) : a;
-    hbuf[row * hrw + fht_pad(i)] = __half2float(__float2half_rn(h)) * __half2float(M.w2_sv[i]);
+  const int per_row = inter >> 3;
+  for (int o = threadIdx.x; o < nrow * per_row; o += blockDim.x) {
+    const int row = o / per_row, i = (o - row * per_row) * 8;
+    float g[8], u[8], sv[8];
+    y13_8(row, i, g);
+    load8_half(M.w2_sv + i, sv);
+    if (M.gated) y13_8(row, inter + i, u);
+    float* dst = hbuf + row * hrw + fht_pad(i);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float a = moe_act(g[k], M.act);
+      dst[k] = round_half(M.gated ? a * u[k] : a) * sv[k];
+    }
   }
   __syncthreads();
-  // -- input transform of w2, results back into the transform area
+  // -- input transform of w2, back into the transform area, then 16-byte stores
   poff = 0;
   for (int b = 0; b < M.nb_n2; ++b) {
-    const int logbs = M.log_n2[b], off = M.off_n2[b], rw = moe_pad_words(1 << logbs);
-    float* reg = fb + sg * poff;
-    const float rs = rsqrtf((float)(1 << logbs));
+    const int logbs = M.log_n2[b], off = M.off_n2[b];
     auto load32 = [&](int row, int i0, float (&v)[32]) {
       const float* src = hbuf + row * hrw + fht_pad(off + i0);    // off and i0 are multiples of 32
 #pragma unroll
       for (int k = 0; k < 32; ++k) v[k] = src[k];
     };
-    auto store1 = [&](int row, int i, float val) { reg[row * rw + fht_pad(i)] = val * rs; };
-    fht_tile(reg, logbs, nrow, load32, none1, store1);
-    poff += rw;
+    fht_tile_core(fb + sg * poff, logbs, nrow, load32);
+    poff += moe_pad_words(1 << logbs);
   }
-  __syncthreads();
-  // -- store: 8 consecutive columns per thread
   poff = 0;
   const int* trow = reinterpret_cast<const int*>(ws + M.o_trow);
   for (int b = 0; b < M.nb_n2; ++b) {
     const int bs = 1 << M.log_n2[b], off = M.off_n2[b], rw = moe_pad_words(bs);
     const float* reg = fb + sg * poff;
-    const int per_row = bs >> 3;
-    for (int o = threadIdx.x; o < nrow * per_row; o += blockDim.x) {
-      const int row = o / per_row, i = (o - row * per_row) * 8;
+    const float rs = rsqrtf((float)bs);
+    const int pr = bs >> 3;
+    for (int o = threadIdx.x; o < nrow * pr; o += blockDim.x) {
+      const int row = o / pr, i = (o - row * pr) * 8;
       const float* src = reg + row * rw + fht_pad(i);
       const int slot = slot0 + row, col = off + i;
       if (M.gemm) {
-        moe_store_tile16(ws + M.o_xr2, trow[slot], M.inter / GM_TILE_K, col >> 3, pack8_half(src, 1.0f));
+        moe_store_tile16(ws + M.o_xr2, trow[slot], inter / GM_TILE_K, col >> 3, pack8_half(src, rs));
       } else {
-        __half2* out = reinterpret_cast<__half2*>(ws + M.o_xr2) + (long long)slot * M.inter;
+        __half2* out = reinterpret_cast<__half2*>(ws + M.o_xr2) + (long long)slot * inter;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const int c = col + k;
           const int pos = (c & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(c & 31);
-          out[pos >> 1] = __halves2half2(__float2half_rn(src[k]), __float2half_rn(0.f));
+          out[pos >> 1] = __halves2half2(__float2half_rn(src[k] * rs), __float2half_rn(0.f));
         }
       }
     }
@@ -493,18 +503,17 @@ __global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_mid_kernel(const __grid
 }
 
 // ---- 6: per token weighted combine ------------------------------------------------------------------------
-// The routings of a token are the rows of one tile transform (`rg` at a time); their results are summed
-// in fixed j order.
+// The routings of a token are the rows of one tile transform (`rg` at a time); a thread then owns 8 output
+// columns and adds the routings' results in fixed j order.
 __global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_out_kernel(const __grid_constant__ MoeDev M, int T, int rg,
-                                                                 const float* __restrict__ topk_w,
-                                                                 const uint8_t* __restrict__ ws, uint8_t* __restrict__ y) {
-  extern __shared__ float fb[];              // rg x padded(hidden)
+                                                                    const float* __restrict__ topk_w,
+                                                                    const uint8_t* __restrict__ ws, uint8_t* __restrict__ y) {
+  extern __shared__ float fb[];              // rg x padded(hidden) (+ hidden floats when several passes are needed)
   const int t = blockIdx.x;
   const int R = T * M.top_k;
   const int* slot_of = reinterpret_cast<const int*>(ws + M.o_slot_of);
   const int* route_exp = reinterpret_cast<const int*>(ws + M.o_route_exp);
   const float* part2 = reinterpret_cast<const float*>(ws + M.o_part2);
-  auto none1 = [](int, int) -> float { return 0.f; };
   __shared__ int row_slot[64], row_e[64];    // per routing j of this token (top_k <= 64)
   __shared__ float row_wsc[64], row_w[64];
   if (threadIdx.x < M.top_k) {
@@ -517,13 +526,14 @@ __global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_out_kernel(const __grid
   }
   __syncthreads();
   float* accs = fb + rg * moe_pad_words(M.hidden);   // running sums over the passes, hidden floats
+  const int hidden = M.hidden, kch = M.kch2;
+  const long long kstride = (long long)R * hidden;
+  const bool y_vec = (reinterpret_cast<uintptr_t>(y) & 15) == 0;
   for (int j0 = 0; j0 < M.top_k; j0 += rg) {
     const int nrow = min(rg, M.top_k - j0);
     int poff = 0;
     for (int b = 0; b < M.nb_m2; ++b) {
-      const int logbs = M.log_m2[b], off = M.off_m2[b], rw = moe_pad_words(1 << logbs);
-      float* reg = fb + rg * poff;
-      const float rs = rsqrtf((float)(1 << logbs));
+      const int logbs = M.log_m2[b], off = M.off_m2[b];
       auto load32 = [&](int row, int i0, float (&v)[32]) {
         const int slot = row_slot[j0 + row];
         if (slot < 0) {
@@ -532,41 +542,61 @@ __global__ void __launch_bounds__(MOE_XF_THREADS, 3) moe_out_kernel(const __grid
           return;
         }
         const float wsc = row_wsc[j0 + row];
-        const float* src = part2 + (long long)slot * M.hidden + off + i0;
+        const float* src = part2 + (long long)slot * hidden + off + i0;
 #pragma unroll
         for (int jj = 0; jj < 8; ++jj) {
           float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int k = 0; k < M.kch2; ++k) {
-            const float4 t4 = *reinterpret_cast<const float4*>(src + 4 * jj + (long long)k * R * M.hidden);
+          for (int k = 0; k < kch; ++k) {
+            const float4 t4 = *reinterpret_cast<const float4*>(src + 4 * jj + k * kstride);
             a.x += t4.x; a.y += t4.y; a.z += t4.z; a.w += t4.w;
           }
           v[4 * jj] = a.x * wsc; v[4 * jj + 1] = a.y * wsc; v[4 * jj + 2] = a.z * wsc; v[4 * jj + 3] = a.w * wsc;
         }
       };
-      auto store1 = [&](int row, int i, float val) {
-        float r = 0.f;
-        if (row_slot[j0 + row] >= 0) {
-          // the reference's w2 op returns fp16 before the weighted sum
-          const __half su = M.w2_su[(long long)row_e[j0 + row] * M.hidden + off + i];
-          r = __half2float(__float2half_rn(val * rs * __half2float(su)));
-        }
-        reg[row * rw + fht_pad(i)] = r;
-      };
-      fht_tile(reg, logbs, nrow, load32, none1, store1);
-      poff += rw;
+      fht_tile_core(fb + rg * poff, logbs, nrow, load32);
+      poff += moe_pad_words(1 << logbs);
     }
-    __syncthreads();
-    const bool last = j0 + rg >= M.top_k;
-    for (int col = threadIdx.x; col < M.hidden; col += blockDim.x) {
+    const bool first = j0 == 0, last = j0 + rg >= M.top_k;
+    for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
       int po = 0, b = 0;
-      while (b + 1 < M.nb_m2 && col >= M.off_m2[b] + (1 << M.log_m2[b])) { po += moe_pad_words(1 << M.log_m2[b]); ++b; }
-      const int rw = moe_pad_words(1 << M.log_m2[b]);
-      const float* reg = fb + rg * po + fht_pad(col - M.off_m2[b]);
-      float a = j0 ? accs[col] : 0.f;
-      for (int row = 0; row < nrow; ++row)
-        if (row_slot[j0 + row] >= 0) a += row_w[j0 + row] * reg[row * rw];
-      if (last) store_act(y, (long long)t * M.hidden + col, M.y_dtype, a);
-      else accs[col] = a;
+      while (b + 1 < M.nb_m2 && c >= M.off_m2[b] + (1 << M.log_m2[b])) { po += moe_pad_words(1 << M.log_m2[b]); ++b; }
+      const int bs = 1 << M.log_m2[b], rw = moe_pad_words(bs);
+      const float rs = rsqrtf((float)bs);
+      const float* reg = fb + rg * po + fht_pad(c - M.off_m2[b]);
+      float a[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) a[k] = first ? 0.f : accs[c + k];
+      for (int row = 0; row < nrow; ++row) {
+        if (row_slot[j0 + row] < 0) continue;
+        float su[8];
+        load8_half(M.w2_su + (long long)row_e[j0 + row] * hidden + c, su);
+        const float w = row_w[j0 + row];
+        const float* p = reg + row * rw;
+        // the reference's w2 op returns fp16 before the weighted sum
+#pragma unroll
+        for (int k = 0; k < 8; ++k) a[k] += w * round_half(p[k] * rs * su[k]);
+      }
+      if (!last) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) accs[c + k] = a[k];
+      } else if (y_vec && M.y_dtype != GLQB_DT_F32) {
+        uint4 o4;
+        if (M.y_dtype == GLQB_DT_F16) {
+          const __half2 h0 = __floats2half2_rn(a[0], a[1]), h1 = __floats2half2_rn(a[2], a[3]);
+          const __half2 h2 = __floats2half2_rn(a[4], a[5]), h3 = __floats2half2_rn(a[6], a[7]);
+          o4 = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                          *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+        } else {
+          const __nv_bfloat162 h0 = __floats2bfloat162_rn(a[0], a[1]), h1 = __floats2bfloat162_rn(a[2], a[3]);
+          const __nv_bfloat162 h2 = __floats2bfloat162_rn(a[4], a[5]), h3 = __floats2bfloat162_rn(a[6], a[7]);
+          o4 = make_uint4(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1),
+                          *reinterpret_cast<const uint32_t*>(&h2), *reinterpret_cast<const uint32_t*>(&h3));
+        }
+        *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(y) + (long long)t * hidden + c) = o4;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) store_act(y, (long long)t * hidden + c + k, M.y_dtype, a[k]);
+      }
     }
     __syncthreads();
   }
@@ -664,6 +694,9 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   if (!d->w13_packed || !d->w2_packed || !d->w13_su || !d->w13_sv || !d->w2_su || !d->w2_sv || !d->w13_wscale ||
       !d->w2_wscale)
     return moe_fail(GLQB_E_INVALID, "moe_plan_create: null weight pointer");
+  if ((reinterpret_cast<uintptr_t>(d->w13_su) | reinterpret_cast<uintptr_t>(d->w13_sv) | reinterpret_cast<uintptr_t>(d->w2_su) |
+       reinterpret_cast<uintptr_t>(d->w2_sv)) & 15)
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: SU/SV tensors must be 16-byte aligned");
   GlqbMoePlan* P = new GlqbMoePlan();
   P->desc = *d;
   MoeDev& M = P->dev;
