@@ -543,7 +543,9 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
 // For large token counts the fused kernel would decode every weight tile once per token tile; this
 // kernel decodes each 128 x 64 tile ONCE into the exact shared-memory image (K-major, 128-byte swizzle),
 // [m_tile][k_chunk] x 16 KiB, which glq_gemm_kernel<2,...> then fetches with one bulk copy per stage.
-// Thread (row = tid >> 1, half = tid & 1) expands 4 indices; two threads write one full 128-byte line.
+// A CTA takes 128 rows x 4 consecutive chunks; thread (row = tid >> 1, half = tid & 1) reads the 16 indices
+// of two chunks with two 16-byte loads per stage (the two threads of a row read 64 contiguous bytes), keeps
+// all 16 * NS gathers in flight, and writes two full 128-byte tile rows.
 template <int NS>
 __global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restrict__ layers, int first, int count,
                                                        uint8_t* __restrict__ ws) {
@@ -552,47 +554,76 @@ __global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restri
     const DevLinear& L = layers[li];
     const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
     const int m_tiles = (L.m + GM_TILE_M - 1) / GM_TILE_M;
-    const int nidx = L.n >> 3;
-    for (int t = blockIdx.x; t < m_tiles * kchunks; t += gridDim.x) {
-      const int mt = t / kchunks, kc = t - mt * kchunks;
+    const int kgroups = (kchunks + 3) >> 2;
+    const int nidx = L.n >> 3, m = L.m;
+    const bool vec_ok = (nidx & 7) == 0;                 // every row starts 16-byte aligned
+    const uint16_t* codes[NS];
+    const uint32_t* table[NS];
+    uint32_t mask[NS];
+    __half2 sc[NS];
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      codes[s] = reinterpret_cast<const uint16_t*>(L.codes[s]);
+      table[s] = L.table[s];
+      mask[s] = (uint32_t)L.table_entries[s] - 1u;
+      sc[s] = __float2half2_rn(L.stage_scale[s]);
+    }
+    uint8_t* tiles = ws + L.atile_off;
+    for (int u = blockIdx.x; u < m_tiles * kgroups; u += gridDim.x) {
+      const int mt = u / kgroups, kg = u - mt * kgroups;
       const int row = mt * GM_TILE_M + row_l;
-      const bool row_ok = row < L.m;
-      const int i0 = kc * 8 + hf * 4;
-      uint32_t ent[NS][4];
+      const bool row_ok = row < m;
+      const int kc0 = kg * 4 + hf * 2;
+      uint32_t ent[NS][2][8];
 #pragma unroll
       for (int s = 0; s < NS; ++s) {
-        const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx;
-        const uint32_t mask = (uint32_t)L.table_entries[s] - 1u;
+        const uint16_t* q = codes[s] + (long long)row * nidx;
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const uint32_t idx = (row_ok && i0 + k < nidx) ? q[i0 + k] : 0u;
-          ent[s][k] = __ldg(L.table[s] + (idx & mask));
+        for (int c = 0; c < 2; ++c) {
+          const int i0 = (kc0 + c) * 8;
+          uint32_t w[4] = {0u, 0u, 0u, 0u};
+          if (row_ok && vec_ok && i0 + 8 <= nidx) {
+            const uint4 t = ld_stream_v4(q + i0);
+            w[0] = t.x; w[1] = t.y; w[2] = t.z; w[3] = t.w;
+          } else if (row_ok) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              if (i0 + k < nidx) w[k >> 1] |= (uint32_t)q[i0 + k] << ((k & 1) * 16);
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            ent[s][c][k] = __ldg(table[s] + (((w[k >> 1] >> ((k & 1) * 16)) & 0xFFFFu) & mask[s]));
         }
       }
-      uint8_t* tile = ws + L.atile_off + (size_t)t * GM_A_BYTES;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        uint4 out = make_uint4(0u, 0u, 0u, 0u);
-        if (row_ok && i0 + k < nidx) {
-          uint32_t h[4];
-          e8_entry_to_half2(ent[0][k], h);
+      for (int c = 0; c < 2; ++c) {
+        const int kc = kc0 + c;
+        if (kc >= kchunks) continue;
+        uint8_t* tile = tiles + ((size_t)mt * kchunks + kc) * GM_A_BYTES;
 #pragma unroll
-          for (int s = 1; s < NS; ++s) {
-            uint32_t h2[4];
-            e8_entry_to_half2(ent[s][k], h2);
-            const __half2 sc = __float2half2_rn(L.stage_scale[s]);
+        for (int k = 0; k < 8; ++k) {
+          uint4 out = make_uint4(0u, 0u, 0u, 0u);
+          if (row_ok && kc * 8 + k < nidx) {
+            uint32_t h[4];
+            e8_entry_to_half2(ent[0][c][k], h);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&h2[j]), sc, *reinterpret_cast<const __half2*>(&h[j]));
-              h[j] = *reinterpret_cast<const uint32_t*>(&r);
+            for (int s = 1; s < NS; ++s) {
+              uint32_t h2[4];
+              e8_entry_to_half2(ent[s][c][k], h2);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __half2 r = __hfma2(*reinterpret_cast<const __half2*>(&h2[j]), sc[s], *reinterpret_cast<const __half2*>(&h[j]));
+                h[j] = *reinterpret_cast<const uint32_t*>(&r);
+              }
             }
+            // natural column order inside the 16-byte chunk: (c0,c1),(c2,c3),(c4,c5),(c6,c7)
+            out.x = __byte_perm(h[0], h[1], 0x5410);
+            out.y = __byte_perm(h[2], h[3], 0x5410);
+            out.z = __byte_perm(h[0], h[1], 0x7632);
+            out.w = __byte_perm(h[2], h[3], 0x7632);
           }
-          out.x = __byte_perm(h[0], h[1], 0x5410);
-          out.y = __byte_perm(h[2], h[3], 0x5410);
-          out.z = __byte_perm(h[0], h[1], 0x7632);
-          out.w = __byte_perm(h[2], h[3], 0x7632);
+          *reinterpret_cast<uint4*>(tile + sw128_offset(row_l, k * 8)) = out;
         }
-        *reinterpret_cast<uint4*>(tile + sw128_offset(row_l, (hf * 4 + k) * 8)) = out;
       }
     }
   }
