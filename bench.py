@@ -186,15 +186,19 @@ def build_workload(name, device, world, rank, tokens=None, n_layers=None):
                 code_bytes=plan.code_bytes, flops=plan.flops, metric=metric, shape=shape, fmt=fmt, par=par)
 
 
-def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768, bits=(4,)):
+def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768, bits=(4,), world=1, rank=0):
     """MoE step of BASELINE config 3: 128 experts, top-8, hidden 2048, expert intermediate 768 (gate/up fused
     2048->1536, down 768->2048), trellis 4 bpw, gelu-tanh gating.  Router logits N(0,1) (near-uniform loads) or
     a Zipf(1.2) popularity over experts."""
     import torch
     from glq_b200 import ops
     from glq_b200.plan import block_decompose
+    from glq_b200 import tp
+    E_all = E
+    e0, e1 = tp.expert_range(E_all, world, rank)
+    E = e1 - e0                                    # experts held by this rank
     gen = torch.Generator(device=device)
-    gen.manual_seed(2025)
+    gen.manual_seed(2025 + rank)                   # weights: every rank its own experts
     ri = lambda *shape: torch.randint(-32768, 32768, shape, generator=gen, device=device, dtype=torch.int32).to(torch.int16)
     sg = lambda *shape: (torch.randint(0, 2, shape, generator=gen, device=device, dtype=torch.int32) * 2 - 1).to(torch.float16)
     K = bits[0]
@@ -203,38 +207,60 @@ def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768,
               su13=sg(E, w13_out), sv13=sg(hidden), su2=sg(E, hidden), sv2=sg(inter),
               ws13=(0.5 + torch.rand(E, generator=gen, device=device)) * 0.02,
               ws2=(0.5 + torch.rand(E, generator=gen, device=device)) * 0.02)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(77)                            # tokens and routing: replicated on all ranks
     x = torch.randn(tokens, hidden, generator=gen, device=device).to(torch.bfloat16)
-    logits = torch.randn(tokens, E, generator=gen, device=device)
+    logits = torch.randn(tokens, E_all, generator=gen, device=device)
     if skew:
-        ranks = torch.arange(1, E + 1, device=device, dtype=torch.float32)
-        logits = logits * 0.0 + torch.log(ranks.pow(-skew))[None, :] - torch.log(-torch.log(torch.rand(tokens, E, generator=gen, device=device)))
+        ranks = torch.arange(1, E_all + 1, device=device, dtype=torch.float32)
+        logits = logits * 0.0 + torch.log(ranks.pow(-skew))[None, :] - torch.log(-torch.log(torch.rand(tokens, E_all, generator=gen, device=device)))
     topw, topi = torch.topk(torch.softmax(logits, -1), top_k, dim=-1)
     topw = (topw / topw.sum(-1, keepdim=True)).float().contiguous()
     sentinel = torch.zeros(E, 1, 1, dtype=torch.int16, device=device)
     bl = lambda n: torch.tensor(block_decompose(n))
 
-    def run(xin):
+    def run_local(xin, ids, tw):
         return ops.fused_moe_trellis_3inst(
-            xin, topi, topw, Wt["w13"], sentinel, Wt["su13"], Wt["sv13"], Wt["ws13"], Wt["ws13"],
+            xin, ids, tw, Wt["w13"], sentinel, Wt["su13"], Wt["sv13"], Wt["ws13"], Wt["ws13"],
             Wt["w2"], sentinel, Wt["su2"], Wt["sv2"], Wt["ws2"], Wt["ws2"], hidden, inter, w13_out,
             hidden, w13_out, inter, hidden, bl(hidden), bl(w13_out), None, None, bl(inter), bl(hidden), None, None, 1)
 
-    code_bytes = Wt["w13"].numel() * 2 + Wt["w2"].numel() * 2
+    def run(xin):
+        # expert parallel: this rank's experts for all tokens, then one all-reduce of (tokens, hidden)
+        return tp.moe_expert_parallel(run_local, xin, topi, topw, E_all)
+
+    code_bytes = (Wt["w13"].numel() * 2 + Wt["w2"].numel() * 2) * world     # all ranks together
     flops = 2 * tokens * top_k * (w13_out * hidden + hidden * inter)
     return dict(run=run, x=x, code_bytes=code_bytes, flops=flops, keep=Wt, tokens=tokens)
 
 
 def bench_moe(args, device):
-    """Separate, simpler driver for the MoE workloads (single GPU): time K steps of the op on resident inputs,
+    """Separate, simpler driver for the MoE workloads (expert parallel under torchrun): time K steps of the op on resident inputs,
     then with host activations copied in and the result copied out."""
     import torch
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
     skew = 1.2 if "zipf" in args.workload else None
     T = args.tokens or 256
-    W = build_moe(device, T, skew)
+    W = build_moe(device, T, skew, world=world, rank=rank)
     x = W["x"]
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v):
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     for _ in range(max(args.warmup, 3)):
         y = W["run"](x)
-    torch.cuda.synchronize()
+    sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(device.index or 0)
     sampler.start()
@@ -242,8 +268,8 @@ def bench_moe(args, device):
     for _ in range(args.steps):
         y = W["run"](x)
     e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
+    sync()
+    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.stop()
     hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True); hx.copy_(x)
     hy = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
@@ -253,17 +279,22 @@ def bench_moe(args, device):
         y = W["run"](x)
         hy.copy_(y, non_blocking=True)
     e1.record()
-    torch.cuda.synchronize()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
+    sync()
+    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+    if rank != 0:
+        return 0
     peak, kind = measured_peaks()
+    peak *= world
     gbs = W["code_bytes"] / (ms * 1e-3) / 1e9
     line = {"metric": "MoE grouped expert matmul: compressed-byte GB/s and TFLOP/s", "value": gbs, "unit": "GB/s",
-            "tflops": W["flops"] / (ms * 1e-3) / 1e12, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "tflops": W["flops"] / (ms * 1e-3) / 1e12, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
+            "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": f"{args.workload}: 128 experts top-8, hidden 2048, expert intermediate 768, trellis 4 bpw, "
                                    f"{T} tokens, {'Zipf(1.2) expert popularity' if skew else 'near-uniform routing'}",
-                       "cache": "302 MB of expert weights per step, larger than L2"},
+                       "cache": "302 MB of expert weights per step, larger than L2",
+                       "parallelism": f"ep{world}: experts sharded over ranks, one all-reduce of (tokens, hidden)" if world > 1 else "single"},
             "e2e": {"value": W["code_bytes"] / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": y.numel() * 2},
             "gpu_launches": 6 * args.steps, "clocks": clocks,
@@ -340,6 +371,10 @@ def main():
     if args.impl == "reference":
         if rank != 0:
             return 0
+        # torchrun exports OMP_NUM_THREADS=1 to every worker; the CPU arm is meant to use all host threads
+        # (the OpenMP runtime reads the variable when the oracle library is loaded, which happens below)
+        if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+            os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
         sample = cpu_layer_sample()
         for _ in range(max(1, min(args.warmup, 3))):
             run_cpu_layer(sample)

@@ -94,3 +94,38 @@ def all_reduce_row_parallel(y: torch.Tensor, layout: ShardLayout, group=None) ->
         return
     import torch.distributed as dist
     dist.all_reduce(y[layout.reduce_begin:layout.y_elems], op=dist.ReduceOp.SUM, group=group)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Expert parallelism for the MoE grouped matmul: rank r holds experts [r*E/G, (r+1)*E/G), tokens and routing
+# are replicated, every rank computes the weighted contributions of ITS experts for all tokens, and one
+# all-reduce (sum) of the (tokens, hidden) outputs combines them.  The reference has no multi-GPU MoE; the
+# sharding is the usual expert-parallel layout of its host framework.
+# ---------------------------------------------------------------------------------------------------
+def expert_range(num_experts: int, world: int, rank: int) -> tuple[int, int]:
+    """Half-open range of global expert ids owned by ``rank`` (experts must divide evenly)."""
+    if num_experts % world:
+        raise ValueError(f"{num_experts} experts do not divide over {world} ranks")
+    per = num_experts // world
+    return rank * per, (rank + 1) * per
+
+
+def localize_topk_ids(topk_ids: torch.Tensor, e0: int, e1: int) -> torch.Tensor:
+    """Global expert ids -> ids local to the rank owning [e0, e1); routings to other ranks' experts become -1,
+    which the grouped matmul skips (their weighted contribution is added by the owning rank)."""
+    local = topk_ids - e0
+    return torch.where((topk_ids >= e0) & (topk_ids < e1), local, torch.full_like(local, -1))
+
+
+def moe_expert_parallel(run_local, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
+                        num_experts: int, group=None) -> torch.Tensor:
+    """``run_local(x, local_ids, topk_weights) -> (tokens, hidden)`` computes this rank's experts; the result is
+    summed over ranks.  With one rank this is just ``run_local``."""
+    import torch.distributed as dist
+    world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    e0, e1 = expert_range(num_experts, world, rank)
+    y = run_local(x, localize_topk_ids(topk_ids, e0, e1), topk_weights)
+    if world > 1:
+        dist.all_reduce(y, group=group)
+    return y

@@ -101,3 +101,64 @@ def test_two_rank_sweep_matches_unsharded_product():
         p.join(120)
         assert p.exitcode == 0
     assert out.get(0) is True and out.get(1) is True
+
+
+# ---- expert parallelism of the MoE grouped matmul -----------------------------------------------------------
+def test_expert_range_and_id_localisation():
+    assert tp.expert_range(128, 8, 3) == (48, 64)
+    with pytest.raises(ValueError):
+        tp.expert_range(10, 4, 0)
+    ids = torch.tensor([[0, 5, 9], [4, 3, 8]])
+    loc = tp.localize_topk_ids(ids, 4, 8)
+    assert loc.tolist() == [[-1, 1, -1], [0, -1, -1]]
+
+
+def _moe_dense(x, ids, w, W13, W2, inter):
+    """Plain fp32 MoE over the experts in W13/W2 (ids index them; negative ids are skipped)."""
+    f13 = lambda e, xb: xb @ W13[e].T
+    f2 = lambda e, hb: hb @ W2[e].T
+    ids = np.asarray(ids)
+    keep = ids >= 0
+    wm = np.where(keep, np.asarray(w, np.float32), 0.0).astype(np.float32)
+    safe = np.where(keep, ids, ids.max() if keep.any() else 0)          # masked routings get weight 0
+    return O.moe_forward(x, safe, wm, f13, f2, inter, "gelu_tanh")
+
+
+def _moe_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        E, H, I, T, k = 8, 32, 16, 11, 3
+        rng = np.random.default_rng(11)                       # same stream on both ranks
+        W13 = rng.standard_normal((E, 2 * I, H)).astype(np.float32) * 0.2
+        W2 = rng.standard_normal((E, H, I)).astype(np.float32) * 0.2
+        x = rng.standard_normal((T, H)).astype(np.float32)
+        ids = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int64)
+        w = rng.random((T, k)).astype(np.float32)
+        e0, e1 = tp.expert_range(E, world, rank)
+
+        def run_local(xt, local_ids, wt):
+            y = _moe_dense(xt.numpy(), local_ids.numpy(), wt.numpy(), W13[e0:e1], W2[e0:e1], I)
+            return torch.from_numpy(y)
+
+        y = tp.moe_expert_parallel(run_local, torch.from_numpy(x), torch.from_numpy(ids), torch.from_numpy(w), E)
+        ref = _moe_dense(x, ids, w, W13, W2, I)
+        out[rank] = bool(np.allclose(y.numpy(), ref, rtol=1e-5, atol=1e-5))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_expert_parallel_moe_matches_unsharded():
+    world = 2
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    mgr = ctx.Manager()
+    out = mgr.dict()
+    procs = [ctx.Process(target=_moe_worker, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert out.get(0) is True and out.get(1) is True
