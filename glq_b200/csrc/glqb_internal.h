@@ -47,9 +47,12 @@ struct RhtItem {
   int ntok;    // tokens in the tile (the CTA's shared memory holds ntok * block floats)
 };
 
-// tokens per CTA of the transform kernels: about 16K floats of shared memory per CTA
+#ifndef GLQB_RHT_TILE
+#define GLQB_RHT_TILE 8192
+#endif
+// tokens per CTA of the transform kernels: about GLQB_RHT_TILE floats of shared memory per CTA
 static inline int rht_tile_tokens(int block_size, int batch) {
-  int t = 16384 / block_size;
+  int t = GLQB_RHT_TILE / block_size;
   if (t < 1) t = 1;
   if (t > 64) t = 64;
   return t < batch ? t : batch;

@@ -115,10 +115,10 @@ __device__ __forceinline__ long long xr_index_e8(long long token, int col, int n
 // PLAIN_F32: write fp32 in natural order instead (the unfused input_rht op).
 // ---------------------------------------------------------------------------------------------
 #ifndef GLQB_RHT_THREADS
-#define GLQB_RHT_THREADS 512
+#define GLQB_RHT_THREADS 256
 #endif
 #ifndef GLQB_RHT_MINB
-#define GLQB_RHT_MINB 2
+#define GLQB_RHT_MINB 4
 #endif
 constexpr int RHT_THREADS = GLQB_RHT_THREADS;
 
