@@ -394,6 +394,8 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
     _require_cuda(x, "x")
     E = w13_trellis_packed.shape[0]
     T = x.shape[0]
+    if T == 0:
+        return torch.empty_like(x)
     x = x.contiguous()
     ids = topk_ids.contiguous()
     if ids.dtype not in (torch.int32, torch.int64):

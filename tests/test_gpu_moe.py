@@ -141,3 +141,32 @@ def test_moe_tensor_core_form(K, K2, T, skew, monkeypatch):
     # same math, different summation order (and one fp16 rounding of the folded second stage)
     rel = (outs["gemm"] - outs["stream"]).abs().max() / outs["stream"].abs().max()
     assert rel <= 4e-3, rel
+
+
+def test_moe_zero_tokens_and_unrouted_tokens():
+    """No tokens: empty result.  Routings with id -1 (what expert parallelism leaves for other ranks' experts)
+    are skipped; a token whose routings are all skipped gets zeros."""
+    from glq_b200 import ops
+    E, hidden, inter, k = 8, 256, 96, 2
+    rng = np.random.default_rng(4242)
+    d, w13_out = _make(rng, E, hidden, inter, 4, 0)
+    x0 = torch.zeros(0, hidden, dtype=torch.float16, device="cuda")
+    y0 = _run(ops, d, x0, torch.zeros(0, k, dtype=torch.int64, device="cuda"),
+              torch.zeros(0, k, dtype=torch.float32, device="cuda"), E, hidden, inter, w13_out, 0, 1)
+    assert y0.shape == (0, hidden)
+    T = 6
+    x = rng.standard_normal((T, hidden)).astype(np.float32)
+    ids = np.stack([rng.permutation(E)[:k] for _ in range(T)]).astype(np.int64)
+    w = rng.random((T, k)).astype(np.float32)
+    x_t = cuda(x, torch.float16)
+    full = _run(ops, d, x_t, cuda(ids), cuda(w), E, hidden, inter, w13_out, 0, 1).float()
+    masked = ids.copy()
+    masked[2, :] = -1                      # token 2: nothing routed here
+    masked[4, 1] = -1                      # token 4: only its first routing
+    y = _run(ops, d, x_t, cuda(masked), cuda(w), E, hidden, inter, w13_out, 0, 1).float()
+    assert torch.count_nonzero(y[2]) == 0
+    keep = [0, 1, 3, 5]
+    assert torch.equal(y[keep], full[keep])
+    only_first = ids.copy(); only_first[:, 1] = -1
+    y_first = _run(ops, d, x_t, cuda(only_first), cuda(w), E, hidden, inter, w13_out, 0, 1).float()
+    assert torch.equal(y[4], y_first[4])

@@ -533,3 +533,46 @@ def test_glq_linear_module_matches_oracle(e8_table, e8_cb):
     xt = cuda(rng.standard_normal((4, 576)).astype(np.float32))
     Wt = O.trellis_decode_layer(p1, 352, 576, 4).astype(np.float32)
     assert relerr(tl(xt).cpu().numpy(), O.linear_forward(xt.cpu().numpy(), Wt, tsu, tsv, 0.02)) <= TOL
+
+
+# ---------------------------------------------------------------------------------------------
+# edge cases: empty and ragged inputs, strided rows
+# ---------------------------------------------------------------------------------------------
+def test_empty_batch_returns_empty(ops):
+    rng = np.random.default_rng(77)
+    m, n = 64, 128
+    p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, 4)
+    x_t = torch.zeros(0, n, dtype=torch.bfloat16, device="cuda")
+    y = _run_trellis(ops, x_t, p1, None, su, sv, wscale, 0.0, m, n)
+    assert y.shape == (0, m) and y.dtype == torch.bfloat16
+
+
+def test_leading_dims_and_strided_rows(ops):
+    """(2, 3, n) activations are flattened like the reference does (x.reshape(-1, in_features)); rows that are
+    a strided view (every second row of a larger buffer) are read in place, without a copy."""
+    rng = np.random.default_rng(78)
+    m, n = 96, 192
+    p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, 3)
+    x = rng.standard_normal((2, 3, n)).astype(np.float32)
+    x_t = cuda(x, torch.float16)
+    ref = O.linear_forward(x_t.float().cpu().numpy().reshape(-1, n), W, su, sv, wscale)
+    y = _run_trellis(ops, x_t, p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
+    assert y.shape == (6, m)
+    assert relerr(y.cpu().numpy(), ref) <= TOL
+    big = torch.zeros(12, n, dtype=torch.float16, device="cuda")
+    big[::2] = x_t.reshape(6, n)
+    ys = _run_trellis(ops, big[::2], p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
+    assert torch.equal(ys, y)
+
+
+@pytest.mark.parametrize("T", [1, 9, 33, 64])
+def test_ragged_token_counts_match_row_by_row(ops, T):
+    """Token counts that do not fill the 8-token MMA column blocks: every row equals the batch-1 result."""
+    rng = np.random.default_rng(500 + T)
+    m, n = 64, 256
+    p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, 4)
+    x_t = cuda(rng.standard_normal((T, n)).astype(np.float32), torch.bfloat16)
+    y = _run_trellis(ops, x_t, p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
+    for r in (0, T // 2, T - 1):
+        y1 = _run_trellis(ops, x_t[r:r + 1], p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
+        assert torch.equal(y[r:r + 1], y1)
