@@ -74,8 +74,77 @@ __device__ __forceinline__ float moe_act(float g, int act) {
 }
 
 // ---- 1: grouping ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__ MoeDev M, const void* __restrict__ ids,
+// phase 0: everything in this one CTA (small steps).  phase 1: the counts were made by moe_count_kernel and the
+// routings are placed by moe_place_kernel (many CTAs each); this kernel only does the prefix sums and tables.
+constexpr int MOE_GROUP_CHUNK = 8192;          // routings per CTA of the count / place kernels
+constexpr int MOE_GROUP_SPLIT_MIN = 8192;      // routings from which the three-kernel form is used
+
+__device__ __forceinline__ int moe_expert_of(const MoeDev& M, const void* ids, int i) {
+  const long long v = M.ids_i64 ? reinterpret_cast<const long long*>(ids)[i] : (long long)reinterpret_cast<const int*>(ids)[i];
+  return (v < 0 || v >= M.E) ? -1 : (int)v;
+}
+
+__global__ void __launch_bounds__(1024) moe_count_kernel(const __grid_constant__ MoeDev M, const void* __restrict__ ids,
                                                          int T, uint8_t* __restrict__ ws) {
+  extern __shared__ int sh[];            // counts[E] of this CTA's chunk
+  const int R = T * M.top_k;
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) sh[e] = 0;
+  __syncthreads();
+  const int i0 = blockIdx.x * MOE_GROUP_CHUNK + threadIdx.x;
+  int ev[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) { const int i = i0 + u * 1024; ev[u] = i < R ? moe_expert_of(M, ids, i) : -1; }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) if (ev[u] >= 0) atomicAdd(&sh[ev[u]], 1);
+  __syncthreads();
+  int* g_count = reinterpret_cast<int*>(ws + M.o_count);
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) if (sh[e]) atomicAdd(&g_count[e], sh[e]);
+}
+
+// Each CTA reserves, per expert, a contiguous run of slots for its chunk's routings (one global atomic per
+// expert and CTA) and places them with shared-memory atomics.
+__global__ void __launch_bounds__(1024) moe_place_kernel(const __grid_constant__ MoeDev M, const void* __restrict__ ids,
+                                                         int T, uint8_t* __restrict__ ws) {
+  extern __shared__ int sh[];            // counts[E], then cursor[E]
+  int* cnt = sh;
+  int* cur = sh + M.E;
+  const int R = T * M.top_k;
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  const int i0 = blockIdx.x * MOE_GROUP_CHUNK + threadIdx.x;
+  int ev[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) { const int i = i0 + u * 1024; ev[u] = i < R ? moe_expert_of(M, ids, i) : -1; }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) if (ev[u] >= 0) atomicAdd(&cnt[ev[u]], 1);
+  __syncthreads();
+  int* g_cursor = reinterpret_cast<int*>(ws + M.o_cursor);
+  for (int e = threadIdx.x; e < M.E; e += blockDim.x) cur[e] = cnt[e] ? atomicAdd(&g_cursor[e], cnt[e]) : 0;
+  __syncthreads();
+  const int* g_base = reinterpret_cast<const int*>(ws + M.o_base);
+  const int* g_tile0 = reinterpret_cast<const int*>(ws + M.o_tile0);
+  int* route_tok = reinterpret_cast<int*>(ws + M.o_route_tok);
+  int* route_exp = reinterpret_cast<int*>(ws + M.o_route_exp);
+  int* slot_of = reinterpret_cast<int*>(ws + M.o_slot_of);
+  int* trow = reinterpret_cast<int*>(ws + M.o_trow);
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int i = i0 + u * 1024;
+    if (i < R) {
+      int slot = -1;
+      if (ev[u] >= 0) {
+        slot = atomicAdd(&cur[ev[u]], 1);
+        route_tok[slot] = i / M.top_k;
+        route_exp[slot] = ev[u];
+        if (M.gemm) trow[slot] = g_tile0[ev[u]] * MOE_TN + (slot - g_base[ev[u]]);
+      }
+      slot_of[i] = slot;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__ MoeDev M, const void* __restrict__ ids,
+                                                         int T, uint8_t* __restrict__ ws, int phase) {
   extern __shared__ int sh[];            // counts[E], cursor[E], first slot[E], first token tile[E + 1]
   int* cnt = sh;
   int* cur = sh + M.E;
@@ -91,28 +160,37 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
   for (int e = threadIdx.x; e < M.E; e += blockDim.x) cnt[e] = 0;
   if (threadIdx.x < 2) g_work[threadIdx.x] = 0;
   __syncthreads();
-  auto expert_of = [&](int i) -> int {
-    long long v = M.ids_i64 ? reinterpret_cast<const long long*>(ids)[i] : (long long)reinterpret_cast<const int*>(ids)[i];
-    return (v < 0 || v >= M.E) ? -1 : (int)v;
-  };
-  // 8 routings per thread and round: the id loads of a round are issued together
-  for (int i0 = threadIdx.x; i0 < R; i0 += 8 * blockDim.x) {
-    int ev[8];
+  auto expert_of = [&](int i) -> int { return moe_expert_of(M, ids, i); };
+  if (phase == 0) {
+    // 8 routings per thread and round: the id loads of a round are issued together
+    for (int i0 = threadIdx.x; i0 < R; i0 += 8 * blockDim.x) {
+      int ev[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) { const int i = i0 + u * blockDim.x; ev[u] = i < R ? expert_of(i) : -1; }
+      for (int u = 0; u < 8; ++u) { const int i = i0 + u * blockDim.x; ev[u] = i < R ? expert_of(i) : -1; }
 #pragma unroll
-    for (int u = 0; u < 8; ++u) if (ev[u] >= 0) atomicAdd(&cnt[ev[u]], 1);
+      for (int u = 0; u < 8; ++u) if (ev[u] >= 0) atomicAdd(&cnt[ev[u]], 1);
+    }
+  } else {
+    __syncthreads();
+    for (int e = threadIdx.x; e < M.E; e += blockDim.x) cnt[e] = g_count[e];
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int run = 0, tiles = 0;
     for (int e = 0; e < M.E; ++e) {
-      cur[e] = run; base_s[e] = run; g_base[e] = run; g_count[e] = cnt[e]; run += cnt[e];
+      cur[e] = run; base_s[e] = run; run += cnt[e];
       tile0[e] = tiles; tiles += (cnt[e] + MOE_TN - 1) / MOE_TN;
     }
     tile0[M.E] = tiles;
   }
   __syncthreads();
+  {
+    int* g_cursor = reinterpret_cast<int*>(ws + M.o_cursor);
+    int* g_tile0 = reinterpret_cast<int*>(ws + M.o_tile0);
+    for (int e = threadIdx.x; e < M.E; e += blockDim.x) {
+      g_base[e] = base_s[e]; g_count[e] = cnt[e]; g_cursor[e] = base_s[e]; g_tile0[e] = tile0[e];
+    }
+  }
   int* trow = reinterpret_cast<int*>(ws + M.o_trow);
   if (M.gemm) {
     // Tensor-core form.  Expert e with c routings owns ceil(c / 128) token tiles; routing number i of the
@@ -170,6 +248,7 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
       I2[idx] = GemmItem{e, idx - tile * mt2, tile - tile0[e], 0, kc2, 0};
     }
   }
+  if (phase != 0) return;
   for (int i0 = threadIdx.x; i0 < R; i0 += 8 * blockDim.x) {
     int ev[8];
 #pragma unroll
@@ -675,6 +754,21 @@ static int fill_blocks(const int32_t* blocks, int nb, int total, int* off, int* 
   return GLQB_OK;
 }
 
+// grouping: one CTA for small steps; count / tables / place kernels (many CTAs) for large ones
+static void moe_launch_group(const MoeDev& M, const void* ids, int tokens, uint8_t* ws, cudaStream_t st) {
+  const int R = tokens * M.top_k;
+  const size_t sh = (4 * (size_t)M.E + 1) * sizeof(int);
+  if (R < MOE_GROUP_SPLIT_MIN) {
+    moe_group_kernel<<<1, 1024, sh, st>>>(M, ids, tokens, ws, 0);
+    return;
+  }
+  const int nb = (R + MOE_GROUP_CHUNK - 1) / MOE_GROUP_CHUNK;
+  cudaMemsetAsync(ws + M.o_count, 0, sizeof(int) * M.E, st);
+  moe_count_kernel<<<nb, 1024, M.E * sizeof(int), st>>>(M, ids, tokens, ws);
+  moe_group_kernel<<<1, 1024, sh, st>>>(M, ids, tokens, ws, 1);
+  moe_place_kernel<<<nb, 1024, 2 * M.E * sizeof(int), st>>>(M, ids, tokens, ws);
+}
+
 extern "C" {
 
 int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
@@ -750,6 +844,7 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   M.o_count = o; o = al(o + 4 * (size_t)M.E);
   M.o_base = o; o = al(o + 4 * (size_t)M.E);
   M.o_cursor = o; o = al(o + 4 * (size_t)M.E);
+  M.o_tile0 = o; o = al(o + 4 * ((size_t)M.E + 1));
   M.o_work = o; o = al(o + 16);
   M.o_route_tok = o; o = al(o + 4 * R);
   M.o_route_exp = o; o = al(o + 4 * R);
@@ -846,7 +941,7 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   if (P->gemm_ok && (long long)tokens * P->dev.top_k >= (long long)P->dev.E * moe_gemm_min_avg()) {
     const MoeDev& G = P->devg;
     const int R = tokens * G.top_k;
-    moe_group_kernel<<<1, 1024, (4 * G.E + 1) * sizeof(int), st>>>(G, topk_ids, tokens, ws);
+    moe_launch_group(G, topk_ids, tokens, ws, st);
     moe_rht_in_gemm_kernel<<<tokens, std::max(64, std::min(1024, G.hidden / 8)), G.hidden * 4, st>>>(
         G, reinterpret_cast<const uint8_t*>(x), ws);
     int* status = reinterpret_cast<int*>(ws + G.o_status);
@@ -866,7 +961,7 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   }
   const MoeDev& M = P->dev;
   const int R = tokens * M.top_k;
-  moe_group_kernel<<<1, 1024, (4 * M.E + 1) * sizeof(int), st>>>(M, topk_ids, tokens, ws);
+  moe_launch_group(M, topk_ids, tokens, ws, st);
   moe_rht_in_kernel<<<tokens, std::max(64, std::min(1024, M.hidden / 8)), M.hidden * 4, st>>>(
       M, reinterpret_cast<const uint8_t*>(x), ws);
   MoeMvArgs A;

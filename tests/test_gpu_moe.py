@@ -170,3 +170,28 @@ def test_moe_zero_tokens_and_unrouted_tokens():
     only_first = ids.copy(); only_first[:, 1] = -1
     y_first = _run(ops, d, x_t, cuda(only_first), cuda(w), E, hidden, inter, w13_out, 0, 1).float()
     assert torch.equal(y[4], y_first[4])
+
+
+def test_moe_large_step_uses_split_grouping():
+    """More than 8192 routings: counting and placement run as many-CTA kernels around the table-building CTA."""
+    from glq_b200 import ops
+    E, hidden, inter, k, T = 8, 256, 128, 2, 4200
+    rng = np.random.default_rng(9001)
+    d, w13_out = _make(rng, E, hidden, inter, 4, 0)
+    x = rng.standard_normal((T, hidden)).astype(np.float32)
+    p = np.array([0.3, 0.25, 0.15, 0.1, 0.08, 0.07, 0.05, 0.0])
+    ids = np.stack([rng.choice(E, size=k, replace=False, p=p) for _ in range(T)]).astype(np.int64)
+    ids[17, 0] = -1                                   # a skipped routing in the middle
+    w = rng.random((T, k)).astype(np.float32)
+    w /= w.sum(1, keepdims=True)
+    x_t = cuda(x, torch.float16)
+    ops.clear_caches()
+    y = _run(ops, d, x_t, cuda(ids), cuda(w), E, hidden, inter, w13_out, 0, 1)
+    y2 = _run(ops, d, x_t, cuda(ids), cuda(w), E, hidden, inter, w13_out, 0, 1)
+    assert torch.equal(y, y2)
+    keep = ids >= 0
+    ref = _oracle(d, x_t.float().cpu().numpy(), np.where(keep, ids, 7), np.where(keep, w, 0.0).astype(np.float32),
+                  E, hidden, inter, w13_out, 4, 0, O.ACT_CODES[1])
+    err = np.abs(y.float().cpu().numpy() - ref).max() / np.abs(ref).max()
+    assert err <= 5e-3, err
+    ops.clear_caches()
