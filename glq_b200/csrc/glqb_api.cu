@@ -158,6 +158,9 @@ static E8SmemKernel pick_e8_smem_kernel(const Segment& s) {
   return nullptr;
 }
 
+#ifndef GLQB_E8_SMEM_MAX_NB
+#define GLQB_E8_SMEM_MAX_NB 2      // token-column blocks up to which the resident-table kernel is used
+#endif
 static long long e8_smem_min_bytes() {
   const char* e = getenv("GLQB_E8_SMEM_MIN_BYTES");
   // Filling the table costs every CTA about 224 KiB of L2 reads per launch (a few microseconds), so small
@@ -435,7 +438,7 @@ static int build_plan(GlqbPlan* P) {
     int warps_per_cta = MV_WARPS;
     // E8: keep the codebook in shared memory when the launch is large enough to pay
     // for filling it and every stage reads either one shared 65,536-entry table or one small table
-    if (s.format == GLQB_FMT_E8_SHELL && s.nb == 1 && pick_e8_smem_kernel(s)) {
+    if (s.format == GLQB_FMT_E8_SHELL && s.nb <= GLQB_E8_SMEM_MAX_NB && pick_e8_smem_kernel(s)) {
       long long bytes = 0;
       bool ok = true;
       const uint32_t* big = nullptr;

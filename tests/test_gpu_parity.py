@@ -468,7 +468,7 @@ def test_e8_gemm_vs_oracle(ops, e8_table, e8_cb, stages, T):
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("stages,small2", [(1, False), (2, False), (2, True), (4, False)])
 @pytest.mark.parametrize("B", [1, 9])
-def test_e8_cluster_table_path_matches_oracle_and_global_path(ops, e8_table, e8_cb, monkeypatch, stages, small2, B):
+def test_e8_resident_table_path_matches_oracle_and_global_path(ops, e8_table, e8_cb, monkeypatch, stages, small2, B):
     full, small = e8_cb
     rng = np.random.default_rng(stages * 31 + B + int(small2))
     m, n = 320, 832
