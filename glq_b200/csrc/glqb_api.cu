@@ -168,6 +168,45 @@ static long long e8_smem_min_bytes() {
   return e ? atoll(e) : (48ll << 20);
 }
 
+typedef void (*TilesSmemKernel)(const DevLinear*, int, int, uint8_t*, const uint32_t*, const uint32_t*, int);
+static TilesSmemKernel pick_tiles_smem_kernel(int ns) {
+  switch (ns) {
+    case 1: return e8_tiles_smem_kernel<1>;
+    case 2: return e8_tiles_smem_kernel<2>;
+    case 3: return e8_tiles_smem_kernel<3>;
+    case 4: return e8_tiles_smem_kernel<4>;
+  }
+  return nullptr;
+}
+
+// Do all layers of the segment read one 65,536-entry table (and at most one small table)?  Also sums the
+// index bytes of the segment.
+static bool e8_uniform_tables(const std::vector<DevLinear>& dev, const Segment& s, const uint32_t** big_out,
+                              const uint32_t** small_out, int* small_n_out, long long* bytes_out) {
+  long long bytes = 0;
+  const uint32_t* big = nullptr;
+  const uint32_t* small = nullptr;
+  int small_n = 0;
+  for (int i = 0; i < s.count; ++i) {
+    const DevLinear& L = dev[s.first + i];
+    bytes += (long long)L.n_stages * L.m * (L.n / 8) * 2;
+    for (int st = 0; st < L.n_stages; ++st) {
+      if (L.table_entries[st] == 65536) {
+        if (big && big != L.table[st]) return false;
+        big = L.table[st];
+      } else if (L.table_entries[st] <= 256) {
+        if (small && (small != L.table[st] || small_n != L.table_entries[st])) return false;
+        small = L.table[st];
+        small_n = L.table_entries[st];
+      } else {
+        return false;
+      }
+    }
+  }
+  *big_out = big; *small_out = small; *small_n_out = small_n; *bytes_out = bytes;
+  return big != nullptr;
+}
+
 static MvKernel pick_kernel(const Segment& s) {
   return s.format == GLQB_FMT_TRELLIS_3INST ? trellis_kernel(s.k1, s.k2, s.nb) : e8_kernel(s.ns, s.nb);
 }
@@ -195,7 +234,7 @@ static TilesKernel pick_tiles_kernel(int ns) {
 // token count from which E8 prefill decodes the weight tiles once instead of once per token tile
 static int e8_two_phase_min_tokens() {
   const char* e = getenv("GLQB_E8_TWO_PHASE_MIN_TOKENS");
-  return e ? atoi(e) : 257;     // more than one token tile: the fused kernel would decode every tile twice or more
+  return e ? atoi(e) : 129;     // measured on B200: above one 128-token tile the tile decode plus a copy-fed GEMM wins
 }
 
 static GemmKernel pick_gemm_kernel(const Segment& s) {
@@ -428,6 +467,24 @@ static int build_plan(GlqbPlan* P) {
       s.per_warp = 1;
       CUDA_TRY(cudaFuncSetAttribute(pick_gemm_kernel(s), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     (int)gemm_smem_bytes(s.tn)));
+      if (s.two_phase) {
+        // tile decode with the codebook resident in shared memory, under the same conditions as the
+        // streaming kernel's resident form
+        long long bytes = 0;
+        const uint32_t* big = nullptr;
+        const uint32_t* small = nullptr;
+        int small_n = 0;
+        if (e8_uniform_tables(P->dev, s, &big, &small, &small_n, &bytes) && bytes >= e8_smem_min_bytes() &&
+            cudaFuncSetAttribute(pick_tiles_smem_kernel(s.ns), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 E8S_SMEM_BYTES) == cudaSuccess) {
+          s.smem_table = true;
+          s.big_table = big;
+          s.small_table = small ? small : big;
+          s.small_entries = small_n;
+        } else {
+          cudaGetLastError();
+        }
+      }
       continue;
     }
     MvKernel kern = pick_kernel(s);
@@ -440,26 +497,10 @@ static int build_plan(GlqbPlan* P) {
     // for filling it and every stage reads either one shared 65,536-entry table or one small table
     if (s.format == GLQB_FMT_E8_SHELL && s.nb <= GLQB_E8_SMEM_MAX_NB && pick_e8_smem_kernel(s)) {
       long long bytes = 0;
-      bool ok = true;
       const uint32_t* big = nullptr;
       const uint32_t* small = nullptr;
       int small_n = 0;
-      for (int i = 0; i < s.count && ok; ++i) {
-        const DevLinear& L = P->dev[s.first + i];
-        bytes += (long long)L.n_stages * L.m * (L.n / 8) * 2;
-        for (int st = 0; st < L.n_stages && ok; ++st) {
-          if (L.table_entries[st] == 65536) {
-            if (big && big != L.table[st]) ok = false;
-            big = L.table[st];
-          } else if (L.table_entries[st] <= 256) {
-            if (small && (small != L.table[st] || small_n != L.table_entries[st])) ok = false;
-            small = L.table[st];
-            small_n = L.table_entries[st];
-          } else {
-            ok = false;
-          }
-        }
-      }
+      const bool ok = e8_uniform_tables(P->dev, s, &big, &small, &small_n, &bytes);
       if (ok && big && bytes >= e8_smem_min_bytes()) {
         E8SmemKernel ck = pick_e8_smem_kernel(s);
         CUDA_TRY(cudaFuncSetAttribute(ck, cudaFuncAttributeMaxDynamicSharedMemorySize, E8S_SMEM_BYTES));
@@ -660,7 +701,10 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   }
   for (const Segment& s : P->segs) {
     if (s.tn) {
-      if (s.two_phase)
+      if (s.two_phase && s.smem_table)
+        pick_tiles_smem_kernel(s.ns)<<<P->sm_count, E8TS_THREADS, E8S_SMEM_BYTES, stream>>>(
+            P->d_layers, s.first, s.count, ws, s.big_table, s.small_table, s.small_entries);
+      else if (s.two_phase)
         pick_tiles_kernel(s.ns)<<<P->sm_count * 8, 256, 0, stream>>>(P->d_layers, s.first, s.count, ws);
       GemmKernel kern = pick_gemm_kernel(s);
       kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,

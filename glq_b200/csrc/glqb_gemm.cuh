@@ -546,10 +546,13 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
 // A CTA takes 128 rows x 4 consecutive chunks; thread (row = tid >> 1, half = tid & 1) reads the 16 indices
 // of two chunks with two 16-byte loads per stage (the two threads of a row read 64 contiguous bytes), keeps
 // all 16 * NS gathers in flight, and writes two full 128-byte tile rows.
-template <int NS>
-__global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restrict__ layers, int first, int count,
-                                                       uint8_t* __restrict__ ws) {
-  const int tid = threadIdx.x, row_l = tid >> 1, hf = tid & 1;
+// TM = 0: table gathers from global memory, one unit per 256-thread CTA.  TM = 1: most of the table resident in
+// shared memory (see e8_gather), 512-thread CTA = two units side by side, one CTA per SM.
+template <int NS, int TM>
+__device__ __forceinline__ void e8_tiles_body(const DevLinear* __restrict__ layers, int first, int count,
+                                              uint8_t* __restrict__ ws, const E8Tables& T, int unit0, int unit_stride,
+                                              int tid) {
+  const int row_l = tid >> 1, hf = tid & 1;
   for (int li = first; li < first + count; ++li) {
     const DevLinear& L = layers[li];
     const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
@@ -558,18 +561,18 @@ __global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restri
     const int nidx = L.n >> 3, m = L.m;
     const bool vec_ok = (nidx & 7) == 0;                 // every row starts 16-byte aligned
     const uint16_t* codes[NS];
-    const uint32_t* table[NS];
-    uint32_t mask[NS];
+    E8Stage stg[NS];
     __half2 sc[NS];
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
       codes[s] = reinterpret_cast<const uint16_t*>(L.codes[s]);
-      table[s] = L.table[s];
-      mask[s] = (uint32_t)L.table_entries[s] - 1u;
+      stg[s].table = L.table[s];
+      stg[s].mask = (uint32_t)L.table_entries[s] - 1u;
+      stg[s].base = L.table_entries[s] == 65536 ? T.table_base : T.small_base;
       sc[s] = __float2half2_rn(L.stage_scale[s]);
     }
     uint8_t* tiles = ws + L.atile_off;
-    for (int u = blockIdx.x; u < m_tiles * kgroups; u += gridDim.x) {
+    for (int u = unit0; u < m_tiles * kgroups; u += unit_stride) {
       const int mt = u / kgroups, kg = u - mt * kgroups;
       const int row = mt * GM_TILE_M + row_l;
       const bool row_ok = row < m;
@@ -592,7 +595,7 @@ __global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restri
           }
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            ent[s][c][k] = __ldg(table[s] + (((w[k >> 1] >> ((k & 1) * 16)) & 0xFFFFu) & mask[s]));
+            ent[s][c][k] = e8_gather<TM>(stg[s], ((w[k >> 1] >> ((k & 1) * 16)) & 0xFFFFu) & stg[s].mask);
         }
       }
 #pragma unroll
@@ -627,6 +630,31 @@ __global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restri
       }
     }
   }
+}
+
+template <int NS>
+__global__ void __launch_bounds__(256) e8_tiles_kernel(const DevLinear* __restrict__ layers, int first, int count,
+                                                       uint8_t* __restrict__ ws) {
+  const E8Tables T = {0u, 0u};
+  e8_tiles_body<NS, 0>(layers, first, count, ws, T, blockIdx.x, gridDim.x, threadIdx.x);
+}
+
+constexpr int E8TS_THREADS = 512;
+template <int NS>
+__global__ void __launch_bounds__(E8TS_THREADS, 1)
+e8_tiles_smem_kernel(const DevLinear* __restrict__ layers, int first, int count, uint8_t* __restrict__ ws,
+                     const uint32_t* __restrict__ big_table, const uint32_t* __restrict__ small_table, int small_entries) {
+  extern __shared__ __align__(16) uint32_t e8t_smem[];
+  const uint4* src = reinterpret_cast<const uint4*>(big_table);
+  uint4* dst = reinterpret_cast<uint4*>(e8t_smem);
+  for (int i = threadIdx.x; i < E8S_RESIDENT / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+  for (int i = threadIdx.x; i < small_entries && i < 256; i += blockDim.x) e8t_smem[E8S_RESIDENT + i] = __ldg(small_table + i);
+  E8Tables T;
+  const uint32_t local = (uint32_t)__cvta_generic_to_shared(e8t_smem);
+  T.table_base = local;
+  T.small_base = local + E8S_RESIDENT * 4;
+  __syncthreads();
+  e8_tiles_body<NS, 1>(layers, first, count, ws, T, blockIdx.x * 2 + (threadIdx.x >> 8), gridDim.x * 2, threadIdx.x & 255);
 }
 
 }  // namespace glqb

@@ -576,3 +576,39 @@ def test_ragged_token_counts_match_row_by_row(ops, T):
     for r in (0, T // 2, T - 1):
         y1 = _run_trellis(ops, x_t[r:r + 1], p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
         assert torch.equal(y[r:r + 1], y1)
+
+
+@pytest.mark.parametrize("stages,small2", [(1, False), (2, False), (2, True), (3, False)])
+def test_e8_two_phase_prefill_resident_table_equals_global_table(ops, e8_table, e8_cb, monkeypatch, stages, small2):
+    """More than 256 tokens: weight tiles are decoded once, with the codebook either gathered from global memory
+    or resident in shared memory.  Both forms must produce the same tiles, hence bit-equal outputs."""
+    full, small = e8_cb
+    rng = np.random.default_rng(900 + stages * 7 + int(small2))
+    m, n, T = 320, 832, 300
+    qs = [rng.integers(0, 65536, size=(m, n // 8), dtype=np.uint16).view(np.int16) for _ in range(stages)]
+    tabs = [e8_table] * stages
+    if small2:
+        qs[1] = rng.integers(0, 256, size=(m, n // 8), dtype=np.uint16).view(np.int16)
+        tabs[1] = e8_table[:256]
+    inv = [0.3, 0.09, 0.027][:stages - 1]
+    su, sv = signs(rng, m), signs(rng, n)
+    W = O.e8_decode_nstage(qs, tabs, inv)
+    x = cuda(rng.standard_normal((T, n)).astype(np.float32), torch.float16)
+    empty_i = torch.empty(0, dtype=torch.int16, device="cuda")
+    empty_h = torch.empty(0, dtype=torch.float16, device="cuda")
+    tail = []
+    for s in range(1, 4):
+        cb = small if (s == 1 and small2) else full
+        tail += [cuda(qs[s]) if stages > s else empty_i, cb if stages > s else empty_h, inv[s - 1] if stages > s else 0.0]
+    args = (x, cuda(sv), cuda(su), cuda(qs[0]), full, 0.02, n, m, n, m,
+            torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m)), None, None, *tail)
+    ops.clear_caches()
+    monkeypatch.setenv("GLQB_E8_SMEM_MIN_BYTES", "0")
+    y_smem = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
+    ops.clear_caches()
+    monkeypatch.setenv("GLQB_E8_SMEM_MIN_BYTES", str(1 << 40))
+    y_glob = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
+    ops.clear_caches()
+    ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02)
+    assert relerr(y_glob.cpu().numpy(), ref) <= TOL
+    assert torch.equal(y_smem, y_glob)
