@@ -3,7 +3,8 @@
 // (reference: glq_fused_moe_trellis_3inst_cuda, glq/csrc/glq_cuda.cu:5042; eager loop
 // glq_vllm/fused_moe_method.py:393-440; storage glq_vllm/moe_shapes.py:56-72).
 //
-// Six launches, fixed grids, no host synchronisation (capture-safe):
+// Six launches (eight kernels and a memset from 8192 routings, see moe_launch_group), fixed grids, no host
+// synchronisation (capture-safe):
 //   1 moe_group_kernel     count tokens per expert, prefix sums, place every (token, j) routing in a slot
 //                          (tensor-core form: also the per-expert layer entries and the GEMM work lists)
 //   2 moe_rht_in_kernel    input transform of every TOKEN once (all experts share SV of w13)
