@@ -157,6 +157,7 @@ def build_workload(name, device, world, rank, tokens=None, n_layers=None):
     specs, layers = [], []
     x_elems = y_elems = 0
     reduce_spans = []
+    pending = []
     for li in range(nl):
         x_of = {}
         for pname, m, n in cfg["proj"]:
@@ -173,10 +174,21 @@ def build_workload(name, device, world, rank, tokens=None, n_layers=None):
             if pname == "up":
                 L.sv = layers[-1].sv
             layers.append(L)
-            specs.append(L.spec(batch=T, x_offset=x_of[group], y_offset=y_elems, x_stride=ns, y_stride=ms))
-            if pname in tp.ROW_PARALLEL and world > 1:
-                reduce_spans.append((y_elems, T * ms))
-            y_elems += T * ms
+            pending.append((L, x_of[group], ns, ms, pname in tp.ROW_PARALLEL))
+    # outputs: column-parallel layers first, row-parallel ones as one contiguous tail, so that the partial sums
+    # of a step are added over the ranks by ONE all-reduce (the layers of the sweep do not depend on each other)
+    y_at = {}
+    for want_row in (False, True):
+        if want_row:
+            tail_begin = y_elems
+        for i, (L, xo, ns, ms, is_row) in enumerate(pending):
+            if is_row == want_row:
+                y_at[i] = y_elems
+                y_elems += T * ms
+    for i, (L, xo, ns, ms, is_row) in enumerate(pending):
+        specs.append(L.spec(batch=T, x_offset=xo, y_offset=y_at[i], x_stride=ns, y_stride=ms))
+    if world > 1 and y_elems > tail_begin:
+        reduce_spans.append((tail_begin, y_elems - tail_begin))
     plan = Plan(specs)
     gx = torch.Generator(device=device)
     gx.manual_seed(77)
