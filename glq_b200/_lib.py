@@ -22,7 +22,7 @@ EXPORTS = [
     "glqb_plan_launches", "glqb_plan_run", "glqb_plan_set_timing", "glqb_plan_kernel_ms",
     "glqb_plan_destroy", "glqb_plan_status", "glqb_linear_workspace_bytes", "glqb_fused_linear",
     "glqb_decompress_trellis_3inst", "glqb_dequant_e8", "glqb_e8_pack_table", "glqb_input_rht",
-    "glqb_output_rht", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
+    "glqb_output_rht", "glqb_output_rht_shards", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
     "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
     "glqb_moe_plan_create", "glqb_moe_plan_workspace_bytes", "glqb_moe_plan_code_bytes", "glqb_moe_plan_run",
     "glqb_moe_plan_status", "glqb_moe_plan_destroy",
@@ -43,6 +43,9 @@ class MoeDesc(C.Structure):
         ("blocks_n_w13", C.c_int32 * MAX_BLOCKS), ("blocks_m_w13", C.c_int32 * MAX_BLOCKS),
         ("blocks_n_w2", C.c_int32 * MAX_BLOCKS), ("blocks_m_w2", C.c_int32 * MAX_BLOCKS),
         ("ids_are_int64", C.c_int32), ("x_dtype", C.c_int32), ("y_dtype", C.c_int32),
+        ("format", C.c_int32), ("e8_stages", C.c_int32),
+        ("w13_qidxs", C.c_void_p * 3), ("w2_qidxs", C.c_void_p * 3), ("e8_table", C.c_void_p * 3),
+        ("e8_table_entries", C.c_int32 * 3), ("w13_inv_rs", C.c_void_p * 2), ("w2_inv_rs", C.c_void_p * 2),
     ]
 
 
@@ -120,6 +123,8 @@ def load() -> C.CDLL:
     lib.glqb_input_rht.restype = C.c_int
     lib.glqb_output_rht.argtypes = [vp, vp, vp, i32, i64, i32, i32, C.POINTER(i32), i32, i32, vp]
     lib.glqb_output_rht.restype = C.c_int
+    lib.glqb_output_rht_shards.argtypes = [vp, vp, vp, i32, i64, i32, i32, C.POINTER(i32), C.POINTER(i32), i32, i32, vp]
+    lib.glqb_output_rht_shards.restype = C.c_int
     lib.glqb_trellis_kernel_supported.argtypes = [i32, i32]
     lib.glqb_trellis_kernel_supported.restype = C.c_int
     lib.glqb_trellis_linear_noalloc.argtypes = [vp, i32, vp, i32, vp, i32, vp, vp, f32, i32, i32,

@@ -34,18 +34,32 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False, out: str = LIB, defines=()) -> str:
-    """``out`` / ``defines`` build a tuning variant beside the default library (see GLQB_LIB_PATH)."""
+    """``out`` / ``defines`` build a tuning variant beside the default library (see GLQB_LIB_PATH).
+    The translation units are compiled side by side, then linked."""
     if not force and out == LIB and not needs_build():
         return LIB
-    cmd = [_nvcc(), *NVCC_FLAGS, *[f"-D{d}" for d in defines]]
+    import tempfile
+    from concurrent.futures import ThreadPoolExecutor
+    flags = [f for f in NVCC_FLAGS if f != "-shared"] + [f"-D{d}" for d in defines]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", out]
-    res = subprocess.run(cmd, capture_output=True, text=True)
-    if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
+        flags += ["-Xptxas", "-v"]
+    with tempfile.TemporaryDirectory(prefix="glqb_build_") as tmp:
+        def compile_one(src):
+            obj = os.path.join(tmp, src.replace(".cu", ".o"))
+            res = subprocess.run([_nvcc(), *flags, "-c", os.path.join(CSRC, src), "-o", obj],
+                                 capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {src}:\n" + res.stdout + res.stderr)
+            return obj, res.stderr
+        with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+            results = list(pool.map(compile_one, SOURCES))
+        if verbose:
+            for _, log in results:
+                print(log)
+        res = subprocess.run([_nvcc(), "-shared", "-Xcompiler", "-fPIC", *[o for o, _ in results], "-o", out],
+                             capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("link failed:\n" + res.stdout + res.stderr)
     return out
 
 

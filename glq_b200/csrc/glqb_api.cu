@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -257,7 +258,7 @@ static GemmKernel pick_gemm_kernel(const Segment& s) {
 }
 
 static size_t gemm_smem_bytes(int tn) {
-  return (size_t)GEMM_STAGES * (GM_A_BYTES + (size_t)tn * 128) + (3 * GEMM_STAGES + 4) * 8 + 16 + 1024;
+  return (size_t)GEMM_STAGES * (GM_A_BYTES + (size_t)tn * 128) + (3 * GEMM_STAGES + 5) * 8 + 16 + 1024;
 }
 
 static int tn_for_batch(int batch) { return batch <= DECODE_MAX_BATCH ? 0 : (batch <= 128 ? 128 : 256); }
@@ -279,6 +280,9 @@ static int validate(const GlqbLinearDesc& d, int idx) {
   if (d.batch < 1) return fail(GLQB_E_INVALID, "layer %d: batch %d", idx, d.batch);
   if (d.batch > 65535) return fail(GLQB_E_INVALID, "layer %d: batch %d exceeds 65535 tokens", idx, d.batch);
   if (!d.su || !d.sv || !d.codes[0]) return fail(GLQB_E_INVALID, "layer %d: null su/sv/codes", idx);
+  // the kernels read the sign vectors and the trellis bit-streams with 16-byte accesses
+  if ((reinterpret_cast<uintptr_t>(d.su) | reinterpret_cast<uintptr_t>(d.sv)) & 15)
+    return fail(GLQB_E_INVALID, "layer %d: su / sv must be 16-byte aligned", idx);
   if (d.format == GLQB_FMT_TRELLIS_3INST) {
     if (d.m_pad % 32 || d.n_pad % 32)
       return fail(GLQB_E_INVALID, "layer %d: trellis needs m %% 32 == 0 and n %% 32 == 0 (got %d x %d)", idx,
@@ -287,6 +291,9 @@ static int validate(const GlqbLinearDesc& d, int idx) {
     for (int s = 0; s < d.n_stages; ++s)
       if (d.bits[s] < 1 || d.bits[s] > 4 || !d.codes[s])
         return fail(GLQB_E_INVALID, "layer %d: trellis stage %d has K=%d (supported 1..4)", idx, s, d.bits[s]);
+    for (int s = 0; s < d.n_stages; ++s)
+      if (reinterpret_cast<uintptr_t>(d.codes[s]) & 15)
+        return fail(GLQB_E_INVALID, "layer %d: trellis stage %d bit-stream must be 16-byte aligned", idx, s);
     if (!trellis_kernel(d.bits[0], d.n_stages > 1 ? d.bits[1] : 0, 1))
       return fail(GLQB_E_INVALID, "layer %d: no kernel for trellis rates K=%d+%d", idx, d.bits[0],
                   d.n_stages > 1 ? d.bits[1] : 0);
@@ -296,6 +303,8 @@ static int validate(const GlqbLinearDesc& d, int idx) {
     if (d.n_stages < 1 || d.n_stages > 4) return fail(GLQB_E_INVALID, "layer %d: E8 stages %d", idx, d.n_stages);
     for (int s = 0; s < d.n_stages; ++s) {
       if (!d.codes[s] || !d.table[s]) return fail(GLQB_E_INVALID, "layer %d: E8 stage %d null codes/table", idx, s);
+      if ((reinterpret_cast<uintptr_t>(d.codes[s]) & 1) || (reinterpret_cast<uintptr_t>(d.table[s]) & 15))
+        return fail(GLQB_E_INVALID, "layer %d: E8 stage %d misaligned index matrix (2 bytes) or table (16 bytes)", idx, s);
       const int e = d.table_entries[s];
       if (e < 1 || e > 65536 || (e & (e - 1)))
         return fail(GLQB_E_INVALID, "layer %d: E8 table entries %d must be a power of two <= 65536", idx, e);
@@ -327,6 +336,16 @@ static int validate(const GlqbLinearDesc& d, int idx) {
 // one thread per 32-value segment of the largest tile, between 64 and RHT_THREADS
 static int rht_threads(int max_elems) { return std::max(64, std::min(RHT_THREADS, (max_elems / 32 + 31) / 32 * 32)); }
 static int rht_smem(int max_elems) { return (max_elems + max_elems / 32) * 4 + 64; }
+
+static cudaError_t raise_rht_smem_limits() {
+  const int lim = rht_smem(32768);
+  cudaError_t e = cudaFuncSetAttribute(rht_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(rht_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(rht_in_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(rht_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(rht_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lim);
+  return e;
+}
 
 // one item per (layer, block, tile of tokens); tracks the largest tile (floats) for the launch's smem
 static void add_rht_items(std::vector<RhtItem>& items, int layer, int nblocks, const int* logs, int batch,
@@ -451,7 +470,6 @@ static int build_plan(GlqbPlan* P) {
         ks = (kchunks + per - 1) / per;
         L.fixed_slots = ks;
         L.slots = ks;
-        L.slot_mult = 1;
         L.gemm_tn = s.tn;
         L.per_warp = 1;
         L.atile_off = s.two_phase ? -1 : 0;      // -1: allocate below
@@ -534,8 +552,7 @@ static int build_plan(GlqbPlan* P) {
     for (int i = 0; i < s.count; ++i) {
       DevLinear& L = P->dev[s.first + i];
       L.per_warp = s.per_warp;
-      L.slot_mult = 1;
-      L.slots = ((L.groups_per_strip - 1) / s.per_warp + 2) * L.slot_mult;
+      L.slots = (L.groups_per_strip - 1) / s.per_warp + 2;
     }
   }
 
@@ -602,14 +619,10 @@ static int build_plan(GlqbPlan* P) {
   CUDA_TRY(cudaMalloc(&P->d_items_out, sizeof(RhtItem) * std::max<size_t>(1, P->items_out.size())));
   CUDA_TRY(cudaMemcpy(P->d_items_out, P->items_out.data(), sizeof(RhtItem) * P->items_out.size(), cudaMemcpyHostToDevice));
 
-  // kernels that may need more than 48 KB of dynamic shared memory
-  const int smem_in = rht_smem(P->max_elems_in), smem_out = rht_smem(P->max_elems_out);
-  if (smem_in > 48 * 1024) {
-    CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
-    CUDA_TRY(cudaFuncSetAttribute(rht_in_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_in));
-  }
-  if (smem_out > 48 * 1024)
-    CUDA_TRY(cudaFuncSetAttribute(rht_out_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_out));
+  // The shared-memory limit is a property of the kernel, not of a plan: every plan sets it to the largest
+  // value any plan can need (one 32768-value Hadamard block), so a later plan never lowers what an earlier
+  // one relies on.
+  CUDA_TRY(raise_rht_smem_limits());
   return GLQB_OK;
 }
 
@@ -810,33 +823,41 @@ int glqb_e8_pack_table(const void* codebook_f16, int32_t entries, uint32_t* out_
   return GLQB_OK;
 }
 
-// The two unfused transform ops build a one-layer table in kernel-argument space is not possible for
-// a pointer-typed table, so they keep a tiny per-call device table alive in a static pool keyed by
-// stream-ordered allocation.
+// The unfused transform ops describe their one layer in kernel-parameter space (rht_in_single_kernel /
+// rht_out_single_kernel): no device table, no allocation, no copy, nothing that would be illegal while the
+// stream is being captured into a CUDA graph.  `offsets` (optional) gives the first column of every
+// Hadamard block; without it the blocks are laid side by side.
 static int run_rht_single(bool input, const void* src, int src_dtype, int64_t src_stride, const void* signs,
                           void* dst, int dst_dtype, int64_t dst_stride, int32_t feat, int32_t pad,
-                          const int32_t* blocks, int32_t n_blocks, int32_t batch, cudaStream_t stream) {
+                          const int32_t* offsets, const int32_t* blocks, int32_t n_blocks, int32_t batch,
+                          cudaStream_t stream) {
   if (!src || !signs || !dst || !blocks || n_blocks < 1 || n_blocks > GLQB_MAX_BLOCKS || batch < 1 || feat < 1 ||
       feat > pad)
-    return fail(GLQB_E_INVALID, "rht: bad arguments");
+    return fail(GLQB_E_INVALID, "rht: bad arguments (at most %d Hadamard blocks per call)", GLQB_MAX_BLOCKS);
+  if (reinterpret_cast<uintptr_t>(signs) & 15) return fail(GLQB_E_INVALID, "rht: sign vector must be 16-byte aligned");
   DevLinear L;
   memset(&L, 0, sizeof L);
-  int off = 0, maxbs = 32;
+  RhtSingle S;
+  memset(&S, 0, sizeof S);
+  int off = 0, max_elems = 32, ctas = 0;
   for (int i = 0; i < n_blocks; ++i) {
     const int b = blocks[i];
     if (b < 1 || (b & (b - 1)) || b > 32768) return fail(GLQB_E_INVALID, "rht: block %d", b);
-    if (input) { L.bn_off[i] = off; L.bn_log[i] = ilog2(b); } else { L.bm_off[i] = off; L.bm_log[i] = ilog2(b); }
+    const int o = offsets ? offsets[i] : off;
+    if (o < 0 || o + b > pad) return fail(GLQB_E_INVALID, "rht: block %d at column %d exceeds %d columns", b, o, pad);
+    if (input) { L.bn_off[i] = o; L.bn_log[i] = ilog2(b); } else { L.bm_off[i] = o; L.bm_log[i] = ilog2(b); }
     off += b;
-    maxbs = std::max(maxbs, b);
+    const int tt = rht_tile_tokens(b, batch);
+    S.first_cta[i] = ctas;
+    S.tile_tokens[i] = tt;
+    ctas += (batch + tt - 1) / tt;
+    max_elems = std::max(max_elems, tt * b);
   }
-  if (off != pad) return fail(GLQB_E_INVALID, "rht: blocks sum to %d, expected %d", off, pad);
+  S.first_cta[n_blocks] = ctas;
+  S.n_blocks = n_blocks;
+  if (!offsets && off != pad) return fail(GLQB_E_INVALID, "rht: blocks sum to %d, expected %d", off, pad);
   L.format = GLQB_FMT_E8_SHELL;
   L.batch = batch;
-  std::vector<RhtItem> items;
-  int max_elems = 32;
-  add_rht_items(items, 0, n_blocks, input ? L.bn_log : L.bm_log, batch, max_elems);
-  DevLinear* d_L = nullptr;
-  RhtItem* d_items = nullptr;
   if (input) {
     L.n = pad; L.in_f = feat; L.sv = reinterpret_cast<const __half*>(signs);
     L.x_dtype = src_dtype; L.x_stride = src_stride; L.nbn = n_blocks; L.xr_off = 0;
@@ -844,60 +865,81 @@ static int run_rht_single(bool input, const void* src, int src_dtype, int64_t sr
     L.m = pad; L.out_f = feat; L.su = reinterpret_cast<const __half*>(signs);
     L.y_dtype = dst_dtype; L.y_stride = dst_stride; L.nbm = n_blocks; L.wscale = 1.f;
   }
-  CUDA_TRY(cudaMallocAsync(&d_L, sizeof L, stream));
-  CUDA_TRY(cudaMallocAsync(&d_items, sizeof(RhtItem) * items.size(), stream));
-  CUDA_TRY(cudaMemcpyAsync(d_L, &L, sizeof L, cudaMemcpyHostToDevice, stream));
-  CUDA_TRY(cudaMemcpyAsync(d_items, items.data(), sizeof(RhtItem) * items.size(), cudaMemcpyHostToDevice, stream));
-  const unsigned grid = (unsigned)items.size();
-  const int smem = rht_smem(max_elems);
-  maxbs = max_elems;
-  if (input) {
-    if (smem > 48 * 1024)
-      CUDA_TRY(cudaFuncSetAttribute(rht_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    rht_in_kernel<true><<<grid, rht_threads(maxbs), smem, stream>>>(d_L, d_items, reinterpret_cast<const uint8_t*>(src),
-                                                                     reinterpret_cast<uint8_t*>(dst));
-  } else {
-    if (smem > 48 * 1024)
-      CUDA_TRY(cudaFuncSetAttribute(rht_out_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    rht_out_kernel<true><<<grid, rht_threads(maxbs), smem, stream>>>(d_L, d_items, nullptr, reinterpret_cast<uint8_t*>(dst),
-                                                                      reinterpret_cast<const float*>(src));
+  int dev_id = 0;
+  CUDA_TRY(cudaGetDevice(&dev_id));
+  {
+    // once per device: the two kernels may need more than the default 48 KiB of dynamic shared memory
+    static std::mutex mu;
+    static bool done[64] = {false};
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev_id >= 0 && dev_id < 64 && !done[dev_id]) {
+      const int lim = rht_smem(32768);
+      CUDA_TRY(cudaFuncSetAttribute(rht_in_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+      CUDA_TRY(cudaFuncSetAttribute(rht_out_single_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lim));
+      done[dev_id] = true;
+    }
   }
+  const int smem = rht_smem(max_elems);
+  if (input)
+    rht_in_single_kernel<<<(unsigned)ctas, rht_threads(max_elems), smem, stream>>>(
+        L, S, reinterpret_cast<const uint8_t*>(src), reinterpret_cast<uint8_t*>(dst));
+  else
+    rht_out_single_kernel<<<(unsigned)ctas, rht_threads(max_elems), smem, stream>>>(
+        L, S, reinterpret_cast<uint8_t*>(dst), reinterpret_cast<const float*>(src));
   CUDA_TRY(cudaGetLastError());
-  // the host copies above were taken from pageable memory: the copy has been staged before
-  // cudaMemcpyAsync returned, so the vectors may go out of scope
-  CUDA_TRY(cudaFreeAsync(d_L, stream));
-  CUDA_TRY(cudaFreeAsync(d_items, stream));
   return GLQB_OK;
 }
 
 int glqb_input_rht(const void* x, int32_t x_dtype, int64_t x_stride, const void* sv, void* out_f32,
                    int32_t in_features, int32_t n_pad, const int32_t* blocks, int32_t n_blocks, int32_t batch,
                    void* stream) {
-  return run_rht_single(true, x, x_dtype, x_stride, sv, out_f32, GLQB_DT_F32, n_pad, in_features, n_pad, blocks,
-                        n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
+  return run_rht_single(true, x, x_dtype, x_stride, sv, out_f32, GLQB_DT_F32, n_pad, in_features, n_pad, nullptr,
+                        blocks, n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int glqb_output_rht(const float* y_rht, const void* su, void* out, int32_t out_dtype, int64_t out_stride,
                     int32_t out_features, int32_t m_pad, const int32_t* blocks, int32_t n_blocks, int32_t batch,
                     void* stream) {
   return run_rht_single(false, y_rht, GLQB_DT_F32, m_pad, su, out, out_dtype, out_stride, out_features, m_pad,
-                        blocks, n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
+                        nullptr, blocks, n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int glqb_output_rht_shards(const float* y_rht, const void* su, void* out, int32_t out_dtype, int64_t out_stride,
+                           int32_t out_features, int32_t total_m, const int32_t* offsets, const int32_t* blocks,
+                           int32_t n_blocks, int32_t batch, void* stream) {
+  if (!offsets) return fail(GLQB_E_INVALID, "output_rht_shards: null offsets");
+  return run_rht_single(false, y_rht, GLQB_DT_F32, total_m, su, out, out_dtype, out_stride, out_features, total_m,
+                        offsets, blocks, n_blocks, batch, reinterpret_cast<cudaStream_t>(stream));
 }
 
 size_t glqb_linear_workspace_bytes(const GlqbLinearDesc* desc) {
-  // Upper bound that does not depend on the device: activations + the largest possible number of
-  // partial-sum slots (one per work group of a strip, plus one).
+  // Upper bound that does not depend on the device, with the roundings build_plan applies: activations
+  // (E8 batches are padded to 8 tokens; the GEMM path stores whole token tiles of whole 64-column chunks),
+  // the largest possible number of partial-sum slots (one per work group of a strip, plus one), and for
+  // E8 above 128 tokens the decoded fp16 weight tiles.
   if (!desc) return 0;
-  const size_t gps = desc->format == GLQB_FMT_TRELLIS_3INST ? desc->n_pad / 32 : (desc->n_pad + 255) / 256;
-  size_t ws = align_up((size_t)desc->batch * desc->n_pad * 2 * XR_TRELLIS_EXPAND, 256);
-  ws += align_up((gps + 1) * (size_t)desc->batch * desc->m_pad * 4, 256);
+  const size_t batch = (size_t)std::max(1, desc->batch);
+  const int tn = tn_for_batch((int)batch);
+  size_t ws = 1024;
+  if (tn) {
+    const size_t n_tiles = (batch + tn - 1) / tn, kchunks = ((size_t)desc->n_pad + GM_TILE_K - 1) / GM_TILE_K;
+    ws += align_up(n_tiles * kchunks * tn * 128, 1024);
+    ws += align_up(16 * batch * desc->m_pad * 4, 1024);                      // at most 16 K splits
+    if (desc->format == GLQB_FMT_E8_SHELL)
+      ws += align_up((size_t)((desc->m_pad + GM_TILE_M - 1) / GM_TILE_M) * kchunks * GM_A_BYTES, 1024) + 1024;
+  } else {
+    const size_t gps = desc->format == GLQB_FMT_TRELLIS_3INST ? desc->n_pad / 32 : (desc->n_pad + 255) / 256;
+    ws += align_up(((batch + 7) / 8 * 8) * desc->n_pad * 2 * XR_TRELLIS_EXPAND, 1024);
+    ws += align_up((gps + 1) * batch * desc->m_pad * 4, 1024);
+  }
   return ws;
 }
 
 int glqb_fused_linear(const GlqbLinearDesc* desc, const void* x, void* y, void* workspace, size_t workspace_bytes,
                       void* stream) {
-  // Stateless form: builds a one-layer plan, runs it and releases it after the stream has consumed
-  // the table.  Callers on a hot path should keep a plan instead (glqb_plan_create once).
+  // Stateless convenience form: builds a one-layer plan (which allocates its small device table), runs it,
+  // waits for the stream and releases the plan.  It therefore synchronises and must not be called while the
+  // stream is being captured; callers on a hot path keep a plan instead (glqb_plan_create once).
   GlqbPlan* P = nullptr;
   int rc = glqb_plan_create(desc, 1, &P);
   if (rc) return rc;

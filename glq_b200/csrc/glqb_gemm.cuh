@@ -53,8 +53,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
                "r"(bytes)
                : "memory");
 }
-// bounded wait; false = gave up
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+// bounded wait; false = gave up.  `abort_flag` (shared memory, optional) is set by any role of the CTA whose
+// own wait ran out: the others then stop waiting at once instead of each running down its own limit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const volatile int* abort_flag = nullptr) {
   const uint32_t addr = smem_u32(bar);
   for (uint32_t it = 0; it < GM_SPIN_LIMIT; ++it) {
     uint32_t ok;
@@ -64,6 +65,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
+    if (abort_flag && (it & 63u) == 63u && *abort_flag) return false;
   }
   return false;
 }
@@ -282,7 +284,8 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
   uint64_t* empty = bars + 2 * STAGES;
   uint64_t* acc_full = bars + 3 * STAGES;          // [2]
   uint64_t* acc_empty = acc_full + 2;              // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* drain = acc_empty + 2;                 // give-up path only: completion of the MMAs issued so far
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(drain + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -296,6 +299,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
+    mbar_init(drain, 1);
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -307,6 +311,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_acc = *tmem_slot;
+  uint32_t loads_issued = 0;                       // activation-loader thread: stages armed so far
 
   if (warp < GM_PRODUCER_WARPS) {
     // ------------------------------------------------------------------ producers (+ epilogue)
@@ -350,7 +355,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
           const Words<(K2 > 0 ? K2 : 1)> v2 = nxt2;
           const bool valid = row_ok && (kc * 2 + cg) < gps;
           if (kc + 2 < it.k_end) fetch(kc + 2);
-          if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t a_tile = smem_u32(a_base) + stage * GM_A_BYTES;
           if (valid) {
             gemm_store_group<K1, K2>(a_tile, off, lane, v, v2, s2);
@@ -371,13 +376,17 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         const int row = it.m_tile * GM_TILE_M + row_l;
         const int nidx = L.n >> 3;
         const bool row_ok = row < L.m;
+        // 8-byte loads need every row (and the matrix itself) to start on an 8-byte boundary
+        bool vec_ok = (nidx & 3) == 0;
+#pragma unroll
+        for (int s = 0; s < K1; ++s) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(L.codes[s]) & 7) == 0;
         uint2 nq[K1];                                     // 4 indices (8 bytes) per stage
         auto fetch = [&](int kc) {
           const int i0 = kc * 8 + hf * 4;
 #pragma unroll
           for (int s = 0; s < K1; ++s) {
             nq[s] = make_uint2(0u, 0u);
-            if (row_ok && i0 + 4 <= nidx) {
+            if (row_ok && vec_ok && i0 + 4 <= nidx) {
               nq[s] = ld_stream_v2(reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx + i0);
             } else if (row_ok) {
               const uint16_t* qd = reinterpret_cast<const uint16_t*>(L.codes[s]) + (long long)row * nidx;
@@ -408,7 +417,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
               ent[s][k] = __ldg(L.table[s] + (idx & mask));
             }
           }
-          if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t a_tile = smem_u32(a_base) + stage * GM_A_BYTES;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -444,7 +453,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
       q0 += (uint32_t)(it.k_end - it.k_begin);
       if (!ok) break;
     }
-    if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(status, 2); }
+    if (!ok) { *abort_flag = 1; if (lane == 0) atomicCAS(status, 0, (int)ST_GAVE_UP_PRODUCER); }
   } else if (warp == GM_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
@@ -456,10 +465,10 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         const GemmItem it = items[item];
         const uint32_t a = seq & 1u, a_phase = (seq >> 1) & 1u;     // accumulator and its use count parity
         const uint32_t d_tmem = tmem_acc + a * TN;
-        if (!mbar_wait(&acc_empty[a], a_phase ^ 1)) { ok = false; break; }
+        if (!mbar_wait(&acc_empty[a], a_phase ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         for (int kc = it.k_begin; kc < it.k_end; ++kc) {
-          if ((FORMAT != 2 && !mbar_wait(&full_a[stage], phase)) || !mbar_wait(&full_b[stage], phase)) { ok = false; break; }
+          if ((FORMAT != 2 && !mbar_wait(&full_a[stage], phase, abort_flag)) || !mbar_wait(&full_b[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint64_t da = umma_desc_sw128(smem_u32(a_base + stage * GM_A_BYTES));
           const uint64_t db = umma_desc_sw128(smem_u32(b_base + stage * B_BYTES));
@@ -472,7 +481,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         if (!ok) break;
         umma_commit(&acc_full[a]);
       }
-      if (!ok) { *abort_flag = 1; atomicExch(status, 3); }
+      if (!ok) { *abort_flag = 1; atomicCAS(status, 0, (int)ST_GAVE_UP_MMA); }
     }
   } else if (warp == GM_LOAD_WARP) {
     // ------------------------------------------------------------------ activation loader
@@ -486,7 +495,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
         const int kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
         const uint8_t* src = ws + L.xr_off + ((size_t)it.n_tile * kchunks) * B_BYTES;
         for (int kc = it.k_begin; kc < it.k_end; ++kc) {
-          if (!mbar_wait(&empty[stage], phase ^ 1)) { ok = false; break; }
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           if constexpr (FORMAT == 2) {
             mbar_expect_tx(&full_b[stage], B_BYTES + GM_A_BYTES);
             bulk_g2s(a_base + stage * GM_A_BYTES,
@@ -495,10 +504,11 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
             mbar_expect_tx(&full_b[stage], B_BYTES);
           }
           bulk_g2s(b_base + stage * B_BYTES, src + (size_t)kc * B_BYTES, B_BYTES, &full_b[stage]);
+          ++loads_issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
-      if (!ok) { *abort_flag = 1; atomicExch(status, 4); }
+      if (!ok) { *abort_flag = 1; atomicCAS(status, 0, (int)ST_GAVE_UP_LOADER); }
     }
   }
   else {
@@ -510,7 +520,7 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
       const GemmItem it = items[item];
       const DevLinear& L = layers[it.layer];
       const uint32_t a = seq & 1u, a_phase = (seq >> 1) & 1u;
-      if (!mbar_wait(&acc_full[a], a_phase)) { ok = false; break; }
+      if (!mbar_wait(&acc_full[a], a_phase, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int row = it.m_tile * GM_TILE_M + quarter * 32 + lane;
       float* part = reinterpret_cast<float*>(ws + L.part_off) + (long long)it.slot * L.batch * L.m;
@@ -531,11 +541,28 @@ glq_gemm_kernel(const DevLinear* __restrict__ layers, const GemmItem* __restrict
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[a]);
     }
-    if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(status, 5); }
+    if (!ok) { *abort_flag = 1; if (lane == 0) atomicCAS(status, 0, (int)ST_GAVE_UP_EPILOGUE); }
   }
   // ---- teardown: every thread arrives here (also after a wait gave up)
   tc_fence_before();
   __syncthreads();
+  if (*abort_flag) {
+    // A role gave up.  Before shared memory and tensor memory are released, wait (bounded again) for what
+    // may still be in flight: the bulk copies into the stages armed last, and the MMAs issued so far.
+    if (warp == GM_LOAD_WARP && lane == 0) {
+      const uint32_t n = loads_issued < (uint32_t)STAGES ? loads_issued : (uint32_t)STAGES;
+      for (uint32_t i = 0; i < n; ++i) {
+        const uint32_t q = loads_issued - 1 - i;
+        mbar_wait(&full_b[q % STAGES], (q / STAGES) & 1u);
+      }
+    }
+    if (warp == GM_MMA_WARP && lane == 0) {
+      umma_commit(drain);
+      mbar_wait(drain, 0);
+    }
+    tc_fence_before();
+    __syncthreads();
+  }
   if (warp == GM_MMA_WARP) tmem_dealloc(tmem_acc, 2 * TN);
 }
 
@@ -559,13 +586,14 @@ __device__ __forceinline__ void e8_tiles_body(const DevLinear* __restrict__ laye
     const int m_tiles = (L.m + GM_TILE_M - 1) / GM_TILE_M;
     const int kgroups = (kchunks + 3) >> 2;
     const int nidx = L.n >> 3, m = L.m;
-    const bool vec_ok = (nidx & 7) == 0;                 // every row starts 16-byte aligned
+    bool vec_ok = (nidx & 7) == 0;                       // every row starts 16-byte aligned
     const uint16_t* codes[NS];
     E8Stage stg[NS];
     __half2 sc[NS];
 #pragma unroll
     for (int s = 0; s < NS; ++s) {
       codes[s] = reinterpret_cast<const uint16_t*>(L.codes[s]);
+      vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(L.codes[s]) & 15) == 0;
       stg[s].table = L.table[s];
       stg[s].mask = (uint32_t)L.table_entries[s] - 1u;
       stg[s].base = L.table_entries[s] == 65536 ? T.table_base : T.small_base;

@@ -33,7 +33,6 @@ struct DevLinear {
   int per_warp;          // work groups handed to each warp of the segment's launch
   int fixed_slots;       // > 0: every strip has exactly this many partial sums (GEMM path: K splits)
   int gemm_tn;           // token tile of the GEMM path (0: streaming decode path)
-  int slot_mult;         // partial sums written per warp range (2 when two CTAs of a cluster split a table)
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];
@@ -61,7 +60,8 @@ static inline int rht_tile_tokens(int block_size, int batch) {
 // Stores the message glqb_last_error() returns for the calling thread (defined in glqb_api.cu).
 void set_error_message(const char* msg);
 
-// Status word written by kernels that detect an internal inconsistency (never a trap).
-enum : int { ST_OK = 0, ST_BAD_RANGE = 1 };
+// Status word of a plan: 0 = every kernel finished normally.  A role of the GEMM kernel whose bounded wait
+// ran out writes its code here (never a trap): 2 producers, 3 MMA issuer, 4 activation loader, 5 epilogue.
+enum : int { ST_OK = 0, ST_GAVE_UP_PRODUCER = 2, ST_GAVE_UP_MMA = 3, ST_GAVE_UP_LOADER = 4, ST_GAVE_UP_EPILOGUE = 5 };
 
 }  // namespace glqb

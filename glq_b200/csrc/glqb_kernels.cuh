@@ -152,13 +152,8 @@ __device__ __forceinline__ void rht_load_x32(const DevLinear& L, const uint8_t* 
 }
 
 template <bool PLAIN_F32>
-__global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_kernel(const DevLinear* __restrict__ layers,
-                                                             const RhtItem* __restrict__ items,
-                                                             const uint8_t* __restrict__ x_base,
-                                                             uint8_t* __restrict__ ws) {
-  extern __shared__ float fbuf[];
-  const RhtItem it = items[blockIdx.x];
-  const DevLinear& L = layers[it.layer];
+__device__ __forceinline__ void rht_in_body(const DevLinear& L, const RhtItem it, const uint8_t* __restrict__ x_base,
+                                            uint8_t* __restrict__ ws, float* fbuf) {
   const int off = L.bn_off[it.block];
   const int logbs = L.bn_log[it.block];
   const int bs = 1 << logbs;
@@ -195,6 +190,38 @@ __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_kernel(cons
   fht_tile(fbuf, logbs, it.ntok, load32, load1, store1);
 }
 
+template <bool PLAIN_F32>
+__global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_kernel(const DevLinear* __restrict__ layers,
+                                                             const RhtItem* __restrict__ items,
+                                                             const uint8_t* __restrict__ x_base,
+                                                             uint8_t* __restrict__ ws) {
+  extern __shared__ float fbuf[];
+  const RhtItem it = items[blockIdx.x];
+  rht_in_body<PLAIN_F32>(layers[it.layer], it, x_base, ws, fbuf);
+}
+
+// One layer described entirely in kernel-parameter space (no device table, nothing to allocate or copy):
+// the unfused input_rht / output_rht ops.  CTA b of Hadamard block k handles the token tile
+// b - first_cta[k]; tile_tokens[k] tokens per tile.
+struct RhtSingle {
+  int first_cta[GLQB_MAX_BLOCKS + 1];
+  int tile_tokens[GLQB_MAX_BLOCKS];
+  int n_blocks;
+};
+__device__ __forceinline__ RhtItem rht_single_item(const RhtSingle& S, int batch) {
+  int k = 0;
+  while (k + 1 < S.n_blocks && (int)blockIdx.x >= S.first_cta[k + 1]) ++k;
+  const int tok0 = ((int)blockIdx.x - S.first_cta[k]) * S.tile_tokens[k];
+  return RhtItem{0, k, tok0, min(S.tile_tokens[k], batch - tok0)};
+}
+static __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_single_kernel(const __grid_constant__ DevLinear L,
+                                                                    const __grid_constant__ RhtSingle S,
+                                                                    const uint8_t* __restrict__ x_base,
+                                                                    uint8_t* __restrict__ out) {
+  extern __shared__ float fbuf[];
+  rht_in_body<true>(L, rht_single_item(S, L.batch), x_base, out, fbuf);
+}
+
 // ---------------------------------------------------------------------------------------------
 // Output transform: sums the partial sums of every strip in fixed (ascending slot) order, applies
 // wscale (and the optional per-row scale), the block Hadamard, 1/sqrt(bs) and SU, and writes
@@ -202,14 +229,9 @@ __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_kernel(cons
 // FROM_F32: input is a plain fp32 (batch, m) matrix (the unfused output_rht op).
 // ---------------------------------------------------------------------------------------------
 template <bool FROM_F32>
-__global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_kernel(const DevLinear* __restrict__ layers,
-                                                              const RhtItem* __restrict__ items,
-                                                              const uint8_t* __restrict__ ws,
-                                                              uint8_t* __restrict__ y_base,
-                                                              const float* __restrict__ yrht_in) {
-  extern __shared__ float fbuf[];
-  const RhtItem it = items[blockIdx.x];
-  const DevLinear& L = layers[it.layer];
+__device__ __forceinline__ void rht_out_body(const DevLinear& L, const RhtItem it, const uint8_t* __restrict__ ws,
+                                             uint8_t* __restrict__ y_base, const float* __restrict__ yrht_in,
+                                             float* fbuf) {
   const int off = L.bm_off[it.block];
   const int logbs = L.bm_log[it.block];
   const int bs = 1 << logbs;
@@ -222,7 +244,7 @@ __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_kernel(con
   auto slots_of = [&](int row) -> int {
     if (fixed_slots > 0) return fixed_slots;
     const long long g0 = L.group_base + (long long)(row / rows_per_strip) * gps;
-    return ((int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1) * L.slot_mult;
+    return (int)((g0 + gps - 1) / per_warp - g0 / per_warp) + 1;
   };
   auto load1 = [&](int trow, int i) -> float {
     const int row = off + i;
@@ -321,6 +343,25 @@ __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_kernel(con
     }
   };
   fht_tile8(fbuf, logbs, it.ntok, load32, load1, store8);
+}
+
+template <bool FROM_F32>
+__global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_kernel(const DevLinear* __restrict__ layers,
+                                                              const RhtItem* __restrict__ items,
+                                                              const uint8_t* __restrict__ ws,
+                                                              uint8_t* __restrict__ y_base,
+                                                              const float* __restrict__ yrht_in) {
+  extern __shared__ float fbuf[];
+  const RhtItem it = items[blockIdx.x];
+  rht_out_body<FROM_F32>(layers[it.layer], it, ws, y_base, yrht_in, fbuf);
+}
+
+static __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_single_kernel(const __grid_constant__ DevLinear L,
+                                                                     const __grid_constant__ RhtSingle S,
+                                                                     uint8_t* __restrict__ y_base,
+                                                                     const float* __restrict__ yrht_in) {
+  extern __shared__ float fbuf[];
+  rht_out_body<true>(L, rht_single_item(S, L.batch), nullptr, y_base, yrht_in, fbuf);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -618,7 +659,9 @@ __device__ __forceinline__ void e8_mv_body(const DevLinear* __restrict__ layers,
     const int c1 = (int)min((long long)gps, c0 + (gend - g));
     const int batch = L.batch;
     const int nidx = L.n >> 3;                 // indices per row
-    const bool vec_ok = (nidx & 7) == 0;       // rows start 16-byte aligned
+    bool vec_ok = (nidx & 7) == 0;             // rows (and the matrices themselves) start 16-byte aligned
+#pragma unroll
+    for (int s = 0; s < NS; ++s) vec_ok = vec_ok && (reinterpret_cast<uintptr_t>(L.codes[s]) & 15) == 0;
     const int rowA = strip * 16 + gq, rowB = rowA + 8;
     const bool okA = rowA < L.m, okB = rowB < L.m;
 

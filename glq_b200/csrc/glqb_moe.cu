@@ -58,6 +58,15 @@ struct MoeDev {
   // tensor-core form (gemm != 0): tile rows, device-built layer tables and work lists
   int gemm, k13a, k13b, k2a, k2b, max_items13, max_items2;
   long long o_trow, o_tile0, o_layers13, o_layers2, o_items13, o_items2, o_nitems, o_status;
+  // E8 shell experts (format == GLQB_FMT_E8_SHELL; tensor-core form only): index matrices per stage,
+  // expert-stacked, the packed tables, and the per-expert cumulative inverse residual scales of stages 2, 3
+  int format, e8_ns;
+  const uint8_t* e8_w13[3];
+  const uint8_t* e8_w2[3];
+  const uint32_t* e8_tab[3];
+  int e8_ent[3];
+  const float* e8_w13_inv[2];
+  const float* e8_w2_inv[2];
 };
 
 constexpr int MOE_TN = 128;                    // routed tokens per GEMM tile
@@ -212,18 +221,30 @@ __global__ void __launch_bounds__(1024) moe_group_kernel(const __grid_constant__
     for (int e = threadIdx.x; e < M.E; e += blockDim.x) {
       DevLinear a;
       memset(&a, 0, sizeof a);
-      a.format = GLQB_FMT_TRELLIS_3INST;
+      a.format = M.format;
       a.batch = cnt[e];
       DevLinear b = a;
-      a.codes[0] = M.w13[0] + (long long)e * M.w13_stride[0];
-      a.codes[1] = M.w13[1] ? M.w13[1] + (long long)e * M.w13_stride[1] : nullptr;
-      a.stage_scale[0] = 1.f; a.stage_scale[1] = M.w13_inv2 ? M.w13_inv2[e] : 0.f;
+      if (M.format == GLQB_FMT_E8_SHELL) {
+        a.n_stages = b.n_stages = M.e8_ns;
+        for (int s = 0; s < M.e8_ns; ++s) {
+          a.codes[s] = M.e8_w13[s] + (long long)e * M.w13_stride[0];
+          b.codes[s] = M.e8_w2[s] + (long long)e * M.w2_stride[0];
+          a.table[s] = b.table[s] = M.e8_tab[s];
+          a.table_entries[s] = b.table_entries[s] = M.e8_ent[s];
+          a.stage_scale[s] = s ? M.e8_w13_inv[s - 1][e] : 1.f;
+          b.stage_scale[s] = s ? M.e8_w2_inv[s - 1][e] : 1.f;
+        }
+      } else {
+        a.codes[0] = M.w13[0] + (long long)e * M.w13_stride[0];
+        a.codes[1] = M.w13[1] ? M.w13[1] + (long long)e * M.w13_stride[1] : nullptr;
+        a.stage_scale[0] = 1.f; a.stage_scale[1] = M.w13_inv2 ? M.w13_inv2[e] : 0.f;
+        b.codes[0] = M.w2[0] + (long long)e * M.w2_stride[0];
+        b.codes[1] = M.w2[1] ? M.w2[1] + (long long)e * M.w2_stride[1] : nullptr;
+        b.stage_scale[0] = 1.f; b.stage_scale[1] = M.w2_inv2 ? M.w2_inv2[e] : 0.f;
+      }
       a.m = M.w13_out; a.n = M.hidden; a.strips = M.w13_out / 32; a.groups_per_strip = M.hidden / 32;
       a.xr_off = M.o_xr1 + (long long)tile0[e] * kc13 * MOE_B_BYTES;
       a.part_off = M.o_part1 + (long long)base_s[e] * M.w13_out * 4;
-      b.codes[0] = M.w2[0] + (long long)e * M.w2_stride[0];
-      b.codes[1] = M.w2[1] ? M.w2[1] + (long long)e * M.w2_stride[1] : nullptr;
-      b.stage_scale[0] = 1.f; b.stage_scale[1] = M.w2_inv2 ? M.w2_inv2[e] : 0.f;
       b.m = M.hidden; b.n = M.inter; b.strips = M.hidden / 32; b.groups_per_strip = M.inter / 32;
       b.xr_off = M.o_xr2 + (long long)tile0[e] * kc2 * MOE_B_BYTES;
       b.part_off = M.o_part2 + (long long)base_s[e] * M.hidden * 4;
@@ -700,8 +721,16 @@ static MoeGemmKernel moe_gemm_pick(int k1, int k2) {
 #undef M_CASE
   return nullptr;
 }
+static MoeGemmKernel moe_gemm_pick_e8(int ns) {
+  switch (ns) {
+    case 1: return glq_gemm_kernel<1, 1, 0, MOE_TN, MOE_GEMM_STAGES>;
+    case 2: return glq_gemm_kernel<1, 2, 0, MOE_TN, MOE_GEMM_STAGES>;
+    case 3: return glq_gemm_kernel<1, 3, 0, MOE_TN, MOE_GEMM_STAGES>;
+  }
+  return nullptr;
+}
 static size_t moe_gemm_smem_bytes() {
-  return (size_t)MOE_GEMM_STAGES * (GM_A_BYTES + (size_t)MOE_B_BYTES) + (3 * MOE_GEMM_STAGES + 4) * 8 + 16 + 1024;
+  return (size_t)MOE_GEMM_STAGES * (GM_A_BYTES + (size_t)MOE_B_BYTES) + (3 * MOE_GEMM_STAGES + 5) * 8 + 16 + 1024;
 }
 // routed tokens per expert (average) from which the tensor-core form is used
 static int moe_gemm_min_avg() {
@@ -779,14 +808,28 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
                     d->max_tokens);
   const bool gated = d->activation >= 0 && d->activation <= 2;
   if (d->activation < 0 || d->activation > 5) return moe_fail(GLQB_E_INVALID, "moe_plan_create: activation %d", d->activation);
+  const bool e8 = d->format == GLQB_FMT_E8_SHELL;
+  if (d->format != GLQB_FMT_TRELLIS_3INST && !e8) return moe_fail(GLQB_E_INVALID, "moe_plan_create: format %d", d->format);
   if (d->hidden % 32 || d->inter % 32 || d->w13_out % 32)
     return moe_fail(GLQB_E_INVALID, "moe_plan_create: hidden/inter/w13_out must be multiples of 32");
+  if (e8) {
+    if (d->hidden % GM_TILE_K || d->inter % GM_TILE_K)
+      return moe_fail(GLQB_E_INVALID, "moe_plan_create: E8 experts need hidden and inter to be multiples of 64");
+    if (d->e8_stages < 1 || d->e8_stages > 3) return moe_fail(GLQB_E_INVALID, "moe_plan_create: E8 stages %d (1..3)", d->e8_stages);
+    for (int s = 0; s < d->e8_stages; ++s) {
+      const int en = d->e8_table_entries[s];
+      if (!d->w13_qidxs[s] || !d->w2_qidxs[s] || !d->e8_table[s] || en < 1 || en > 65536 || (en & (en - 1)))
+        return moe_fail(GLQB_E_INVALID, "moe_plan_create: E8 stage %d: null index matrix / table, or %d table entries", s, en);
+      if (s && (!d->w13_inv_rs[s - 1] || !d->w2_inv_rs[s - 1]))
+        return moe_fail(GLQB_E_INVALID, "moe_plan_create: E8 stage %d without its inverse residual scales", s);
+    }
+  }
   if (d->w13_out != (gated ? 2 : 1) * d->inter)
     return moe_fail(GLQB_E_INVALID, "moe_plan_create: w13_out=%d does not match inter=%d for activation %d", d->w13_out,
                     d->inter, d->activation);
   if (d->hidden > 8 * 1024 || d->inter > 4 * 1024 || d->w13_out > 16384)
     return moe_fail(GLQB_E_INVALID, "moe_plan_create: hidden <= 8192, inter <= 4096 supported");
-  if (!d->w13_packed || !d->w2_packed || !d->w13_su || !d->w13_sv || !d->w2_su || !d->w2_sv || !d->w13_wscale ||
+  if ((!e8 && (!d->w13_packed || !d->w2_packed)) || !d->w13_su || !d->w13_sv || !d->w2_su || !d->w2_sv || !d->w13_wscale ||
       !d->w2_wscale)
     return moe_fail(GLQB_E_INVALID, "moe_plan_create: null weight pointer");
   if ((reinterpret_cast<uintptr_t>(d->w13_su) | reinterpret_cast<uintptr_t>(d->w13_sv) | reinterpret_cast<uintptr_t>(d->w2_su) |
@@ -805,8 +848,10 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
     return rc;
   }
   M.nb_n13 = d->n_blocks_n_w13; M.nb_m13 = d->n_blocks_m_w13; M.nb_n2 = d->n_blocks_n_w2; M.nb_m2 = d->n_blocks_m_w2;
-  const int k13a = d->w13_bits, k13b = d->w13_packed2 ? d->w13_bits2 : 0;
-  const int k2a = d->w2_bits, k2b = d->w2_packed2 ? d->w2_bits2 : 0;
+  // E8 experts run the tensor-core form at every token count; the streaming kernels below are picked with
+  // placeholder rates and never launched for them
+  const int k13a = e8 ? 4 : d->w13_bits, k13b = (!e8 && d->w13_packed2) ? d->w13_bits2 : 0;
+  const int k2a = e8 ? 4 : d->w2_bits, k2b = (!e8 && d->w2_packed2) ? d->w2_bits2 : 0;
   // tokens per decode pass: 16 for small steps, 32 when experts see many tokens
   const double avg = (double)d->max_tokens * d->top_k / d->num_experts;
   (void)avg;
@@ -824,6 +869,20 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   M.w13_stride[1] = (long long)d->w13_out * d->hidden * k13b / 8;
   M.w2_stride[0] = (long long)d->hidden * d->inter * k2a / 8;
   M.w2_stride[1] = (long long)d->hidden * d->inter * k2b / 8;
+  M.format = d->format;
+  if (e8) {
+    M.e8_ns = d->e8_stages;
+    M.w13_stride[0] = (long long)d->w13_out * (d->hidden / 8) * 2;     // int16 per 8 weights, every stage
+    M.w2_stride[0] = (long long)d->hidden * (d->inter / 8) * 2;
+    M.w13_stride[1] = M.w2_stride[1] = 0;
+    for (int s = 0; s < d->e8_stages; ++s) {
+      M.e8_w13[s] = (const uint8_t*)d->w13_qidxs[s];
+      M.e8_w2[s] = (const uint8_t*)d->w2_qidxs[s];
+      M.e8_tab[s] = d->e8_table[s];
+      M.e8_ent[s] = d->e8_table_entries[s];
+      if (s) { M.e8_w13_inv[s - 1] = d->w13_inv_rs[s - 1]; M.e8_w2_inv[s - 1] = d->w2_inv_rs[s - 1]; }
+    }
+  }
   M.w13_su = (const __half*)d->w13_su; M.w13_sv = (const __half*)d->w13_sv;
   M.w13_wscale = d->w13_wscale; M.w13_inv2 = d->w13_inv_resid_scale2;
   M.w2_su = (const __half*)d->w2_su; M.w2_sv = (const __half*)d->w2_sv;
@@ -856,10 +915,10 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
   M.o_part2 = o; o = al(o + (size_t)M.kch2 * R * d->hidden * 4);
   P->ws_bytes = o;
   // tensor-core form: its buffers overlay the decode form's (a step runs one or the other)
-  P->g13 = moe_gemm_pick(k13a, k13b);
-  P->g2 = moe_gemm_pick(k2a, k2b);
+  P->g13 = e8 ? moe_gemm_pick_e8(d->e8_stages) : moe_gemm_pick(k13a, k13b);
+  P->g2 = e8 ? moe_gemm_pick_e8(d->e8_stages) : moe_gemm_pick(k2a, k2b);
   P->gemm_ok = P->g13 && P->g2 && d->hidden % GM_TILE_K == 0 && d->inter % GM_TILE_K == 0 && M.E <= 4096 &&
-               R >= (size_t)M.E * moe_gemm_min_avg();
+               (e8 || R >= (size_t)M.E * moe_gemm_min_avg());
   if (P->gemm_ok) {
     MoeDev& G = P->devg;
     G = M;
@@ -907,6 +966,10 @@ int glqb_moe_plan_create(const GlqbMoeDesc* d, GlqbMoePlan** out) {
       return moe_fail(GLQB_E_CUDA, "moe_plan_create: %s", cudaGetErrorString(cudaGetLastError()));
     }
   }
+  if (e8 && !P->gemm_ok) {
+    delete P;
+    return moe_fail(GLQB_E_INVALID, "moe_plan_create: the tensor-core form is unavailable for these E8 experts");
+  }
   int dev_id = 0;
   if (cudaGetDevice(&dev_id) != cudaSuccess ||
       cudaDeviceGetAttribute(&P->sm_count, cudaDevAttrMultiProcessorCount, dev_id) != cudaSuccess) {
@@ -926,6 +989,7 @@ size_t glqb_moe_plan_workspace_bytes(const GlqbMoePlan* p) { return p ? p->ws_by
 int64_t glqb_moe_plan_code_bytes(const GlqbMoePlan* p) {
   if (!p) return 0;
   const MoeDev& M = p->dev;
+  if (M.format == GLQB_FMT_E8_SHELL) return (int64_t)M.E * M.e8_ns * (M.w13_stride[0] + M.w2_stride[0]);
   return (int64_t)M.E * (M.w13_stride[0] + M.w13_stride[1] + M.w2_stride[0] + M.w2_stride[1]);
 }
 
@@ -939,7 +1003,8 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   if (reinterpret_cast<uintptr_t>(workspace) & 255) return moe_fail(GLQB_E_WORKSPACE, "workspace must be 256-byte aligned");
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream_);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
-  if (P->gemm_ok && (long long)tokens * P->dev.top_k >= (long long)P->dev.E * moe_gemm_min_avg()) {
+  if (P->gemm_ok && (P->dev.format == GLQB_FMT_E8_SHELL ||
+                     (long long)tokens * P->dev.top_k >= (long long)P->dev.E * moe_gemm_min_avg())) {
     const MoeDev& G = P->devg;
     const int R = tokens * G.top_k;
     moe_launch_group(G, topk_ids, tokens, ws, st);
@@ -1004,7 +1069,7 @@ int glqb_moe_plan_status(const GlqbMoePlan* P, const void* workspace, void* stre
           cudaSuccess ||
       cudaStreamSynchronize(s) != cudaSuccess)
     return moe_fail(GLQB_E_CUDA, "moe_plan_status: %s", cudaGetErrorString(cudaGetLastError()));
-  if (st != 0) return moe_fail(GLQB_E_CUDA, "moe: a bounded wait inside the GEMM kernel gave up (role %d); results are invalid", st);
+  if (st != 0) return moe_fail(GLQB_E_DEVICE, "moe: a bounded wait inside the GEMM kernel gave up (role %d); results are invalid", st);
   return GLQB_OK;
 }
 

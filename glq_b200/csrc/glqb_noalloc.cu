@@ -232,7 +232,6 @@ int glqb_trellis_linear_noalloc(const void* x, int32_t x_dtype, void* y, int32_t
     ++per_warp;
   }
   L.per_warp = (int)per_warp;
-  L.slot_mult = 1;
   L.slots = (L.groups_per_strip - 1) / L.per_warp + 2;
   const long long used_warps = (total + per_warp - 1) / per_warp;
   const int grid = (int)((used_warps + MV_WARPS - 1) / MV_WARPS);

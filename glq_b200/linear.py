@@ -55,6 +55,7 @@ class GLQLinear(nn.Module):
         self.codebook = None          # fp16 (65536, 8) tensor, or an object with .codebook_half
         self.codebook2 = None
         self._scalars = None          # cached host copies of the scalar buffers (no sync per forward)
+        self._tables = {}             # converted codebooks per device
 
     # -- loading ---------------------------------------------------------------------------------------
     def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
@@ -69,11 +70,20 @@ class GLQLinear(nn.Module):
         """E8 layers: the shared codebook(s), as the reference's objects or as fp16 (entries, 8) tensors."""
         self.codebook, self.codebook2 = codebook, codebook2
         self._scalars = None
+        self._tables = {}
 
-    @staticmethod
-    def _table(cb, device):
+    def _table(self, cb, device):
+        """fp16 copy of a codebook on ``device``, converted once per (codebook, device) and kept: the packed
+        table cache of the operator layer is keyed on the tensor's address."""
         t = getattr(cb, "codebook_half", cb)
-        return t.to(device=device, dtype=torch.float16)
+        if t.device == device and t.dtype == torch.float16:
+            return t
+        key = (id(cb), str(device))
+        hit = self._tables.get(key)
+        if hit is None or hit[0] is not t:
+            hit = (t, t.to(device=device, dtype=torch.float16))
+            self._tables[key] = hit
+        return hit[1]
 
     def _resolve(self):
         if self._scalars is None:
@@ -151,6 +161,21 @@ class GLQLinear(nn.Module):
         cb = self._table(self.codebook, dev)
         cbs = [cb, self._table(self.codebook2, dev) if ns >= 2 else cb, cb, cb][:ns]
         return ops.dequant_e8(qs, cbs, s["inv"][:ns - 1])
+
+    def dequantize(self) -> torch.Tensor:
+        """Dense fp32 (out_features, in_features) weight: the rotated-domain weights the kernels reconstruct,
+        scaled by Wscale and taken back through both Hadamard transforms (glq/quantized_linear.py:1237-1265),
+        so that ``forward(x) == x @ dequantize().T`` up to rounding.  Every residual stage is included (the
+        reference's helper stops after the second)."""
+        W = self.dequantize_rotated().contiguous()                       # (m_pad, n_pad)
+        dev = W.device
+        bn, bm = self.blocks_n, self.blocks_m
+        # columns: rows of W are "tokens" of the unfused transform, which gives SV * H_n(row) / sqrt(block)
+        t = torch.empty_like(W)
+        ops.output_rht_blocks(W, self.SV, t, self.n_pad, self.n_pad, bn)
+        t2 = torch.empty(self.n_pad, self.m_pad, dtype=torch.float32, device=dev)
+        ops.output_rht_blocks(t.t().contiguous(), self.SU, t2, self.m_pad, self.m_pad, bm)
+        return (t2.t() * float(self.Wscale.item()))[:self.out_features, :self.in_features].contiguous()
 
     def extra_repr(self) -> str:
         return (f"in_features={self.in_features}, out_features={self.out_features}, bias={self.bias is not None}, "

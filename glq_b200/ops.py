@@ -14,7 +14,8 @@ There is no CPU or PyTorch fallback: without a CUDA device and the built library
 from __future__ import annotations
 
 import ctypes as C
-import math
+import os
+from collections import OrderedDict
 from typing import Optional, Sequence
 
 import torch
@@ -23,8 +24,16 @@ from . import _lib
 from .plan import LinearSpec, Plan, block_decompose
 
 DECODE_MAX_TOKENS = 64
-_PLAN_CACHE: dict = {}
+# Plans are cheap (a small device table each); what costs memory is the workspace, and that is shared: one
+# buffer per (device, stream), grown to the largest plan that ran there.  The cache is least-recently-used
+# and bounded; token counts are rounded up to a few bucket sizes so that varying prompt lengths cannot
+# create an unbounded number of plans per layer.
+PLAN_CACHE_MAX = int(os.environ.get("GLQB_PLAN_CACHE_MAX", "16384"))
+_PLAN_CACHE: "OrderedDict" = OrderedDict()
 _TABLE_CACHE: dict = {}
+_WORKSPACES: dict = {}
+_RETIRED_WORKSPACES: list = []      # outgrown buffers stay alive: captured CUDA graphs may still point at them
+_META_CACHE: dict = {}
 
 
 def _stream(t: torch.Tensor) -> int:
@@ -49,47 +58,113 @@ def _blocks(t, fallback: int) -> list[int]:
 def e8_packed_table(codebook: torch.Tensor) -> torch.Tensor:
     """fp16 (entries, 8) codebook -> cached nibble-packed int32 (entries,) table on its device."""
     _require_cuda(codebook, "codebook")
-    key = (codebook.data_ptr(), codebook.shape[0], codebook.device.index)
+    key = (codebook.data_ptr(), codebook.shape[0], codebook.device.index, codebook.dtype)
     tb = _TABLE_CACHE.get(key)
     if tb is None:
         cb = codebook.to(torch.float16).contiguous()
         tb = torch.empty(cb.shape[0], dtype=torch.int32, device=cb.device)
         _lib.check(_lib.load().glqb_e8_pack_table(cb.data_ptr(), cb.shape[0], tb.data_ptr(), _stream(cb)),
                    "e8_pack_table")
-        _TABLE_CACHE[key] = tb
-    return tb
+        # the key is an address: keep the source alive so the address cannot be handed to another tensor
+        _TABLE_CACHE[key] = (tb, codebook)
+        return tb
+    return tb[0]
+
+
+def token_bucket(b: int) -> int:
+    """Token count a plan is built for when ``b`` tokens arrive: exact up to 8, multiples of 8 up to 64
+    (the streaming kernels), 128, then multiples of 256 (the tensor-core path).  Inputs are zero-padded to
+    the bucket and the extra output rows dropped."""
+    if b <= 8:
+        return b
+    if b <= DECODE_MAX_TOKENS:
+        return (b + 7) // 8 * 8
+    if b <= 128:
+        return 128
+    return (b + 255) // 256 * 256
+
+
+def shared_workspace(device, nbytes: int) -> torch.Tensor:
+    """The workspace every cached plan on (device, current stream) runs in; grows geometrically."""
+    dev = torch.device(device)
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(),
+           torch.cuda.current_stream(dev).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _RETIRED_WORKSPACES.append(ws)
+        size = max(nbytes, 2 * ws.numel() if ws is not None else 0, 1 << 20)
+        ws = torch.empty(size, dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = ws
+    return ws
 
 
 def _cached_plan(key, make_specs) -> Plan:
     p = _PLAN_CACHE.get(key)
-    if p is None:
-        p = Plan(make_specs())
-        _PLAN_CACHE[key] = p
+    if p is not None:
+        _PLAN_CACHE.move_to_end(key)
+        return p
+    p = Plan(make_specs(), own_workspace=False)
+    _PLAN_CACHE[key] = p
+    if len(_PLAN_CACHE) > PLAN_CACHE_MAX and not torch.cuda.is_current_stream_capturing():
+        # evict the least recently used plans; their device tables may still be read by queued work
+        torch.cuda.synchronize()
+        while len(_PLAN_CACHE) > PLAN_CACHE_MAX:
+            _, old = _PLAN_CACHE.popitem(last=False)
+            old.close()
     return p
 
 
+def check_device_status() -> None:
+    """Synchronise and raise RuntimeError (code GLQB_E_DEVICE) if a kernel of any cached plan gave up on one
+    of its bounded waits since the plan was built: the results of that run are invalid.  Cheap enough for
+    the points where a caller synchronises anyway (end of a request, a test, a benchmark step)."""
+    for p in list(_PLAN_CACHE.values()):
+        if hasattr(p, "check_status"):
+            p.check_status()
+
+
 def clear_caches() -> None:
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
     for p in _PLAN_CACHE.values():
         p.close()
     _PLAN_CACHE.clear()
     _TABLE_CACHE.clear()
+    _WORKSPACES.clear()
+    _RETIRED_WORKSPACES.clear()
+    _META_CACHE.clear()
 
 
-def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_tokens=DECODE_MAX_TOKENS) -> None:
-    """Run a single-layer op over x2d (B, in) -> out (B, out) in slices of <= max_tokens tokens."""
+def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_tokens=DECODE_MAX_TOKENS,
+                y_offset: int = 0, out_cols: Optional[int] = None) -> None:
+    """Run a single-layer op over x2d (B, in) into out[:, y_offset : y_offset + out_cols].  Up to 64 tokens go
+    through the streaming kernels in slices of <= max_tokens, more through one tensor-core plan; token counts
+    are rounded up to ``token_bucket`` sizes (zero-padded copy in, extra rows dropped)."""
     B = x2d.shape[0]
+    cols = out_cols if out_cols is not None else out.shape[1]
+
+    def run(xs, b, dst_rows):
+        bb = token_bucket(b)
+        if bb == b:
+            xin, yout, yoff = xs, dst_rows, y_offset
+        else:
+            xin = xs.new_zeros((bb, xs.shape[1]))
+            xin[:b] = xs
+            yout, yoff = torch.empty((bb, cols), dtype=out.dtype, device=out.device), 0
+        key = key_base + (bb, xin.dtype, yout.dtype, xin.stride(0), yout.stride(0), yoff)
+        plan = _cached_plan(key, lambda: [make_spec(bb, xin.stride(0), yout.stride(0), yoff)])
+        plan.run(xin, yout, workspace=shared_workspace(xin.device, plan.workspace_bytes))
+        if bb != b:
+            dst_rows[:b, y_offset:y_offset + cols] = yout[:b]
+
     if B > DECODE_MAX_TOKENS:
-        # prefill: one tensor-core GEMM plan for the whole token count
-        plan = _cached_plan(key_base + (B, x2d.dtype, out.dtype, x2d.stride(0), out.stride(0)),
-                            lambda: [make_spec(B)])
-        plan.run(x2d, out)
+        run(x2d, B, out)
         return
     done = 0
     while done < B:
         b = min(max_tokens, B - done)
-        plan = _cached_plan(key_base + (b, x2d.dtype, out.dtype, x2d.stride(0), out.stride(0)),
-                            lambda: [make_spec(b)])
-        plan.run(x2d[done:], out[done:])
+        run(x2d[done:done + b], b, out[done:done + b])
         done += b
 
 
@@ -116,17 +191,18 @@ def _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_r
     else:
         tgt, yoff, stop = y_rht_out, int(col), True
 
-    def make_spec(b):
+    def make_spec(b, x_stride, y_stride, y_offset):
         return LinearSpec(format=_lib.FMT_TRELLIS_3INST, m_pad=m_pad, n_pad=n_pad, in_features=in_features,
                           out_features=out_features if not stop else m_pad, codes=codes, bits=bits, su=su, sv=sv,
                           wscale=float(wscale), stage_scale=[float(inv_rs2)] if has2 else [],
                           blocks_n=bn, blocks_m=bm, batch=b, x_dtype=x2d.dtype, y_dtype=tgt.dtype,
-                          x_stride=x2d.stride(0), y_stride=tgt.stride(0), y_offset=yoff, stop_at_yrht=stop)
+                          x_stride=x_stride, y_stride=y_stride, y_offset=y_offset, stop_at_yrht=stop)
 
     key = ("trellis", packed.data_ptr(), packed2.data_ptr() if has2 else 0, su.data_ptr() if su is not None else 0,
-           sv.data_ptr(), float(wscale), float(inv_rs2), m_pad, n_pad, out_features, stop, yoff)
+           sv.data_ptr(), float(wscale), float(inv_rs2), m_pad, n_pad, out_features, stop)
     # two decoded stages keep two accumulator sets: 32 tokens per pass instead of 64
-    _run_sliced(x2d, tgt, key, make_spec, 32 if has2 else DECODE_MAX_TOKENS)
+    _run_sliced(x2d, tgt, key, make_spec, 32 if has2 else DECODE_MAX_TOKENS, y_offset=yoff,
+                out_cols=m_pad if stop else out_features)
     return None if stop else tgt
 
 
@@ -175,16 +251,29 @@ def _ones_f16(n: int, device) -> torch.Tensor:
 
 def output_rht_shards(y_rht, su, y, out_features, shard_meta, max_bs):
     """One output transform over the sub-blocks of several shards (glq_vllm/custom_ops.py:424-426).
-    shard_meta rows are (global column offset, block size, log2, optional normalisation bits)."""
+    shard_meta rows are (global column offset, block size, log2, optional normalisation bits); the offsets are
+    honoured.  The reference keeps the meta on the device; its host copy is read once per tensor (the first
+    call, which therefore has to happen outside stream capture, like the reference's own warm-up) and cached."""
     _require_cuda(y_rht, "y_rht")
-    meta = shard_meta.cpu().tolist() if isinstance(shard_meta, torch.Tensor) else list(shard_meta)
+    if isinstance(shard_meta, torch.Tensor):
+        key = (shard_meta.data_ptr(), shard_meta.numel(), str(shard_meta.device))
+        hit = _META_CACHE.get(key)
+        if hit is None:
+            hit = (shard_meta.cpu().tolist(), shard_meta)       # keeps the tensor (and its address) alive
+            _META_CACHE[key] = hit
+        meta = hit[0]
+    else:
+        meta = list(shard_meta)
+    offsets = [int(r[0]) for r in meta]
     blocks = [int(r[1]) for r in meta]
-    total = sum(blocks)
     B = y_rht.shape[0]
-    arr = (C.c_int32 * len(blocks))(*blocks)
-    _lib.check(_lib.load().glqb_output_rht(y_rht.data_ptr(), su.data_ptr(), y.data_ptr(), _dt(y.dtype), y.stride(0),
-                                           int(out_features), total, arr, len(blocks), B, _stream(y)),
-               "output_rht_shards")
+    lib = _lib.load()
+    # at most MAX_BLOCKS sub-blocks per launch
+    for i in range(0, len(blocks), _lib.MAX_BLOCKS):
+        o, b = offsets[i:i + _lib.MAX_BLOCKS], blocks[i:i + _lib.MAX_BLOCKS]
+        _lib.check(lib.glqb_output_rht_shards(y_rht.data_ptr(), su.data_ptr(), y.data_ptr(), _dt(y.dtype), y.stride(0),
+                                              int(out_features), int(y_rht.shape[1]), (C.c_int32 * len(o))(*o),
+                                              (C.c_int32 * len(b))(*b), len(b), B, _stream(y)), "output_rht_shards")
 
 
 def _dt(dtype) -> int:
@@ -215,12 +304,12 @@ def _fused_e8(x, sv, su, codes, tables, scales, wscale, in_features, out_feature
     odt = torch.float32 if stop else (out_dtype or x2d.dtype)
     out = torch.empty(x2d.shape[0], m_pad if stop else out_features, dtype=odt, device=x2d.device)
 
-    def make_spec(b):
+    def make_spec(b, x_stride, y_stride, y_offset):
         return LinearSpec(format=_lib.FMT_E8_SHELL, m_pad=m_pad, n_pad=n_pad, in_features=feat_in,
                           out_features=m_pad if stop else out_features, codes=codes, tables=tables,
                           stage_scale=scales, su=su, sv=sv, wscale=float(wscale), blocks_n=bn, blocks_m=bm,
-                          batch=b, x_dtype=x2d.dtype, y_dtype=odt, x_stride=x2d.stride(0), y_stride=out.stride(0),
-                          stop_at_yrht=stop, x_is_rotated=x_is_rotated)
+                          batch=b, x_dtype=x2d.dtype, y_dtype=odt, x_stride=x_stride, y_stride=y_stride,
+                          y_offset=y_offset, stop_at_yrht=stop, x_is_rotated=x_is_rotated)
 
     key = ("e8", tuple(c.data_ptr() for c in codes), tuple(t.data_ptr() for t in tables), tuple(scales),
            su.data_ptr(), sv.data_ptr(), float(wscale), m_pad, n_pad, in_features, out_features, stop, x_is_rotated)
@@ -299,6 +388,18 @@ def output_rht(y_rht, su, out, out_features, m_pad, log_m, rsqrt_m):
                "output_rht")
 
 
+def output_rht_blocks(y_rht, su, out, out_features, m_pad, blocks):
+    """Block-diagonal form of :func:`output_rht`."""
+    _require_cuda(y_rht, "y_rht")
+    bl = _blocks(blocks, m_pad)
+    lib = _lib.load()
+    if len(bl) > _lib.MAX_BLOCKS:
+        raise RuntimeError(f"glq_b200: at most {_lib.MAX_BLOCKS} Hadamard blocks per transform")
+    _lib.check(lib.glqb_output_rht(y_rht.data_ptr(), su.data_ptr(), out.data_ptr(), _dt(out.dtype), out.stride(0),
+                                   int(out_features), int(m_pad), (C.c_int32 * len(bl))(*bl), len(bl),
+                                   y_rht.shape[0], _stream(out)), "output_rht")
+
+
 # ------------------------------------------------------------------------------------------------
 # decode dumps and probes (glq/csrc/glq_bindings.cpp:345-352)
 # ------------------------------------------------------------------------------------------------
@@ -365,9 +466,11 @@ class MoePlan:
                                               y.data_ptr(), x.shape[0], self.workspace.data_ptr(),
                                               self.workspace.numel(), _stream(x)), "moe_plan_run")
 
-    def check_status(self, x):
-        """Synchronises the stream of ``x`` and raises if a bounded wait inside the GEMM kernels gave up."""
-        _lib.check(self.lib.glqb_moe_plan_status(self.handle, self.workspace.data_ptr(), _stream(x)), "moe_plan_status")
+    def check_status(self, x=None):
+        """Synchronises the stream of ``x`` (default: the current stream of the plan's device) and raises if a
+        bounded wait inside the GEMM kernels gave up."""
+        _lib.check(self.lib.glqb_moe_plan_status(self.handle, self.workspace.data_ptr(),
+                                                 _stream(x if x is not None else self.workspace)), "moe_plan_status")
 
     def close(self):
         if getattr(self, "handle", None):
@@ -407,6 +510,8 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
     key = ("moe3", w13_trellis_packed.data_ptr(), w2_trellis_packed.data_ptr(), cap, ids.shape[1], x.dtype, ids.dtype,
            int(activation_type), has13, has2)
     plan = _PLAN_CACHE.get(key)
+    if plan is not None:
+        _PLAN_CACHE.move_to_end(key)
     if plan is None:
         d = _lib.MoeDesc()
         d.num_experts, d.top_k, d.hidden, d.inter, d.w13_out = E, ids.shape[1], hidden_size, intermediate_size, w13_out_features
@@ -424,13 +529,7 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
         d.w2_packed, d.w2_packed2 = w2_trellis_packed.data_ptr(), (w2_trellis_packed2.data_ptr() if has2 else None)
         d.w2_su, d.w2_sv, d.w2_wscale = w2_SU.data_ptr(), w2_SV.data_ptr(), ws2.data_ptr()
         d.w2_inv_resid_scale2 = i2.data_ptr() if has2 else None
-        for name, blocks, total in (("n_w13", blocks_n_w13, n_pad_w13), ("m_w13", blocks_m_w13, m_pad_w13),
-                                    ("n_w2", blocks_n_w2, n_pad_w2), ("m_w2", blocks_m_w2, m_pad_w2)):
-            bl = _blocks(blocks, total)
-            setattr(d, "n_blocks_" + name, len(bl))
-            arr = getattr(d, "blocks_" + name)
-            for i, b in enumerate(bl):
-                arr[i] = b
+        _fill_moe_blocks(d, blocks_n_w13, n_pad_w13, blocks_m_w13, m_pad_w13, blocks_n_w2, n_pad_w2, blocks_m_w2, m_pad_w2)
         d.ids_are_int64 = 1 if ids.dtype == torch.int64 else 0
         d.x_dtype = d.y_dtype = _dt(x.dtype)
         plan = MoePlan(d, x.device, [w13_trellis_packed, w13_trellis_packed2, w13_SU, w13_SV, ws13, i13,
@@ -441,7 +540,93 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
     return y
 
 
+def _fill_moe_blocks(d, blocks_n_w13, n_pad_w13, blocks_m_w13, m_pad_w13, blocks_n_w2, n_pad_w2, blocks_m_w2, m_pad_w2):
+    for name, blocks, total in (("n_w13", blocks_n_w13, n_pad_w13), ("m_w13", blocks_m_w13, m_pad_w13),
+                                ("n_w2", blocks_n_w2, n_pad_w2), ("m_w2", blocks_m_w2, m_pad_w2)):
+        bl = _blocks(blocks, total)
+        setattr(d, "n_blocks_" + name, len(bl))
+        arr = getattr(d, "blocks_" + name)
+        for i, b in enumerate(bl):
+            arr[i] = b
+
+
+def fused_moe_grouped_gemm(x, topk_ids, topk_weights,
+                           w13_Qidxs, w13_SU, w13_SV, w13_Wscale, w13_Qidxs2, w13_inv_rs,
+                           w2_Qidxs, w2_SU, w2_SV, w2_Wscale, w2_Qidxs2, w2_inv_rs,
+                           codebook, codebook2,
+                           hidden_size, intermediate_size, w13_out_features,
+                           n_pad_w13, m_pad_w13, n_pad_w2, m_pad_w2,
+                           blocks_n_w13, blocks_m_w13, blocks_n_w13_meta, blocks_m_w13_meta,
+                           blocks_n_w2, blocks_m_w2, blocks_n_w2_meta, blocks_m_w2_meta, activation_type,
+                           w13_Qidxs3=None, w13_inv_rs2=None, w2_Qidxs3=None, w2_inv_rs2=None, codebook3=None):
+    """E8-shell routed experts (glq_vllm/custom_ops.py:203-246): (T, hidden) -> (T, hidden).  Every expert is
+    an E8 layer (m_pad, n_pad/8) of up to three stages with per-expert Wscale and inverse residual scales; a
+    stage is present when its index tensor has the full (E, m_pad, n_pad/8) shape (the reference keeps an
+    (E,1,1) placeholder otherwise).  Any token count; gated (0-2) and plain (3-5) activations."""
+    _require_cuda(x, "x")
+    E = w13_Qidxs.shape[0]
+    T = x.shape[0]
+    if T == 0:
+        return torch.empty_like(x)
+    if m_pad_w13 != w13_out_features or n_pad_w13 != hidden_size or n_pad_w2 != intermediate_size or m_pad_w2 != hidden_size:
+        raise RuntimeError("glq_b200: E8 experts padded to powers of two are not served (block-diagonal layers only)")
+    x = x.contiguous()
+    ids = topk_ids.contiguous()
+    if ids.dtype not in (torch.int32, torch.int64):
+        ids = ids.to(torch.int64)
+    tw = topk_weights.to(torch.float32).contiguous()
+    full13, full2 = w13_Qidxs.numel(), w2_Qidxs.numel()
+    stages13 = [(w13_Qidxs, None, codebook)]
+    stages2 = [(w2_Qidxs, None, codebook)]
+    for q13, i13, q2, i2, cb in ((w13_Qidxs2, w13_inv_rs, w2_Qidxs2, w2_inv_rs, codebook2),
+                                 (w13_Qidxs3, w13_inv_rs2, w2_Qidxs3, w2_inv_rs2, codebook3)):
+        ok = (q13 is not None and q2 is not None and cb is not None and i13 is not None and i2 is not None and
+              q13.numel() == full13 and q2.numel() == full2 and cb.numel() > 0 and i13.numel() == E and i2.numel() == E)
+        if not ok:
+            break
+        stages13.append((q13, i13.to(torch.float32).contiguous(), cb))
+        stages2.append((q2, i2.to(torch.float32).contiguous(), cb))
+    ns = len(stages13)
+    cap = _moe_capacity(T)
+    key = ("moe_e8", tuple(s[0].data_ptr() for s in stages13), tuple(s[0].data_ptr() for s in stages2), cap,
+           ids.shape[1], x.dtype, ids.dtype, int(activation_type))
+    plan = _PLAN_CACHE.get(key)
+    if plan is None:
+        d = _lib.MoeDesc()
+        d.format, d.e8_stages = _lib.FMT_E8_SHELL, ns
+        d.num_experts, d.top_k, d.hidden, d.inter, d.w13_out = E, ids.shape[1], hidden_size, intermediate_size, w13_out_features
+        d.max_tokens, d.activation = cap, int(activation_type)
+        ws13 = w13_Wscale.to(torch.float32).contiguous()
+        ws2 = w2_Wscale.to(torch.float32).contiguous()
+        tables = [e8_packed_table(s[2]) for s in stages13]
+        for s in range(ns):
+            d.w13_qidxs[s] = stages13[s][0].data_ptr()
+            d.w2_qidxs[s] = stages2[s][0].data_ptr()
+            d.e8_table[s] = tables[s].data_ptr()
+            d.e8_table_entries[s] = tables[s].numel()
+            if s:
+                d.w13_inv_rs[s - 1] = stages13[s][1].data_ptr()
+                d.w2_inv_rs[s - 1] = stages2[s][1].data_ptr()
+        d.w13_su, d.w13_sv, d.w13_wscale = w13_SU.data_ptr(), w13_SV.data_ptr(), ws13.data_ptr()
+        d.w2_su, d.w2_sv, d.w2_wscale = w2_SU.data_ptr(), w2_SV.data_ptr(), ws2.data_ptr()
+        _fill_moe_blocks(d, blocks_n_w13, n_pad_w13, blocks_m_w13, m_pad_w13, blocks_n_w2, n_pad_w2, blocks_m_w2, m_pad_w2)
+        d.ids_are_int64 = 1 if ids.dtype == torch.int64 else 0
+        d.x_dtype = d.y_dtype = _dt(x.dtype)
+        plan = MoePlan(d, x.device, [stages13, stages2, tables, w13_SU, w13_SV, ws13, w2_SU, w2_SV, ws2])
+        _PLAN_CACHE[key] = plan
+    else:
+        _PLAN_CACHE.move_to_end(key)
+    y = torch.empty(T, hidden_size, dtype=x.dtype, device=x.device)
+    plan.run(x, ids, tw, y)
+    return y
+
+
+# the reference's per-(token, expert) op has the same signature and result (glq_vllm/custom_ops.py:203-224)
+fused_moe_block_diag = fused_moe_grouped_gemm
+
 glq_fused_moe_trellis_3inst_cuda = fused_moe_trellis_3inst
+glq_fused_moe_grouped_gemm_cuda = fused_moe_grouped_gemm
+glq_fused_moe_block_diag_cuda = fused_moe_block_diag
 
 # names under which the reference's extension module exposes the same entry points
 glq_fused_linear_cuda = fused_linear

@@ -104,7 +104,8 @@ class LinearSpec:
 class Plan:
     """Owns a GlqbPlan handle and its workspace tensor."""
 
-    def __init__(self, specs: Sequence[LinearSpec], device: Optional[torch.device] = None):
+    def __init__(self, specs: Sequence[LinearSpec], device: Optional[torch.device] = None,
+                 own_workspace: bool = True):
         self.lib = _lib.load()
         self.specs = list(specs)
         if not self.specs:
@@ -116,16 +117,22 @@ class Plan:
             _lib.check(self.lib.glqb_plan_create(arr, len(self.specs), C.byref(handle)), "plan_create")
         self.handle = handle
         self.workspace_bytes = int(self.lib.glqb_plan_workspace_bytes(handle))
-        self.workspace = torch.empty(max(256, self.workspace_bytes), dtype=torch.uint8, device=self.device)
+        # own_workspace=False: the caller passes a (shared) workspace to every run
+        self.workspace = (torch.empty(max(256, self.workspace_bytes), dtype=torch.uint8, device=self.device)
+                          if own_workspace else None)
         self.code_bytes = int(self.lib.glqb_plan_code_bytes(handle))
         self.flops = int(self.lib.glqb_plan_flops(handle))
         self.launches = int(self.lib.glqb_plan_launches(handle))
 
-    def run(self, x: torch.Tensor, y: torch.Tensor, stream: Optional[torch.cuda.Stream] = None) -> None:
+    def run(self, x: torch.Tensor, y: torch.Tensor, stream: Optional[torch.cuda.Stream] = None,
+            workspace: Optional[torch.Tensor] = None) -> None:
         """Enqueue on ``stream`` (default: the current torch stream); does not synchronise."""
         st = stream if stream is not None else torch.cuda.current_stream(self.device)
-        _lib.check(self.lib.glqb_plan_run(self.handle, x.data_ptr(), y.data_ptr(), self.workspace.data_ptr(),
-                                          self.workspace.numel(), st.cuda_stream), "plan_run")
+        ws = workspace if workspace is not None else self.workspace
+        if ws is None:
+            raise RuntimeError("glq_b200: this plan owns no workspace; pass one to run()")
+        _lib.check(self.lib.glqb_plan_run(self.handle, x.data_ptr(), y.data_ptr(), ws.data_ptr(), ws.numel(),
+                                          st.cuda_stream), "plan_run")
 
     def set_timing(self, on: bool) -> None:
         _lib.check(self.lib.glqb_plan_set_timing(self.handle, 1 if on else 0), "plan_set_timing")

@@ -2,10 +2,13 @@
  * glq_b200 — C ABI of the B200 (sm_100a) compressed-weight matmul library for GLQ checkpoints.
  *
  * Everything here is plain C: device pointers travel as void*, sizes as integers, the CUDA
- * stream as an opaque pointer (a cudaStream_t).  No entry point allocates device memory on the
- * per-call path: callers hand in a workspace (size reported by the plan), so every run call may be
- * captured into a CUDA graph.  Every function returns 0 on success or a negative GLQB_E_* code
- * and never throws; glqb_last_error() gives the message for the calling thread.
+ * stream as an opaque pointer (a cudaStream_t).  The run entry points (glqb_plan_run, glqb_moe_plan_run,
+ * glqb_input_rht, glqb_output_rht, glqb_output_rht_shards, the dump functions) allocate nothing, copy
+ * nothing from host memory and do not synchronise: callers hand in a workspace (size reported by the
+ * plan), so these calls may be captured into a CUDA graph.  Plan creation allocates a small device table;
+ * glqb_fused_linear is a convenience wrapper that creates, runs and destroys a plan and synchronises.
+ * Every function returns 0 on success or a negative GLQB_E_* code and never throws; glqb_last_error()
+ * gives the message for the calling thread.
  *
  * Citations of the form file:line name the interface of the reference project (cnygaard/glq)
  * that the entry point stands in for.
@@ -108,6 +111,7 @@ void glqb_plan_destroy(GlqbPlan* plan);
  * glq_vllm/custom_ops.py:22-36) with the expert-stacked storage of glq_vllm/moe_shapes.py:56-72:
  * w13 = [gate; up] rows per expert, one SV per projection shared by all experts, SU / Wscale /
  * inv_resid_scale2 per expert.  Works for any token count (no 256-token cap, no host synchronisation).
+ * The same plan type serves E8-shell experts (fields at the end of the struct).
  */
 typedef struct GlqbMoeDesc {
   int32_t num_experts, top_k, hidden, inter, w13_out;
@@ -131,6 +135,18 @@ typedef struct GlqbMoeDesc {
   int32_t blocks_n_w2[GLQB_MAX_BLOCKS], blocks_m_w2[GLQB_MAX_BLOCKS];
   int32_t ids_are_int64;                 /* topk_ids dtype: 1 = int64, 0 = int32 */
   int32_t x_dtype, y_dtype;              /* GLQB_DT_* */
+  /* E8 shell experts: glq_fused_moe_grouped_gemm_cuda / glq_fused_moe_block_diag_cuda
+   * (glq/csrc/glq_cuda.cu:4599, 5241; schemas glq_vllm/custom_ops.py:203-246; storage
+   * glq_vllm/fused_moe_method.py:157-213).  With format == GLQB_FMT_E8_SHELL the trellis fields above
+   * (w13_packed.., *_bits) are ignored; SU / SV / Wscale / blocks are shared with them. */
+  int32_t format;                        /* GLQB_FMT_TRELLIS_3INST (0) or GLQB_FMT_E8_SHELL */
+  int32_t e8_stages;                     /* 1..3 */
+  const void* w13_qidxs[3];              /* per stage (E, w13_out, hidden/8) int16 */
+  const void* w2_qidxs[3];               /* per stage (E, hidden, inter/8) int16 */
+  const uint32_t* e8_table[3];           /* nibble-packed table of the stage (glqb_e8_pack_table) */
+  int32_t e8_table_entries[3];
+  const float* w13_inv_rs[2];            /* (E,) fp32 device: cumulative inverse residual scale of stages 2, 3 */
+  const float* w2_inv_rs[2];
 } GlqbMoeDesc;
 
 typedef struct GlqbMoePlan GlqbMoePlan;
@@ -143,12 +159,14 @@ int64_t glqb_moe_plan_code_bytes(const GlqbMoePlan* plan);
 int glqb_moe_plan_run(GlqbMoePlan* plan, const void* x, const void* topk_ids, const float* topk_weights, void* y,
                       int32_t tokens, void* workspace, size_t workspace_bytes, void* stream);
 /* Synchronises `stream` and reports whether a bounded wait inside the GEMM kernels of the last run gave up
- * (GLQB_E_CUDA, results invalid); GLQB_OK otherwise.  No counterpart in the reference. */
+ * (GLQB_E_DEVICE, results invalid); GLQB_OK otherwise.  No counterpart in the reference. */
 int glqb_moe_plan_status(const GlqbMoePlan* plan, const void* workspace, void* stream);
 void glqb_moe_plan_destroy(GlqbMoePlan* plan);
 
-/* Stateless single-layer forms of the reference's fused ops.  `workspace` must hold
- * glqb_linear_workspace_bytes(desc) bytes. */
+/* Stateless single-layer form of the reference's fused ops, for occasional calls: it builds a one-layer
+ * plan, runs it, waits for `stream` and destroys the plan (so it allocates, synchronises and cannot be
+ * captured).  `workspace` must hold glqb_linear_workspace_bytes(desc) bytes, a device-independent upper
+ * bound of what the plan needs. */
 size_t glqb_linear_workspace_bytes(const GlqbLinearDesc* desc);
 int glqb_fused_linear(const GlqbLinearDesc* desc, const void* x, void* y,
                       void* workspace, size_t workspace_bytes, void* stream);
@@ -176,6 +194,14 @@ int glqb_input_rht(const void* x, int32_t x_dtype, int64_t x_stride, const void*
 int glqb_output_rht(const float* y_rht, const void* su, void* out, int32_t out_dtype, int64_t out_stride,
                     int32_t out_features, int32_t m_pad, const int32_t* blocks, int32_t n_blocks,
                     int32_t batch, void* stream);
+
+/* Output transform over the sub-blocks of several fused shards in one launch: glq_output_rht_shards_cuda
+ * (glq/csrc/glq_cuda.cu:2882, schema glq_vllm/custom_ops.py:424-426).  y_rht is fp32 (batch, total_m);
+ * block i covers columns [offsets[i], offsets[i] + blocks[i]) of y_rht, su and out.  At most
+ * GLQB_MAX_BLOCKS blocks per call. */
+int glqb_output_rht_shards(const float* y_rht, const void* su, void* out, int32_t out_dtype, int64_t out_stride,
+                           int32_t out_features, int32_t total_m, const int32_t* offsets, const int32_t* blocks,
+                           int32_t n_blocks, int32_t batch, void* stream);
 
 /* glq_trellis_kernel_supported(m, k) (glq/csrc/glq_bindings.cpp:345). */
 int glqb_trellis_kernel_supported(int32_t m, int32_t n);

@@ -47,6 +47,22 @@ def test_struct_layout_matches_header(tmp_path):
     assert [int(v) for v in out] == [ctypes.sizeof(D), D.su.offset, D.batch.offset, D.x_is_rotated.offset]
 
 
+def test_moe_struct_layout_matches_header(tmp_path):
+    from glq_b200 import _lib
+    src = tmp_path / "szm.c"
+    src.write_text('#include <stdio.h>\n#include "glq_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu\\n",'
+                   'sizeof(GlqbMoeDesc), __builtin_offsetof(GlqbMoeDesc, w2_packed),'
+                   '__builtin_offsetof(GlqbMoeDesc, ids_are_int64), __builtin_offsetof(GlqbMoeDesc, format),'
+                   '__builtin_offsetof(GlqbMoeDesc, w2_inv_rs));}')
+    exe = tmp_path / "szm"
+    import subprocess
+    subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()
+    D = _lib.MoeDesc
+    assert [int(v) for v in out] == [ctypes.sizeof(D), D.w2_packed.offset, D.ids_are_int64.offset, D.format.offset,
+                                     D.w2_inv_rs.offset]
+
+
 def test_host_side_calls_without_gpu(lib):
     assert lib.glqb_trellis_kernel_supported(64, 64) == 1
     assert lib.glqb_trellis_kernel_supported(48, 64) == 0
