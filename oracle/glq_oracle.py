@@ -269,12 +269,19 @@ def _act(name):
         return lambda g: g / (1.0 + np.exp(-g))
     if name == "gelu_tanh":
         return lambda g: 0.5 * g * (1.0 + np.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
-    if name == "relu2":
+    if name in ("relu2", "relu2_no_mul"):
         return lambda g: np.square(np.maximum(g, 0.0))
+    if name == "silu_no_mul":
+        return lambda g: g / (1.0 + np.exp(-g))
+    if name == "gelu_no_mul":                      # F.gelu with the exact (erf) form
+        from math import erf
+        verf = np.vectorize(erf, otypes=[np.float64])
+        return lambda g: (0.5 * g * (1.0 + verf(g.astype(np.float64) * 0.7071067811865476))).astype(np.float32)
     raise ValueError(name)
 
 
-ACT_CODES = {0: "silu", 1: "gelu_tanh", 2: "relu2"}
+# integer codes of the fused ops (glq_vllm/fused_moe_method.py:671-677): 0-2 gated, 3-5 without the gate
+ACT_CODES = {0: "silu", 1: "gelu_tanh", 2: "relu2", 3: "silu_no_mul", 4: "gelu_no_mul", 5: "relu2_no_mul"}
 
 
 def moe_forward(x, topk_ids, topk_w, expert_fn13, expert_fn2, inter, activation="gelu_tanh"):
@@ -288,7 +295,10 @@ def moe_forward(x, topk_ids, topk_w, expert_fn13, expert_fn2, inter, activation=
         if tok.size == 0:
             continue
         h13 = expert_fn13(int(e), x[tok]).astype(np.float32)
-        h = (act(h13[:, :inter]) * h13[:, inter:2 * inter]).astype(np.float32)
+        if activation.endswith("_no_mul"):         # w13 has `inter` rows: no up projection
+            h = act(h13[:, :inter]).astype(np.float32)
+        else:
+            h = (act(h13[:, :inter]) * h13[:, inter:2 * inter]).astype(np.float32)
         y = expert_fn2(int(e), h)
         np.add.at(out, tok, y * np.asarray(topk_w, dtype=np.float32)[tok, slot][:, None])
     return out

@@ -58,12 +58,18 @@ def test_two_calls_in_a_row_match_the_plan_entry_point():
     got = [_noalloc(lib, x, packed, su, sv, ws, m, n, K) for ((packed, su, sv, x), m, n, K, ws) in layers]
     got2 = [_noalloc(lib, x, packed, su, sv, ws, m, n, K) for ((packed, su, sv, x), m, n, K, ws) in layers]
     torch.cuda.synchronize()
+    from oracle import c_oracle as CO
+    from oracle import glq_oracle as O
     for ((packed, su, sv, x), m, n, K, ws), y, y2 in zip(layers, got, got2):
         ref = ops.fused_linear_trellis_3inst(x, sv, su, packed, None, None, None, None, ws, n, m, n, m,
                                              out_dtype=torch.float32)
         err = (y - ref).abs().max().item() / ref.abs().max().item()
         assert err <= TOL, (m, n, K, err)
         assert torch.equal(y, y2)          # same call, same scratch, same bits
+        # and against the CPU oracle directly, not only against the other CUDA entry point
+        W = CO.trellis_decode(packed.cpu().numpy(), m, n, K).astype(np.float32)
+        oracle = O.linear_forward(x.cpu().numpy(), W, su.cpu().numpy(), sv.cpu().numpy(), ws)
+        assert np.abs(y.cpu().numpy() - oracle).max() / np.abs(oracle).max() <= TOL, (m, n, K)
 
 
 def test_sizes_beyond_the_built_in_scratch_are_refused():
