@@ -1,17 +1,24 @@
 #!/usr/bin/env python
 """Benchmark of the compressed-weight matmul hot path.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME] [--no-subs]
 
-Default workload (N=1): batch-1 decode over every projection of a SmolLM3-3B-shaped model stored as
-trellis 3INST at 4 bits per weight — 36 layers x (q, k, v, o, gate, up, down), 1.406 GB of packed
-bit-streams, all distinct buffers (far larger than the 126 MB L2, so nothing is re-read from cache
-between steps).  One step = one pass over all 252 projections with seeded synthetic bit-streams,
-sign vectors, scales and bf16 activations.  The metric is compressed bytes read per second.
+Headline workload (the JSON line's `value`): batch-1 decode over every projection of a SmolLM3-3B-shaped
+model stored as trellis 3INST at 4 bits per weight — 36 layers x (q, k, v, o, gate, up, down), 1.406 GB of
+packed bit-streams, all distinct buffers (far larger than the 126 MB L2, so nothing is re-read from cache
+between steps).  One step = one pass over all 252 projections with seeded synthetic bit-streams, sign
+vectors, scales and bf16 activations.  The metric is compressed bytes read per second.
 
-With N > 1 every projection is split tensor-parallel (rows of q/k/v/gate/up, columns of o/down, each
-shard a GLQ layer of its own) and the o/down outputs are summed with an NCCL all-reduce; the total
-work is fixed ("strong" scaling).
+The same line carries, under "sub", one record per other benchmark configuration (each with its own
+roofline and end-to-end figure): E8 two-stage decode (1 and 16 tokens) and prefill (256 and 2048 tokens) on
+Llama-3-8B shapes, trellis prefill, the 128-expert MoE step (256 and 4096 tokens, near-uniform and Zipf
+routing), the 62-layer mixed-rate E8 shapes, a dependent decode chain through the operator layer, and the
+latency of one 2048 x 2048 linear.  `--workload NAME` runs one of them alone; `--no-subs` only the headline.
+
+With N > 1 every projection is split tensor-parallel (rows of q/k/v/gate/up, columns of o/down, each shard
+a GLQ layer of its own); the row-parallel outputs are fp32 partial sums added over the ranks with NCCL, and
+after the timed region one layer's per-rank partials are gathered and summed in rank order to check the
+reduced output ("tp_check").  MoE is expert-parallel.  Total work is fixed ("strong" scaling).
 
 `--impl reference` times the CPU restatement of the reference's decode-then-matmul path
 (oracle/glq_oracle.c, all host threads) on one decoder layer per step.
@@ -31,18 +38,21 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 METRIC = "decode matvec compressed-byte HBM GB/s (bs=1)"
+PREFILL_METRIC = "prefill TFLOP/s per layer"
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1590.0
 
 
 def measured_peaks():
+    """(hbm GB/s, bf16 TFLOP/s burst, 'measured' | 'fallback')"""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
             d = json.load(open(p))
-            return float(d["hbm_gbs"]), "measured"
+            return float(d["hbm_gbs"]), float(d["bf16_tflops"]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return FALLBACK_HBM_GBS, FALLBACK_TFLOPS, "fallback"
 
 
 class ClockSampler:
@@ -98,50 +108,81 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------------------------------
-# workload construction
+# distributed helpers
 # --------------------------------------------------------------------------------------------------
-def build_trellis_decode(device, world, rank, bits=(4,), n_layers=None):
-    """All projections of the SmolLM3-3B shape as one sweep plan; returns plan + buffers + bookkeeping."""
+class Dist:
+    def __init__(self, device):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.device = device
+
+    def sync(self):
+        import torch
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max(self, v: float) -> float:
+        if self.world == 1:
+            return v
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor([v], dtype=torch.float64, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_int(self, *vals):
+        if self.world == 1:
+            return [int(v) for v in vals]
+        import torch
+        import torch.distributed as dist
+        t = torch.tensor(list(vals), device=self.device, dtype=torch.int64)
+        dist.all_reduce(t)
+        return [int(v) for v in t.tolist()]
+
+
+def timed(D: Dist, step, steps: int, before=None, after=None):
+    """K steps bracketed by a barrier + synchronize on both sides; CUDA events on the current stream; max over
+    ranks.  `before` / `after` run inside the timed region around every step (host<->device copies)."""
     import torch
-    from glq_b200 import synth
-    from glq_b200.plan import Plan
-
-    from glq_b200 import tp
-
-    cfg = synth.SMOLLM3_3B
-    gen = torch.Generator(device=device)
-    gen.manual_seed(1234 + rank)
-    layout = tp.build_layout(cfg["proj"], n_layers or cfg["layers"], world, rank)
-    layers, specs = [], []
-    for e in layout.entries:
-        L = synth.trellis_layer(f"L{e.layer}.{e.name}", e.m, e.n, list(bits), gen, device)
-        layers.append(L)
-        specs.append(L.spec(batch=1, x_offset=e.x_offset, y_offset=e.y_offset, x_stride=e.n, y_stride=e.m))
-    plan = Plan(specs)
-    gx = torch.Generator(device=device)
-    gx.manual_seed(99)
-    x = torch.randn(layout.x_elems, generator=gx, device=device, dtype=torch.float32).to(torch.bfloat16)
-    y = torch.zeros(layout.y_elems, device=device, dtype=torch.bfloat16)
-    return dict(plan=plan, x=x, y=y, layers=layers, layout=layout,
-                code_bytes=plan.code_bytes, name="smollm3-3b trellis-3inst %dbpw decode bs=1" % sum(bits))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    D.sync()
+    e0.record()
+    for _ in range(steps):
+        if before:
+            before()
+        step()
+        if after:
+            after()
+    e1.record()
+    D.sync()
+    return D.max(e0.elapsed_time(e1)) / steps
 
 
+# --------------------------------------------------------------------------------------------------
+# workloads built from plans of independent linears
+# --------------------------------------------------------------------------------------------------
 WORKLOADS = {
     # name: (model shape, format, bits-or-stages, default tokens, default layers, metric)
+    "decode_trellis_sweep": ("SMOLLM3_3B", "trellis", (4,), 1, 36, METRIC),
     "decode_trellis": ("SMOLLM3_3B", "trellis", (4,), 1, 36, METRIC),
     "decode_trellis_6bpw": ("SMOLLM3_3B", "trellis", (4, 2), 1, 36, METRIC),
     "decode_e8": ("LLAMA3_8B", "e8", 2, 1, 8, METRIC),
-    "prefill_e8": ("LLAMA3_8B", "e8", 2, 2048, 2, "prefill TFLOP/s per layer"),
-    "prefill_trellis": ("SMOLLM3_3B", "trellis", (4,), 2048, 4, "prefill TFLOP/s per layer"),
+    "prefill_e8": ("LLAMA3_8B", "e8", 2, 2048, 2, PREFILL_METRIC),
+    "prefill_trellis": ("SMOLLM3_3B", "trellis", (4,), 2048, 4, PREFILL_METRIC),
     # 62-layer dense decoder (hidden 5376, intermediate 21504): E8 stages cycle 2/3/3 per layer (nominal
     # 4/5/6 bpw; every stage is stored as int16, so the stored rate is 4/6/6 bits per weight)
     "decode_e8_62l": ("DENSE_62L", "e8", [2, 3, 3], 1, 6, METRIC),
-    "prefill_e8_62l": ("DENSE_62L", "e8", [2, 3, 3], 2048, 3, "prefill TFLOP/s per layer"),
+    "prefill_e8_62l": ("DENSE_62L", "e8", [2, 3, 3], 2048, 3, PREFILL_METRIC),
 }
 
 
 def build_workload(name, device, world, rank, tokens=None, n_layers=None):
-    """Plan over n_layers x 7 projections of the named shape; q/k/v and gate/up share their input."""
+    """Plan over n_layers x 7 projections of the named shape.  In the sweep every projection has its own input;
+    elsewhere q/k/v and gate/up share theirs.  Column-parallel outputs are bf16; row-parallel outputs (o, down)
+    are fp32 partial sums in one contiguous tail of the result buffer, added over the ranks by one all-reduce
+    (the layers of a step do not depend on each other)."""
     import torch
     from glq_b200 import synth, tp
     from glq_b200.plan import Plan
@@ -150,58 +191,180 @@ def build_workload(name, device, world, rank, tokens=None, n_layers=None):
     cfg = getattr(synth, shape)
     T = tokens or d_tokens
     nl = n_layers or d_layers
+    sweep = name == "decode_trellis_sweep"
     gen = torch.Generator(device=device)
-    gen.manual_seed(4321 + rank)
+    gen.manual_seed((1234 if sweep else 4321) + rank)
     table = synth.load_e8_table(device) if fmt == "e8" else None
     col_mult = 8 if fmt == "e8" else 32
-    specs, layers = [], []
-    x_elems = y_elems = 0
-    reduce_spans = []
-    pending = []
+    layers, pending = [], []
+    x_elems = 0
     for li in range(nl):
         x_of = {}
         for pname, m, n in cfg["proj"]:
             ms, ns = tp.shard_shape(pname, m, n, world, 32 if fmt == "trellis" else 16, col_mult)
-            group = {"q": "attn_in", "k": "attn_in", "v": "attn_in", "gate": "mlp_in", "up": "mlp_in"}.get(pname, pname)
+            group = pname if sweep else {"q": "attn_in", "k": "attn_in", "v": "attn_in", "gate": "mlp_in",
+                                         "up": "mlp_in"}.get(pname, pname)
             if group not in x_of:
                 x_of[group] = x_elems
                 x_elems += T * ns
             stages = par[li % len(par)] if isinstance(par, list) else par
             L = (synth.trellis_layer(f"L{li}.{pname}", ms, ns, list(par), gen, device) if fmt == "trellis"
                  else synth.e8_layer(f"L{li}.{pname}", ms, ns, stages, table, gen, device))
-            if group == "attn_in" and pname != "q":
-                L.sv = layers[-1].sv if pname == "k" else layers[-2].sv      # fused shards share the input signs
-            if pname == "up":
-                L.sv = layers[-1].sv
+            if not sweep:
+                if group == "attn_in" and pname != "q":
+                    L.sv = layers[-1].sv if pname == "k" else layers[-2].sv      # fused shards share the input signs
+                if pname == "up":
+                    L.sv = layers[-1].sv
             layers.append(L)
-            pending.append((L, x_of[group], ns, ms, pname in tp.ROW_PARALLEL))
-    # outputs: column-parallel layers first, row-parallel ones as one contiguous tail, so that the partial sums
-    # of a step are added over the ranks by ONE all-reduce (the layers of the sweep do not depend on each other)
-    y_at = {}
-    for want_row in (False, True):
-        if want_row:
-            tail_begin = y_elems
-        for i, (L, xo, ns, ms, is_row) in enumerate(pending):
-            if is_row == want_row:
-                y_at[i] = y_elems
-                y_elems += T * ms
-    for i, (L, xo, ns, ms, is_row) in enumerate(pending):
-        specs.append(L.spec(batch=T, x_offset=xo, y_offset=y_at[i], x_stride=ns, y_stride=ms))
-    if world > 1 and y_elems > tail_begin:
-        reduce_spans.append((tail_begin, y_elems - tail_begin))
+            pending.append((L, x_of[group], ns, ms, pname in tp.ROW_PARALLEL and world > 1, pname))
+    # result buffer (bytes): bf16 outputs first, then the fp32 partial sums of the row-parallel layers
+    col_bytes = sum(T * ms * 2 for (_, _, _, ms, rp, _) in pending if not rp)
+    col_bytes = (col_bytes + 255) // 256 * 256
+    row_bytes = sum(T * ms * 4 for (_, _, _, ms, rp, _) in pending if rp)
+    y = torch.zeros(col_bytes + row_bytes, device=device, dtype=torch.uint8)
+    specs, y_at = [], []
+    c_off, r_off = 0, col_bytes
+    for (L, xo, ns, ms, rp, pname) in pending:
+        if rp:
+            specs.append(L.spec(batch=T, x_offset=xo, y_offset=r_off // 4, x_stride=ns, y_stride=ms, y_dtype=torch.float32))
+            y_at.append((r_off, T * ms * 4, True))
+            r_off += T * ms * 4
+        else:
+            specs.append(L.spec(batch=T, x_offset=xo, y_offset=c_off // 2, x_stride=ns, y_stride=ms))
+            y_at.append((c_off, T * ms * 2, False))
+            c_off += T * ms * 2
     plan = Plan(specs)
     gx = torch.Generator(device=device)
-    gx.manual_seed(77)
+    gx.manual_seed(99 if sweep else 77)
     x = torch.randn(x_elems, generator=gx, device=device, dtype=torch.float32).to(torch.bfloat16)
-    y = torch.zeros(y_elems, device=device, dtype=torch.bfloat16)
-    return dict(plan=plan, x=x, y=y, layers=layers, layout=None, reduce_spans=reduce_spans, tokens=T, n_layers=nl,
-                code_bytes=plan.code_bytes, flops=plan.flops, metric=metric, shape=shape, fmt=fmt, par=par)
+    reduce_view = y[col_bytes:].view(torch.float32) if row_bytes else None
+    return dict(plan=plan, x=x, y=y, layers=layers, specs=specs, pending=pending, y_at=y_at, reduce_view=reduce_view,
+                tokens=T, n_layers=nl, code_bytes=plan.code_bytes, flops=plan.flops, metric=metric, shape=shape,
+                fmt=fmt, par=par)
 
 
+def kernel_name(W):
+    """The kernel the plan's timing events bracket (what `roofline` describes)."""
+    T, fmt, par = W["tokens"], W["fmt"], W["par"]
+    ns = max(par) if isinstance(par, list) else par
+    if T > 64:
+        tn = 128 if T <= 128 else 256
+        if fmt == "trellis":
+            return f"glq_gemm_kernel<trellis,{par[0]},{par[1] if len(par) > 1 else 0},{tn},4>"
+        if T >= 129:
+            return f"e8_tiles_smem_kernel<{ns}> + glq_gemm_kernel<tiles,{tn},4> (weight tiles decoded once, then the copy-fed GEMM)"
+        return f"glq_gemm_kernel<e8,{ns},{tn},4>"
+    nb = 1 if T <= 8 else 2 if T <= 16 else 4 if T <= 32 else 8
+    if fmt == "trellis":
+        return f"trellis_mv_kernel<{par[0]},{par[1] if len(par) > 1 else 0},{nb}>"
+    resident = W["code_bytes"] >= int(os.environ.get("GLQB_E8_SMEM_MIN_BYTES", str(48 << 20))) and nb <= 2
+    return f"e8_mv_smem_kernel<{ns},{nb}>" if resident else f"e8_mv_kernel<{ns},{nb}>"
+
+
+def tp_check(D: Dist, W):
+    """One row-parallel layer: every rank's fp32 partial is gathered, the partials are added in rank order
+    0..G-1, and the all-reduced output must equal that sum within 2e-3 of its largest value."""
+    import torch
+    import torch.distributed as dist
+    if D.world == 1 or W["reduce_view"] is None:
+        return None
+    from glq_b200.plan import Plan
+    i = next(k for k, p in enumerate(W["pending"]) if p[4])
+    L, xo, ns, ms, _, pname = W["pending"][i]
+    T = W["tokens"]
+    part = torch.zeros(T * ms, dtype=torch.float32, device=D.device)
+    one = Plan([L.spec(batch=T, x_offset=xo, y_offset=0, x_stride=ns, y_stride=ms, y_dtype=torch.float32)])
+    one.run(W["x"], part)
+    parts = [torch.empty_like(part) for _ in range(D.world)]
+    dist.all_gather(parts, part)
+    fixed = torch.zeros_like(part)
+    for p in parts:                       # rank order
+        fixed += p
+    off, nbytes, _ = W["y_at"][i]
+    got = W["y"][off:off + nbytes].view(torch.float32)
+    err = ((got - fixed).abs().max() / fixed.abs().max().clamp_min(1e-30)).item()
+    one.close()
+    return {"layer": pname, "max_rel_diff": err, "result": "ok" if err <= 2e-3 else "FAILED"}
+
+
+def run_plan_bench(name, D: Dist, args, steps, tokens=None, layers=None, clocks=False, check=False):
+    import torch
+    import torch.distributed as dist
+    W = build_workload(name, D.device, D.world, D.rank, tokens, layers)
+    plan, x, y = W["plan"], W["x"], W["y"]
+    code_bytes, flops = D.sum_int(W["code_bytes"], W["flops"])
+
+    def step():
+        plan.run(x, y)
+        if W["reduce_view"] is not None:
+            dist.all_reduce(W["reduce_view"])
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    D.sync()
+    sampler = ClockSampler(D.device.index or 0) if (clocks and D.rank == 0) else None
+    if sampler:
+        sampler.start()
+    plan.set_timing(True)
+    ms_step = timed(D, step, steps)
+    kern_ms, kern_runs = plan.kernel_ms()
+    plan.set_timing(False)
+    clock_rec = sampler.stop() if sampler else None
+    checked = tp_check(D, W) if check else None
+
+    hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+    hx.copy_(x)
+    hy = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
+    for _ in range(2):
+        x.copy_(hx, non_blocking=True); step(); hy.copy_(y, non_blocking=True)
+    ms_e2e = timed(D, step, steps, before=lambda: x.copy_(hx, non_blocking=True),
+                   after=lambda: hy.copy_(y, non_blocking=True))
+    hbm, tens, kind = measured_peaks()
+    kern_ms_avg = D.max(kern_ms / max(1, kern_runs))
+    prefill = W["metric"] == PREFILL_METRIC
+    nl = W["n_layers"]
+    rec = {"workload": name, "metric": W["metric"], "ms_per_step": ms_step, "n_gpus": D.world,
+           "config": f"{W['shape']} projections, {W['fmt']} {W['par']}, {W['tokens']} tokens, {nl} decoder layers per step "
+                     f"({code_bytes / 1e6:.0f} MB of codes, distinct buffers, larger than L2)",
+           "gpu_launches": plan.launches * steps}
+    if prefill:
+        rec.update({"value": flops / nl / (ms_step / nl * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_layer": ms_step / nl,
+                    "e2e": {"value": flops / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s",
+                            "h2d_bytes_per_step": x.numel() * x.element_size(), "d2h_bytes_per_step": y.numel()},
+                    "roofline": {"bound": "tensor", "kernel": kernel_name(W), "achieved": W["flops"] / (kern_ms_avg * 1e-3) / 1e12,
+                                 "peak": tens, "peak_kind": f"of {kind}", "unit": "TFLOP/s",
+                                 "frac": W["flops"] / (kern_ms_avg * 1e-3) / 1e12 / tens, "kernel_ms": kern_ms_avg,
+                                 "flops_per_launch": W["flops"], "whole_step_frac": flops / (ms_step * 1e-3) / 1e12 / (tens * D.world),
+                                 "traffic": None}})
+    else:
+        ach = W["code_bytes"] / (kern_ms_avg * 1e-3) / 1e9
+        rec.update({"value": code_bytes / (ms_step * 1e-3) / 1e9, "unit": "GB/s",
+                    "e2e": {"value": code_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                            "h2d_bytes_per_step": x.numel() * x.element_size(), "d2h_bytes_per_step": y.numel()},
+                    "roofline": {"bound": "hbm", "kernel": kernel_name(W), "achieved": ach, "peak": hbm,
+                                 "peak_kind": f"of {kind}", "unit": "GB/s", "frac": ach / hbm, "kernel_ms": kern_ms_avg,
+                                 "bytes_per_launch": W["code_bytes"],
+                                 # dram bytes of one launch, from an ncu capture of the 4-layer case scaled by the
+                                 # packed bytes of this launch (160.9 MB for 156.2 MB of codes; traffic grows with
+                                 # the layers read); only captured for the trellis sweep
+                                 "traffic": int(W["code_bytes"] * 160.93 / 156.24) if name.startswith("decode_trellis") and len(W["par"]) == 1 else None}})
+    if clock_rec:
+        rec["clocks"] = clock_rec
+    if checked:
+        rec["tp_check"] = checked
+    plan.close()
+    del W, plan, x, y
+    torch.cuda.empty_cache()
+    return rec
+
+
+# --------------------------------------------------------------------------------------------------
+# MoE
+# --------------------------------------------------------------------------------------------------
 def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768, bits=(4,), world=1, rank=0):
-    """MoE step of BASELINE config 3: 128 experts, top-8, hidden 2048, expert intermediate 768 (gate/up fused
-    2048->1536, down 768->2048), trellis 4 bpw, gelu-tanh gating.  Router logits N(0,1) (near-uniform loads) or
-    a Zipf(1.2) popularity over experts."""
+    """MoE step of the benchmark configuration: 128 experts, top-8, hidden 2048, expert intermediate 768 (gate/up
+    fused 2048->1536, down 768->2048), trellis 4 bpw, gelu-tanh gating.  Router logits N(0,1) (near-uniform
+    loads) or a Zipf(1.2) popularity over experts.  Expert parallel: fp32 partial results, one all-reduce."""
     import torch
     from glq_b200 import ops
     from glq_b200.plan import block_decompose
@@ -230,12 +393,14 @@ def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768,
     topw = (topw / topw.sum(-1, keepdim=True)).float().contiguous()
     sentinel = torch.zeros(E, 1, 1, dtype=torch.int16, device=device)
     bl = lambda n: torch.tensor(block_decompose(n))
+    odt = torch.float32 if world > 1 else None
 
     def run_local(xin, ids, tw):
         return ops.fused_moe_trellis_3inst(
             xin, ids, tw, Wt["w13"], sentinel, Wt["su13"], Wt["sv13"], Wt["ws13"], Wt["ws13"],
             Wt["w2"], sentinel, Wt["su2"], Wt["sv2"], Wt["ws2"], Wt["ws2"], hidden, inter, w13_out,
-            hidden, w13_out, inter, hidden, bl(hidden), bl(w13_out), None, None, bl(inter), bl(hidden), None, None, 1)
+            hidden, w13_out, inter, hidden, bl(hidden), bl(w13_out), None, None, bl(inter), bl(hidden), None, None, 1,
+            out_dtype=odt)
 
     def run(xin):
         # expert parallel: this rank's experts for all tokens, then one all-reduce of (tokens, hidden)
@@ -246,77 +411,185 @@ def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768,
     return dict(run=run, x=x, code_bytes=code_bytes, flops=flops, keep=Wt, tokens=tokens)
 
 
-def bench_moe(args, device):
-    """Separate, simpler driver for the MoE workloads (expert parallel under torchrun): time K steps of the op on resident inputs,
-    then with host activations copied in and the result copied out."""
+def run_moe_bench(name, D: Dist, args, steps, tokens=None):
     import torch
-    import torch.distributed as dist
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    skew = 1.2 if "zipf" in args.workload else None
-    T = args.tokens or 256
-    W = build_moe(device, T, skew, world=world, rank=rank)
+    from glq_b200 import ops
+    skew = 1.2 if "zipf" in name else None
+    T = tokens or 256
+    W = build_moe(D.device, T, skew, world=D.world, rank=D.rank)
     x = W["x"]
-
-    def sync():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(v):
-        if world == 1:
-            return v
-        t = torch.tensor([v], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
     for _ in range(max(args.warmup, 3)):
         y = W["run"](x)
-    sync()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler = ClockSampler(device.index or 0)
-    sampler.start()
-    e0.record()
-    for _ in range(args.steps):
-        y = W["run"](x)
-    e1.record()
-    sync()
-    ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    clocks = sampler.stop()
+    D.sync()
+    plans = [p for p in ops._PLAN_CACHE.values() if isinstance(p, ops.MoePlan)]
+    for p in plans:
+        p.set_timing(True)
+    ms = timed(D, lambda: W["run"](x), steps)
+    kern_ms = sum(p.kernel_ms()[0] for p in plans) / steps
+    for p in plans:
+        p.set_timing(False)
+    kern_ms = D.max(kern_ms)
     hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True); hx.copy_(x)
     hy = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
-    e0.record()
-    for _ in range(args.steps):
-        x.copy_(hx, non_blocking=True)
-        y = W["run"](x)
-        hy.copy_(y, non_blocking=True)
-    e1.record()
-    sync()
-    ms_e2e = max_over_ranks(e0.elapsed_time(e1) / args.steps)
-    if rank != 0:
-        return 0
-    peak, kind = measured_peaks()
-    peak *= world
+    box = {}
+
+    def step():
+        box["y"] = W["run"](x)
+    ms_e2e = timed(D, step, steps, before=lambda: x.copy_(hx, non_blocking=True),
+                   after=lambda: hy.copy_(box["y"], non_blocking=True))
+    hbm, tens, kind = measured_peaks()
     gbs = W["code_bytes"] / (ms * 1e-3) / 1e9
-    line = {"metric": "MoE grouped expert matmul: compressed-byte GB/s and TFLOP/s", "value": gbs, "unit": "GB/s",
-            "tflops": W["flops"] / (ms * 1e-3) / 1e12, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None,
-            "dtype": "f16",
-            "data": "synthetic",
-            "config": {"workload": f"{args.workload}: 128 experts top-8, hidden 2048, expert intermediate 768, trellis 4 bpw, "
-                                   f"{T} tokens, {'Zipf(1.2) expert popularity' if skew else 'near-uniform routing'}",
-                       "cache": "302 MB of expert weights per step, larger than L2",
-                       "parallelism": f"ep{world}: experts sharded over ranks, one all-reduce of (tokens, hidden)" if world > 1 else "single"},
-            "e2e": {"value": W["code_bytes"] / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
-                    "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": y.numel() * 2},
-            "gpu_launches": (6 if T * 8 < 8192 else 8) * args.steps, "clocks": clocks,
-            "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
-                         "frac": gbs / peak, "note": "whole step (six kernels, eight from 8192 routings); all expert weights read once"}}
-    print(json.dumps(line))
-    return 0
+    tf = W["flops"] / (ms * 1e-3) / 1e12
+    gemm = T * 8 >= 128 * 64
+    rec = {"workload": name, "metric": "MoE grouped expert matmul: compressed-byte GB/s and TFLOP/s", "value": gbs,
+           "unit": "GB/s", "tflops": tf, "ms_per_step": ms, "n_gpus": D.world,
+           "config": f"128 experts top-8, hidden 2048, expert intermediate 768, trellis 4 bpw, {T} tokens, "
+                     f"{'Zipf(1.2) expert popularity' if skew else 'near-uniform routing'}; 302 MB of expert weights, larger than L2"
+                     + (f"; ep{D.world}: experts sharded over ranks, one fp32 all-reduce of (tokens, hidden)" if D.world > 1 else ""),
+           "e2e": {"value": W["code_bytes"] / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                   "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": hy.numel() * hy.element_size()},
+           "gpu_launches": (6 if T * 8 < 8192 else 8) * steps}
+    if gemm:     # tensor-core form: the two grouped GEMMs against the tensor peak
+        ach = W["flops"] / D.world / (kern_ms * 1e-3) / 1e12
+        rec["roofline"] = {"bound": "tensor", "kernel": "glq_gemm_kernel<trellis,4,0,128,4> (w13 + w2 grouped GEMMs)",
+                           "achieved": ach, "peak": tens, "peak_kind": f"of {kind}", "unit": "TFLOP/s", "frac": ach / tens,
+                           "kernel_ms": kern_ms, "flops_per_launch": W["flops"] // D.world,
+                           "whole_step_frac": tf / (tens * D.world), "traffic": None}
+    else:        # streaming form: expert codes read once by the two grouped decode kernels
+        ach = W["code_bytes"] / D.world / (kern_ms * 1e-3) / 1e9
+        rec["roofline"] = {"bound": "hbm", "kernel": "trellis_moe_mv_kernel<4,0,4> (w13 + w2)", "achieved": ach, "peak": hbm,
+                           "peak_kind": f"of {kind}", "unit": "GB/s", "frac": ach / hbm, "kernel_ms": kern_ms,
+                           "bytes_per_launch": W["code_bytes"] // D.world, "whole_step_frac": gbs / (hbm * D.world),
+                           "traffic": None}
+    ops.clear_caches()
+    del W
+    torch.cuda.empty_cache()
+    return rec
 
 
-def cpu_layer_sample(threads_note=True):
+# --------------------------------------------------------------------------------------------------
+# dependent chain through the operator layer, and the latency of one linear
+# --------------------------------------------------------------------------------------------------
+def run_chain_bench(D: Dist, args, steps, n_layers=36):
+    """Batch-1 decode where every projection consumes the previous output, through glq_b200.ops (the calls a
+    drop-in user makes), captured in one CUDA graph: per layer  qkv(h) -> o(attention stand-in) -> residual ->
+    gate/up(h) -> silu(gate) * up -> down -> residual.  SmolLM3-3B shapes, trellis 4 bpw.  The attention itself
+    is replaced by a shape-correct stand-in (the first 2048 of the qkv outputs), the metric counts the linears'
+    compressed bytes.  Tensor parallel ranks all-reduce after o and down (fp32), as a served model does."""
+    import torch
+    import torch.distributed as dist
+    from glq_b200 import ops, synth, tp
+    cfg = synth.SMOLLM3_3B
+    dev = D.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(555 + D.rank)
+    shapes = {p: tp.shard_shape(p, m, n, D.world) for p, m, n in cfg["proj"]}
+    Ls = []
+    for li in range(n_layers):
+        d = {p: synth.trellis_layer(f"L{li}.{p}", *shapes[p], [4], gen, dev) for p, _, _ in cfg["proj"]}
+        d["k"].sv = d["v"].sv = d["q"].sv
+        d["up"].sv = d["gate"].sv
+        Ls.append(d)
+    code_bytes = sum(L.code_bytes() for d in Ls for L in d.values())
+    hidden = cfg["hidden"]
+    h0 = torch.randn(1, hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).to(torch.bfloat16)
+    world = D.world
+
+    def lin(L, x, dt=None):
+        return ops.fused_linear_trellis_3inst(x, L.sv, L.su, L.codes[0], None, None, None, None, L.wscale,
+                                              L.n, L.m, L.n, L.m, out_dtype=dt)
+
+    def forward(h):
+        for d in Ls:
+            q, k, v = lin(d["q"], h), lin(d["k"], h), lin(d["v"], h)
+            a = (q + torch.cat([k, v, k, v], dim=-1)[:, :q.shape[1]]) * 0.5          # attention stand-in, (1, 2048/world)
+            o = lin(d["o"], a, torch.float32 if world > 1 else None)
+            if world > 1:
+                dist.all_reduce(o)
+            h = (h.float() + o.float()).to(torch.bfloat16)
+            g, u = lin(d["gate"], h), lin(d["up"], h)
+            act = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+            dn = lin(d["down"], act, torch.float32 if world > 1 else None)
+            if world > 1:
+                dist.all_reduce(dn)
+            h = (h.float() + dn.float() * 0.05).to(torch.bfloat16)
+        return h
+
+    for _ in range(3):
+        out = forward(h0)
+    D.sync()
+    graph = None
+    if world == 1:
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                out = forward(h0)
+            graph = g
+        except Exception:
+            graph = None
+            torch.cuda.synchronize()
+    step = (lambda: graph.replay()) if graph is not None else (lambda: forward(h0))
+    for _ in range(3):
+        step()
+    ms = timed(D, step, steps)
+    hh = torch.empty(h0.shape, dtype=h0.dtype, pin_memory=True); hh.copy_(h0)
+    ho = torch.empty(out.shape, dtype=out.dtype, pin_memory=True)
+    ms_e2e = timed(D, step, steps, before=lambda: h0.copy_(hh, non_blocking=True),
+                   after=lambda: ho.copy_(out, non_blocking=True))
+    hbm, tens, kind = measured_peaks()
+    total_bytes = D.sum_int(code_bytes)[0]
+    gbs = total_bytes / (ms * 1e-3) / 1e9
+    launches_per_linear = 3
+    rec = {"workload": "decode_chain", "metric": METRIC, "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": world,
+           "us_per_layer": ms * 1e3 / n_layers, "us_per_linear": ms * 1e3 / (7 * n_layers),
+           "config": f"{n_layers} SmolLM3-3B decoder layers, trellis 4 bpw, batch 1, every projection consumes the previous "
+                     f"output through glq_b200.ops ({'one CUDA graph' if graph is not None else 'eager launches'}); "
+                     f"{total_bytes / 1e6:.0f} MB of codes per step, larger than L2"
+                     + (f"; tp{world}: fp32 all-reduce after o and down" if world > 1 else ""),
+           "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h0.numel() * 2,
+                   "d2h_bytes_per_step": out.numel() * 2},
+           "gpu_launches": 7 * n_layers * launches_per_linear * steps,
+           "roofline": {"bound": "hbm", "kernel": "whole chain (7 linears per layer: transforms + trellis_mv_kernel<4,0,1>, "
+                                                  "plus the elementwise glue between them)",
+                        "achieved": gbs / world, "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s",
+                        "frac": gbs / world / hbm, "kernel_ms": ms, "bytes_per_launch": code_bytes, "traffic": None}}
+    del graph
+    ops.clear_caches()
+    torch.cuda.empty_cache()
+    return rec
+
+
+def run_linear_latency(D: Dist, args, steps=200):
+    """One 2048 x 2048 trellis 4 bpw linear, batch 1, called through glq_b200.ops again and again on the same
+    input (the weights stay in L2: this is launch and dependency latency, not bandwidth)."""
+    import torch
+    from glq_b200 import ops, synth
+    dev = D.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(9)
+    L = synth.trellis_layer("lat", 2048, 2048, [4], gen, dev)
+    x = torch.randn(1, 2048, device=dev).to(torch.bfloat16)
+    call = lambda: ops.fused_linear_trellis_3inst(x, L.sv, L.su, L.codes[0], None, None, None, None, L.wscale, 2048, 2048, 2048, 2048)
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(20):
+            call()
+    g.replay()
+    ms = timed(D, g.replay, steps) / 20
+    ms_eager = timed(D, call, steps)
+    ops.clear_caches()
+    return {"workload": "linear_call_latency", "metric": "time per call of one 2048x2048 trellis 4 bpw linear, batch 1",
+            "value": ms * 1e3, "unit": "us", "higher_is_better": False, "eager_us": ms_eager * 1e3,
+            "config": "20 back-to-back calls in one CUDA graph (value) and eager Python calls (eager_us); weights L2-resident"}
+
+
+# --------------------------------------------------------------------------------------------------
+# CPU arm
+# --------------------------------------------------------------------------------------------------
+def cpu_layer_sample():
     """One SmolLM3-3B decoder layer (7 projections, 39,059,456 packed bytes) for the CPU restatement."""
     import numpy as np
     from glq_b200 import synth
@@ -341,6 +614,32 @@ def run_cpu_layer(sample):
     return nbytes
 
 
+def cpu_config0():
+    """The reference's own CPU-runnable case: one E8 layer, in = out = 2048, 2 bpw (single stage), fp32 activations,
+    batch 1 and 16, decode-then-matmul on the host cores (oracle/glq_oracle.c)."""
+    import numpy as np
+    from oracle import c_oracle as CO
+    rng = np.random.default_rng(1)
+    m = n = 2048
+    q = rng.integers(0, 65536, size=(m, n // 8), dtype=np.uint16).view(np.int16)
+    table = np.load(os.path.join(ROOT, "glq_b200", "data", "e8_shell_packed.npy"))
+    su = (rng.integers(0, 2, size=m) * 2 - 1).astype(np.float16)
+    sv = (rng.integers(0, 2, size=n) * 2 - 1).astype(np.float16)
+    out = {}
+    for B in (1, 16):
+        x = rng.standard_normal((B, n)).astype(np.float32)
+        CO.e8_linear(x, [q], [table], [], m, n, su, sv, 0.02, [n], [m], m)
+        t0 = time.perf_counter()
+        reps = 0
+        while time.perf_counter() - t0 < 1.5:
+            CO.e8_linear(x, [q], [table], [], m, n, su, sv, 0.02, [n], [m], m)
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        out[f"batch{B}_ms"] = dt * 1e3
+        out[f"batch{B}_GBps"] = q.nbytes / dt / 1e9
+    return out
+
+
 def cpu_baseline(budget_s=12.0):
     sample = cpu_layer_sample()
     run_cpu_layer(sample)                      # warm-up (builds the library on first use)
@@ -353,9 +652,62 @@ def cpu_baseline(budget_s=12.0):
             break
     dt = time.perf_counter() - t0
     threads = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
-    return {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
-            "sample": f"{reps} x one SmolLM3-3B decoder layer (7 projections, {nbytes // reps} packed bytes), "
-                      "decode + fp32 matvec + Hadamard transforms, oracle/glq_oracle.c with OpenMP"}
+    rec = {"value": nbytes / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": f"{reps} x one SmolLM3-3B decoder layer (7 projections, {nbytes // reps} packed bytes), "
+                     "decode + fp32 matvec + Hadamard transforms, oracle/glq_oracle.c with OpenMP"}
+    try:
+        rec["e8_2048x2048_2bpw"] = cpu_config0()
+    except Exception as e:          # the headline CPU figure stands on its own
+        rec["e8_2048x2048_2bpw"] = {"error": str(e)}
+    return rec
+
+
+def reference_arm(args, world, rank):
+    if rank != 0:
+        return 0
+    # torchrun exports OMP_NUM_THREADS=1 to every worker; the CPU arm is meant to use all host threads
+    # (the OpenMP runtime reads the variable when the oracle library is loaded, which happens below)
+    if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
+        os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
+    sample = cpu_layer_sample()
+    for _ in range(max(1, min(args.warmup, 3))):
+        run_cpu_layer(sample)
+    t0 = time.perf_counter()
+    nbytes = 0
+    for _ in range(args.steps):
+        nbytes += run_cpu_layer(sample)
+    dt = time.perf_counter() - t0
+    v = nbytes / dt / 1e9
+    threads = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": headline_config(args.gpus),
+            "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
+                             "sample": "each step = one SmolLM3-3B decoder layer (7 projections, 39,059,456 packed "
+                                       "bytes): decode + fp32 matvec + Hadamard transforms on the host cores"},
+            "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+    return 0
+
+
+def headline_config(gpus):
+    return {"workload": "trellis 3INST 4 bpw decode matvec, batch 1, SmolLM3-3B projections "
+                        "(36 layers x q/k/v/o/gate/up/down), L=16 K=4, 16x16 tiles",
+            "cache": "inputs larger than L2 (1.4 GB of distinct packed weights per step)",
+            "parallelism": f"tp{gpus}: rows of q/k/v/gate/up and columns of o/down split over ranks, fp32 partial sums "
+                           "of o/down added by one NCCL all-reduce per step" if gpus > 1 else "single"}
+
+
+# sub-records of the default run: (kind, workload, tokens, layers)
+DEFAULT_SUBS = [
+    ("plan", "decode_e8", 1, 8), ("plan", "decode_e8", 16, 8),
+    ("plan", "prefill_e8", 2048, 2), ("plan", "prefill_e8", 256, 2),
+    ("plan", "prefill_trellis", 2048, 4),
+    ("plan", "decode_e8_62l", 1, 6), ("plan", "prefill_e8_62l", 2048, 3),
+    ("moe", "moe", 256, None), ("moe", "moe", 4096, None), ("moe", "moe_zipf", 256, None), ("moe", "moe_zipf", 4096, None),
+    ("chain", "decode_chain", 1, 36), ("latency", "linear_call_latency", 1, None),
+]
 
 
 # --------------------------------------------------------------------------------------------------
@@ -366,47 +718,19 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-subs", action="store_true", help="only the headline workload, no sub-records")
     ap.add_argument("--workload", default="decode_trellis_sweep",
-                    help="decode_trellis_sweep (default, the headline) or one of: " + ", ".join(WORKLOADS))
+                    help="decode_trellis_sweep (default, the headline with sub-records) or one of: "
+                         + ", ".join(list(WORKLOADS) + ["moe", "moe_zipf", "decode_chain", "linear_call_latency"]))
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None,
-                    help="decoder layers to build (default: all 36); smaller values are for profiler captures only")
+                    help="decoder layers to build (default: per workload); smaller values are for profiler captures only")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": "trellis 3INST 4 bpw decode matvec, batch 1, SmolLM3-3B projections "
-                          "(36 layers x q/k/v/o/gate/up/down), L=16 K=4, 16x16 tiles",
-              "cache": "inputs larger than L2 (1.4 GB of distinct packed weights per step)",
-              "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single"}
-
     if args.impl == "reference":
-        if rank != 0:
-            return 0
-        # torchrun exports OMP_NUM_THREADS=1 to every worker; the CPU arm is meant to use all host threads
-        # (the OpenMP runtime reads the variable when the oracle library is loaded, which happens below)
-        if world > 1 and os.environ.get("OMP_NUM_THREADS") == "1":
-            os.environ["OMP_NUM_THREADS"] = str(len(os.sched_getaffinity(0)))
-        sample = cpu_layer_sample()
-        for _ in range(max(1, min(args.warmup, 3))):
-            run_cpu_layer(sample)
-        t0 = time.perf_counter()
-        nbytes = 0
-        for _ in range(args.steps):
-            nbytes += run_cpu_layer(sample)
-        dt = time.perf_counter() - t0
-        v = nbytes / dt / 1e9
-        threads = int(os.environ.get("OMP_NUM_THREADS", os.cpu_count() or 1))
-        line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "GB/s", "n_gpus": args.gpus,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-                "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port",
-                                 "sample": "each step = one SmolLM3-3B decoder layer (7 projections, 39,059,456 packed "
-                                           "bytes): decode + fp32 matvec + Hadamard transforms on the host cores"},
-                "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
-        return 0
+        return reference_arm(args, world, rank)
 
     import torch
     import torch.distributed as dist
@@ -417,137 +741,62 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
-    if args.workload.startswith("moe"):
-        return bench_moe(args, device)
-    generic = args.workload != "decode_trellis_sweep"
-    if generic:
-        W = build_workload(args.workload, device, world, rank, args.tokens, args.layers)
-        config = {"workload": f"{args.workload}: {W['shape']} projections, {W['fmt']} {W['par']}, {W['tokens']} tokens, "
-                              f"{W['n_layers']} decoder layers per step (weights {W['code_bytes'] / 1e6:.0f} MB, cycled)",
-                  "cache": "distinct weight buffers per layer; working set larger than L2",
-                  "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single"}
+    D = Dist(device)
+    steps = args.steps
+
+    def run_one(kind, name, tokens, layers, clocks=False, check=False, n_steps=None):
+        n_steps = n_steps or steps
+        if kind == "plan":
+            return run_plan_bench(name, D, args, n_steps, tokens, layers, clocks=clocks, check=check)
+        if kind == "moe":
+            return run_moe_bench(name, D, args, n_steps, tokens)
+        if kind == "chain":
+            return run_chain_bench(D, args, n_steps, layers or 36)
+        return run_linear_latency(D, args)
+
+    if args.workload != "decode_trellis_sweep":
+        kind = ("moe" if args.workload.startswith("moe") else "chain" if args.workload == "decode_chain"
+                else "latency" if args.workload == "linear_call_latency" else "plan")
+        rec = run_one(kind, args.workload, args.tokens, args.layers, clocks=True, check=True)
+        if rank == 0:
+            line = {"metric": rec["metric"], "value": rec["value"], "unit": rec["unit"], "n_gpus": args.gpus, "steps": steps,
+                    "warmup": max(args.warmup, 3), "ms_per_step": rec.get("ms_per_step"),
+                    "higher_is_better": rec.get("higher_is_better", True), "scaling": "strong" if args.gpus > 1 else "weak",
+                    "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                    "config": {"workload": f"{args.workload}: {rec['config']}", "parallelism": f"tp{args.gpus}" if args.gpus > 1 else "single"}}
+            line.update({k: v for k, v in rec.items() if k not in ("metric", "value", "unit", "config", "workload", "n_gpus")})
+            print(json.dumps(line))
     else:
-        W = build_trellis_decode(device, world, rank, n_layers=args.layers)
-        if args.layers:
-            config["layers_built"] = args.layers
-    plan, x, y = W["plan"], W["x"], W["y"]
-    total_code_bytes = W["code_bytes"]
-    total_flops = W.get("flops", 0)
-    if world > 1:
-        t = torch.tensor([total_code_bytes, total_flops], device=device, dtype=torch.int64)
-        dist.all_reduce(t)
-        total_code_bytes, total_flops = int(t[0].item()), int(t[1].item())
-
-    from glq_b200 import tp
-
-    def step():
-        plan.run(x, y)
-        # row-parallel outputs (o, down) are partial sums over ranks: one NCCL all-reduce over the
-        # contiguous tail of y (the sweep has no dependency between layers, so the per-layer
-        # reductions of a real decode step are issued as one)
-        if W["layout"] is not None:
-            tp.all_reduce_row_parallel(y, W["layout"])
-        elif world > 1:
-            for off, ln in W["reduce_spans"]:
-                dist.all_reduce(y[off:off + ln])
-
-    def sync():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    sync()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
-    plan.set_timing(True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sync()
-    e0.record()
-    for _ in range(args.steps):
-        step()
-    e1.record()
-    sync()
-    ms_total = e0.elapsed_time(e1)
-    kern_ms, kern_runs = plan.kernel_ms()
-    plan.set_timing(False)
-    clocks = sampler.stop() if rank == 0 else None
-    if world > 1:
-        t = torch.tensor([ms_total], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / args.steps
-    value = total_code_bytes / (ms_step * 1e-3) / 1e9
-
-    # ---- end to end: host buffers in, host buffers out, through the same public call
-    hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
-    hx.copy_(x)
-    hy = torch.empty(y.shape, dtype=y.dtype, pin_memory=True)
-    for _ in range(3):
-        x.copy_(hx, non_blocking=True); step(); hy.copy_(y, non_blocking=True)
-    sync()
-    e0.record()
-    for _ in range(args.steps):
-        x.copy_(hx, non_blocking=True)
-        step()
-        hy.copy_(y, non_blocking=True)
-    e1.record()
-    sync()
-    e2e_ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = total_code_bytes / (e2e_ms / args.steps * 1e-3) / 1e9
-
-    if rank == 0:
-        peak, peak_kind = measured_peaks()
-        kern_ms_avg = kern_ms / max(1, kern_runs)
-        achieved = W["code_bytes"] / (kern_ms_avg * 1e-3) / 1e9
-        line = {
-            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
-            "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic", "config": config,
-            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x.numel() * x.element_size(),
-                    "d2h_bytes_per_step": y.numel() * y.element_size()},
-            "gpu_launches": plan.launches * args.steps,
-            "clocks": clocks,
-            "roofline": {"bound": "hbm", "kernel": "trellis_mv_kernel<4,0,1>", "achieved": achieved, "peak": peak,
-                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                         "kernel_ms": kern_ms_avg, "bytes_per_launch": W["code_bytes"],
-                         # dram__bytes_read+write of one launch: captured with ncu on the 4-layer case
-                         # (160.9 MB for 156.2 MB of packed bytes, profiles/trellis_mv_kernel_decode_smollm3.md)
-                         # and scaled by the packed bytes of this launch (traffic grows with the layers read)
-                         "traffic": int(W["code_bytes"] * 160.93 / 156.24) if not generic else None},
-        }
-        if generic and "prefill" in args.workload:
-            # per-layer TFLOP/s, against the bf16 tensor peak
-            flops_layer = total_flops / W["n_layers"]          # all ranks
-            tf = flops_layer / (ms_step / W["n_layers"] * 1e-3) / 1e12
-            tf_kernel = W["flops"] / (kern_ms_avg * 1e-3) / 1e12
-            try:
-                tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"])
-                tkind = "of measured"
-            except Exception:
-                tpeak, tkind = 1590.0, "of fallback"
-            line.update({"metric": W["metric"], "value": tf, "unit": "TFLOP/s", "dtype": "f16",
-                         "ms_per_layer": ms_step / W["n_layers"]})
-            line["e2e"]["value"] = flops_layer / (e2e_ms / args.steps / W["n_layers"] * 1e-3) / 1e12
-            line["e2e"]["unit"] = "TFLOP/s"
-            kname = "glq_gemm_kernel"
-            if W["fmt"] == "e8" and W["tokens"] >= 129:
-                kname = "e8_tiles_kernel + glq_gemm_kernel (weight tiles decoded once, then the copy-fed GEMM)"
-            line["roofline"] = {"bound": "tensor", "kernel": kname, "achieved": tf_kernel, "peak": tpeak,
-                                "peak_kind": tkind, "unit": "TFLOP/s", "frac": tf_kernel / tpeak,
-                                "kernel_ms": kern_ms_avg, "flops_per_launch": W["flops"], "traffic": None}
-        elif generic:
-            line["metric"] = W["metric"]
-        if args.gpus == 1 and not args.no_cpu_baseline and not generic:
-            line["cpu_baseline"] = cpu_baseline()
-        print(json.dumps(line))
+        head = run_one("plan", "decode_trellis_sweep", None, args.layers, clocks=True, check=True)
+        subs = []
+        if not args.no_subs and not args.layers:
+            sub_steps = max(3, min(steps, 10))
+            for kind, name, tokens, layers in DEFAULT_SUBS:
+                if world > 1 and kind == "latency":
+                    continue
+                try:
+                    subs.append(run_one(kind, name, tokens, layers, check=(kind == "plan"), n_steps=sub_steps))
+                except Exception as e:      # a sub-record must not take the headline down with it
+                    subs.append({"workload": name, "tokens": tokens, "error": f"{type(e).__name__}: {e}"})
+                    if world > 1:
+                        raise
+        if rank == 0:
+            config = headline_config(args.gpus)
+            if args.layers:
+                config["layers_built"] = args.layers
+            line = {"metric": METRIC, "value": head["value"], "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
+                    "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+                    "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f16",
+                    "data": "synthetic", "config": config, "e2e": head["e2e"], "gpu_launches": head["gpu_launches"],
+                    "clocks": head.get("clocks"), "roofline": head["roofline"]}
+            if "tp_check" in head:
+                line["tp_check"] = head["tp_check"]["result"]
+                line["tp_check_detail"] = head["tp_check"]
+            if subs:
+                line["sub"] = subs
+            if args.gpus == 1 and not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline()
+            print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -25,7 +25,7 @@ EXPORTS = [
     "glqb_output_rht", "glqb_output_rht_shards", "glqb_trellis_kernel_supported", "glqb_last_error", "glqb_version",
     "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
     "glqb_moe_plan_create", "glqb_moe_plan_workspace_bytes", "glqb_moe_plan_code_bytes", "glqb_moe_plan_run",
-    "glqb_moe_plan_status", "glqb_moe_plan_destroy",
+    "glqb_moe_plan_status", "glqb_moe_plan_destroy", "glqb_moe_plan_set_timing", "glqb_moe_plan_kernel_ms",
 ]
 
 
@@ -142,6 +142,10 @@ def load() -> C.CDLL:
     lib.glqb_moe_plan_run.restype = C.c_int
     lib.glqb_moe_plan_status.argtypes = [vp, vp, vp]
     lib.glqb_moe_plan_status.restype = C.c_int
+    lib.glqb_moe_plan_set_timing.argtypes = [vp, i32]
+    lib.glqb_moe_plan_set_timing.restype = C.c_int
+    lib.glqb_moe_plan_kernel_ms.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(i32)]
+    lib.glqb_moe_plan_kernel_ms.restype = C.c_int
     lib.glqb_moe_plan_destroy.argtypes = [vp]
     lib.glqb_moe_plan_destroy.restype = None
     lib.glqb_last_error.argtypes = []

@@ -756,6 +756,31 @@ struct GlqbMoePlan {
   bool gemm_ok = false;
   MoeDev devg;             // same weights, workspace laid out for the GEMM kernels
   MoeGemmKernel g13 = nullptr, g2 = nullptr;
+  // optional timing of the two expert matmuls (event pairs around each, on the launching stream)
+  bool timing = false;
+  std::vector<cudaEvent_t> ev;
+  size_t ev_used = 0;
+};
+
+// brackets one matmul launch with an event pair when timing is on
+struct MoeTimer {
+  GlqbMoePlan* P;
+  cudaStream_t st;
+  bool on;
+  MoeTimer(GlqbMoePlan* p, cudaStream_t s) : P(p), st(s), on(p->timing) {
+    if (!on) return;
+    while (P->ev.size() < P->ev_used + 2) {
+      cudaEvent_t e;
+      if (cudaEventCreate(&e) != cudaSuccess) { on = false; return; }
+      P->ev.push_back(e);
+    }
+    cudaEventRecord(P->ev[P->ev_used], st);
+  }
+  ~MoeTimer() {
+    if (!on) return;
+    cudaEventRecord(P->ev[P->ev_used + 1], st);
+    P->ev_used += 2;
+  }
 };
 
 static int moe_fail(int code, const char* fmt, ...) {
@@ -1012,13 +1037,19 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
         G, reinterpret_cast<const uint8_t*>(x), ws);
     int* status = reinterpret_cast<int*>(ws + G.o_status);
     const int* nitems = reinterpret_cast<const int*>(ws + G.o_nitems);
-    P->g13<<<std::min(P->sm_count, G.max_items13), GM_THREADS, moe_gemm_smem_bytes(), st>>>(
-        reinterpret_cast<const DevLinear*>(ws + G.o_layers13), reinterpret_cast<const GemmItem*>(ws + G.o_items13),
-        G.max_items13, ws, status, nitems);
+    {
+      MoeTimer t(P, st);
+      P->g13<<<std::min(P->sm_count, G.max_items13), GM_THREADS, moe_gemm_smem_bytes(), st>>>(
+          reinterpret_cast<const DevLinear*>(ws + G.o_layers13), reinterpret_cast<const GemmItem*>(ws + G.o_items13),
+          G.max_items13, ws, status, nitems);
+    }
     moe_mid_kernel<<<(R + P->mid_sg - 1) / P->mid_sg, MOE_XF_THREADS, P->mid_smem, st>>>(G, tokens, P->mid_sg, ws);
-    P->g2<<<std::min(P->sm_count, G.max_items2), GM_THREADS, moe_gemm_smem_bytes(), st>>>(
-        reinterpret_cast<const DevLinear*>(ws + G.o_layers2), reinterpret_cast<const GemmItem*>(ws + G.o_items2),
-        G.max_items2, ws, status, nitems + 1);
+    {
+      MoeTimer t(P, st);
+      P->g2<<<std::min(P->sm_count, G.max_items2), GM_THREADS, moe_gemm_smem_bytes(), st>>>(
+          reinterpret_cast<const DevLinear*>(ws + G.o_layers2), reinterpret_cast<const GemmItem*>(ws + G.o_items2),
+          G.max_items2, ws, status, nitems + 1);
+    }
     moe_out_kernel<<<tokens, MOE_XF_THREADS, P->out_smem, st>>>(G, tokens, P->out_rg, topk_weights, ws,
                                                                reinterpret_cast<uint8_t*>(y));
     cudaError_t e = cudaGetLastError();
@@ -1042,7 +1073,10 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   A.work = reinterpret_cast<int*>(ws + M.o_work);
   A.E = M.E; A.m = M.w13_out; A.n = M.hidden; A.gps = M.hidden / 32; A.strips = M.w13_out / 32;
   A.kchunks = M.kch13; A.gpc = M.gpc13; A.R = R;
-  P->k13<<<P->grid13, MV_THREADS, 0, st>>>(A);
+  {
+    MoeTimer t(P, st);
+    P->k13<<<P->grid13, MV_THREADS, 0, st>>>(A);
+  }
   moe_mid_kernel<<<(R + P->mid_sg - 1) / P->mid_sg, MOE_XF_THREADS, P->mid_smem, st>>>(M, tokens, P->mid_sg, ws);
   A.codes[0] = M.w2[0]; A.codes[1] = M.w2[1]; A.stride[0] = M.w2_stride[0]; A.stride[1] = M.w2_stride[1];
   A.inv2 = M.w2_inv2;
@@ -1052,7 +1086,10 @@ int glqb_moe_plan_run(GlqbMoePlan* P, const void* x, const void* topk_ids, const
   A.work = reinterpret_cast<int*>(ws + M.o_work) + 1;
   A.m = M.hidden; A.n = M.inter; A.gps = M.inter / 32; A.strips = M.hidden / 32;
   A.kchunks = M.kch2; A.gpc = M.gpc2;
-  P->k2<<<P->grid2, MV_THREADS, 0, st>>>(A);
+  {
+    MoeTimer t(P, st);
+    P->k2<<<P->grid2, MV_THREADS, 0, st>>>(A);
+  }
   moe_out_kernel<<<tokens, MOE_XF_THREADS, P->out_smem, st>>>(M, tokens, P->out_rg, topk_weights, ws,
                                                              reinterpret_cast<uint8_t*>(y));
   cudaError_t e = cudaGetLastError();
@@ -1073,6 +1110,31 @@ int glqb_moe_plan_status(const GlqbMoePlan* P, const void* workspace, void* stre
   return GLQB_OK;
 }
 
-void glqb_moe_plan_destroy(GlqbMoePlan* p) { delete p; }
+int glqb_moe_plan_set_timing(GlqbMoePlan* P, int32_t enable) {
+  if (!P) return moe_fail(GLQB_E_INVALID, "moe_plan_set_timing: null plan");
+  P->timing = enable != 0;
+  P->ev_used = 0;
+  return GLQB_OK;
+}
+
+int glqb_moe_plan_kernel_ms(GlqbMoePlan* P, double* total_ms_out, int32_t* runs_out) {
+  if (!P || !total_ms_out || !runs_out) return moe_fail(GLQB_E_INVALID, "moe_plan_kernel_ms: null argument");
+  double total = 0.0;
+  for (size_t i = 0; i + 1 < P->ev_used; i += 2) {
+    float ms = 0.f;
+    if (cudaEventSynchronize(P->ev[i + 1]) != cudaSuccess || cudaEventElapsedTime(&ms, P->ev[i], P->ev[i + 1]) != cudaSuccess)
+      return moe_fail(GLQB_E_CUDA, "moe_plan_kernel_ms: %s", cudaGetErrorString(cudaGetLastError()));
+    total += ms;
+  }
+  *total_ms_out = total;
+  *runs_out = (int32_t)(P->ev_used / 4);        // two matmuls per run
+  return GLQB_OK;
+}
+
+void glqb_moe_plan_destroy(GlqbMoePlan* p) {
+  if (!p) return;
+  for (cudaEvent_t e : p->ev) cudaEventDestroy(e);
+  delete p;
+}
 
 }  // extern "C"

@@ -472,6 +472,15 @@ class MoePlan:
         _lib.check(self.lib.glqb_moe_plan_status(self.handle, self.workspace.data_ptr(),
                                                  _stream(x if x is not None else self.workspace)), "moe_plan_status")
 
+    def set_timing(self, on: bool) -> None:
+        _lib.check(self.lib.glqb_moe_plan_set_timing(self.handle, 1 if on else 0), "moe_plan_set_timing")
+
+    def kernel_ms(self):
+        """(summed time of the two expert matmuls in ms, runs recorded) since timing was enabled; synchronises."""
+        ms, runs = C.c_double(), C.c_int32()
+        _lib.check(self.lib.glqb_moe_plan_kernel_ms(self.handle, C.byref(ms), C.byref(runs)), "moe_plan_kernel_ms")
+        return float(ms.value), int(runs.value)
+
     def close(self):
         if getattr(self, "handle", None):
             self.lib.glqb_moe_plan_destroy(self.handle)
@@ -491,9 +500,12 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
                             hidden_size, intermediate_size, w13_out_features,
                             n_pad_w13, m_pad_w13, n_pad_w2, m_pad_w2,
                             blocks_n_w13, blocks_m_w13, blocks_n_w13_meta, blocks_m_w13_meta,
-                            blocks_n_w2, blocks_m_w2, blocks_n_w2_meta, blocks_m_w2_meta, activation_type):
+                            blocks_n_w2, blocks_m_w2, blocks_n_w2_meta, blocks_m_w2_meta, activation_type,
+                            out_dtype=None):
     """(T, hidden) -> (T, hidden): routed experts, gated activation, weighted combine; any token count,
-    no host synchronisation.  A second-stage tensor with numel() <= E is the reference's "absent" sentinel."""
+    no host synchronisation.  A second-stage tensor with numel() <= E is the reference's "absent" sentinel.
+    ``out_dtype`` (not in the reference) selects the result dtype, e.g. fp32 partial results of one
+    expert-parallel rank; default: the dtype of x."""
     _require_cuda(x, "x")
     E = w13_trellis_packed.shape[0]
     T = x.shape[0]
@@ -507,8 +519,9 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
     has13 = w13_trellis_packed2 is not None and w13_trellis_packed2.numel() > E
     has2 = w2_trellis_packed2 is not None and w2_trellis_packed2.numel() > E
     cap = _moe_capacity(T)
+    odt = out_dtype or x.dtype
     key = ("moe3", w13_trellis_packed.data_ptr(), w2_trellis_packed.data_ptr(), cap, ids.shape[1], x.dtype, ids.dtype,
-           int(activation_type), has13, has2)
+           int(activation_type), has13, has2, odt)
     plan = _PLAN_CACHE.get(key)
     if plan is not None:
         _PLAN_CACHE.move_to_end(key)
@@ -531,11 +544,11 @@ def fused_moe_trellis_3inst(x, topk_ids, topk_weights,
         d.w2_inv_resid_scale2 = i2.data_ptr() if has2 else None
         _fill_moe_blocks(d, blocks_n_w13, n_pad_w13, blocks_m_w13, m_pad_w13, blocks_n_w2, n_pad_w2, blocks_m_w2, m_pad_w2)
         d.ids_are_int64 = 1 if ids.dtype == torch.int64 else 0
-        d.x_dtype = d.y_dtype = _dt(x.dtype)
+        d.x_dtype, d.y_dtype = _dt(x.dtype), _dt(odt)
         plan = MoePlan(d, x.device, [w13_trellis_packed, w13_trellis_packed2, w13_SU, w13_SV, ws13, i13,
                                      w2_trellis_packed, w2_trellis_packed2, w2_SU, w2_SV, ws2, i2])
         _PLAN_CACHE[key] = plan
-    y = torch.empty(T, hidden_size, dtype=x.dtype, device=x.device)
+    y = torch.empty(T, hidden_size, dtype=odt, device=x.device)
     plan.run(x, ids, tw, y)
     return y
 

@@ -161,6 +161,11 @@ int glqb_moe_plan_run(GlqbMoePlan* plan, const void* x, const void* topk_ids, co
 /* Synchronises `stream` and reports whether a bounded wait inside the GEMM kernels of the last run gave up
  * (GLQB_E_DEVICE, results invalid); GLQB_OK otherwise.  No counterpart in the reference. */
 int glqb_moe_plan_status(const GlqbMoePlan* plan, const void* workspace, void* stream);
+/* With timing enabled every run brackets its two expert matmuls (w13, w2) with CUDA event pairs on the
+ * launching stream; glqb_moe_plan_kernel_ms waits for them and returns the summed matmul time (ms) and the
+ * number of runs recorded since timing was (re-)enabled.  No counterpart in the reference. */
+int glqb_moe_plan_set_timing(GlqbMoePlan* plan, int32_t enable);
+int glqb_moe_plan_kernel_ms(GlqbMoePlan* plan, double* total_ms_out, int32_t* runs_out);
 void glqb_moe_plan_destroy(GlqbMoePlan* plan);
 
 /* Stateless single-layer form of the reference's fused ops, for occasional calls: it builds a one-layer
