@@ -12,6 +12,7 @@
 
 #include "glqb_kernels.cuh"
 #include "glqb_gemm.cuh"
+#include "glqb_launch.h"
 
 namespace glqb {
 
@@ -38,25 +39,6 @@ static int fail(int code, const char* fmt, ...) {
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 static inline int ilog2(int v) { int l = 0; while ((1 << l) < v) ++l; return l; }
 
-// One launch of a streaming decode kernel: a set of layers that share format / bit widths /
-// token-column blocks, contiguous in the device table.
-struct Segment {
-  int format, k1, k2, ns, nb;
-  int tn;                    // 0: streaming decode kernel; 128 / 256: tensor-core GEMM with that token tile
-  int two_phase = 0;         // E8 GEMM with many tokens: weight tiles decoded once beforehand
-  int first, count;          // range in the device table
-  long long total_groups;
-  int per_warp;
-  int grid;
-  int item_first, item_count;   // GEMM work items (range in the plan's item array)
-  // E8 only: most of the codebook resident in shared memory (one CTA per SM)
-  bool smem_table = false;
-  const uint32_t* big_table = nullptr;
-  const uint32_t* small_table = nullptr;
-  int small_entries = 0;
-};
-
-constexpr int GEMM_STAGES = 4;
 constexpr int DECODE_MAX_BATCH = 64;   // above this the GEMM path is used
 
 }  // namespace glqb
@@ -77,6 +59,8 @@ struct GlqbPlan {
   RhtItem* d_items_out = nullptr;
   GemmItem* d_gemm_items = nullptr;
   int* d_status = nullptr;
+  int* d_tickets = nullptr;      // completion tickets of the single-launch form, all zero between runs
+  int n_tickets = 0;
   int max_batch_gemm = 1;
   size_t ws_bytes = 0;
   int max_batch = 1;
@@ -111,7 +95,6 @@ static MvKernel trellis_kernel(int k1, int k2, int nb) {
 #define T_CASE(A, B) if (k1 == A && k2 == B) return trellis_kernel_nb<A, B>(nb);
   T_CASE(1, 0) T_CASE(2, 0) T_CASE(3, 0) T_CASE(4, 0)
   T_CASE(4, 1) T_CASE(4, 2) T_CASE(4, 3) T_CASE(4, 4)
-  T_CASE(2, 2) T_CASE(3, 3) T_CASE(2, 1) T_CASE(3, 1) T_CASE(3, 2)
 #undef T_CASE
   return nullptr;
 }
@@ -135,6 +118,19 @@ static MvKernel e8_kernel(int ns, int nb) {
     case 4: return e8_kernel_nb<4>(nb);
   }
   return nullptr;
+}
+
+constexpr size_t FUSED_SMEM_LIMIT = 200 * 1024;
+static bool fused_enabled() {
+  const char* e = getenv("GLQB_FUSED_DECODE");
+  return !e || atoi(e) != 0;
+}
+// do two layers read the same transformed input?
+static bool same_input(const GlqbLinearDesc& a, const GlqbLinearDesc& b) {
+  return a.format == b.format && a.n_pad == b.n_pad && a.in_features == b.in_features && a.sv == b.sv &&
+         a.batch == b.batch && a.x_offset == b.x_offset && a.x_stride == b.x_stride && a.x_dtype == b.x_dtype &&
+         a.x_is_rotated == b.x_is_rotated && a.n_blocks_n == b.n_blocks_n &&
+         memcmp(a.blocks_n, b.blocks_n, sizeof(int32_t) * a.n_blocks_n) == 0;
 }
 
 typedef void (*E8SmemKernel)(const DevLinear*, int, long long, int, uint8_t*, const uint32_t*, const uint32_t*, int);
@@ -169,17 +165,6 @@ static long long e8_smem_min_bytes() {
   return e ? atoll(e) : (48ll << 20);
 }
 
-typedef void (*TilesSmemKernel)(const DevLinear*, int, int, uint8_t*, const uint32_t*, const uint32_t*, int);
-static TilesSmemKernel pick_tiles_smem_kernel(int ns) {
-  switch (ns) {
-    case 1: return e8_tiles_smem_kernel<1>;
-    case 2: return e8_tiles_smem_kernel<2>;
-    case 3: return e8_tiles_smem_kernel<3>;
-    case 4: return e8_tiles_smem_kernel<4>;
-  }
-  return nullptr;
-}
-
 // Do all layers of the segment read one 65,536-entry table (and at most one small table)?  Also sums the
 // index bytes of the segment.
 static bool e8_uniform_tables(const std::vector<DevLinear>& dev, const Segment& s, const uint32_t** big_out,
@@ -212,53 +197,10 @@ static MvKernel pick_kernel(const Segment& s) {
   return s.format == GLQB_FMT_TRELLIS_3INST ? trellis_kernel(s.k1, s.k2, s.nb) : e8_kernel(s.ns, s.nb);
 }
 
-typedef void (*GemmKernel)(const DevLinear*, const GemmItem*, int, uint8_t*, int*, const int*);
-
-template <int FORMAT, int K1, int K2>
-static GemmKernel gemm_kernel_tn(int tn) {
-  if (tn == 128) return glq_gemm_kernel<FORMAT, K1, K2, 128, GEMM_STAGES>;
-  if (tn == 256) return glq_gemm_kernel<FORMAT, K1, K2, 256, GEMM_STAGES>;
-  return nullptr;
-}
-
-typedef void (*TilesKernel)(const DevLinear*, int, int, uint8_t*);
-static TilesKernel pick_tiles_kernel(int ns) {
-  switch (ns) {
-    case 1: return e8_tiles_kernel<1>;
-    case 2: return e8_tiles_kernel<2>;
-    case 3: return e8_tiles_kernel<3>;
-    case 4: return e8_tiles_kernel<4>;
-  }
-  return nullptr;
-}
-
 // token count from which E8 prefill decodes the weight tiles once instead of once per token tile
 static int e8_two_phase_min_tokens() {
   const char* e = getenv("GLQB_E8_TWO_PHASE_MIN_TOKENS");
   return e ? atoi(e) : 129;     // measured on B200: above one 128-token tile the tile decode plus a copy-fed GEMM wins
-}
-
-static GemmKernel pick_gemm_kernel(const Segment& s) {
-  if (s.two_phase) return gemm_kernel_tn<2, 0, 0>(s.tn);
-  if (s.format == GLQB_FMT_TRELLIS_3INST) {
-#define G_CASE(A, B) if (s.k1 == A && s.k2 == B) return gemm_kernel_tn<0, A, B>(s.tn);
-    G_CASE(1, 0) G_CASE(2, 0) G_CASE(3, 0) G_CASE(4, 0)
-    G_CASE(4, 1) G_CASE(4, 2) G_CASE(4, 3) G_CASE(4, 4)
-    G_CASE(2, 2) G_CASE(3, 3) G_CASE(2, 1) G_CASE(3, 1) G_CASE(3, 2)
-#undef G_CASE
-    return nullptr;
-  }
-  switch (s.ns) {
-    case 1: return gemm_kernel_tn<1, 1, 0>(s.tn);
-    case 2: return gemm_kernel_tn<1, 2, 0>(s.tn);
-    case 3: return gemm_kernel_tn<1, 3, 0>(s.tn);
-    case 4: return gemm_kernel_tn<1, 4, 0>(s.tn);
-  }
-  return nullptr;
-}
-
-static size_t gemm_smem_bytes(int tn) {
-  return (size_t)GEMM_STAGES * (GM_A_BYTES + (size_t)tn * 128) + (3 * GEMM_STAGES + 5) * 8 + 16 + 1024;
 }
 
 static int tn_for_batch(int batch) { return batch <= DECODE_MAX_BATCH ? 0 : (batch <= 128 ? 128 : 256); }
@@ -393,7 +335,7 @@ static int build_plan(GlqbPlan* P) {
     s.first = (int)P->order.size();
     s.count = (int)groups[k].size();
     for (int i : groups[k]) P->order.push_back(i);
-    if (s.tn ? !pick_gemm_kernel(s) : !pick_kernel(s))
+    if (s.tn ? !gemm_available(s) : !pick_kernel(s))
       return fail(GLQB_E_INVALID, "no kernel variant for format=%d K=%d+%d stages=%d token blocks=%d", s.format,
                   s.k1, s.k2, s.ns, s.nb);
     P->segs.push_back(s);
@@ -449,7 +391,56 @@ static int build_plan(GlqbPlan* P) {
 
   // ---- per segment: group prefix, range length per warp, grid
   P->gemm_items.clear();
+  P->n_tickets = 0;
   for (Segment& s : P->segs) {
+    if (!s.tn && s.format == GLQB_FMT_TRELLIS_3INST && s.nb == 1 && fused_enabled() && fused_available(s.k1, s.k2)) {
+      // single-launch form: every layer of the segment reads the same input, at most 8 tokens, and the
+      // activations plus the transform scratch fit in shared memory
+      const GlqbLinearDesc& d0 = P->descs[P->order[s.first]];
+      bool ok = !d0.x_is_rotated && d0.batch <= FUSED_MAX_TOKENS;
+      for (int i = 1; i < s.count && ok; ++i) ok = same_input(d0, P->descs[P->order[s.first + i]]);
+      int scratch = 32;
+      for (int i = 0; i < d0.n_blocks_n; ++i) scratch = std::max(scratch, d0.blocks_n[i]);
+      for (int i = 0; i < s.count && ok; ++i) {
+        const GlqbLinearDesc& d = P->descs[P->order[s.first + i]];
+        for (int b = 0; b < d.n_blocks_m; ++b)
+          scratch = std::max(scratch, std::min(d.batch, std::max(1, GLQB_RHT_TILE / d.blocks_m[b])) * d.blocks_m[b]);
+      }
+      const size_t smem = fused_smem_bytes(d0.n_pad, d0.batch, scratch);
+      if (ok && smem <= FUSED_SMEM_LIMIT) {
+        int resident = 0;
+        CUDA_TRY(fused_prepare(s.k1, s.k2, FUSED_SMEM_LIMIT, smem, &resident));
+        if (resident > 0) {
+          long long units = 0;
+          for (int i = 0; i < s.count; ++i) {
+            const DevLinear& L = P->dev[s.first + i];
+            units += (long long)L.strips * ((L.groups_per_strip + FUSED_CHUNK_GROUPS - 1) / FUSED_CHUNK_GROUPS);
+          }
+          if (units < (1ll << 30)) {
+            units = 0;
+            for (int i = 0; i < s.count; ++i) {
+              DevLinear& L = P->dev[s.first + i];
+              const int kch = (L.groups_per_strip + FUSED_CHUNK_GROUPS - 1) / FUSED_CHUNK_GROUPS;
+              L.group_base = units;                       // first work unit of the layer
+              L.fixed_slots = kch;
+              L.slots = kch;
+              L.per_warp = 1;
+              L.ticket_base = P->n_tickets;
+              P->n_tickets += L.nbm;
+              units += (long long)L.strips * kch;
+            }
+            s.fused = true;
+            s.total_units = (int)units;
+            s.scratch_elems = scratch;
+            s.fused_smem = smem;
+            s.grid = (int)std::min<long long>(units, (long long)P->sm_count * std::min(resident, 2));
+            s.total_groups = 0;
+            s.per_warp = 1;
+            continue;
+          }
+        }
+      }
+    }
     if (s.tn) {
       // tensor-core GEMM: work items = (layer, 128-row tile, token tile[, K split]); the K range is
       // split only when there are too few tiles to occupy the SMs
@@ -483,8 +474,7 @@ static int build_plan(GlqbPlan* P) {
       s.grid = std::min(s.item_count, P->sm_count);
       s.total_groups = 0;
       s.per_warp = 1;
-      CUDA_TRY(cudaFuncSetAttribute(pick_gemm_kernel(s), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)gemm_smem_bytes(s.tn)));
+      CUDA_TRY(gemm_prepare(s));
       if (s.two_phase) {
         // tile decode with the codebook resident in shared memory, under the same conditions as the
         // streaming kernel's resident form
@@ -493,8 +483,7 @@ static int build_plan(GlqbPlan* P) {
         const uint32_t* small = nullptr;
         int small_n = 0;
         if (e8_uniform_tables(P->dev, s, &big, &small, &small_n, &bytes) && bytes >= e8_smem_min_bytes() &&
-            cudaFuncSetAttribute(pick_tiles_smem_kernel(s.ns), cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 E8S_SMEM_BYTES) == cudaSuccess) {
+            tiles_smem_prepare(s.ns) == cudaSuccess) {
           s.smem_table = true;
           s.big_table = big;
           s.small_table = small ? small : big;
@@ -561,11 +550,23 @@ static int build_plan(GlqbPlan* P) {
   P->items_in.clear();
   P->items_in_gemm.clear();
   P->items_out.clear();
+  std::vector<char> layer_fused(n, 0);
+  for (const Segment& s : P->segs)
+    if (s.fused)
+      for (int i = 0; i < s.count; ++i) layer_fused[s.first + i] = 1;
   for (int pos = 0; pos < n; ++pos) {
     DevLinear& L = P->dev[pos];
     const GlqbLinearDesc& d = P->descs[P->order[pos]];
+    if (layer_fused[pos]) {                 // activations live in shared memory, transforms run inside the kernel
+      ws = align_up(ws, 1024);
+      L.xr_off = 0;
+      L.part_off = (long long)ws;
+      ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
+      continue;
+    }
     int same = -1;
     for (int q = 0; q < pos && same < 0; ++q) {
+      if (layer_fused[q]) continue;
       const DevLinear& Q = P->dev[q];
       const GlqbLinearDesc& e = P->descs[P->order[q]];
       if (Q.format == L.format && Q.gemm_tn == L.gemm_tn && Q.n == L.n && Q.in_f == L.in_f && Q.sv == L.sv &&
@@ -616,6 +617,8 @@ static int build_plan(GlqbPlan* P) {
                       cudaMemcpyHostToDevice));
   CUDA_TRY(cudaMalloc(&P->d_status, sizeof(int)));
   CUDA_TRY(cudaMemset(P->d_status, 0, sizeof(int)));
+  CUDA_TRY(cudaMalloc(&P->d_tickets, sizeof(int) * std::max(1, P->n_tickets)));
+  CUDA_TRY(cudaMemset(P->d_tickets, 0, sizeof(int) * std::max(1, P->n_tickets)));
   CUDA_TRY(cudaMalloc(&P->d_items_out, sizeof(RhtItem) * std::max<size_t>(1, P->items_out.size())));
   CUDA_TRY(cudaMemcpy(P->d_items_out, P->items_out.data(), sizeof(RhtItem) * P->items_out.size(), cudaMemcpyHostToDevice));
 
@@ -661,7 +664,8 @@ int64_t glqb_plan_code_bytes(const GlqbPlan* plan) { return plan ? plan->code_by
 int64_t glqb_plan_flops(const GlqbPlan* plan) { return plan ? plan->flops : 0; }
 int32_t glqb_plan_launches(const GlqbPlan* plan) {
   if (!plan) return 0;
-  int n = (plan->items_in.empty() ? 0 : 1) + (plan->items_in_gemm.empty() ? 0 : 1) + (int)plan->segs.size() + 1;
+  int n = (plan->items_in.empty() ? 0 : 1) + (plan->items_in_gemm.empty() ? 0 : 1) + (int)plan->segs.size() +
+          (plan->items_out.empty() ? 0 : 1);
   for (const Segment& s : plan->segs) n += s.two_phase;
   return n;
 }
@@ -713,15 +717,11 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     CUDA_TRY(cudaEventRecord(P->ev[P->ev_used], stream));
   }
   for (const Segment& s : P->segs) {
-    if (s.tn) {
-      if (s.two_phase && s.smem_table)
-        pick_tiles_smem_kernel(s.ns)<<<P->sm_count, E8TS_THREADS, E8S_SMEM_BYTES, stream>>>(
-            P->d_layers, s.first, s.count, ws, s.big_table, s.small_table, s.small_entries);
-      else if (s.two_phase)
-        pick_tiles_kernel(s.ns)<<<P->sm_count * 8, 256, 0, stream>>>(P->d_layers, s.first, s.count, ws);
-      GemmKernel kern = pick_gemm_kernel(s);
-      kern<<<s.grid, GM_THREADS, gemm_smem_bytes(s.tn), stream>>>(P->d_layers, P->d_gemm_items + s.item_first,
-                                                                   s.item_count, ws, P->d_status, nullptr);
+    if (s.fused) {
+      fused_launch(s, P->d_layers + s.first, reinterpret_cast<const uint8_t*>(x_base), reinterpret_cast<uint8_t*>(y_base),
+                   ws, P->d_tickets, stream);
+    } else if (s.tn) {
+      gemm_launch(s, P->d_layers, P->d_gemm_items + s.item_first, ws, P->d_status, P->sm_count, stream);
     } else if (s.smem_table) {
       pick_e8_smem_kernel(s)<<<s.grid, E8S_THREADS, E8S_SMEM_BYTES, stream>>>(
           P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws, s.big_table, s.small_table, s.small_entries);
@@ -734,7 +734,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     CUDA_TRY(cudaEventRecord(P->ev[P->ev_used + 1], stream));
     P->ev_used += 2;
   }
-  {
+  if (!P->items_out.empty()) {
     rht_out_kernel<false><<<(unsigned)P->items_out.size(), rht_threads(P->max_elems_out), rht_smem(P->max_elems_out), stream>>>(
         P->d_layers, P->d_items_out, ws, reinterpret_cast<uint8_t*>(y_base), nullptr);
   }
@@ -759,6 +759,7 @@ void glqb_plan_destroy(GlqbPlan* plan) {
   if (plan->d_items_in_gemm) cudaFree(plan->d_items_in_gemm);
   if (plan->d_gemm_items) cudaFree(plan->d_gemm_items);
   if (plan->d_status) cudaFree(plan->d_status);
+  if (plan->d_tickets) cudaFree(plan->d_tickets);
   for (cudaEvent_t e : plan->ev) cudaEventDestroy(e);
   delete plan;
 }
@@ -787,7 +788,6 @@ int glqb_decompress_trellis_3inst(const void* packed, int32_t bits, const void* 
   }
   D_CASE(1, 0) D_CASE(2, 0) D_CASE(3, 0) D_CASE(4, 0)
   D_CASE(4, 1) D_CASE(4, 2) D_CASE(4, 3) D_CASE(4, 4)
-  D_CASE(2, 2) D_CASE(3, 3) D_CASE(2, 1) D_CASE(3, 1) D_CASE(3, 2)
 #undef D_CASE
   return fail(GLQB_E_INVALID, "decompress_trellis_3inst: no kernel for K=%d+%d", bits, k2);
 }

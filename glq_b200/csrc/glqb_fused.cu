@@ -1,0 +1,31 @@
+// Instantiations and launches of the single-launch decode kernels (trellis_fused_kernel, glqb_kernels.cuh).
+#include "glqb_kernels.cuh"
+#include "glqb_launch.h"
+
+namespace glqb {
+
+typedef void (*FusedKernel)(const DevLinear*, int, int, int, const uint8_t*, uint8_t*, uint8_t*, int*);
+static FusedKernel trellis_fused_pick(int k1, int k2) {
+#define F_CASE(A, B) if (k1 == A && k2 == B) return trellis_fused_kernel<A, B>;
+  F_CASE(1, 0) F_CASE(2, 0) F_CASE(3, 0) F_CASE(4, 0)
+  F_CASE(4, 1) F_CASE(4, 2) F_CASE(4, 3) F_CASE(4, 4)
+#undef F_CASE
+  return nullptr;
+}
+
+bool fused_available(int k1, int k2) { return trellis_fused_pick(k1, k2) != nullptr; }
+
+cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* resident_ctas_out) {
+  FusedKernel fk = trellis_fused_pick(k1, k2);
+  cudaError_t e = cudaFuncSetAttribute(fk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
+  if (e != cudaSuccess) return e;
+  return cudaOccupancyMaxActiveBlocksPerMultiprocessor(resident_ctas_out, fk, MV_THREADS, smem);
+}
+
+void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_base, uint8_t* y_base, uint8_t* ws,
+                  int* tickets, cudaStream_t stream) {
+  trellis_fused_pick(s.k1, s.k2)<<<s.grid, MV_THREADS, s.fused_smem, stream>>>(layers, s.count, s.total_units, s.scratch_elems,
+                                                                               x_base, y_base, ws, tickets);
+}
+
+}  // namespace glqb

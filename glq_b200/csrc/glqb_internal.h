@@ -33,6 +33,7 @@ struct DevLinear {
   int per_warp;          // work groups handed to each warp of the segment's launch
   int fixed_slots;       // > 0: every strip has exactly this many partial sums (GEMM path: K splits)
   int gemm_tn;           // token tile of the GEMM path (0: streaming decode path)
+  int ticket_base;       // single-launch form: first completion ticket of this layer (one per output Hadamard block)
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];

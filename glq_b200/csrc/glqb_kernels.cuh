@@ -254,7 +254,7 @@ __device__ __forceinline__ void rht_out_body(const DevLinear& L, const RhtItem i
     const int cnt = slots_of(row);
     const float* p = part + token * m + row;
     float s = 0.f;
-    for (int k = 0; k < cnt; ++k) s += p[k * slot_stride];
+    for (int k = 0; k < cnt; ++k) s += __ldcg(p + k * slot_stride);
     s *= wscale;
     if (row_scale) s *= row_scale[row];
     return s;
@@ -289,7 +289,7 @@ __device__ __forceinline__ void rht_out_body(const DevLinear& L, const RhtItem i
       } else {
         const int cnt = j < 4 ? cnt_lo : cnt_hi;
         for (int k = 0; k < cnt; ++k) {
-          const float4 t = *reinterpret_cast<const float4*>(src + 4 * j + k * slot_stride);
+          const float4 t = __ldcg(reinterpret_cast<const float4*>(src + 4 * j + k * slot_stride));
           s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
         }
         s.x *= wscale; s.y *= wscale; s.z *= wscale; s.w *= wscale;
@@ -574,6 +574,182 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
     }
     g += ng;
     if (c1 == gps && strip == L.strips - 1) ++li;
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// One launch per decode linear (up to 8 tokens): input transform, 3INST decode + mma, output transform.
+//
+// Used for plans whose layers all read the same input (one layer, or the q/k/v / gate/up shards of a fused
+// projection).  The reference's counterpart is its FUSE_IN matvec (glq/csrc/glq_trellis.cu:315-370, chosen at
+// :1290-1295), which still needs a second launch for the output transform.
+//   phase 1  every CTA recomputes the (cheap) input transform of the shared input into its own shared memory,
+//            in the B-fragment layout of the MMAs — fht_tile, the same arithmetic as rht_in_kernel;
+//   phase 2  work unit = (layer, 32-row strip, chunk of 64 column groups): warp w of the CTA decodes groups
+//            [8w, 8w + 8) of the chunk; the eight warps' partial sums are added in warp order through shared
+//            memory and written as partial sum number `chunk` of the strip (a strip of up to 2048 columns has
+//            exactly one);
+//   phase 3  a CTA that finishes the last unit of a Hadamard block of the output (integer ticket per block,
+//            __threadfence before the increment; nobody ever waits) runs that block's output transform —
+//            rht_out_body, the same arithmetic as rht_out_kernel.  The result does not depend on which CTA
+//            that is.  Tickets are returned to zero by the CTA that completes them.
+// ---------------------------------------------------------------------------------------------
+constexpr int FUSED_CHUNK_GROUPS = 64;          // column groups per work unit: 8 warps x 8 groups
+constexpr int FUSED_MAX_TOKENS = 8;
+constexpr int FUSED_MAX_TODO = 32;
+
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// shared-memory bytes of the fused kernel: activations (2 halfs per column and token), transform scratch
+// (the largest input block, or output tile, padded by one word per 32), the warps' partial sums
+__host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, int scratch_elems) {
+  return (size_t)batch * n * 4 + ((size_t)scratch_elems + scratch_elems / 32) * 4 + 8 * 256 * 4 + 64;
+}
+
+template <int K1, int K2>
+__global__ void __launch_bounds__(MV_THREADS, 2)
+trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int total_units, int scratch_elems,
+                     const uint8_t* __restrict__ x_base, uint8_t* __restrict__ y_base, uint8_t* __restrict__ ws,
+                     int* __restrict__ tickets) {
+  extern __shared__ __align__(16) uint8_t fsm[];
+  const DevLinear& L0 = layers[0];
+  const int n = L0.n, batch = L0.batch;
+  __half2* xs = reinterpret_cast<__half2*>(fsm);                              // [batch][n] (x, 0) pairs, fragment order
+  float* fbuf = reinterpret_cast<float*>(fsm + (size_t)batch * n * 4);
+  float* red = fbuf + scratch_elems + scratch_elems / 32;                       // [8 warps][8 values][32 lanes]
+  __shared__ int todo[FUSED_MAX_TODO];
+  __shared__ int n_todo;
+  if (threadIdx.x == 0) n_todo = 0;
+
+  // ---- phase 1: input transform of the shared input, token by token, block by block
+  {
+    const bool vec_ok = act_rows_aligned4(x_base, L0.x_off, L0.x_stride, L0.x_dtype);
+    for (int b = 0; b < L0.nbn; ++b) {
+      const int off = L0.bn_off[b], logbs = L0.bn_log[b];
+      const float rs = rsqrtf((float)(1 << logbs));
+      const bool vok = vec_ok && (off & 3) == 0;
+      for (int tok = 0; tok < batch; ++tok) {
+        auto store1 = [&](int, int i, float val) {
+          const int col = off + i;
+          const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);      // half index, even
+          xs[((size_t)tok * n * XR_TRELLIS_EXPAND + pos) >> 1] = __halves2half2(__float2half_rn(val * rs), __float2half_rn(0.f));
+        };
+        auto load1 = [&](int, int i) -> float {
+          const int col = off + i;
+          return load_act(x_base, L0.x_off + (long long)tok * L0.x_stride + col, L0.x_dtype) * __half2float(L0.sv[col]);
+        };
+        auto load32 = [&](int, int i0, float (&v)[32]) { rht_load_x32(L0, x_base, tok, off + i0, vok, v); };
+        fht_tile(fbuf, logbs, 1, load32, load1, store1);
+        __syncthreads();
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 2: work units
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+  const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
+  for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+    int li = 0;
+    while (li + 1 < n_layers && layers[li + 1].group_base <= u) ++li;
+    const DevLinear& L = layers[li];
+    const int kch = L.fixed_slots;                          // chunks (= partial sums) per strip
+    const int local = u - (int)L.group_base;
+    const int strip = local / kch, chunk = local - strip * kch;
+    const int gps = L.groups_per_strip;
+    const int c0 = chunk * FUSED_CHUNK_GROUPS + warp * 8;
+    const int ng = max(0, min(8, gps - c0));
+    float acc[1][2][4], acc2[1][2][4];
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { acc[0][mi][i] = 0.f; acc2[0][mi][i] = 0.f; }
+    if (ng > 0) {
+      const uint8_t* p1 = L.codes[0] + ((long long)strip * gps + c0) * (128 * K1) + lane * (4 * K1);
+      const uint8_t* p2 = nullptr;
+      if constexpr (K2 > 0) p2 = L.codes[1] + ((long long)strip * gps + c0) * (128 * K2) + lane * (4 * K2);
+      const int token = min(gq, batch - 1);                 // columns past the batch repeat the last token
+      const uint32_t xa = xs_addr + (uint32_t)((((size_t)token * n + (size_t)c0 * 32) * XR_TRELLIS_EXPAND + tq * 16) * 2);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {                         // two rounds of four groups: all codes of a round in flight
+        Words<K1> w1[4];
+        Words<(K2 > 0 ? K2 : 1)> w2[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (h * 4 + i < ng) {
+            w1[i] = load_words<K1>(p1 + (h * 4 + i) * (128 * K1));
+            if constexpr (K2 > 0) w2[i] = load_words<K2>(p2 + (h * 4 + i) * (128 * K2));
+          }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (h * 4 + i < ng) {                             // uniform per warp: the shuffles inside see all lanes
+            uint4 xb[1][2];
+            xb[0][0] = lds_v4(xa + (h * 4 + i) * 128);      // 64 halfs = 128 bytes per group
+            xb[0][1] = lds_v4(xa + (h * 4 + i) * 128 + 16);
+            group_mma<K1, 1>(w1[i], lane, xb, acc);
+            if constexpr (K2 > 0) group_mma<K2, 1>(w2[i], lane, xb, acc2);
+          }
+      }
+    }
+    {
+      const float s2 = L.stage_scale[1];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float v = acc[0][mi][i];
+          if constexpr (K2 > 0) v = __fadd_rn(v, __fmul_rn(s2, acc2[0][mi][i]));
+          red[(warp * 8 + mi * 4 + i) * 32 + lane] = v;
+        }
+    }
+    __syncthreads();
+    {
+      // thread (f, ln): fragment value f = mi * 4 + i of lane ln, summed over the warps in warp order
+      const int f = threadIdx.x >> 5, ln = threadIdx.x & 31;
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < MV_WARPS; ++w) s += red[(w * 8 + f) * 32 + ln];
+      const int mi = f >> 2, i = f & 3;
+      const int row = strip * 32 + mi * 16 + (ln >> 2) + ((i >> 1) ? 8 : 0);
+      const int token = (ln & 3) * 2 + (i & 1);
+      if (token < batch) {
+        reinterpret_cast<float*>(ws + L.part_off)[((long long)chunk * batch + token) * L.m + row] = s;
+        __threadfence();
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      // which Hadamard block of the output holds this strip, and how many units make it complete
+      int b = 0;
+      while (b + 1 < L.nbm && strip * 32 >= L.bm_off[b + 1]) ++b;
+      const int need = ((1 << L.bm_log[b]) >> 5) * kch;
+      __threadfence();
+      const int old = atomicAdd(&tickets[L.ticket_base + b], 1);
+      if (old + 1 == need) {
+        tickets[L.ticket_base + b] = 0;                                 // ready for the next run
+        __threadfence();
+        if (n_todo < FUSED_MAX_TODO) todo[n_todo++] = (li << 8) | b;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: output transforms of the blocks this CTA completed
+  const int nt = n_todo;
+  for (int k = 0; k < nt; ++k) {
+    const int li = todo[k] >> 8, b = todo[k] & 255;
+    const DevLinear& L = layers[li];
+    const int bs = 1 << L.bm_log[b];
+    const int tt = max(1, min(batch, scratch_elems / bs));
+    for (int t0 = 0; t0 < batch; t0 += tt) {
+      rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0)}, ws, y_base, nullptr, fbuf);
+      __syncthreads();
+    }
   }
 }
 

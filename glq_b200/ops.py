@@ -237,6 +237,47 @@ def fused_linear_trellis_3inst_yrht_rvq2(x, sv, trellis_packed, trellis_packed2,
                    in_features, m_pad, n_pad, m_pad, y_rht_out=y_rht_out, col=col)
 
 
+def fused_linear_trellis_3inst_shards(x, sv, shards, blocks_n=None, out_dtype=None):
+    """Several trellis layers that read the same input (the q/k/v or gate/up shards of a fused projection, which
+    share SV: glq_vllm/linear_method.py:825-826, 902-909) as ONE plan: one launch for up to 8 tokens instead of
+    one fused call per shard plus a shard-batched output transform (glq_vllm/linear_method.py:662-710).
+    ``shards`` is a sequence of (su, trellis_packed, trellis_packed2 or None, wscale, inv_resid_scale2, m_pad);
+    returns (B, sum of m_pad) with the shards' outputs side by side.  Not in the reference."""
+    _require_cuda(x, "x")
+    n = sv.numel()
+    x2d = x.reshape(-1, n)
+    if x2d.stride(-1) != 1:
+        x2d = x2d.contiguous()
+    B = x2d.shape[0]
+    total_m = sum(int(sh[5]) for sh in shards)
+    odt = out_dtype or x2d.dtype
+    bn = _blocks(blocks_n, n)
+    bb = token_bucket(B)
+    xin = x2d
+    if bb != B:
+        xin = x2d.new_zeros((bb, n))
+        xin[:B] = x2d
+    out = torch.empty((bb, total_m), dtype=odt, device=x2d.device)
+    key = ("trellis_shards", tuple(sh[1].data_ptr() for sh in shards), sv.data_ptr(), tuple(float(sh[3]) for sh in shards),
+           bb, xin.dtype, odt, xin.stride(0))
+
+    def make_specs():
+        specs, col = [], 0
+        for su, packed, packed2, wscale, inv2, m in shards:
+            has2 = packed2 is not None and packed2.numel() > 0
+            specs.append(LinearSpec(format=_lib.FMT_TRELLIS_3INST, m_pad=int(m), n_pad=n, in_features=n, out_features=int(m),
+                                    codes=[packed] + ([packed2] if has2 else []),
+                                    bits=[_trellis_bits(packed)] + ([_trellis_bits(packed2)] if has2 else []),
+                                    su=su, sv=sv, wscale=float(wscale), stage_scale=[float(inv2)] if has2 else [],
+                                    blocks_n=bn, blocks_m=block_decompose(int(m)), batch=bb, x_dtype=xin.dtype, y_dtype=odt,
+                                    x_stride=xin.stride(0), y_stride=total_m, y_offset=col))
+            col += int(m)
+        return specs
+    plan = _cached_plan(key, make_specs)
+    plan.run(xin, out, workspace=shared_workspace(xin.device, plan.workspace_bytes))
+    return out[:B]
+
+
 _ONES: dict = {}
 
 

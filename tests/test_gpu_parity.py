@@ -183,7 +183,10 @@ def test_trellis_decode_shapes_b1(ops, shape):
 
 
 def test_trellis_row_parity_and_determinism(ops):
-    """Row b of a batched call equals the batch-1 call on x[b], bit for bit; repeated calls are identical."""
+    """Row b of a batched call equals the call on x[b] alone, bit for bit, within a kernel family (up to 8
+    tokens: the single-launch kernel; 9 to 64: the streaming kernel); across the two families the partial sums
+    are grouped differently, so rows agree to one unit in the last place of the fp16 result.  Repeated calls
+    are identical."""
     rng = np.random.default_rng(77)
     m, n = 256, 1024
     p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, 4)
@@ -192,9 +195,75 @@ def test_trellis_row_parity_and_determinism(ops):
     yb = _run_trellis(ops, x, *args)
     yb2 = _run_trellis(ops, x, *args)
     assert torch.equal(yb, yb2)
-    for b in (0, 7, 8, 18):
+    y12 = _run_trellis(ops, x[:12], *args)                 # streaming family, other token-block count
+    assert torch.equal(y12, yb[:12])
+    y7 = _run_trellis(ops, x[:7], *args)                   # single-launch family
+    for b in (0, 3, 6):
         y1 = _run_trellis(ops, x[b:b + 1], *args)
-        assert torch.equal(y1[0], yb[b])
+        assert torch.equal(y1[0], y7[b])
+        assert torch.equal(y1, _run_trellis(ops, x[b:b + 1], *args))
+    ulp = 2.0 ** -10 * yb.float().abs().max().item()
+    assert (y7.float() - yb[:7].float()).abs().max().item() <= ulp
+
+
+@pytest.mark.parametrize("K,K2", [(4, 0), (2, 0), (4, 2)])
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_trellis_single_launch_matches_three_launch_form(ops, K, K2, B, monkeypatch):
+    """Up to 8 tokens run as ONE kernel (input transform, decode, output transform by the CTA that completes a
+    Hadamard block).  Same oracle tolerance as the three-launch form, which stays selectable, and the two agree
+    with each other far inside it."""
+    rng = np.random.default_rng(300 + K * 10 + K2 + B)
+    m, n = 352, 11008 if B == 1 else 576
+    p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, K, K2)
+    x_t = cuda(rng.standard_normal((B, n)).astype(np.float32), torch.bfloat16)
+    ref = O.linear_forward(x_t.float().cpu().numpy(), W, su, sv, wscale)
+    outs = {}
+    for form in ("1", "0"):
+        monkeypatch.setenv("GLQB_FUSED_DECODE", form)
+        ops.clear_caches()
+        y = _run_trellis(ops, x_t, p1, p2, su, sv, wscale, inv, m, n, out_dtype=torch.float32)
+        assert relerr(y.cpu().numpy(), ref) <= TOL, form
+        plan = next(iter(ops._PLAN_CACHE.values()))
+        assert plan.launches == (1 if form == "1" else 3)
+        outs[form] = y
+    assert relerr(outs["1"].cpu().numpy(), outs["0"].cpu().numpy()) <= 1e-5
+    ops.clear_caches()
+
+
+def test_trellis_shards_in_one_launch(ops):
+    """q/k/v-style shards that share their input run as one plan and one launch; every shard's output equals the
+    single-layer call bit for bit and the oracle within tolerance; the call can be captured in a CUDA graph."""
+    rng = np.random.default_rng(91)
+    n, ms = 2048, [2048, 512, 512]
+    sv = signs(rng, n)
+    layers = []
+    for m in ms:
+        p1 = rand_packed(rng, m, n, 4)
+        layers.append((p1, signs(rng, m), float(np.float16(rng.uniform(0.5, 1.5) * 0.02)), O.trellis_decode_layer(p1, m, n, 4).astype(np.float32)))
+    x_t = cuda(rng.standard_normal((2, n)).astype(np.float32), torch.bfloat16)
+    sv_t = cuda(sv)
+    dev = [(cuda(su), cuda(p1), None, ws, 0.0, m) for (p1, su, ws, W), m in zip(layers, ms)]
+    y = ops.fused_linear_trellis_3inst_shards(x_t, sv_t, dev, out_dtype=torch.float32)
+    assert y.shape == (2, sum(ms))
+    plan = [p for k, p in ops._PLAN_CACHE.items() if k[0] == "trellis_shards"][0]
+    assert plan.launches == 1
+    col = 0
+    for (p1, su, ws, W), (su_t, p_t, _, _, _, m) in zip(layers, dev):
+        ref = O.linear_forward(x_t.float().cpu().numpy(), W, su, sv, ws)
+        assert relerr(y[:, col:col + m].cpu().numpy(), ref) <= TOL
+        single = ops.fused_linear_trellis_3inst(x_t, sv_t, su_t, p_t, None, None, None, None, ws, n, m, n, m,
+                                                out_dtype=torch.float32)
+        assert torch.equal(single, y[:, col:col + m])
+        col += m
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        yg = ops.fused_linear_trellis_3inst_shards(x_t, sv_t, dev, out_dtype=torch.float32)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(yg, y)
+    ops.clear_caches()
 
 
 def test_trellis_more_than_64_tokens(ops):
