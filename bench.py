@@ -495,28 +495,35 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
     h0 = torch.randn(1, hidden, device=dev, generator=torch.Generator(device=dev).manual_seed(5)).to(torch.bfloat16)
     world = D.world
 
-    def lin(L, x, dt=None):
+    norm1 = [torch.ones(hidden, device=dev, dtype=torch.bfloat16) for _ in Ls]
+    norm2 = [torch.ones(hidden, device=dev, dtype=torch.bfloat16) for _ in Ls]
+
+    def lin(L, x, **kw):
         return ops.fused_linear_trellis_3inst(x, L.sv, L.su, L.codes[0], None, None, None, None, L.wscale,
-                                              L.n, L.m, L.n, L.m, out_dtype=dt)
+                                              L.n, L.m, L.n, L.m, **kw)
 
-    def shards(x, group):
-        return ops.fused_linear_trellis_3inst_shards(x, group[0].sv, [(L.su, L.codes[0], None, L.wscale, 0.0, L.m) for L in group])
+    def shards(x, group, norm_w):
+        return ops.fused_linear_trellis_3inst_shards(x, group[0].sv, [(L.su, L.codes[0], None, L.wscale, 0.0, L.m) for L in group],
+                                                     in_norm_weight=norm_w, in_norm_eps=1e-6)
 
-    def forward(h):
-        for d in Ls:
-            qkv = shards(h, (d["q"], d["k"], d["v"]))                     # one launch for the three shards
-            a = qkv[:, :d["q"].m]                                         # attention stand-in: a view, (1, 2048 / world)
-            o = lin(d["o"], a, torch.float32 if world > 1 else None)
-            if world > 1:
+    def forward(h0_):
+        h = h0_.clone()
+        for d, w1, w2 in zip(Ls, norm1, norm2):
+            qkv = shards(h, (d["q"], d["k"], d["v"]), w1)             # RMSNorm + q/k/v: one launch
+            a = qkv[:, :d["q"].m]                                     # attention stand-in: a view, (1, 2048 / world)
+            if world == 1:
+                lin(d["o"], a, accumulate_into=h)                     # o projection + residual add: one launch
+            else:
+                o = lin(d["o"], a, out_dtype=torch.float32)
                 dist.all_reduce(o)
-            h = torch.add(h, o.to(h.dtype)) if world > 1 else torch.add(h, o)
-            gu = shards(h, (d["gate"], d["up"]))
-            mg = d["gate"].m
-            act = torch.nn.functional.silu(gu[:, :mg]) * gu[:, mg:]
-            dn = lin(d["down"], act, torch.float32 if world > 1 else None)
-            if world > 1:
+                h.add_(o.to(h.dtype))
+            gu = shards(h, (d["gate"], d["up"]), w2)                  # RMSNorm + gate/up: one launch
+            if world == 1:
+                lin(d["down"], gu, gated_act=0, accumulate_into=h)    # silu(gate) * up + down + residual: one launch
+            else:
+                dn = lin(d["down"], gu, gated_act=0, out_dtype=torch.float32)
                 dist.all_reduce(dn)
-            h = torch.add(h, dn.to(h.dtype) if world > 1 else dn, alpha=0.05)
+                h.add_(dn.to(h.dtype))
         return h
 
     for _ in range(3):
@@ -547,16 +554,16 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
     rec = {"workload": "decode_chain", "metric": METRIC, "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": world,
            "us_per_layer": ms * 1e3 / n_layers, "us_per_linear": ms * 1e3 / (7 * n_layers),
            "config": f"{n_layers} SmolLM3-3B decoder layers, trellis 4 bpw, batch 1, every projection consumes the previous "
-                     f"output through glq_b200.ops, q/k/v and gate/up as one call each "
-                     f"({'one CUDA graph' if graph is not None else 'eager launches'}; between the linears: a residual add, "
-                     f"silu(gate) * up and a stand-in for attention as torch kernels); "
+                     f"output through glq_b200.ops: per layer RMSNorm + q/k/v, o + residual, RMSNorm + gate/up, "
+                     f"silu(gate) * up + down + residual as four calls (attention replaced by a view of the q output; "
+                     f"{'one CUDA graph' if graph is not None else 'eager launches'}); "
                      f"{total_bytes / 1e6:.0f} MB of codes per step, larger than L2"
                      + (f"; tp{world}: fp32 all-reduce after o and down" if world > 1 else ""),
            "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h0.numel() * 2,
                    "d2h_bytes_per_step": out.numel() * 2},
            "gpu_launches": glq_launches * steps, "glq_launches_per_layer": glq_launches / n_layers,
-           "roofline": {"bound": "hbm", "kernel": "whole chain (4 trellis_fused_kernel<4,0> launches per layer for its 7 linears, "
-                                                  "plus the elementwise kernels between them)",
+           "roofline": {"bound": "hbm", "kernel": "whole chain: 4 trellis_fused_kernel<4,0> launches per layer for its 7 linears, norms, "
+                                                  "activation and residual adds",
                         "achieved": gbs / world, "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s",
                         "frac": gbs / world / hbm, "kernel_ms": ms, "bytes_per_launch": code_bytes, "traffic": None}}
     del graph

@@ -71,6 +71,8 @@ class LinearDesc(C.Structure):
         ("x_stride", C.c_int64), ("y_stride", C.c_int64),
         ("x_offset", C.c_int64), ("y_offset", C.c_int64),
         ("stop_at_yrht", C.c_int32), ("x_is_rotated", C.c_int32),
+        ("in_norm_weight", C.c_void_p), ("in_norm_dtype", C.c_int32), ("in_norm_eps", C.c_float),
+        ("in_gated_act", C.c_int32), ("y_accumulate", C.c_int32),
     ]
 
 

@@ -127,7 +127,9 @@ static bool fused_enabled() {
 }
 // do two layers read the same transformed input?
 static bool same_input(const GlqbLinearDesc& a, const GlqbLinearDesc& b) {
-  return a.format == b.format && a.n_pad == b.n_pad && a.in_features == b.in_features && a.sv == b.sv &&
+  return a.in_norm_weight == b.in_norm_weight && a.in_norm_dtype == b.in_norm_dtype && a.in_norm_eps == b.in_norm_eps &&
+         a.in_gated_act == b.in_gated_act &&
+         a.format == b.format && a.n_pad == b.n_pad && a.in_features == b.in_features && a.sv == b.sv &&
          a.batch == b.batch && a.x_offset == b.x_offset && a.x_stride == b.x_stride && a.x_dtype == b.x_dtype &&
          a.x_is_rotated == b.x_is_rotated && a.n_blocks_n == b.n_blocks_n &&
          memcmp(a.blocks_n, b.blocks_n, sizeof(int32_t) * a.n_blocks_n) == 0;
@@ -272,6 +274,12 @@ static int validate(const GlqbLinearDesc& d, int idx) {
     return fail(GLQB_E_INVALID, "layer %d: dtype", idx);
   if (d.stop_at_yrht && d.y_dtype != GLQB_DT_F32)
     return fail(GLQB_E_INVALID, "layer %d: rotated-domain output must be fp32", idx);
+  if (d.in_gated_act < 0 || d.in_gated_act > 3 || (d.in_norm_weight && (d.in_norm_dtype < 0 || d.in_norm_dtype > 2)))
+    return fail(GLQB_E_INVALID, "layer %d: input activation code %d / norm weight dtype %d", idx, d.in_gated_act, d.in_norm_dtype);
+  if ((d.in_gated_act || d.in_norm_weight) && d.x_is_rotated)
+    return fail(GLQB_E_INVALID, "layer %d: input fusions need an untransformed input", idx);
+  if (d.y_accumulate && d.stop_at_yrht)
+    return fail(GLQB_E_INVALID, "layer %d: the residual add applies to the final output only", idx);
   return GLQB_OK;
 }
 
@@ -365,6 +373,8 @@ static int build_plan(GlqbPlan* P) {
     L.n_stages = d.n_stages;
     L.batch = d.batch; L.x_dtype = d.x_dtype; L.y_dtype = d.y_dtype; L.stop_at_yrht = d.stop_at_yrht; L.x_is_rotated = d.x_is_rotated;
     L.x_stride = d.x_stride; L.y_stride = d.y_stride; L.x_off = d.x_offset; L.y_off = d.y_offset;
+    L.in_norm_w = d.in_norm_weight; L.in_norm_dtype = d.in_norm_dtype; L.in_norm_eps = d.in_norm_eps;
+    L.in_gated_act = d.in_gated_act; L.y_accumulate = d.y_accumulate;
     L.nbn = d.n_blocks_n; L.nbm = d.n_blocks_m;
     int off = 0;
     for (int i = 0; i < d.n_blocks_n; ++i) {
@@ -554,6 +564,13 @@ static int build_plan(GlqbPlan* P) {
   for (const Segment& s : P->segs)
     if (s.fused)
       for (int i = 0; i < s.count; ++i) layer_fused[s.first + i] = 1;
+  for (int pos = 0; pos < n; ++pos) {
+    const GlqbLinearDesc& d = P->descs[P->order[pos]];
+    if (!layer_fused[pos] && (d.in_norm_weight || d.in_gated_act || d.y_accumulate))
+      return fail(GLQB_E_INVALID,
+                  "layer %d: the fused norm / activation / residual steps are served by the single-launch decode form only "
+                  "(trellis, at most %d tokens, all layers of the call reading one input)", P->order[pos], FUSED_MAX_TOKENS);
+  }
   for (int pos = 0; pos < n; ++pos) {
     DevLinear& L = P->dev[pos];
     const GlqbLinearDesc& d = P->descs[P->order[pos]];

@@ -315,4 +315,128 @@ __device__ __forceinline__ void fht_tile8(float* smem, int logbs, int rows, Load
   }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Low-latency transform of ONE array of 32 .. 8192 values by a 256-thread CTA, for the single-launch decode
+// kernel where the transform sits on the critical path of a few-microsecond kernel: one round of global
+// loads, one shared-memory exchange, one __syncthreads.
+//   thread t holds E = max(1, bs / 256) consecutive values (index t * E + j): stages 0 .. log2(E) - 1 run in
+//   registers, the next five across the lanes of a warp with shuffles, the last log2(W) (W = warps holding the
+//   array, at most 8) after an exchange through shared memory, where a thread gathers the W values that differ
+//   in the warp bits, finishes the butterflies and hands every finished value to `store(i, value)`; for a fixed
+//   call of `store` the lanes of a warp hold consecutive i.
+// Same butterflies in the same (ascending) order as fht_tile, so the results are bit-identical to it.
+// `smem` needs bs + bs / 32 floats.  All 256 threads must call; `load(i0, v)` fills v[0..E) with values
+// i0 .. i0 + E - 1.
+// ---------------------------------------------------------------------------------------------------
+template <int E, class Load, class Pre, class Store>
+__device__ __forceinline__ void fht_fast_e(float* smem, int logbs, Load& load, Pre& pre, Store& store) {
+  constexpr int LOGE = E == 1 ? 0 : E == 2 ? 1 : E == 4 ? 2 : E == 8 ? 3 : E == 16 ? 4 : 5;
+  constexpr int QMAX = E >= 8 ? E / 8 : 1;         // rounds of the final loop (values per warp / 256)
+  const int bs = 1 << logbs;
+  const int t = threadIdx.x, lane = t & 31;
+  const int nthreads = bs >> LOGE;                 // threads that hold values (32 .. 256)
+  const int W = nthreads >> 5;                     // warps that hold values (1 .. 8)
+  const bool active = t < nthreads;
+  const int span = 32 << LOGE;                     // values per warp = distance between the W partners
+  // What `store` needs besides the transformed value (a sign, the old output, ...) is requested first by
+  // `pre(i)`, for exactly the indices this thread will store, so that it arrives while the transform runs.
+  float aux[QMAX][8];
+  if (W == 1) {
+    if (active) {
+#pragma unroll
+      for (int j = 0; j < E; ++j) aux[0][j] = pre(t * E + j);        // E <= 1 here (32 values, one warp)
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < QMAX; ++q) {
+      const int r = t + 256 * q;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) aux[q][w] = (r < span && w < W) ? pre(w * span + r) : 0.f;
+    }
+  }
+  float v[E];
+  if (active) {
+    load(t * E, v);
+    fht_regs<LOGE>(v);
+#pragma unroll
+    for (int k = 0; k < 5; ++k) {
+      const bool upper = (lane >> k) & 1;
+#pragma unroll
+      for (int j = 0; j < E; ++j) {
+        const float p = __shfl_xor_sync(0xffffffffu, v[j], 1 << k);
+        v[j] = upper ? (p - v[j]) : (v[j] + p);    // lower index: a + b, upper index: a - b (a = lower element)
+      }
+    }
+  }
+  if (W == 1) {
+    if (active) {
+#pragma unroll
+      for (int j = 0; j < E; ++j) store(t * E + j, v[j], aux[0][j]);
+    }
+    return;
+  }
+  if (active) {
+#pragma unroll
+    for (int j = 0; j < E; ++j) smem[fht_pad(t * E + j)] = v[j];
+  }
+  __syncthreads();
+  const int logw = W == 2 ? 1 : W == 4 ? 2 : 3;
+#pragma unroll
+  for (int q = 0; q < QMAX; ++q) {
+    const int r = t + 256 * q;
+    if (r < span) {
+      float u[8];
+#pragma unroll
+      for (int w = 0; w < 8; ++w) u[w] = w < W ? smem[fht_pad(w * span + r)] : 0.f;
+      if (logw == 1) {
+        const float a = u[0], b = u[1];
+        u[0] = a + b; u[1] = a - b;
+      } else if (logw == 2) {
+        float h[4] = {u[0], u[1], u[2], u[3]};
+        fht_regs<2>(h);
+        u[0] = h[0]; u[1] = h[1]; u[2] = h[2]; u[3] = h[3];
+      } else {
+        fht_regs<3>(u);
+      }
+#pragma unroll
+      for (int w = 0; w < 8; ++w)
+        if (w < W) store(w * span + r, u[w], aux[q][w]);
+    }
+  }
+}
+
+// dispatch on the array length (2^logbs, 32 .. 8192)
+template <class Load1, class Load4, class Pre, class Store>
+__device__ __forceinline__ void fht_fast(float* smem, int logbs, Load1 load1, Load4 load4, Pre pre, Store store) {
+  // load1(i) -> value i;  load4(i0, float (&q)[4]) -> values i0 .. i0 + 3 (i0 a multiple of 4);
+  // pre(i) -> float handed back to store(i, value, that float)
+  auto ld1 = [&](int i0, float (&v)[1]) { v[0] = load1(i0); };
+  auto ld2 = [&](int i0, float (&v)[2]) { v[0] = load1(i0); v[1] = load1(i0 + 1); };
+  auto ld4 = [&](int i0, float (&v)[4]) { load4(i0, v); };
+  auto ld8 = [&](int i0, float (&v)[8]) {
+    float q[4];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) { load4(i0 + 4 * k, q); v[4 * k] = q[0]; v[4 * k + 1] = q[1]; v[4 * k + 2] = q[2]; v[4 * k + 3] = q[3]; }
+  };
+  auto ld16 = [&](int i0, float (&v)[16]) {
+    float q[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { load4(i0 + 4 * k, q); v[4 * k] = q[0]; v[4 * k + 1] = q[1]; v[4 * k + 2] = q[2]; v[4 * k + 3] = q[3]; }
+  };
+  auto ld32 = [&](int i0, float (&v)[32]) {
+    float q[4];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) { load4(i0 + 4 * k, q); v[4 * k] = q[0]; v[4 * k + 1] = q[1]; v[4 * k + 2] = q[2]; v[4 * k + 3] = q[3]; }
+  };
+  switch (logbs) {
+    case 9: fht_fast_e<2>(smem, logbs, ld2, pre, store); break;
+    case 10: fht_fast_e<4>(smem, logbs, ld4, pre, store); break;
+    case 11: fht_fast_e<8>(smem, logbs, ld8, pre, store); break;
+    case 12: fht_fast_e<16>(smem, logbs, ld16, pre, store); break;
+    case 13: fht_fast_e<32>(smem, logbs, ld32, pre, store); break;
+    default: fht_fast_e<1>(smem, logbs, ld1, pre, store); break;      // 32 .. 256 values
+  }
+}
+constexpr int FHT_FAST_MAX_LOG = 13;
+
 }  // namespace glqb

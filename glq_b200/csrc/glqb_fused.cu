@@ -1,5 +1,7 @@
 // Instantiations and launches of the single-launch decode kernels (trellis_fused_kernel, glqb_kernels.cuh).
 #include "glqb_kernels.cuh"
+#include <cstdlib>
+
 #include "glqb_launch.h"
 
 namespace glqb {
@@ -24,8 +26,22 @@ cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* r
 
 void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_base, uint8_t* y_base, uint8_t* ws,
                   int* tickets, cudaStream_t stream) {
-  trellis_fused_pick(s.k1, s.k2)<<<s.grid, MV_THREADS, s.fused_smem, stream>>>(layers, s.count, s.total_units, s.scratch_elems,
-                                                                               x_base, y_base, ws, tickets);
+  // Launched with programmatic stream serialization: when the previous kernel of the stream is another
+  // single-launch decode kernel, this one's prologue (scheduling, table reads, the first weight loads) overlaps
+  // its tail; the kernel itself waits (griddepcontrol.wait) before it reads activations or writes anything.
+  static const bool pdl = [] { const char* e = getenv("GLQB_PDL"); return !e || atoi(e) != 0; }();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)s.grid);
+  cfg.blockDim = dim3(MV_THREADS);
+  cfg.dynamicSmemBytes = s.fused_smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, trellis_fused_pick(s.k1, s.k2), layers, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
+                     tickets);
 }
 
 }  // namespace glqb

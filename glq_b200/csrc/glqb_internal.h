@@ -34,6 +34,11 @@ struct DevLinear {
   int fixed_slots;       // > 0: every strip has exactly this many partial sums (GEMM path: K splits)
   int gemm_tn;           // token tile of the GEMM path (0: streaming decode path)
   int ticket_base;       // single-launch form: first completion ticket of this layer (one per output Hadamard block)
+  const void* in_norm_w; // optional fusions (single-launch form): RMSNorm weight, its dtype and epsilon,
+  int in_norm_dtype;     // gated activation of a [gate | up] input (0 none, 1 + GLQB_ACT_*), residual accumulate
+  float in_norm_eps;
+  int in_gated_act;
+  int y_accumulate;
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];

@@ -61,6 +61,23 @@ __device__ __forceinline__ bool act_rows_aligned4(const void* base, long long of
   return ((off | stride) & 3) == 0 && (reinterpret_cast<uintptr_t>(base) & (4 * es - 1)) == 0;
 }
 
+// value after a round trip through the activation dtype (what a separate kernel would have stored)
+__device__ __forceinline__ float round_act(float v, int dtype) {
+  if (dtype == GLQB_DT_F16) return __half2float(__float2half_rn(v));
+  if (dtype == GLQB_DT_BF16) return __bfloat162float(__float2bfloat16_rn(v));
+  return v;
+}
+// gated / plain activations of the MoE ops and of the fused decode input (GLQB_ACT_*)
+__device__ __forceinline__ float act_fn(float g, int act) {
+  if (act == GLQB_ACT_SILU) return g / (1.0f + __expf(-g));
+  if (act == GLQB_ACT_GELU_TANH) {
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.0f + tanhf(u));
+  }
+  const float r = fmaxf(g, 0.f);
+  return r * r;
+}
+
 // streaming 128/64/32-bit loads of weight codes: read once, keep out of L1
 __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
   uint4 v;
@@ -311,7 +328,7 @@ __device__ __forceinline__ void rht_out_body(const DevLinear& L, const RhtItem i
   auto store8 = [&](int trow, int i0, const float (&v)[8], int count) {
     const int row0 = off + i0;
     const long long o = y_off + (long long)(tok0 + trow) * y_stride + row0;
-    if (count == 8 && row0 + 8 <= out_f && su_vec && y_vec && (o & 7) == 0) {
+    if (count == 8 && row0 + 8 <= out_f && su_vec && y_vec && (o & 7) == 0 && !L.y_accumulate) {
       const uint4 s4 = *reinterpret_cast<const uint4*>(su + row0);
       const float2 s0 = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
       const float2 s1 = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
@@ -339,7 +356,11 @@ __device__ __forceinline__ void rht_out_body(const DevLinear& L, const RhtItem i
     } else {
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        if (k < count && row0 + k < out_f) store_act(y_base, o + k, y_dtype, v[k] * rs * __half2float(su[row0 + k]));
+        if (k < count && row0 + k < out_f) {
+          float r = v[k] * rs * __half2float(su[row0 + k]);
+          if (L.y_accumulate) r += load_act(y_base, o + k, y_dtype);          // residual add
+          store_act(y_base, o + k, y_dtype, r);
+        }
     }
   };
   fht_tile8(fbuf, logbs, it.ntok, load32, load1, store8);
@@ -610,6 +631,57 @@ __host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, in
   return (size_t)batch * n * 4 + ((size_t)scratch_elems + scratch_elems / 32) * 4 + 8 * 256 * 4 + 64;
 }
 
+// Output transform of one (layer, Hadamard block, token) with the low-latency transform; same arithmetic
+// as rht_out_body.  Blocks of up to 8192 values.
+__device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int tok, const uint8_t* __restrict__ ws,
+                                                uint8_t* __restrict__ y_base, float* fbuf) {
+  const int off = L.bm_off[b], logbs = L.bm_log[b];
+  const int m = L.m, cnt = L.fixed_slots, out_f = L.out_f, y_dtype = L.y_dtype;
+  const long long slot_stride = (long long)L.batch * m;
+  const float wscale = L.wscale;
+  const float* row_scale = L.row_scale;
+  const float* part = reinterpret_cast<const float*>(ws + L.part_off) + (long long)tok * m + off;
+  const float rs = rsqrtf((float)(1 << logbs));
+  const __half* su = L.su + off;
+  const long long yo = L.y_off + (long long)tok * L.y_stride + off;
+  auto load1 = [&](int i) -> float {
+    float s = 0.f;
+    for (int k = 0; k < cnt; ++k) s += __ldcg(part + i + k * slot_stride);
+    s *= wscale;
+    if (row_scale) s *= row_scale[off + i];
+    return s;
+  };
+  auto load4 = [&](int i0, float (&q)[4]) {
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < cnt; ++k) {
+      const float4 t = __ldcg(reinterpret_cast<const float4*>(part + i0 + k * slot_stride));
+      s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+    }
+    q[0] = s.x * wscale; q[1] = s.y * wscale; q[2] = s.z * wscale; q[3] = s.w * wscale;
+    if (row_scale) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) q[k] *= row_scale[off + i0 + k];
+    }
+  };
+  if (L.stop_at_yrht) {            // rotated-domain result wanted: reduce and scale only
+    for (int i = threadIdx.x; i < (1 << logbs); i += blockDim.x)
+      reinterpret_cast<float*>(y_base)[yo + i] = load1(i);
+    return;
+  }
+  // the sign (and, for a residual add, the old output) are requested before the partial sums; the old output
+  // travels in the same float as sign * 2^k would not be exact, so it is fetched in `store` when needed
+  const bool accumulate = L.y_accumulate != 0;
+  auto pre = [&](int i) -> float { return __half2float(su[i]); };
+  auto store = [&](int i, float val, float sign) {
+    if (off + i < out_f) {
+      float r = val * rs * sign;
+      if (accumulate) r += load_act(y_base, yo + i, y_dtype);
+      store_act(y_base, yo + i, y_dtype, r);
+    }
+  };
+  fht_fast(fbuf, logbs, load1, load4, pre, store);
+}
+
 template <int K1, int K2>
 __global__ void __launch_bounds__(MV_THREADS, 2)
 trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int total_units, int scratch_elems,
@@ -624,78 +696,154 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
   __shared__ int todo[FUSED_MAX_TODO];
   __shared__ int n_todo;
   if (threadIdx.x == 0) n_todo = 0;
-
-  // ---- phase 1: input transform of the shared input, token by token, block by block
-  {
-    const bool vec_ok = act_rows_aligned4(x_base, L0.x_off, L0.x_stride, L0.x_dtype);
-    for (int b = 0; b < L0.nbn; ++b) {
-      const int off = L0.bn_off[b], logbs = L0.bn_log[b];
-      const float rs = rsqrtf((float)(1 << logbs));
-      const bool vok = vec_ok && (off & 3) == 0;
-      for (int tok = 0; tok < batch; ++tok) {
-        auto store1 = [&](int, int i, float val) {
-          const int col = off + i;
-          const int pos = (col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31);      // half index, even
-          xs[((size_t)tok * n * XR_TRELLIS_EXPAND + pos) >> 1] = __halves2half2(__float2half_rn(val * rs), __float2half_rn(0.f));
-        };
-        auto load1 = [&](int, int i) -> float {
-          const int col = off + i;
-          return load_act(x_base, L0.x_off + (long long)tok * L0.x_stride + col, L0.x_dtype) * __half2float(L0.sv[col]);
-        };
-        auto load32 = [&](int, int i0, float (&v)[32]) { rht_load_x32(L0, x_base, tok, off + i0, vok, v); };
-        fht_tile(fbuf, logbs, 1, load32, load1, store1);
-        __syncthreads();
-      }
-    }
-  }
-  __syncthreads();
-
-  // ---- phase 2: work units
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int gq = lane >> 2, tq = lane & 3;
-  const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
-  for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+
+  // position of work unit u: layer, strip, chunk, this warp's first group and group count
+  struct Unit { int li, strip, chunk, c0, ng; };
+  auto locate = [&](int u) -> Unit {
     int li = 0;
     while (li + 1 < n_layers && layers[li + 1].group_base <= u) ++li;
     const DevLinear& L = layers[li];
     const int kch = L.fixed_slots;                          // chunks (= partial sums) per strip
     const int local = u - (int)L.group_base;
     const int strip = local / kch, chunk = local - strip * kch;
-    const int gps = L.groups_per_strip;
     const int c0 = chunk * FUSED_CHUNK_GROUPS + warp * 8;
-    const int ng = max(0, min(8, gps - c0));
+    return Unit{li, strip, chunk, c0, max(0, min(8, L.groups_per_strip - c0))};
+  };
+  // the stage-1 codes of a unit: all of a warp's (up to eight) groups in flight at once
+  auto fetch = [&](const Unit& U, Words<K1> (&w1)[8]) {
+    const DevLinear& L = layers[U.li];
+    const uint8_t* p1 = L.codes[0] + ((long long)U.strip * L.groups_per_strip + U.c0) * (128 * K1) + lane * (4 * K1);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < U.ng) w1[i] = load_words<K1>(p1 + i * (128 * K1));
+  };
+
+  // The codes do not depend on the activations: request the first unit's before the input transform, so the
+  // trip to HBM overlaps it.
+  int u = blockIdx.x;
+  Unit U = locate(min(u, total_units - 1));
+  Words<K1> w1[8];
+  if (u < total_units) fetch(U, w1);
+  // Programmatic dependent launch: let the next kernel of the stream start its own prologue, and wait here for
+  // the previous kernel (which may have produced x) to finish.  Everything above reads only weights and the
+  // plan's table.  Both are no-ops when the launch did not ask for the overlap.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  // ---- phase 1: input transform of the shared input, token by token, block by block
+  {
+    const int x_dtype = L0.x_dtype, in_f = L0.in_f;
+    const int gact = L0.in_gated_act;                        // 0, or 1 + activation code: x rows are [gate | up]
+    const void* nw = L0.in_norm_w;
+    const bool plain = gact == 0 && nw == nullptr;
+    const bool vec_ok = plain && act_rows_aligned4(x_base, L0.x_off, L0.x_stride, x_dtype);
+    const __half* sv = L0.sv;
+    for (int tok = 0; tok < batch; ++tok) {
+      const long long xt0 = L0.x_off + (long long)tok * L0.x_stride;
+      // raw input value of column `col`, before the sign: x, act(gate) * up, or the RMS-normalised x
+      float rstd = 1.f;
+      auto raw = [&](int col) -> float {
+        float v = load_act(x_base, xt0 + col, x_dtype);
+        if (gact) v = round_act(round_act(act_fn(v, gact - 1), x_dtype) * load_act(x_base, xt0 + in_f + col, x_dtype), x_dtype);
+        return v;
+      };
+      if (nw) {                                              // mean of squares over the token, then 1 / sqrt(. + eps)
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < in_f; i += blockDim.x) { const float v = raw(i); ss += v * v; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < MV_WARPS; ++w) tot += red[w];
+        rstd = rsqrtf(tot / (float)in_f + L0.in_norm_eps);
+        __syncthreads();
+      }
+      const int nw_dtype = L0.in_norm_dtype;
+      auto load1 = [&](int i_abs) -> float {                 // absolute column
+        float v = raw(i_abs);
+        if (nw) v = round_act(load_act(nw, i_abs, nw_dtype) * round_act(v * rstd, x_dtype), x_dtype);
+        return v * __half2float(sv[i_abs]);
+      };
+      for (int b = 0; b < L0.nbn; ++b) {
+        const int off = L0.bn_off[b], logbs = L0.bn_log[b];
+        const float rs = rsqrtf((float)(1 << logbs));
+        const bool vok = vec_ok && (off & 3) == 0;
+        __half2* xt = xs + (size_t)tok * n;                  // n half2 per token
+        auto none = [](int) -> float { return 0.f; };
+        auto put = [&](int i, float val, float = 0.f) {
+          const int col = off + i;
+          xt[((col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31)) >> 1] =
+              __halves2half2(__float2half_rn(val * rs), __float2half_rn(0.f));
+        };
+        auto ld1 = [&](int i) -> float { return load1(off + i); };
+        if (logbs <= FHT_FAST_MAX_LOG) {
+          auto load4 = [&](int i0, float (&q)[4]) {
+            if (vok) {
+              load_act4(x_base, xt0 + off + i0, x_dtype, q);
+              const uint2 s4 = *reinterpret_cast<const uint2*>(sv + off + i0);
+              const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+              const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+              q[0] *= a.x; q[1] *= a.y; q[2] *= c.x; q[3] *= c.y;
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) q[k] = load1(off + i0 + k);
+            }
+          };
+          fht_fast(fbuf, logbs, ld1, load4, none, put);
+        } else {
+          auto store1 = [&](int, int i, float val) { put(i, val); };
+          auto l1 = [&](int, int i) -> float { return load1(off + i); };
+          auto load32 = [&](int, int i0, float (&v)[32]) {
+            if (plain) { rht_load_x32(L0, x_base, tok, off + i0, vok, v); return; }
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = load1(off + i0 + k);
+          };
+          fht_tile(fbuf, logbs, 1, load32, l1, store1);
+        }
+        __syncthreads();
+      }
+    }
+  }
+
+  // ---- phase 2: work units
+  const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
+  while (u < total_units) {
+    const DevLinear& L = layers[U.li];
+    const int kch = L.fixed_slots, strip = U.strip, chunk = U.chunk, ng = U.ng, c0 = U.c0;
+    const int gps = L.groups_per_strip;
     float acc[1][2][4], acc2[1][2][4];
 #pragma unroll
     for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
       for (int i = 0; i < 4; ++i) { acc[0][mi][i] = 0.f; acc2[0][mi][i] = 0.f; }
     if (ng > 0) {
-      const uint8_t* p1 = L.codes[0] + ((long long)strip * gps + c0) * (128 * K1) + lane * (4 * K1);
-      const uint8_t* p2 = nullptr;
-      if constexpr (K2 > 0) p2 = L.codes[1] + ((long long)strip * gps + c0) * (128 * K2) + lane * (4 * K2);
+      Words<(K2 > 0 ? K2 : 1)> w2[8];
+      if constexpr (K2 > 0) {
+        const uint8_t* p2 = L.codes[1] + ((long long)strip * gps + c0) * (128 * K2) + lane * (4 * K2);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < ng) w2[i] = load_words<K2>(p2 + i * (128 * K2));
+      }
       const int token = min(gq, batch - 1);                 // columns past the batch repeat the last token
       const uint32_t xa = xs_addr + (uint32_t)((((size_t)token * n + (size_t)c0 * 32) * XR_TRELLIS_EXPAND + tq * 16) * 2);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {                         // two rounds of four groups: all codes of a round in flight
-        Words<K1> w1[4];
-        Words<(K2 > 0 ? K2 : 1)> w2[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (h * 4 + i < ng) {
-            w1[i] = load_words<K1>(p1 + (h * 4 + i) * (128 * K1));
-            if constexpr (K2 > 0) w2[i] = load_words<K2>(p2 + (h * 4 + i) * (128 * K2));
-          }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (h * 4 + i < ng) {                             // uniform per warp: the shuffles inside see all lanes
-            uint4 xb[1][2];
-            xb[0][0] = lds_v4(xa + (h * 4 + i) * 128);      // 64 halfs = 128 bytes per group
-            xb[0][1] = lds_v4(xa + (h * 4 + i) * 128 + 16);
-            group_mma<K1, 1>(w1[i], lane, xb, acc);
-            if constexpr (K2 > 0) group_mma<K2, 1>(w2[i], lane, xb, acc2);
-          }
-      }
+      for (int i = 0; i < 8; ++i)
+        if (i < ng) {                                       // uniform per warp: the shuffles inside see all lanes
+          uint4 xb[1][2];
+          xb[0][0] = lds_v4(xa + i * 128);                  // 64 halfs = 128 bytes per group
+          xb[0][1] = lds_v4(xa + i * 128 + 16);
+          group_mma<K1, 1>(w1[i], lane, xb, acc);
+          if constexpr (K2 > 0) group_mma<K2, 1>(w2[i], lane, xb, acc2);
+        }
     }
+    // next unit of this CTA: its codes travel while this one is reduced
+    const int li_now = U.li;
+    u += gridDim.x;
+    if (u < total_units) { U = locate(u); fetch(U, w1); }
     {
       const float s2 = L.stage_scale[1];
 #pragma unroll
@@ -717,23 +865,21 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
       const int mi = f >> 2, i = f & 3;
       const int row = strip * 32 + mi * 16 + (ln >> 2) + ((i >> 1) ? 8 : 0);
       const int token = (ln & 3) * 2 + (i & 1);
-      if (token < batch) {
-        reinterpret_cast<float*>(ws + L.part_off)[((long long)chunk * batch + token) * L.m + row] = s;
-        __threadfence();
-      }
+      if (token < batch) reinterpret_cast<float*>(ws + L.part_off)[((long long)chunk * batch + token) * L.m + row] = s;
     }
-    __syncthreads();
+    __syncthreads();                                        // the partial sums of the unit are written (and `red` is free)
     if (threadIdx.x == 0) {
       // which Hadamard block of the output holds this strip, and how many units make it complete
       int b = 0;
       while (b + 1 < L.nbm && strip * 32 >= L.bm_off[b + 1]) ++b;
       const int need = ((1 << L.bm_log[b]) >> 5) * kch;
-      __threadfence();
-      const int old = atomicAdd(&tickets[L.ticket_base + b], 1);
+      // release (the CTA's stores, ordered before this by the barrier) and acquire (the other CTAs' stores,
+      // released before their increments) in one device-scope atomic
+      int old;
+      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(tickets + L.ticket_base + b) : "memory");
       if (old + 1 == need) {
-        tickets[L.ticket_base + b] = 0;                                 // ready for the next run
-        __threadfence();
-        if (n_todo < FUSED_MAX_TODO) todo[n_todo++] = (li << 8) | b;
+        tickets[L.ticket_base + b] = 0;                     // ready for the next run
+        if (n_todo < FUSED_MAX_TODO) todo[n_todo++] = (li_now << 8) | b;
       }
     }
   }
@@ -744,11 +890,18 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
   for (int k = 0; k < nt; ++k) {
     const int li = todo[k] >> 8, b = todo[k] & 255;
     const DevLinear& L = layers[li];
-    const int bs = 1 << L.bm_log[b];
-    const int tt = max(1, min(batch, scratch_elems / bs));
-    for (int t0 = 0; t0 < batch; t0 += tt) {
-      rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0)}, ws, y_base, nullptr, fbuf);
-      __syncthreads();
+    if (L.bm_log[b] <= FHT_FAST_MAX_LOG) {
+      for (int tok = 0; tok < batch; ++tok) {
+        fused_out_block(L, b, tok, ws, y_base, fbuf);
+        __syncthreads();
+      }
+    } else {
+      const int bs = 1 << L.bm_log[b];
+      const int tt = max(1, min(batch, scratch_elems / bs));
+      for (int t0 = 0; t0 < batch; t0 += tt) {
+        rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0)}, ws, y_base, nullptr, fbuf);
+        __syncthreads();
+      }
     }
   }
 }

@@ -137,7 +137,7 @@ def clear_caches() -> None:
 
 
 def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_tokens=DECODE_MAX_TOKENS,
-                y_offset: int = 0, out_cols: Optional[int] = None) -> None:
+                y_offset: int = 0, out_cols: Optional[int] = None, accumulate: bool = False) -> None:
     """Run a single-layer op over x2d (B, in) into out[:, y_offset : y_offset + out_cols].  Up to 64 tokens go
     through the streaming kernels in slices of <= max_tokens, more through one tensor-core plan; token counts
     are rounded up to ``token_bucket`` sizes (zero-padded copy in, extra rows dropped)."""
@@ -152,6 +152,8 @@ def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_t
             xin = xs.new_zeros((bb, xs.shape[1]))
             xin[:b] = xs
             yout, yoff = torch.empty((bb, cols), dtype=out.dtype, device=out.device), 0
+            if accumulate:
+                yout[:b] = dst_rows[:b, y_offset:y_offset + cols]
         key = key_base + (bb, xin.dtype, yout.dtype, xin.stride(0), yout.stride(0), yoff)
         plan = _cached_plan(key, lambda: [make_spec(bb, xin.stride(0), yout.stride(0), yoff)])
         plan.run(xin, yout, workspace=shared_workspace(xin.device, plan.workspace_bytes))
@@ -175,17 +177,53 @@ def _trellis_bits(packed: torch.Tensor) -> int:
     return packed.shape[-1] // 16
 
 
+FUSED_MAX_TOKENS = 8        # the single-launch decode form, which also serves the fused norm / activation / residual
+
+
+def _apply_input_steps(x2d, in_features, in_norm_weight, in_norm_eps, gated_act):
+    """The steps the single-launch form fuses, as separate torch kernels (more than 8 tokens)."""
+    if gated_act is not None:
+        g, u = x2d[:, :in_features], x2d[:, in_features:2 * in_features]
+        a = (torch.nn.functional.silu(g) if gated_act == 0 else
+             torch.nn.functional.gelu(g, approximate="tanh") if gated_act == 1 else torch.relu(g).square())
+        x2d = a * u
+    if in_norm_weight is not None:
+        xf = x2d.float()
+        xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + in_norm_eps)).to(x2d.dtype)
+        x2d = (in_norm_weight.to(x2d.dtype) * xn)
+    return x2d.contiguous()
+
+
 def _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_rs2, in_features,
-                   out_features, n_pad, m_pad, y_rht_out=None, col=0, out_dtype=None):
+                   out_features, n_pad, m_pad, y_rht_out=None, col=0, out_dtype=None,
+                   in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None):
     _require_cuda(x, "x")
-    x2d = x.reshape(-1, in_features)
+    x_cols = in_features * (2 if gated_act is not None else 1)
+    x2d = x.reshape(-1, x_cols)
     if x2d.stride(-1) != 1:
         x2d = x2d.contiguous()
+    extras = in_norm_weight is not None or gated_act is not None or accumulate_into is not None
+    if extras:
+        if y_rht_out is not None:
+            raise RuntimeError("glq_b200: fused norm / activation / residual steps apply to complete linears only")
+        if x2d.shape[0] > FUSED_MAX_TOKENS:
+            # more tokens than the single-launch form takes: run the steps as their own kernels
+            xin = _apply_input_steps(x2d, in_features, in_norm_weight, in_norm_eps, gated_act)
+            y = _fused_trellis(xin, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_rs2, in_features,
+                               out_features, n_pad, m_pad, out_dtype=out_dtype)
+            if accumulate_into is not None:
+                accumulate_into.add_(y.reshape(accumulate_into.shape).to(accumulate_into.dtype))
+                return accumulate_into
+            return y
     has2 = packed2 is not None and packed2.numel() > 0
     codes = [packed] + ([packed2] if has2 else [])
     bits = [_trellis_bits(packed)] + ([_trellis_bits(packed2)] if has2 else [])
     bn, bm = _blocks(blocks_n, n_pad), _blocks(blocks_m, m_pad)
-    if y_rht_out is None:
+    if accumulate_into is not None:
+        tgt, yoff, stop = accumulate_into.reshape(-1, out_features), 0, False
+        if tgt.data_ptr() != accumulate_into.data_ptr() or tgt.stride(-1) != 1:
+            raise RuntimeError("glq_b200: accumulate_into must be a dense (tokens, out_features) tensor")
+    elif y_rht_out is None:
         out = torch.empty(x2d.shape[0], out_features, dtype=out_dtype or x2d.dtype, device=x2d.device)
         tgt, yoff, stop = out, 0, False
     else:
@@ -196,22 +234,46 @@ def _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_r
                           out_features=out_features if not stop else m_pad, codes=codes, bits=bits, su=su, sv=sv,
                           wscale=float(wscale), stage_scale=[float(inv_rs2)] if has2 else [],
                           blocks_n=bn, blocks_m=bm, batch=b, x_dtype=x2d.dtype, y_dtype=tgt.dtype,
-                          x_stride=x_stride, y_stride=y_stride, y_offset=y_offset, stop_at_yrht=stop)
+                          x_stride=x_stride, y_stride=y_stride, y_offset=y_offset, stop_at_yrht=stop,
+                          in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps, in_gated_act=gated_act,
+                          y_accumulate=accumulate_into is not None)
 
     key = ("trellis", packed.data_ptr(), packed2.data_ptr() if has2 else 0, su.data_ptr() if su is not None else 0,
-           sv.data_ptr(), float(wscale), float(inv_rs2), m_pad, n_pad, out_features, stop)
+           sv.data_ptr(), float(wscale), float(inv_rs2), m_pad, n_pad, out_features, stop,
+           in_norm_weight.data_ptr() if in_norm_weight is not None else 0, float(in_norm_eps), gated_act,
+           accumulate_into is not None)
     # two decoded stages keep two accumulator sets: 32 tokens per pass instead of 64
-    _run_sliced(x2d, tgt, key, make_spec, 32 if has2 else DECODE_MAX_TOKENS, y_offset=yoff,
-                out_cols=m_pad if stop else out_features)
+    try:
+        _run_sliced(x2d, tgt, key, make_spec, 32 if has2 else DECODE_MAX_TOKENS, y_offset=yoff,
+                    out_cols=m_pad if stop else out_features, accumulate=accumulate_into is not None)
+    except RuntimeError as e:
+        if not extras or "single-launch" not in str(e):
+            raise
+        # the single-launch form is unavailable for this layer (switched off, or the input does not fit in
+        # shared memory): run the steps as their own kernels
+        xin = _apply_input_steps(x2d, in_features, in_norm_weight, in_norm_eps, gated_act)
+        y = _fused_trellis(xin, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_rs2, in_features,
+                           out_features, n_pad, m_pad, out_dtype=out_dtype)
+        if accumulate_into is None:
+            return y
+        accumulate_into.add_(y.reshape(accumulate_into.shape).to(accumulate_into.dtype))
+    if accumulate_into is not None:
+        return accumulate_into
     return None if stop else tgt
 
 
 def fused_linear_trellis_3inst(x, sv, su, trellis_packed, blocks_n, blocks_m, blocks_n_meta, blocks_m_meta,
-                               wscale, in_features, out_features, n_pad, m_pad, out_dtype=None):
+                               wscale, in_features, out_features, n_pad, m_pad, *, out_dtype=None,
+                               in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None):
     """input RHT -> 3INST decode + matmul -> x Wscale -> output RHT, (B, in) -> (B, out).
-    ``out_dtype`` (not in the reference) selects the result dtype; default: the dtype of x."""
+    Keyword arguments that are not in the reference: ``out_dtype`` selects the result dtype (default: that of
+    x); ``in_norm_weight`` / ``in_norm_eps`` apply an RMSNorm to x first; ``gated_act`` (0 silu, 1 gelu-tanh,
+    2 relu^2) takes x as [gate | up] of 2 * in_features values and feeds act(gate) * up; ``accumulate_into``
+    adds the result to that (B, out) tensor in place (residual add) and returns it.  Up to 8 tokens these run
+    inside the one decode kernel, above that as separate torch kernels around the linear."""
     return _fused_trellis(x, sv, su, trellis_packed, None, blocks_n, blocks_m, wscale, 0.0,
-                          in_features, out_features, n_pad, m_pad, out_dtype=out_dtype)
+                          in_features, out_features, n_pad, m_pad, out_dtype=out_dtype, in_norm_weight=in_norm_weight,
+                          in_norm_eps=in_norm_eps, gated_act=gated_act, accumulate_into=accumulate_into)
 
 
 def fused_linear_trellis_3inst_rvq2(x, sv, su, trellis_packed, trellis_packed2, blocks_n, blocks_m,
@@ -237,18 +299,21 @@ def fused_linear_trellis_3inst_yrht_rvq2(x, sv, trellis_packed, trellis_packed2,
                    in_features, m_pad, n_pad, m_pad, y_rht_out=y_rht_out, col=col)
 
 
-def fused_linear_trellis_3inst_shards(x, sv, shards, blocks_n=None, out_dtype=None):
+def fused_linear_trellis_3inst_shards(x, sv, shards, blocks_n=None, out_dtype=None, in_norm_weight=None, in_norm_eps=1e-6):
     """Several trellis layers that read the same input (the q/k/v or gate/up shards of a fused projection, which
     share SV: glq_vllm/linear_method.py:825-826, 902-909) as ONE plan: one launch for up to 8 tokens instead of
     one fused call per shard plus a shard-batched output transform (glq_vllm/linear_method.py:662-710).
     ``shards`` is a sequence of (su, trellis_packed, trellis_packed2 or None, wscale, inv_resid_scale2, m_pad);
-    returns (B, sum of m_pad) with the shards' outputs side by side.  Not in the reference."""
+    returns (B, sum of m_pad) with the shards' outputs side by side.  ``in_norm_weight`` applies an RMSNorm to x
+    first (inside the kernel up to 8 tokens).  Not in the reference."""
     _require_cuda(x, "x")
     n = sv.numel()
     x2d = x.reshape(-1, n)
     if x2d.stride(-1) != 1:
         x2d = x2d.contiguous()
     B = x2d.shape[0]
+    if in_norm_weight is not None and B > FUSED_MAX_TOKENS:
+        x2d, in_norm_weight = _apply_input_steps(x2d, n, in_norm_weight, in_norm_eps, None), None
     total_m = sum(int(sh[5]) for sh in shards)
     odt = out_dtype or x2d.dtype
     bn = _blocks(blocks_n, n)
@@ -259,7 +324,7 @@ def fused_linear_trellis_3inst_shards(x, sv, shards, blocks_n=None, out_dtype=No
         xin[:B] = x2d
     out = torch.empty((bb, total_m), dtype=odt, device=x2d.device)
     key = ("trellis_shards", tuple(sh[1].data_ptr() for sh in shards), sv.data_ptr(), tuple(float(sh[3]) for sh in shards),
-           bb, xin.dtype, odt, xin.stride(0))
+           bb, xin.dtype, odt, xin.stride(0), in_norm_weight.data_ptr() if in_norm_weight is not None else 0, float(in_norm_eps))
 
     def make_specs():
         specs, col = [], 0
@@ -270,7 +335,8 @@ def fused_linear_trellis_3inst_shards(x, sv, shards, blocks_n=None, out_dtype=No
                                     bits=[_trellis_bits(packed)] + ([_trellis_bits(packed2)] if has2 else []),
                                     su=su, sv=sv, wscale=float(wscale), stage_scale=[float(inv2)] if has2 else [],
                                     blocks_n=bn, blocks_m=block_decompose(int(m)), batch=bb, x_dtype=xin.dtype, y_dtype=odt,
-                                    x_stride=xin.stride(0), y_stride=total_m, y_offset=col))
+                                    x_stride=xin.stride(0), y_stride=total_m, y_offset=col,
+                                    in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps))
             col += int(m)
         return specs
     plan = _cached_plan(key, make_specs)

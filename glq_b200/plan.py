@@ -57,6 +57,11 @@ class LinearSpec:
     y_offset: int = 0
     stop_at_yrht: bool = False
     x_is_rotated: bool = False
+    # fusions of the single-launch decode form (at most 8 tokens; plan creation refuses them otherwise)
+    in_norm_weight: Optional[torch.Tensor] = None  # RMSNorm weight (in_features,), fp16 / bf16 / fp32
+    in_norm_eps: float = 1e-6
+    in_gated_act: Optional[int] = None             # 0 silu, 1 gelu-tanh, 2 relu^2: x rows hold [gate | up]
+    y_accumulate: bool = False                     # y <- y + result (residual add)
     keep: list = field(default_factory=list)      # tensors kept alive for the plan
 
     def to_desc(self) -> _lib.LinearDesc:
@@ -98,6 +103,13 @@ class LinearSpec:
         d.x_offset, d.y_offset = self.x_offset, self.y_offset
         d.stop_at_yrht = 1 if self.stop_at_yrht else 0
         d.x_is_rotated = 1 if self.x_is_rotated else 0
+        if self.in_norm_weight is not None:
+            w = self.in_norm_weight
+            if not w.is_cuda or not w.is_contiguous() or w.numel() != self.in_features:
+                raise RuntimeError("glq_b200: the norm weight must be a contiguous CUDA tensor of in_features values")
+            d.in_norm_weight, d.in_norm_dtype, d.in_norm_eps = w.data_ptr(), _DT[w.dtype], float(self.in_norm_eps)
+        d.in_gated_act = 0 if self.in_gated_act is None else 1 + int(self.in_gated_act)
+        d.y_accumulate = 1 if self.y_accumulate else 0
         return d
 
 

@@ -76,6 +76,19 @@ typedef struct GlqbLinearDesc {
                                             to y (the "_yrht" ops, glq_vllm/custom_ops.py:388-392) */
   int32_t x_is_rotated;                  /* 1: x already holds H_n(SV * pad(x)) for n_pad columns (the unfused
                                             dequant_matvec / dequant_matmul ops, glq_vllm/custom_ops.py:58-71) */
+  /* Optional fusions of the steps a decoder layer runs around its linears.  The reference has no such ops: its
+   * callers launch RMSNorm, silu(gate) * up and the residual add as separate kernels between the GLQ ops
+   * (glq_vllm/linear_method.py:1466; the host framework's decoder layer).  Served by the single-launch decode
+   * form only (trellis, at most 8 tokens, every layer of the plan segment reading the same input): plan
+   * creation refuses them otherwise, and callers then run those steps themselves. */
+  const void* in_norm_weight;            /* RMSNorm weight (in_features,) of dtype in_norm_dtype, or NULL: the input becomes
+                                            round(w * round(x * rsqrt(mean(x^2) + eps))), rounded to the x dtype */
+  int32_t in_norm_dtype;                 /* GLQB_DT_* */
+  float in_norm_eps;
+  int32_t in_gated_act;                  /* 0: none; 1 + GLQB_ACT_{SILU,GELU_TANH,RELU2}: a row of x holds [gate | up]
+                                            (2 * in_features values, x_stride apart); the input is
+                                            round(round(act(gate)) * up), rounded to the x dtype */
+  int32_t y_accumulate;                  /* 1: y <- y + result (residual add), y read in y_dtype */
 } GlqbLinearDesc;
 
 typedef struct GlqbPlan GlqbPlan;

@@ -27,7 +27,8 @@ def test_ops_module_exports_reference_names():
 ])
 def test_positional_arity_matches_reference_schema(name, arity):
     from glq_b200 import ops
-    params = [p for p in inspect.signature(getattr(ops, name)).parameters.values() if p.name != "out_dtype"]
+    params = [p for p in inspect.signature(getattr(ops, name)).parameters.values()
+              if p.name != "out_dtype" and p.kind == p.POSITIONAL_OR_KEYWORD]
     assert len(params) == arity
 
 
@@ -79,7 +80,8 @@ def test_every_served_op_is_registered_with_the_reference_arity(registered):
     for name, (schema, impl, fake) in dropin.OPS.items():
         op = getattr(registered, name)
         n_schema = len(op.default._schema.arguments)
-        n_impl = len([p for p in inspect.signature(getattr(ops, name)).parameters.values() if p.name != "out_dtype"])
+        n_impl = len([p for p in inspect.signature(getattr(ops, name)).parameters.values()
+                      if p.name != "out_dtype" and p.kind == p.POSITIONAL_OR_KEYWORD])
         assert n_schema == n_impl, name
         n_fake = inspect.signature(fake).parameters
         assert any(p.kind == p.VAR_POSITIONAL for p in n_fake.values()) or len(n_fake) == n_schema, name

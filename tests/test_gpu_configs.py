@@ -501,3 +501,77 @@ def test_large_block_plan_survives_a_later_smaller_plan(ops):
     W = CO.trellis_decode(packed, 64, 32768, 2).astype(np.float32)
     assert relerr(again.cpu().numpy(), O.linear_forward(x.cpu().numpy(), W, su, sv, 0.02)) <= TOL
     ops.clear_caches()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# decoder-layer steps fused into the single-launch decode kernel: RMSNorm, act(gate) * up, residual add
+# ---------------------------------------------------------------------------------------------------------
+def _bf16(a):
+    return torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(torch.bfloat16).float().numpy()
+
+
+@pytest.mark.parametrize("B", [1, 5, 20])
+def test_fused_norm_activation_residual(ops, B):
+    """Up to 8 tokens the three steps run inside the decode kernel, above that as torch kernels around it; both
+    must equal the same steps done on the host (intermediate values rounded to bf16 as separate kernels would
+    store them) followed by the oracle's linear."""
+    rng = np.random.default_rng(7000 + B)
+    m, n = 352, 576
+    packed = idx(rng, (m // 16) * (n // 16), 64)
+    W = CO.trellis_decode(packed, m, n, 4).astype(np.float32)
+    su, sv, ws = signs(rng, m), signs(rng, n), 0.02
+    t = dict(p=cuda(packed), su=cuda(su), sv=cuda(sv))
+    call = lambda x, **kw: ops.fused_linear_trellis_3inst(x, t["sv"], t["su"], t["p"], None, None, None, None, ws,
+                                                          n, m, n, m, **kw)
+    x = cuda(rng.standard_normal((B, n)).astype(np.float32) * 3.0, torch.bfloat16)
+    xf = x.float().cpu().numpy()
+    # RMSNorm in front of the linear
+    w = cuda(1.0 + 0.2 * rng.standard_normal(n).astype(np.float32), torch.bfloat16)
+    eps = 1e-5
+    y = call(x, in_norm_weight=w, in_norm_eps=eps, out_dtype=torch.float32)
+    xn = _bf16(xf / np.sqrt((xf.astype(np.float64) ** 2).mean(-1, keepdims=True) + eps))
+    xin = _bf16(w.float().cpu().numpy() * xn)
+    assert relerr(y.cpu().numpy(), O.linear_forward(xin, W, su, sv, ws)) <= TOL + 2.0 ** -8
+    # act(gate) * up in front of the linear, every gated activation
+    xg = cuda(rng.standard_normal((B, 2 * n)).astype(np.float32), torch.bfloat16)
+    g, u = xg.float().cpu().numpy()[:, :n], xg.float().cpu().numpy()[:, n:]
+    for code in (0, 1, 2):
+        y = call(xg, gated_act=code, out_dtype=torch.float32)
+        xin = _bf16(_bf16(O._act(O.ACT_CODES[code])(g)) * u)
+        assert relerr(y.cpu().numpy(), O.linear_forward(xin, W, su, sv, ws)) <= TOL + 2.0 ** -8, code
+    # residual add behind the linear, in place
+    res = cuda(rng.standard_normal((B, m)).astype(np.float32), torch.bfloat16)
+    h = res.clone()
+    out = call(x, accumulate_into=h)
+    assert out.data_ptr() == h.data_ptr()
+    ref = res.float().cpu().numpy() + O.linear_forward(xf, W, su, sv, ws)
+    assert relerr(h.float().cpu().numpy(), ref) <= TOL + 2.0 ** -7
+    # all three at once equal the same composition
+    h2 = res.clone()
+    call(xg, gated_act=0, accumulate_into=h2)
+    xin = _bf16(_bf16(O._act("silu")(g)) * u)
+    ref = res.float().cpu().numpy() + O.linear_forward(xin, W, su, sv, ws)
+    assert relerr(h2.float().cpu().numpy(), ref) <= TOL + 2.0 ** -7
+    ops.clear_caches()
+
+
+def test_fused_norm_on_shards_in_one_launch(ops):
+    rng = np.random.default_rng(7100)
+    n, ms = 2048, [2048, 512, 512]
+    sv = signs(rng, n)
+    shards, refs = [], []
+    x = cuda(rng.standard_normal((1, n)).astype(np.float32) * 2.0, torch.bfloat16)
+    w = cuda(1.0 + 0.1 * rng.standard_normal(n).astype(np.float32), torch.float32)
+    xf = x.float().cpu().numpy()
+    xn = _bf16(xf / np.sqrt((xf.astype(np.float64) ** 2).mean(-1, keepdims=True) + 1e-6))
+    xin = _bf16(w.cpu().numpy() * xn)
+    for m in ms:
+        packed = idx(rng, (m // 16) * (n // 16), 64)
+        su = signs(rng, m)
+        shards.append((cuda(su), cuda(packed), None, 0.02, 0.0, m))
+        refs.append(O.linear_forward(xin, CO.trellis_decode(packed, m, n, 4).astype(np.float32), su, sv, 0.02))
+    y = ops.fused_linear_trellis_3inst_shards(x, cuda(sv), shards, out_dtype=torch.float32, in_norm_weight=w, in_norm_eps=1e-6)
+    plan = [p for k, p in ops._PLAN_CACHE.items() if k[0] == "trellis_shards"][0]
+    assert plan.launches == 1
+    assert relerr(y.cpu().numpy(), np.concatenate(refs, axis=1)) <= TOL + 2.0 ** -8
+    ops.clear_caches()

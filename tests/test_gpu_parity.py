@@ -635,16 +635,20 @@ def test_leading_dims_and_strided_rows(ops):
 
 
 @pytest.mark.parametrize("T", [1, 9, 33, 64])
-def test_ragged_token_counts_match_row_by_row(ops, T):
-    """Token counts that do not fill the 8-token MMA column blocks: every row equals the batch-1 result."""
+def test_ragged_token_counts_match_row_by_row(ops, T, monkeypatch):
+    """Token counts that do not fill the 8-token MMA column blocks: every row equals the batch-1 result of the
+    same kernel family bit for bit (the streaming kernels here: the single-launch form is switched off)."""
     rng = np.random.default_rng(500 + T)
     m, n = 64, 256
     p1, p2, su, sv, wscale, inv, W = _trellis_layer(rng, m, n, 4)
     x_t = cuda(rng.standard_normal((T, n)).astype(np.float32), torch.bfloat16)
+    monkeypatch.setenv("GLQB_FUSED_DECODE", "0")
+    ops.clear_caches()
     y = _run_trellis(ops, x_t, p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
     for r in (0, T // 2, T - 1):
         y1 = _run_trellis(ops, x_t[r:r + 1], p1, None, su, sv, wscale, 0.0, m, n, out_dtype=torch.float32)
         assert torch.equal(y[r:r + 1], y1)
+    ops.clear_caches()
 
 
 @pytest.mark.parametrize("stages,small2", [(1, False), (2, False), (2, True), (3, False)])
