@@ -93,8 +93,12 @@ static MvKernel trellis_kernel_nb(int nb) {
 
 static MvKernel trellis_kernel(int k1, int k2, int nb) {
 #define T_CASE(A, B) if (k1 == A && k2 == B) return trellis_kernel_nb<A, B>(nb);
+#ifdef GLQB_FAST_BUILD   /* developer builds for kernel experiments: the 4-bit single-stage rate only */
+  T_CASE(4, 0)
+#else
   T_CASE(1, 0) T_CASE(2, 0) T_CASE(3, 0) T_CASE(4, 0)
   T_CASE(4, 1) T_CASE(4, 2) T_CASE(4, 3) T_CASE(4, 4)
+#endif
 #undef T_CASE
   return nullptr;
 }
@@ -407,34 +411,52 @@ static int build_plan(GlqbPlan* P) {
       // single-launch form: every layer of the segment reads the same input, at most 8 tokens, and the
       // activations plus the transform scratch fit in shared memory
       const GlqbLinearDesc& d0 = P->descs[P->order[s.first]];
-      bool ok = !d0.x_is_rotated && d0.batch <= FUSED_MAX_TOKENS;
+      bool ok = !d0.x_is_rotated && d0.batch <= FUSED_MAX_TOKENS && s.count <= FUSED_MAX_LAYERS;
       for (int i = 1; i < s.count && ok; ++i) ok = same_input(d0, P->descs[P->order[s.first + i]]);
+      // wide inputs are transformed once by rht_in_kernel (every CTA recomputing them would cost more than
+      // the extra launch); so is a fused RMSNorm whose output block is too long for the in-kernel transform
+      static const int in_max_n = [] { const char* e = getenv("GLQB_FUSED_IN_MAX_N"); return e ? std::min(atoi(e), 1 << FUSED_IN_MAX_LOG) : 4096; }();
+      bool xr_global = d0.n_pad > in_max_n;
+      static const int cta_factor = [] { const char* e = getenv("GLQB_FUSED_CTA_FACTOR"); return e ? std::max(1, atoi(e)) : 1; }();
       int scratch = 32;
-      for (int i = 0; i < d0.n_blocks_n; ++i) scratch = std::max(scratch, d0.blocks_n[i]);
       for (int i = 0; i < s.count && ok; ++i) {
         const GlqbLinearDesc& d = P->descs[P->order[s.first + i]];
-        for (int b = 0; b < d.n_blocks_m; ++b)
+        for (int b = 0; b < d.n_blocks_m; ++b) {
           scratch = std::max(scratch, std::min(d.batch, std::max(1, GLQB_RHT_TILE / d.blocks_m[b])) * d.blocks_m[b]);
+          if (d0.in_norm_weight && d.blocks_m[b] > (1 << FUSED_OUT_MAX_LOG)) xr_global = true;   // rht_out_body knows no 1 / rms
+        }
       }
+      if (!xr_global)
+        for (int i = 0; i < d0.n_blocks_n; ++i) scratch = std::max(scratch, d0.blocks_n[i]);
       const size_t smem = fused_smem_bytes(d0.n_pad, d0.batch, scratch);
       if (ok && smem <= FUSED_SMEM_LIMIT) {
         int resident = 0;
         CUDA_TRY(fused_prepare(s.k1, s.k2, FUSED_SMEM_LIMIT, smem, &resident));
         if (resident > 0) {
-          long long units = 0;
-          for (int i = 0; i < s.count; ++i) {
-            const DevLinear& L = P->dev[s.first + i];
-            units += (long long)L.strips * ((L.groups_per_strip + FUSED_CHUNK_GROUPS - 1) / FUSED_CHUNK_GROUPS);
-          }
+          // column groups per warp and unit: fewer for small layers, so that every SM gets work
+          auto units_for = [&](int gpw) {
+            long long u = 0;
+            for (int i = 0; i < s.count; ++i) {
+              const DevLinear& L = P->dev[s.first + i];
+              u += (long long)L.strips * ((L.groups_per_strip + MV_WARPS * gpw - 1) / (MV_WARPS * gpw));
+            }
+            return u;
+          };
+          // (every CTA repeats the input transform, so more CTAs than SMs only pays when there is more
+          // streaming work than one CTA per SM can take)
+          int gpw = 8;
+          while (gpw > 2 && units_for(gpw) < (long long)cta_factor * P->sm_count) gpw >>= 1;
+          long long units = units_for(gpw);
           if (units < (1ll << 30)) {
             units = 0;
             for (int i = 0; i < s.count; ++i) {
               DevLinear& L = P->dev[s.first + i];
-              const int kch = (L.groups_per_strip + FUSED_CHUNK_GROUPS - 1) / FUSED_CHUNK_GROUPS;
+              const int kch = (L.groups_per_strip + MV_WARPS * gpw - 1) / (MV_WARPS * gpw);
               L.group_base = units;                       // first work unit of the layer
               L.fixed_slots = kch;
               L.slots = kch;
-              L.per_warp = 1;
+              L.per_warp = gpw;
+              L.xr_global = xr_global ? 1 : 0;
               L.ticket_base = P->n_tickets;
               P->n_tickets += L.nbm;
               units += (long long)L.strips * kch;
@@ -577,6 +599,18 @@ static int build_plan(GlqbPlan* P) {
     if (layer_fused[pos]) {                 // activations live in shared memory, transforms run inside the kernel
       ws = align_up(ws, 1024);
       L.xr_off = 0;
+      if (L.xr_global) {                    // ... except wide inputs: transformed once into the workspace
+        int first = pos;
+        while (first > 0 && layer_fused[first - 1] && P->dev[first - 1].xr_global &&
+               same_input(P->descs[P->order[first - 1]], d)) --first;
+        if (first == pos) {
+          L.xr_off = (long long)ws;
+          ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) * XR_TRELLIS_EXPAND, 1024);
+          add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
+        } else {
+          L.xr_off = P->dev[first].xr_off;
+        }
+      }
       L.part_off = (long long)ws;
       ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
       continue;
@@ -735,7 +769,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   }
   for (const Segment& s : P->segs) {
     if (s.fused) {
-      fused_launch(s, P->d_layers + s.first, reinterpret_cast<const uint8_t*>(x_base), reinterpret_cast<uint8_t*>(y_base),
+      fused_launch(s, P->dev.data() + s.first, reinterpret_cast<const uint8_t*>(x_base), reinterpret_cast<uint8_t*>(y_base),
                    ws, P->d_tickets, stream);
     } else if (s.tn) {
       gemm_launch(s, P->d_layers, P->d_gemm_items + s.item_first, ws, P->d_status, P->sm_count, stream);
@@ -803,8 +837,12 @@ int glqb_decompress_trellis_3inst(const void* packed, int32_t bits, const void* 
     CUDA_TRY(cudaGetLastError());                                                                         \
     return GLQB_OK;                                                                                       \
   }
+#ifdef GLQB_FAST_BUILD   /* developer builds for kernel experiments: the 4-bit single-stage rate only */
+  D_CASE(4, 0)
+#else
   D_CASE(1, 0) D_CASE(2, 0) D_CASE(3, 0) D_CASE(4, 0)
   D_CASE(4, 1) D_CASE(4, 2) D_CASE(4, 3) D_CASE(4, 4)
+#endif
 #undef D_CASE
   return fail(GLQB_E_INVALID, "decompress_trellis_3inst: no kernel for K=%d+%d", bits, k2);
 }

@@ -406,7 +406,7 @@ __device__ __forceinline__ void fht_fast_e(float* smem, int logbs, Load& load, P
 }
 
 // dispatch on the array length (2^logbs, 32 .. 8192)
-template <class Load1, class Load4, class Pre, class Store>
+template <int MAXLOG = 13, class Load1, class Load4, class Pre, class Store>
 __device__ __forceinline__ void fht_fast(float* smem, int logbs, Load1 load1, Load4 load4, Pre pre, Store store) {
   // load1(i) -> value i;  load4(i0, float (&q)[4]) -> values i0 .. i0 + 3 (i0 a multiple of 4);
   // pre(i) -> float handed back to store(i, value, that float)
@@ -428,14 +428,13 @@ __device__ __forceinline__ void fht_fast(float* smem, int logbs, Load1 load1, Lo
 #pragma unroll
     for (int k = 0; k < 8; ++k) { load4(i0 + 4 * k, q); v[4 * k] = q[0]; v[4 * k + 1] = q[1]; v[4 * k + 2] = q[2]; v[4 * k + 3] = q[3]; }
   };
-  switch (logbs) {
-    case 9: fht_fast_e<2>(smem, logbs, ld2, pre, store); break;
-    case 10: fht_fast_e<4>(smem, logbs, ld4, pre, store); break;
-    case 11: fht_fast_e<8>(smem, logbs, ld8, pre, store); break;
-    case 12: fht_fast_e<16>(smem, logbs, ld16, pre, store); break;
-    case 13: fht_fast_e<32>(smem, logbs, ld32, pre, store); break;
-    default: fht_fast_e<1>(smem, logbs, ld1, pre, store); break;      // 32 .. 256 values
-  }
+  // arrays longer than 2^MAXLOG never reach this instantiation (their cases are not compiled)
+  if (logbs == 9) { fht_fast_e<2>(smem, logbs, ld2, pre, store); return; }
+  if (logbs == 10) { fht_fast_e<4>(smem, logbs, ld4, pre, store); return; }
+  if constexpr (MAXLOG >= 11) if (logbs == 11) { fht_fast_e<8>(smem, logbs, ld8, pre, store); return; }
+  if constexpr (MAXLOG >= 12) if (logbs == 12) { fht_fast_e<16>(smem, logbs, ld16, pre, store); return; }
+  if constexpr (MAXLOG >= 13) if (logbs == 13) { fht_fast_e<32>(smem, logbs, ld32, pre, store); return; }
+  fht_fast_e<1>(smem, logbs, ld1, pre, store);                        // 32 .. 256 values
 }
 constexpr int FHT_FAST_MAX_LOG = 13;
 

@@ -1,16 +1,21 @@
 // Instantiations and launches of the single-launch decode kernels (trellis_fused_kernel, glqb_kernels.cuh).
 #include "glqb_kernels.cuh"
 #include <cstdlib>
+#include <cstring>
 
 #include "glqb_launch.h"
 
 namespace glqb {
 
-typedef void (*FusedKernel)(const DevLinear*, int, int, int, const uint8_t*, uint8_t*, uint8_t*, int*);
+typedef void (*FusedKernel)(const FusedLayers, int, int, int, const uint8_t*, uint8_t*, uint8_t*, int*);
 static FusedKernel trellis_fused_pick(int k1, int k2) {
 #define F_CASE(A, B) if (k1 == A && k2 == B) return trellis_fused_kernel<A, B>;
+#ifdef GLQB_FAST_BUILD   /* developer builds for kernel experiments: the 4-bit single-stage rate only */
+  F_CASE(4, 0)
+#else
   F_CASE(1, 0) F_CASE(2, 0) F_CASE(3, 0) F_CASE(4, 0)
   F_CASE(4, 1) F_CASE(4, 2) F_CASE(4, 3) F_CASE(4, 4)
+#endif
 #undef F_CASE
   return nullptr;
 }
@@ -40,7 +45,9 @@ void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_ba
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cudaLaunchKernelEx(&cfg, trellis_fused_pick(s.k1, s.k2), layers, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
+  FusedLayers T;
+  memcpy(T.L, layers, sizeof(DevLinear) * (size_t)s.count);          // `layers`: the plan's HOST copy of the segment's entries
+  cudaLaunchKernelEx(&cfg, trellis_fused_pick(s.k1, s.k2), T, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
                      tickets);
 }
 

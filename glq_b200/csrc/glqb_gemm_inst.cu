@@ -40,8 +40,12 @@ static GemmKernel pick_gemm_kernel(const Segment& s) {
   if (s.two_phase) return gemm_kernel_tn<2, 0, 0>(s.tn);
   if (s.format == GLQB_FMT_TRELLIS_3INST) {
 #define G_CASE(A, B) if (s.k1 == A && s.k2 == B) return gemm_kernel_tn<0, A, B>(s.tn);
+#ifdef GLQB_FAST_BUILD   /* developer builds for kernel experiments: the 4-bit single-stage rate only */
+    G_CASE(4, 0)
+#else
     G_CASE(1, 0) G_CASE(2, 0) G_CASE(3, 0) G_CASE(4, 0)
     G_CASE(4, 1) G_CASE(4, 2) G_CASE(4, 3) G_CASE(4, 4)
+#endif
   #undef G_CASE
     return nullptr;
   }

@@ -39,6 +39,9 @@ struct DevLinear {
   float in_norm_eps;
   int in_gated_act;
   int y_accumulate;
+  int xr_global;         // single-launch form, wide inputs: the transformed activations come from the workspace
+                         // (written by rht_in_kernel just before) instead of being recomputed by every CTA
+  long long rstd_off;    // workspace bytes: 1/rms of every token (fused RMSNorm), written by the kernel that transforms x
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];

@@ -139,6 +139,31 @@ __device__ __forceinline__ long long xr_index_e8(long long token, int col, int n
 #endif
 constexpr int RHT_THREADS = GLQB_RHT_THREADS;
 
+constexpr int FUSED_MAX_TOKENS_C = 8;     // tokens served by the single-launch decode form and its fused steps
+
+// Input value of column `col` of token row starting at element `xt0`, before the sign vector: x itself, or
+// act(gate) * up for a [gate | up] row (both factors and the product rounded to the activation dtype, as
+// separate kernels would store them).
+__device__ __forceinline__ float input_value(const DevLinear& L, const uint8_t* x_base, long long xt0, int col) {
+  float v = load_act(x_base, xt0 + col, L.x_dtype);
+  if (L.in_gated_act)
+    v = round_act(round_act(act_fn(v, L.in_gated_act - 1), L.x_dtype) * load_act(x_base, xt0 + L.in_f + col, L.x_dtype), L.x_dtype);
+  return v;
+}
+// 1 / rms of a token's input values (fused RMSNorm), by all threads of the CTA; `red` holds >= 32 floats
+__device__ __forceinline__ float token_rstd(const DevLinear& L, const uint8_t* x_base, long long xt0, float* red) {
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < L.in_f; i += blockDim.x) { const float v = input_value(L, x_base, xt0, i); ss += v * v; }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (int)(blockDim.x >> 5); ++w) tot += red[w];
+  return rsqrtf(tot / (float)L.in_f + L.in_norm_eps);
+}
+
 // 32 consecutive activations of one token, times SV, zero past in_features
 __device__ __forceinline__ void rht_load_x32(const DevLinear& L, const uint8_t* x_base, long long token, int col0,
                                              bool vec_ok, float (&v)[32]) {
@@ -191,16 +216,42 @@ __device__ __forceinline__ void rht_in_body(const DevLinear& L, const RhtItem it
       reinterpret_cast<__half*>(ws + L.xr_off)[xr_index_e8(token, col, L.n, L.batch)] = __float2half_rn(v);
     }
   };
+  const bool fusions = L.in_gated_act != 0 || L.in_norm_w != nullptr;
   auto load1 = [&](int row, int i) -> float {
     const int col = off + i;
     if (col >= L.in_f) return 0.f;
-    float v = load_act(x_base, L.x_off + (long long)(it.tok0 + row) * L.x_stride + col, L.x_dtype);
+    const long long xt0 = L.x_off + (long long)(it.tok0 + row) * L.x_stride;
+    float v = fusions ? input_value(L, x_base, xt0, col) : load_act(x_base, xt0 + col, L.x_dtype);
+    if (L.in_norm_w) v *= load_act(L.in_norm_w, col, L.in_norm_dtype);
     if (!L.x_is_rotated) v *= __half2float(L.sv[col]);
     return v;
   };
   if (L.x_is_rotated) {            // already transformed by the caller: convert and lay out only
     const int total = it.ntok << logbs;
     for (int o = threadIdx.x; o < total; o += blockDim.x) store1(o >> logbs, o & (bs - 1), load1(o >> logbs, o & (bs - 1)));
+    return;
+  }
+  if (fusions) {
+    // fused RMSNorm / gated activation in front of the transform (decode: one token per CTA and block):
+    // 1 / rms of the token is folded into the stored values
+    float rstd[FUSED_MAX_TOKENS_C];                 // per token of the tile (at most 8 tokens take this path)
+#pragma unroll
+    for (int r = 0; r < FUSED_MAX_TOKENS_C; ++r) {
+      rstd[r] = 1.f;
+      if (L.in_norm_w && r < it.ntok) rstd[r] = token_rstd(L, x_base, L.x_off + (long long)(it.tok0 + r) * L.x_stride, fbuf);
+    }
+    __syncthreads();
+    auto store_n = [&](int row, int i, float val) {
+      float sc = 1.f;
+#pragma unroll
+      for (int r = 0; r < FUSED_MAX_TOKENS_C; ++r) if (r == row) sc = rstd[r];
+      store1(row, i, val * sc);
+    };
+    auto load32f = [&](int row, int i0, float (&v)[32]) {
+#pragma unroll
+      for (int k = 0; k < 32; ++k) v[k] = load1(row, i0 + k);
+    };
+    fht_tile(fbuf, logbs, it.ntok, load32f, load1, store_n);
     return;
   }
   auto load32 = [&](int row, int i0, float (&v)[32]) { rht_load_x32(L, x_base, it.tok0 + row, off + i0, vec_ok, v); };
@@ -213,6 +264,9 @@ __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_kernel(cons
                                                              const uint8_t* __restrict__ x_base,
                                                              uint8_t* __restrict__ ws) {
   extern __shared__ float fbuf[];
+  // a successor launched with programmatic stream serialization (the single-launch decode kernel) may start
+  // its prologue now; it waits for this kernel's completion before it reads the activations
+  asm volatile("griddepcontrol.launch_dependents;");
   const RhtItem it = items[blockIdx.x];
   rht_in_body<PLAIN_F32>(layers[it.layer], it, x_base, ws, fbuf);
 }
@@ -616,7 +670,7 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
 //            that is.  Tickets are returned to zero by the CTA that completes them.
 // ---------------------------------------------------------------------------------------------
 constexpr int FUSED_CHUNK_GROUPS = 64;          // column groups per work unit: 8 warps x 8 groups
-constexpr int FUSED_MAX_TOKENS = 8;
+constexpr int FUSED_MAX_TOKENS = FUSED_MAX_TOKENS_C;
 constexpr int FUSED_MAX_TODO = 32;
 
 __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
@@ -631,19 +685,20 @@ __host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, in
   return (size_t)batch * n * 4 + ((size_t)scratch_elems + scratch_elems / 32) * 4 + 8 * 256 * 4 + 64;
 }
 
-// Output transform of one (layer, Hadamard block, token) with the low-latency transform; same arithmetic
-// as rht_out_body.  Blocks of up to 8192 values.
-__device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int tok, const uint8_t* __restrict__ ws,
-                                                uint8_t* __restrict__ y_base, float* fbuf) {
-  const int off = L.bm_off[b], logbs = L.bm_log[b];
+// Output transform of one (layer, Hadamard block, token) by the CTA that completed the block, with the
+// low-latency transform; same butterflies in the same order as rht_out_body, hence the same bits.  Blocks of up
+// to 8192 rows (longer ones go through rht_out_body).
+constexpr int FUSED_IN_MAX_LOG = 12;             // longest input block transformed inside the kernel: 4096
+constexpr int FUSED_OUT_MAX_LOG = 13;            // longest output block of the low-latency transform: 8192
+
+__device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int tok, float in_scale,
+                                                const uint8_t* __restrict__ ws, uint8_t* __restrict__ y_base, float* fbuf) {
+  const int logbs = L.bm_log[b], off = L.bm_off[b];
   const int m = L.m, cnt = L.fixed_slots, out_f = L.out_f, y_dtype = L.y_dtype;
   const long long slot_stride = (long long)L.batch * m;
-  const float wscale = L.wscale;
+  const float wscale = L.wscale * in_scale;                  // in_scale: 1 / rms of the token (fused RMSNorm), else 1
   const float* row_scale = L.row_scale;
   const float* part = reinterpret_cast<const float*>(ws + L.part_off) + (long long)tok * m + off;
-  const float rs = rsqrtf((float)(1 << logbs));
-  const __half* su = L.su + off;
-  const long long yo = L.y_off + (long long)tok * L.y_stride + off;
   auto load1 = [&](int i) -> float {
     float s = 0.f;
     for (int k = 0; k < cnt; ++k) s += __ldcg(part + i + k * slot_stride);
@@ -663,31 +718,42 @@ __device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int t
       for (int k = 0; k < 4; ++k) q[k] *= row_scale[off + i0 + k];
     }
   };
+  const long long yo = L.y_off + (long long)tok * L.y_stride + off;
   if (L.stop_at_yrht) {            // rotated-domain result wanted: reduce and scale only
-    for (int i = threadIdx.x; i < (1 << logbs); i += blockDim.x)
-      reinterpret_cast<float*>(y_base)[yo + i] = load1(i);
+    for (int i = threadIdx.x; i < (1 << logbs); i += blockDim.x) reinterpret_cast<float*>(y_base)[yo + i] = load1(i);
     return;
   }
-  // the sign (and, for a residual add, the old output) are requested before the partial sums; the old output
-  // travels in the same float as sign * 2^k would not be exact, so it is fetched in `store` when needed
+  const float rs = rsqrtf((float)(1 << logbs));
+  const __half* su = L.su + off;
   const bool accumulate = L.y_accumulate != 0;
-  auto pre = [&](int i) -> float { return __half2float(su[i]); };
+  auto pre = [&](int i) -> float { return __half2float(su[i]); };      // the sign, requested before the partial sums
   auto store = [&](int i, float val, float sign) {
     if (off + i < out_f) {
       float r = val * rs * sign;
-      if (accumulate) r += load_act(y_base, yo + i, y_dtype);
+      if (accumulate) r += load_act(y_base, yo + i, y_dtype);          // residual add
       store_act(y_base, yo + i, y_dtype, r);
     }
   };
-  fht_fast(fbuf, logbs, load1, load4, pre, store);
+  fht_fast<FUSED_OUT_MAX_LOG>(fbuf, logbs, load1, load4, pre, store);
 }
 
+#ifndef GLQB_FUSED_MINB
+#define GLQB_FUSED_MINB 2
+#endif
+// The layers of a single-launch call travel in kernel-parameter space (constant bank): reading the plan's table
+// from global memory would put several dependent L2 round trips at the head of a few-microsecond kernel.
+constexpr int FUSED_MAX_LAYERS = 8;
+struct FusedLayers {
+  DevLinear L[FUSED_MAX_LAYERS];
+};
+
 template <int K1, int K2>
-__global__ void __launch_bounds__(MV_THREADS, 2)
-trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int total_units, int scratch_elems,
+__global__ void __launch_bounds__(MV_THREADS, GLQB_FUSED_MINB)
+trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int total_units, int scratch_elems,
                      const uint8_t* __restrict__ x_base, uint8_t* __restrict__ y_base, uint8_t* __restrict__ ws,
                      int* __restrict__ tickets) {
   extern __shared__ __align__(16) uint8_t fsm[];
+  const DevLinear* layers = T.L;
   const DevLinear& L0 = layers[0];
   const int n = L0.n, batch = L0.batch;
   __half2* xs = reinterpret_cast<__half2*>(fsm);                              // [batch][n] (x, 0) pairs, fragment order
@@ -708,8 +774,9 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
     const int kch = L.fixed_slots;                          // chunks (= partial sums) per strip
     const int local = u - (int)L.group_base;
     const int strip = local / kch, chunk = local - strip * kch;
-    const int c0 = chunk * FUSED_CHUNK_GROUPS + warp * 8;
-    return Unit{li, strip, chunk, c0, max(0, min(8, L.groups_per_strip - c0))};
+    const int gpw = L.per_warp;                             // column groups per warp and unit: 2, 4 or 8
+    const int c0 = (chunk * MV_WARPS + warp) * gpw;
+    return Unit{li, strip, chunk, c0, max(0, min(gpw, L.groups_per_strip - c0))};
   };
   // the stage-1 codes of a unit: all of a warp's (up to eight) groups in flight at once
   auto fetch = [&](const Unit& U, Words<K1> (&w1)[8]) {
@@ -732,40 +799,33 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  // ---- phase 1: input transform of the shared input, token by token, block by block
-  {
-    const int x_dtype = L0.x_dtype, in_f = L0.in_f;
-    const int gact = L0.in_gated_act;                        // 0, or 1 + activation code: x rows are [gate | up]
+  // ---- phase 1: the transformed activations of the shared input, in shared memory
+  __shared__ float rstd_s[FUSED_MAX_TOKENS];                 // fused RMSNorm: 1 / rms per token, applied to the OUTPUT
+  if (threadIdx.x < FUSED_MAX_TOKENS) rstd_s[threadIdx.x] = 1.f;
+  if (L0.xr_global) {
+    // wide inputs: rht_in_kernel transformed them once, just before this kernel; every CTA copies the result
+    const uint4* src = reinterpret_cast<const uint4*>(ws + L0.xr_off);
+    uint4* dst = reinterpret_cast<uint4*>(xs);
+    const int n16 = (int)(((size_t)batch * n * 4) >> 4);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
+    __syncthreads();
+  } else {
+    const int x_dtype = L0.x_dtype;
     const void* nw = L0.in_norm_w;
-    const bool plain = gact == 0 && nw == nullptr;
-    const bool vec_ok = plain && act_rows_aligned4(x_base, L0.x_off, L0.x_stride, x_dtype);
+    const int nw_dtype = L0.in_norm_dtype;
+    const bool gated = L0.in_gated_act != 0;
+    const bool vec_ok = !gated && act_rows_aligned4(x_base, L0.x_off, L0.x_stride, x_dtype) &&
+                        (nw == nullptr || (reinterpret_cast<uintptr_t>(nw) & 15) == 0);
     const __half* sv = L0.sv;
     for (int tok = 0; tok < batch; ++tok) {
       const long long xt0 = L0.x_off + (long long)tok * L0.x_stride;
-      // raw input value of column `col`, before the sign: x, act(gate) * up, or the RMS-normalised x
-      float rstd = 1.f;
-      auto raw = [&](int col) -> float {
-        float v = load_act(x_base, xt0 + col, x_dtype);
-        if (gact) v = round_act(round_act(act_fn(v, gact - 1), x_dtype) * load_act(x_base, xt0 + in_f + col, x_dtype), x_dtype);
-        return v;
-      };
-      if (nw) {                                              // mean of squares over the token, then 1 / sqrt(. + eps)
-        float ss = 0.f;
-        for (int i = threadIdx.x; i < in_f; i += blockDim.x) { const float v = raw(i); ss += v * v; }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-#pragma unroll
-        for (int w = 0; w < MV_WARPS; ++w) tot += red[w];
-        rstd = rsqrtf(tot / (float)in_f + L0.in_norm_eps);
-        __syncthreads();
-      }
-      const int nw_dtype = L0.in_norm_dtype;
-      auto load1 = [&](int i_abs) -> float {                 // absolute column
-        float v = raw(i_abs);
-        if (nw) v = round_act(load_act(nw, i_abs, nw_dtype) * round_act(v * rstd, x_dtype), x_dtype);
+      float ss = 0.f;                                        // this thread's share of sum(x^2) (fused RMSNorm)
+      // value of column i_abs fed to the transform: x (or act(gate) * up), times the norm weight, times the sign.
+      // The 1 / rms factor of the norm is a scalar per token and is applied to the output instead.
+      auto load1 = [&](int i_abs) -> float {
+        float v = input_value(L0, x_base, xt0, i_abs);
+        ss += v * v;
+        if (nw) v *= load_act(nw, i_abs, nw_dtype);
         return v * __half2float(sv[i_abs]);
       };
       for (int b = 0; b < L0.nbn; ++b) {
@@ -773,17 +833,24 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
         const float rs = rsqrtf((float)(1 << logbs));
         const bool vok = vec_ok && (off & 3) == 0;
         __half2* xt = xs + (size_t)tok * n;                  // n half2 per token
-        auto none = [](int) -> float { return 0.f; };
-        auto put = [&](int i, float val, float = 0.f) {
+        auto put = [&](int i, float val) {
           const int col = off + i;
           xt[((col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31)) >> 1] =
               __halves2half2(__float2half_rn(val * rs), __float2half_rn(0.f));
         };
         auto ld1 = [&](int i) -> float { return load1(off + i); };
-        if (logbs <= FHT_FAST_MAX_LOG) {
+        auto none = [](int) -> float { return 0.f; };
+        auto put3 = [&](int i, float val, float) { put(i, val); };
+        if (logbs <= FUSED_IN_MAX_LOG) {
           auto load4 = [&](int i0, float (&q)[4]) {
             if (vok) {
               load_act4(x_base, xt0 + off + i0, x_dtype, q);
+              ss += q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3];
+              if (nw) {
+                float w4[4];
+                load_act4(nw, off + i0, nw_dtype, w4);
+                q[0] *= w4[0]; q[1] *= w4[1]; q[2] *= w4[2]; q[3] *= w4[3];
+              }
               const uint2 s4 = *reinterpret_cast<const uint2*>(sv + off + i0);
               const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
               const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
@@ -793,16 +860,27 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
               for (int k = 0; k < 4; ++k) q[k] = load1(off + i0 + k);
             }
           };
-          fht_fast(fbuf, logbs, ld1, load4, none, put);
+          fht_fast<FUSED_IN_MAX_LOG>(fbuf, logbs, ld1, load4, none, put3);
         } else {
           auto store1 = [&](int, int i, float val) { put(i, val); };
           auto l1 = [&](int, int i) -> float { return load1(off + i); };
           auto load32 = [&](int, int i0, float (&v)[32]) {
-            if (plain) { rht_load_x32(L0, x_base, tok, off + i0, vok, v); return; }
 #pragma unroll
             for (int k = 0; k < 32; ++k) v[k] = load1(off + i0 + k);
           };
           fht_tile(fbuf, logbs, 1, load32, l1, store1);
+        }
+        __syncthreads();
+      }
+      if (nw) {                                              // every value of the token was loaded exactly once
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          float tot = 0.f;
+          for (int w = 0; w < MV_WARPS; ++w) tot += red[w];
+          rstd_s[tok] = rsqrtf(tot / (float)L0.in_f + L0.in_norm_eps);
         }
         __syncthreads();
       }
@@ -874,7 +952,7 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
       while (b + 1 < L.nbm && strip * 32 >= L.bm_off[b + 1]) ++b;
       const int need = ((1 << L.bm_log[b]) >> 5) * kch;
       // release (the CTA's stores, ordered before this by the barrier) and acquire (the other CTAs' stores,
-      // released before their increments) in one device-scope atomic
+      // released before their increments) in one device-scope atomic; nobody ever waits on a ticket
       int old;
       asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(tickets + L.ticket_base + b) : "memory");
       if (old + 1 == need) {
@@ -890,9 +968,9 @@ trellis_fused_kernel(const DevLinear* __restrict__ layers, int n_layers, int tot
   for (int k = 0; k < nt; ++k) {
     const int li = todo[k] >> 8, b = todo[k] & 255;
     const DevLinear& L = layers[li];
-    if (L.bm_log[b] <= FHT_FAST_MAX_LOG) {
+    if (L.bm_log[b] <= FUSED_OUT_MAX_LOG) {
       for (int tok = 0; tok < batch; ++tok) {
-        fused_out_block(L, b, tok, ws, y_base, fbuf);
+        fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf);
         __syncthreads();
       }
     } else {

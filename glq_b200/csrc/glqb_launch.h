@@ -44,6 +44,7 @@ void gemm_launch(const Segment& s, const DevLinear* layers, const GemmItem* item
 // ---- glqb_fused.cu
 bool fused_available(int k1, int k2);
 cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* resident_ctas_out);
+// `layers`: HOST copy of the segment's table entries (they are passed to the kernel by value)
 void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_base, uint8_t* y_base, uint8_t* ws,
                   int* tickets, cudaStream_t stream);
 

@@ -224,7 +224,8 @@ def test_trellis_single_launch_matches_three_launch_form(ops, K, K2, B, monkeypa
         y = _run_trellis(ops, x_t, p1, p2, su, sv, wscale, inv, m, n, out_dtype=torch.float32)
         assert relerr(y.cpu().numpy(), ref) <= TOL, form
         plan = next(iter(ops._PLAN_CACHE.values()))
-        assert plan.launches == (1 if form == "1" else 3)
+        # inputs wider than 4096 columns are transformed once by a kernel of their own
+        assert plan.launches == ((1 if n <= 4096 else 2) if form == "1" else 3)
         outs[form] = y
     assert relerr(outs["1"].cpu().numpy(), outs["0"].cpu().numpy()) <= 1e-5
     ops.clear_caches()
