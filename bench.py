@@ -256,7 +256,9 @@ def kernel_name(W):
         return f"glq_gemm_kernel<e8,{ns},{tn},4>"
     nb = 1 if T <= 8 else 2 if T <= 16 else 4 if T <= 32 else 8
     if fmt == "trellis":
-        return f"trellis_mv_kernel<{par[0]},{par[1] if len(par) > 1 else 0},{nb}>"
+        # large single-stage batch-1 launches take the table form (two of eight states per lane looked up)
+        lut = nb == 1 and len(par) == 1 and W["code_bytes"] >= int(os.environ.get("GLQB_TRELLIS_LUT_MIN_BYTES", str(48 << 20)))
+        return f"trellis_mv_kernel<{par[0]},{par[1] if len(par) > 1 else 0},{nb}{',2' if lut else ''}>"
     resident = W["code_bytes"] >= int(os.environ.get("GLQB_E8_SMEM_MIN_BYTES", str(48 << 20))) and nb <= 2
     return f"e8_mv_smem_kernel<{ns},{nb}>" if resident else f"e8_mv_kernel<{ns},{nb}>"
 

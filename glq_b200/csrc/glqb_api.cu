@@ -91,6 +91,23 @@ static MvKernel trellis_kernel_nb(int nb) {
   return nullptr;
 }
 
+// table form of the single-stage batch-1 kernels (large launches only)
+static MvKernel trellis_lut_kernel(int k1) {
+  switch (k1) {
+#ifndef GLQB_FAST_BUILD
+    case 2: return trellis_mv_kernel<2, 0, 1, MV_LUT_STATES>;
+    case 3: return trellis_mv_kernel<3, 0, 1, MV_LUT_STATES>;
+#endif
+    case 4: return trellis_mv_kernel<4, 0, 1, MV_LUT_STATES>;
+  }
+  return nullptr;
+}
+static long long trellis_lut_min_bytes() {
+  // every CTA spends a microsecond or two filling its table, so small launches keep the arithmetic decode
+  const char* e = getenv("GLQB_TRELLIS_LUT_MIN_BYTES");
+  return e ? atoll(e) : (48ll << 20);
+}
+
 static MvKernel trellis_kernel(int k1, int k2, int nb) {
 #define T_CASE(A, B) if (k1 == A && k2 == B) return trellis_kernel_nb<A, B>(nb);
 #ifdef GLQB_FAST_BUILD   /* developer builds for kernel experiments: the 4-bit single-stage rate only */
@@ -557,6 +574,18 @@ static int build_plan(GlqbPlan* P) {
         }
       }
     }
+    if (s.format == GLQB_FMT_TRELLIS_3INST && s.nb == 1 && s.k2 == 0 && trellis_lut_kernel(s.k1)) {
+      long long bytes = 0;
+      for (int i = 0; i < s.count; ++i) bytes += (long long)P->dev[s.first + i].m * P->dev[s.first + i].n * s.k1 / 8;
+      if (bytes >= trellis_lut_min_bytes() &&
+          cudaFuncSetAttribute(trellis_lut_kernel(s.k1), cudaFuncAttributeMaxDynamicSharedMemorySize, MV_LUT_SMEM_BYTES) == cudaSuccess) {
+        s.lut_table = true;
+        warps_per_cta = MV_LUT_THREADS / 32;
+        warps_avail = (long long)P->sm_count * warps_per_cta;
+      } else {
+        cudaGetLastError();
+      }
+    }
     long long total = 0;
     for (int i = 0; i < s.count; ++i) {
       DevLinear& L = P->dev[s.first + i];
@@ -778,7 +807,11 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
           P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws, s.big_table, s.small_table, s.small_entries);
     } else {
       MvKernel kern = pick_kernel(s);
-      kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);
+      if (s.lut_table)
+        trellis_lut_kernel(s.k1)<<<s.grid, MV_LUT_THREADS, MV_LUT_SMEM_BYTES, stream>>>(P->d_layers + s.first, s.count,
+                                                                                       s.total_groups, s.per_warp, ws);
+      else
+        kern<<<s.grid, MV_THREADS, 0, stream>>>(P->d_layers + s.first, s.count, s.total_groups, s.per_warp, ws);
     }
   }
   if (P->timing) {

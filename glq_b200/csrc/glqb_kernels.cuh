@@ -7,6 +7,9 @@
 
 namespace glqb {
 
+#ifndef GLQB_LUT_THREADS
+#define GLQB_LUT_THREADS 768
+#endif
 constexpr int MV_THREADS = 256;               // 8 warps per CTA in the streaming kernels
 constexpr int MV_WARPS = MV_THREADS / 32;
 
@@ -477,9 +480,9 @@ __device__ __forceinline__ Words<K> shfl_words(const Words<K>& v, int src) {
 
 // decode the four tiles of a group and issue their MMAs against the B fragments xb[nb][ni]
 // (xb[nb][ni] = {e0:(x,0) k-lo, e0 k-hi, e1 k-lo, e1 k-hi})
-template <int K, int NB>
+template <int K, int NB, int LUT = 0>
 __device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uint4 (&xb)[NB][2],
-                                          float (&acc)[NB][2][4]) {
+                                          float (&acc)[NB][2][4], uint32_t lut_base = 0u) {
   const Words<K> vn = shfl_words<K>(v, (lane + 1) & 31);
   Words<K> vn2 = vn;
   if constexpr (K == 1) vn2 = shfl_words<K>(v, (lane + 2) & 31);
@@ -489,7 +492,7 @@ __device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uin
     for (int mi = 0; mi < 2; ++mi) {
       const int q = ni * 2 + mi;
       uint32_t a[8];
-      decode_tile<K>(chunk_of<K>(v, q), chunk_of<K>(vn, q), chunk_of<K>(vn2, q), a);
+      decode_tile<K, LUT>(chunk_of<K>(v, q), chunk_of<K>(vn, q), chunk_of<K>(vn2, q), a, lut_base);
       const uint32_t a_even[4] = {a[0], a[2], a[4], a[6]};   // columns 2t   / 8+2t   of the tile
       const uint32_t a_odd[4] = {a[1], a[3], a[5], a[7]};    // columns 2t+1 / 8+2t+1
 #pragma unroll
@@ -501,19 +504,31 @@ __device__ __forceinline__ void group_mma(const Words<K>& v, int lane, const uin
   }
 }
 
-template <int K1, int K2, int NB>
 #ifndef GLQB_MINB
 #define GLQB_MINB 3
 #endif
-__global__ void __launch_bounds__(MV_THREADS, (NB == 1 && K2 == 0) ? GLQB_MINB : 1)
+// LUT > 0: the table form for large launches — one CTA of MV_LUT_THREADS per SM next to the 128 KiB table of the
+// code's 65,536 fp16 values, which the CTA fills with the arithmetic decode when it starts (see decode_tile).
+constexpr int MV_LUT_STATES = 2;
+constexpr int MV_LUT_THREADS = GLQB_LUT_THREADS;
+constexpr int MV_LUT_SMEM_BYTES = 65536 * 2;
+template <int K1, int K2, int NB, int LUT = 0>
+__global__ void __launch_bounds__(LUT ? MV_LUT_THREADS : MV_THREADS, LUT ? 1 : ((NB == 1 && K2 == 0) ? GLQB_MINB : 1))
 trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long total_groups,
                   int per_warp, uint8_t* __restrict__ ws) {
+  uint32_t lut_base = 0u;
+  if constexpr (LUT > 0) {
+    extern __shared__ __align__(16) unsigned short lut3[];
+    for (int st = threadIdx.x; st < 65536; st += blockDim.x) lut3[st] = (unsigned short)(sum_dup3(hash3((uint32_t)st)) & 0xFFFFu);
+    __syncthreads();
+    lut_base = (uint32_t)__cvta_generic_to_shared(lut3);
+  }
 #ifndef GLQB_PF
 #define GLQB_PF 4
 #endif
   constexpr int PF = GLQB_PF;   // codes of PF groups in flight per lane
   const int lane = threadIdx.x & 31;
-  const long long w = (long long)blockIdx.x * MV_WARPS + (threadIdx.x >> 5);
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   long long g = w * per_warp;
   const long long gend = min(g + per_warp, total_groups);
   if (g >= gend) return;
@@ -588,8 +603,8 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
           xb[nb][0] = __ldg(xq[nb] + i * 8);               // 64 halfs = 8 uint4 per group
           xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
         }
-        group_mma<K1, NB>(v, lane, xb, acc);
-        if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
+        group_mma<K1, NB, LUT>(v, lane, xb, acc, lut_base);
+        if constexpr (K2 > 0) group_mma<K2, NB, LUT>(v2, lane, xb, acc2, lut_base);
       }
       q1 += PF * (128 * K1);
       q2 += PF * (128 * K2);
@@ -614,8 +629,8 @@ trellis_mv_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
             xb[nb][0] = __ldg(xq[nb] + i * 8);
             xb[nb][1] = __ldg(xq[nb] + i * 8 + 1);
           }
-          group_mma<K1, NB>(v, lane, xb, acc);
-          if constexpr (K2 > 0) group_mma<K2, NB>(v2, lane, xb, acc2);
+          group_mma<K1, NB, LUT>(v, lane, xb, acc, lut_base);
+          if constexpr (K2 > 0) group_mma<K2, NB, LUT>(v2, lane, xb, acc2, lut_base);
         }
       }
       q1 += PF * (128 * K1);

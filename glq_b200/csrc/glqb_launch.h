@@ -24,6 +24,7 @@ struct Segment {
   int grid;
   int item_first, item_count;   // GEMM work items (range in the plan's item array)
   // E8 only: most of the codebook resident in shared memory (one CTA per SM)
+  bool lut_table = false;    // trellis: table form of the streaming kernel (large batch-1 launches)
   bool smem_table = false;
   const uint32_t* big_table = nullptr;
   const uint32_t* small_table = nullptr;
