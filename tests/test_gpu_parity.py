@@ -232,8 +232,9 @@ def test_trellis_single_launch_matches_three_launch_form(ops, K, K2, B, monkeypa
 
 
 def test_trellis_shards_in_one_launch(ops):
-    """q/k/v-style shards that share their input run as one plan and one launch; every shard's output equals the
-    single-layer call bit for bit and the oracle within tolerance; the call can be captured in a CUDA graph."""
+    """q/k/v-style shards that share their input run as one plan and one launch; every shard's output matches the
+    oracle within tolerance and the single-layer call to rounding (the work-unit size, hence the grouping of the
+    fp32 partial sums, follows the total work of a call); the call can be captured in a CUDA graph."""
     rng = np.random.default_rng(91)
     n, ms = 2048, [2048, 512, 512]
     sv = signs(rng, n)
@@ -254,7 +255,7 @@ def test_trellis_shards_in_one_launch(ops):
         assert relerr(y[:, col:col + m].cpu().numpy(), ref) <= TOL
         single = ops.fused_linear_trellis_3inst(x_t, sv_t, su_t, p_t, None, None, None, None, ws, n, m, n, m,
                                                 out_dtype=torch.float32)
-        assert torch.equal(single, y[:, col:col + m])
+        assert relerr(single.cpu().numpy(), y[:, col:col + m].cpu().numpy()) <= 1e-5
         col += m
     torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
