@@ -305,7 +305,11 @@ static int validate(const GlqbLinearDesc& d, int idx) {
 }
 
 // one thread per 32-value segment of the largest tile, between 64 and RHT_THREADS
-static int rht_threads(int max_elems) { return std::max(64, std::min(RHT_THREADS, (max_elems / 32 + 31) / 32 * 32)); }
+// ... except for decode-sized plans (at most 8 tokens), whose transforms use all 256 threads per array
+static int rht_threads(int max_elems, int max_batch = 1 << 30) {
+  if (max_batch <= FUSED_MAX_TOKENS) return RHT_THREADS;
+  return std::max(64, std::min(RHT_THREADS, (max_elems / 32 + 31) / 32 * 32));
+}
 static int rht_smem(int max_elems) { return (max_elems + max_elems / 32) * 4 + 64; }
 
 static cudaError_t raise_rht_smem_limits() {
@@ -318,15 +322,24 @@ static cudaError_t raise_rht_smem_limits() {
   return e;
 }
 
-// one item per (layer, block, tile of tokens); tracks the largest tile (floats) for the launch's smem
+// one item per (layer, block, tile of tokens); tracks the largest tile (floats) for the launch's smem.
+// Decode-sized layers (at most 8 tokens): a block of 4096 values or more is shared by S = bs / 1024 CTAs, each
+// producing one run of 1024 outputs for all tokens (RhtItem::sub).  `min_log`: only blocks of at least
+// 2^min_log values get items (the single-launch kernel transforms the shorter output blocks itself).
 static void add_rht_items(std::vector<RhtItem>& items, int layer, int nblocks, const int* logs, int batch,
-                          int& max_elems) {
+                          int& max_elems, bool latency, int min_log = 0) {
   for (int b = 0; b < nblocks; ++b) {
+    if (logs[b] < min_log) continue;
     const int bs = 1 << logs[b];
+    if (latency && batch <= FUSED_MAX_TOKENS && logs[b] >= RHT_SPLIT_MIN_LOG) {
+      for (int k = 0; k < (bs >> RHT_SPLIT_LOG); ++k) items.push_back(RhtItem{layer, b, 0, batch, k});
+      max_elems = std::max(max_elems, 1 << RHT_SPLIT_LOG);
+      continue;
+    }
     const int tt = rht_tile_tokens(bs, batch);
     for (int t0 = 0; t0 < batch; t0 += tt) {
       const int nt = std::min(tt, batch - t0);
-      items.push_back(RhtItem{layer, b, t0, nt});
+      items.push_back(RhtItem{layer, b, t0, nt, -1});
       max_elems = std::max(max_elems, nt * bs);
     }
   }
@@ -432,16 +445,22 @@ static int build_plan(GlqbPlan* P) {
       for (int i = 1; i < s.count && ok; ++i) ok = same_input(d0, P->descs[P->order[s.first + i]]);
       // wide inputs are transformed once by rht_in_kernel (every CTA recomputing them would cost more than
       // the extra launch); so is a fused RMSNorm whose output block is too long for the in-kernel transform
-      static const int in_max_n = [] { const char* e = getenv("GLQB_FUSED_IN_MAX_N"); return e ? std::min(atoi(e), 1 << FUSED_IN_MAX_LOG) : 4096; }();
+      static const int in_max_n = [] { const char* e = getenv("GLQB_FUSED_IN_MAX_N"); return e ? atoi(e) : 4096; }();
       bool xr_global = d0.n_pad > in_max_n;
+      // Output blocks of at least 2^out_split_log rows are left to rht_out_kernel (S CTAs share one); shorter
+      // ones are transformed inside the decode kernel by the CTA that completes them.  Measured on B200 (decoder
+      // chain, SmolLM3-3B shapes): an extra launch costs more than the 8192-row transform it takes out of the
+      // kernel's tail (101 vs 90 us per layer), so only blocks beyond 8192 rows are split off.
+      static const int out_split_log = [] {
+        const char* e = getenv("GLQB_FUSED_OUT_SPLIT_LOG");
+        return std::max(RHT_SPLIT_MIN_LOG, std::min(e ? atoi(e) : FUSED_OUT_MAX_LOG + 1, FUSED_OUT_MAX_LOG + 1));
+      }();
       static const int cta_factor = [] { const char* e = getenv("GLQB_FUSED_CTA_FACTOR"); return e ? std::max(1, atoi(e)) : 1; }();
       int scratch = 32;
       for (int i = 0; i < s.count && ok; ++i) {
         const GlqbLinearDesc& d = P->descs[P->order[s.first + i]];
-        for (int b = 0; b < d.n_blocks_m; ++b) {
-          scratch = std::max(scratch, std::min(d.batch, std::max(1, GLQB_RHT_TILE / d.blocks_m[b])) * d.blocks_m[b]);
-          if (d0.in_norm_weight && d.blocks_m[b] > (1 << FUSED_OUT_MAX_LOG)) xr_global = true;   // rht_out_body knows no 1 / rms
-        }
+        for (int b = 0; b < d.n_blocks_m; ++b)           // longer output blocks are left to rht_out_kernel
+          if (d.blocks_m[b] < (1 << out_split_log)) scratch = std::max(scratch, d.blocks_m[b]);
       }
       if (!xr_global)
         for (int i = 0; i < d0.n_blocks_n; ++i) scratch = std::max(scratch, d0.blocks_n[i]);
@@ -474,6 +493,7 @@ static int build_plan(GlqbPlan* P) {
               L.slots = kch;
               L.per_warp = gpw;
               L.xr_global = xr_global ? 1 : 0;
+              L.out_split_log = out_split_log;
               L.ticket_base = P->n_tickets;
               P->n_tickets += L.nbm;
               units += (long long)L.strips * kch;
@@ -622,6 +642,8 @@ static int build_plan(GlqbPlan* P) {
                   "layer %d: the fused norm / activation / residual steps are served by the single-launch decode form only "
                   "(trellis, at most %d tokens, all layers of the call reading one input)", P->order[pos], FUSED_MAX_TOKENS);
   }
+  // a call of a few layers is bound by the latency of one transform item, a sweep of many by their throughput
+  const bool latency = n <= FUSED_MAX_LAYERS;
   for (int pos = 0; pos < n; ++pos) {
     DevLinear& L = P->dev[pos];
     const GlqbLinearDesc& d = P->descs[P->order[pos]];
@@ -635,13 +657,16 @@ static int build_plan(GlqbPlan* P) {
         if (first == pos) {
           L.xr_off = (long long)ws;
           ws = align_up(ws + (size_t)L.batch * L.n * sizeof(__half) * XR_TRELLIS_EXPAND, 1024);
-          add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
+          add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in, latency);
         } else {
           L.xr_off = P->dev[first].xr_off;
         }
       }
       L.part_off = (long long)ws;
       ws = align_up(ws + (size_t)L.slots * L.batch * L.m * sizeof(float), 256);
+      L.rstd_off = (long long)ws;
+      ws += 256;
+      add_rht_items(P->items_out, pos, L.nbm, L.bm_log, L.batch, P->max_elems_out, latency, L.stop_at_yrht ? 64 : L.out_split_log);
       continue;
     }
     int same = -1;
@@ -664,13 +689,13 @@ static int build_plan(GlqbPlan* P) {
       if (L.gemm_tn) {
         const size_t n_tiles = (L.batch + L.gemm_tn - 1) / L.gemm_tn, kchunks = (L.n + GM_TILE_K - 1) / GM_TILE_K;
         ws = align_up(ws + n_tiles * kchunks * L.gemm_tn * 128, 256);
-        add_rht_items(P->items_in_gemm, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
+        add_rht_items(P->items_in_gemm, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in, false);
       } else {
         // E8 with several tokens interleaves groups of 8 tokens: round the token count up
         const size_t xr_tokens = (L.format == GLQB_FMT_E8_SHELL && L.batch > 1) ? (size_t)((L.batch + 7) / 8 * 8) : (size_t)L.batch;
         ws = align_up(ws + xr_tokens * L.n * sizeof(__half) *
                                (L.format == GLQB_FMT_TRELLIS_3INST ? XR_TRELLIS_EXPAND : 1), 256);
-        add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in);
+        add_rht_items(P->items_in, pos, L.nbn, L.bn_log, L.batch, P->max_elems_in, latency);
       }
     }
     L.part_off = (long long)ws;
@@ -680,7 +705,7 @@ static int build_plan(GlqbPlan* P) {
       L.atile_off = (long long)ws;
       ws += (size_t)((L.m + GM_TILE_M - 1) / GM_TILE_M) * ((L.n + GM_TILE_K - 1) / GM_TILE_K) * GM_A_BYTES;
     }
-    add_rht_items(P->items_out, pos, L.nbm, L.bm_log, L.batch, P->max_elems_out);
+    add_rht_items(P->items_out, pos, L.nbm, L.bm_log, L.batch, P->max_elems_out, latency);
   }
   P->ws_bytes = ws;
 
@@ -781,7 +806,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
   if (!P->items_in.empty()) {
-    rht_in_kernel<false><<<(unsigned)P->items_in.size(), rht_threads(P->max_elems_in), rht_smem(P->max_elems_in), stream>>>(
+    rht_in_kernel<false><<<(unsigned)P->items_in.size(), rht_threads(P->max_elems_in, P->max_batch), rht_smem(P->max_elems_in), stream>>>(
         P->d_layers, P->d_items_in, reinterpret_cast<const uint8_t*>(x_base), ws);
   }
   if (!P->items_in_gemm.empty()) {
@@ -819,8 +844,24 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     P->ev_used += 2;
   }
   if (!P->items_out.empty()) {
-    rht_out_kernel<false><<<(unsigned)P->items_out.size(), rht_threads(P->max_elems_out), rht_smem(P->max_elems_out), stream>>>(
-        P->d_layers, P->d_items_out, ws, reinterpret_cast<uint8_t*>(y_base), nullptr);
+    // with programmatic stream serialization: behind the single-launch decode kernel its launch overlaps that
+    // kernel's tail (it waits for it before reading anything)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)P->items_out.size());
+    cfg.blockDim = dim3(rht_threads(P->max_elems_out, P->max_batch));
+    cfg.dynamicSmemBytes = rht_smem(P->max_elems_out);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const DevLinear* dl = P->d_layers;
+    const RhtItem* di = P->d_items_out;
+    const uint8_t* cws = ws;
+    uint8_t* yb = reinterpret_cast<uint8_t*>(y_base);
+    const float* none = nullptr;
+    CUDA_TRY(cudaLaunchKernelEx(&cfg, rht_out_kernel<false>, dl, di, cws, yb, none));
   }
   CUDA_TRY(cudaGetLastError());
   return GLQB_OK;

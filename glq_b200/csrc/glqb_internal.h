@@ -41,7 +41,9 @@ struct DevLinear {
   int y_accumulate;
   int xr_global;         // single-launch form, wide inputs: the transformed activations come from the workspace
                          // (written by rht_in_kernel just before) instead of being recomputed by every CTA
-  long long rstd_off;    // workspace bytes: 1/rms of every token (fused RMSNorm), written by the kernel that transforms x
+  long long rstd_off;    // workspace bytes: 1 / rms of every token (fused RMSNorm applied to the output), written by the
+                         // single-launch kernel for the output transforms that run as a kernel of their own
+  int out_split_log;     // single-launch form: output blocks of at least 2^this rows are transformed by rht_out_kernel
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];
@@ -53,6 +55,9 @@ struct RhtItem {
   int block;
   int tok0;    // first token of the tile this CTA transforms
   int ntok;    // tokens in the tile (the CTA's shared memory holds ntok * block floats)
+  int sub;     // -1: the whole block.  k >= 0 (decode-sized plans, blocks of 4096 values or more): the CTA produces
+               // the k-th run of 1024 outputs only, as H_1024( sum_k' H_S[k][k'] * input run k' ) — H_(S*1024) =
+               // H_S (x) H_1024 with the short factor applied first, so S CTAs share a long block without talking
 };
 
 #ifndef GLQB_RHT_TILE

@@ -141,6 +141,15 @@ __device__ __forceinline__ long long xr_index_e8(long long token, int col, int n
 #define GLQB_RHT_MINB 4
 #endif
 constexpr int RHT_THREADS = GLQB_RHT_THREADS;
+// longest array the transform kernels hand to the shuffle-based transform (their 64-register budget holds 8
+// values per thread plus what travels with them); longer arrays keep the tiled passes
+constexpr int RHT_FAST_MAX_LOG = 11;
+// The low-latency forms (shuffle transform per token, split blocks) serve launches of a few items, where the
+// time of one item is the time of the launch; launches of many items keep the tiled passes, which move more
+// values per clock (measured: 252 layers, one token: 33 us for both transforms tiled, 77 us in the low-latency form).
+constexpr int RHT_LATENCY_MAX_ITEMS = 128;
+constexpr int RHT_SPLIT_LOG = 10;                // run length of the split form (RhtItem::sub): 1024
+constexpr int RHT_SPLIT_MIN_LOG = 12;            // blocks of at least 4096 values are split in decode-sized plans
 
 constexpr int FUSED_MAX_TOKENS_C = 8;     // tokens served by the single-launch decode form and its fused steps
 
@@ -234,6 +243,77 @@ __device__ __forceinline__ void rht_in_body(const DevLinear& L, const RhtItem it
     for (int o = threadIdx.x; o < total; o += blockDim.x) store1(o >> logbs, o & (bs - 1), load1(o >> logbs, o & (bs - 1)));
     return;
   }
+  if (it.sub >= 0) {
+    // split form: this CTA produces outputs [sub * 1024, sub * 1024 + 1024) of the block (see RhtItem::sub)
+    const int S = bs >> RHT_SPLIT_LOG, k = it.sub;
+    for (int row = 0; row < it.ntok; ++row) {
+      const long long xt0 = L.x_off + (long long)(it.tok0 + row) * L.x_stride;
+      float rstd = 1.f;
+      if (L.in_norm_w) rstd = token_rstd(L, x_base, xt0, fbuf);
+      __syncthreads();
+      auto ld1 = [&](int i) -> float {
+        float a = 0.f;
+        for (int kk = 0; kk < S; ++kk) {
+          const float v = load1(row, (kk << RHT_SPLIT_LOG) + i);
+          a += (__popc(k & kk) & 1) ? -v : v;
+        }
+        return a;
+      };
+      auto ld4 = [&](int i0, float (&q)[4]) {
+        q[0] = q[1] = q[2] = q[3] = 0.f;
+        for (int kk = 0; kk < S; ++kk) {
+          float t[4];
+          const int i = (kk << RHT_SPLIT_LOG) + i0;
+          if (vec_ok && !fusions && off + i + 3 < L.in_f) {
+            load_act4(x_base, xt0 + off + i, L.x_dtype, t);
+            const uint2 s4 = *reinterpret_cast<const uint2*>(L.sv + off + i);
+            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+            const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+            t[0] *= a.x; t[1] *= a.y; t[2] *= c.x; t[3] *= c.y;
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) t[j] = load1(row, i + j);
+          }
+          const float sg = (__popc(k & kk) & 1) ? -1.f : 1.f;
+          q[0] += sg * t[0]; q[1] += sg * t[1]; q[2] += sg * t[2]; q[3] += sg * t[3];
+        }
+      };
+      auto none = [](int) -> float { return 0.f; };
+      auto st = [&](int i, float val, float) { store1(row, (k << RHT_SPLIT_LOG) + i, val * rstd); };
+      fht_fast<RHT_SPLIT_LOG>(fbuf, RHT_SPLIT_LOG, ld1, ld4, none, st);
+      __syncthreads();
+    }
+    return;
+  }
+  if (blockDim.x == 256 && L.batch <= FUSED_MAX_TOKENS_C && gridDim.x <= RHT_LATENCY_MAX_ITEMS && logbs >= 5 && logbs <= RHT_FAST_MAX_LOG) {
+    // Decode-sized tile (a few tokens): latency matters, not throughput.  Every token's block is transformed by
+    // all 256 threads with the shuffle-based transform: one round of loads, one shared-memory exchange.
+    const bool plain_vec = vec_ok && !fusions;
+    for (int row = 0; row < it.ntok; ++row) {
+      const long long xt0 = L.x_off + (long long)(it.tok0 + row) * L.x_stride;
+      float rstd = 1.f;
+      if (L.in_norm_w) rstd = token_rstd(L, x_base, xt0, fbuf);
+      __syncthreads();
+      auto ld1 = [&](int i) -> float { return load1(row, i); };
+      auto ld4 = [&](int i0, float (&q)[4]) {
+        if (plain_vec && off + i0 + 3 < L.in_f) {
+          load_act4(x_base, xt0 + off + i0, L.x_dtype, q);
+          const uint2 s4 = *reinterpret_cast<const uint2*>(L.sv + off + i0);
+          const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+          const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+          q[0] *= a.x; q[1] *= a.y; q[2] *= c.x; q[3] *= c.y;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) q[k] = load1(row, i0 + k);
+        }
+      };
+      auto none = [](int) -> float { return 0.f; };
+      auto st = [&](int i, float val, float) { store1(row, i, val * rstd); };
+      fht_fast<RHT_FAST_MAX_LOG>(fbuf, logbs, ld1, ld4, none, st);
+      __syncthreads();
+    }
+    return;
+  }
   if (fusions) {
     // fused RMSNorm / gated activation in front of the transform (decode: one token per CTA and block):
     // 1 / rms of the token is folded into the stored values
@@ -286,7 +366,7 @@ __device__ __forceinline__ RhtItem rht_single_item(const RhtSingle& S, int batch
   int k = 0;
   while (k + 1 < S.n_blocks && (int)blockIdx.x >= S.first_cta[k + 1]) ++k;
   const int tok0 = ((int)blockIdx.x - S.first_cta[k]) * S.tile_tokens[k];
-  return RhtItem{0, k, tok0, min(S.tile_tokens[k], batch - tok0)};
+  return RhtItem{0, k, tok0, min(S.tile_tokens[k], batch - tok0), -1};
 }
 static __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_in_single_kernel(const __grid_constant__ DevLinear L,
                                                                     const __grid_constant__ RhtSingle S,
@@ -343,6 +423,63 @@ __device__ __forceinline__ void rht_out_body(const DevLinear& L, const RhtItem i
   }
   const bool vec_ok = (m & 3) == 0 && (off & 3) == 0;
   const int tok0 = it.tok0;
+  if (it.sub >= 0) {
+    // split form: this CTA produces outputs [sub * 1024, sub * 1024 + 1024) of the block (see RhtItem::sub)
+    const int S = bs >> RHT_SPLIT_LOG, k = it.sub;
+    const float rs = rsqrtf((float)bs);
+    for (int trow = 0; trow < it.ntok; ++trow) {
+      // a fused RMSNorm of the single-launch kernel scales the output: its 1 / rms sits in the workspace
+      const float in_scale = (L.in_norm_w && !L.xr_global) ? reinterpret_cast<const float*>(ws + L.rstd_off)[tok0 + trow] : 1.f;
+      const long long o0 = L.y_off + (long long)(tok0 + trow) * L.y_stride + off + (k << RHT_SPLIT_LOG);
+      auto ld1 = [&](int i) -> float {
+        float a = 0.f;
+        for (int kk = 0; kk < S; ++kk) {
+          const float v = load1(trow, (kk << RHT_SPLIT_LOG) + i);
+          a += (__popc(k & kk) & 1) ? -v : v;
+        }
+        return a * in_scale;
+      };
+      auto ld4 = [&](int i0, float (&q)[4]) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) q[j] = ld1(i0 + j);
+      };
+      const int r0 = off + (k << RHT_SPLIT_LOG);
+      auto pre = [&](int i) -> float { return (r0 + i < L.out_f) ? __half2float(L.su[r0 + i]) : 0.f; };
+      auto st = [&](int i, float val, float sign) {
+        if (r0 + i < L.out_f) {
+          float r = val * rs * sign;
+          if (L.y_accumulate) r += load_act(y_base, o0 + i, L.y_dtype);
+          store_act(y_base, o0 + i, L.y_dtype, r);
+        }
+      };
+      fht_fast<RHT_SPLIT_LOG>(fbuf, RHT_SPLIT_LOG, ld1, ld4, pre, st);
+      __syncthreads();
+    }
+    return;
+  }
+  if (blockDim.x == 256 && L.batch <= FUSED_MAX_TOKENS_C && gridDim.x <= RHT_LATENCY_MAX_ITEMS && logbs >= 5 && logbs <= RHT_FAST_MAX_LOG) {
+    // decode-sized tile: the low-latency transform, token by token (see rht_in_body)
+    const float rs = rsqrtf((float)bs);
+    for (int trow = 0; trow < it.ntok; ++trow) {
+      const long long o0 = L.y_off + (long long)(tok0 + trow) * L.y_stride + off;
+      auto ld1 = [&](int i) -> float { return load1(trow, i); };
+      auto ld4 = [&](int i0, float (&q)[4]) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) q[k] = load1(trow, i0 + k);
+      };
+      auto pre = [&](int i) -> float { return (off + i < L.out_f) ? __half2float(L.su[off + i]) : 0.f; };
+      auto st = [&](int i, float val, float sign) {
+        if (off + i < L.out_f) {
+          float r = val * rs * sign;
+          if (L.y_accumulate) r += load_act(y_base, o0 + i, L.y_dtype);
+          store_act(y_base, o0 + i, L.y_dtype, r);
+        }
+      };
+      fht_fast<RHT_FAST_MAX_LOG>(fbuf, logbs, ld1, ld4, pre, st);
+      __syncthreads();
+    }
+    return;
+  }
   auto load32 = [&](int trow, int i0, float (&v)[32]) {
     const int row0 = off + i0;
     const long long token = tok0 + trow;
@@ -430,6 +567,10 @@ __global__ void __launch_bounds__(RHT_THREADS, GLQB_RHT_MINB) rht_out_kernel(con
                                                               uint8_t* __restrict__ y_base,
                                                               const float* __restrict__ yrht_in) {
   extern __shared__ float fbuf[];
+  // launched with programmatic stream serialization behind the decode kernels: wait for them here; the next
+  // kernel of the stream may start its prologue
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const RhtItem it = items[blockIdx.x];
   rht_out_body<FROM_F32>(layers[it.layer], it, ws, y_base, yrht_in, fbuf);
 }
@@ -703,8 +844,8 @@ __host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, in
 // Output transform of one (layer, Hadamard block, token) by the CTA that completed the block, with the
 // low-latency transform; same butterflies in the same order as rht_out_body, hence the same bits.  Blocks of up
 // to 8192 rows (longer ones go through rht_out_body).
-constexpr int FUSED_IN_MAX_LOG = 12;             // longest input block transformed inside the kernel: 4096
-constexpr int FUSED_OUT_MAX_LOG = 13;            // longest output block of the low-latency transform: 8192
+constexpr int FUSED_IN_MAX_LOG = 13;             // longest input block of the in-kernel shuffle transform: 8192
+constexpr int FUSED_OUT_MAX_LOG = 13;            // longest output block the kernel can transform itself: 8192 (see out_split_log)
 
 __device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int tok, float in_scale,
                                                 const uint8_t* __restrict__ ws, uint8_t* __restrict__ y_base, float* fbuf) {
@@ -902,6 +1043,9 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
     }
   }
 
+  if (blockIdx.x == 0 && threadIdx.x < batch && L0.in_norm_w && !L0.xr_global)      // for rht_out_kernel (long blocks)
+    for (int li = 0; li < n_layers; ++li) reinterpret_cast<float*>(ws + layers[li].rstd_off)[threadIdx.x] = rstd_s[threadIdx.x];
+
   // ---- phase 2: work units
   const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
   while (u < total_units) {
@@ -967,9 +1111,11 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
       while (b + 1 < L.nbm && strip * 32 >= L.bm_off[b + 1]) ++b;
       const int need = ((1 << L.bm_log[b]) >> 5) * kch;
       // release (the CTA's stores, ordered before this by the barrier) and acquire (the other CTAs' stores,
-      // released before their increments) in one device-scope atomic; nobody ever waits on a ticket
-      int old;
-      asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(tickets + L.ticket_base + b) : "memory");
+      // released before their increments) in one device-scope atomic; nobody ever waits on a ticket.
+      // Long output blocks are left to rht_out_kernel, launched right behind this kernel: S CTAs share one there.
+      int old = -2;
+      if (L.bm_log[b] < L.out_split_log || L.stop_at_yrht)
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(tickets + L.ticket_base + b) : "memory");
       if (old + 1 == need) {
         tickets[L.ticket_base + b] = 0;                     // ready for the next run
         if (n_todo < FUSED_MAX_TODO) todo[n_todo++] = (li_now << 8) | b;
@@ -988,11 +1134,11 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
         fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf);
         __syncthreads();
       }
-    } else {
+    } else {   // not reached: blocks longer than the split threshold are transformed by rht_out_kernel
       const int bs = 1 << L.bm_log[b];
       const int tt = max(1, min(batch, scratch_elems / bs));
       for (int t0 = 0; t0 < batch; t0 += tt) {
-        rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0)}, ws, y_base, nullptr, fbuf);
+        rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0), -1}, ws, y_base, nullptr, fbuf);
         __syncthreads();
       }
     }
