@@ -263,6 +263,25 @@ def kernel_name(W):
     return f"e8_mv_smem_kernel<{ns},{nb}>" if resident else f"e8_mv_kernel<{ns},{nb}>"
 
 
+_COMM = {}
+
+
+def rank_comm(D: Dist):
+    """The communicator of the library's own sums over ranks (glq_b200.comm), built once per process; None (and the
+    reason in _COMM["why"]) when the peers' memory cannot be mapped here, in which case NCCL does the sums."""
+    if "c" not in _COMM:
+        _COMM["c"], _COMM["why"] = None, None
+        if D.world > 1 and os.environ.get("GLQB_BENCH_NCCL") != "1":
+            try:
+                from glq_b200.comm import Comm
+                _COMM["c"] = Comm.from_process_group(max_floats=1 << 20, device=D.device)
+            except Exception as e:          # e.g. CUDA IPC closed to this container
+                _COMM["why"] = f"{type(e).__name__}: {e}"
+        elif D.world > 1:
+            _COMM["why"] = "GLQB_BENCH_NCCL=1"
+    return _COMM["c"]
+
+
 def tp_check(D: Dist, W):
     """One row-parallel layer: every rank's fp32 partial is gathered, the partials are added in rank order
     0..G-1, and the all-reduced output must equal that sum within 2e-3 of its largest value."""
@@ -296,10 +315,17 @@ def run_plan_bench(name, D: Dist, args, steps, tokens=None, layers=None, clocks=
     plan, x, y = W["plan"], W["x"], W["y"]
     code_bytes, flops = D.sum_int(W["code_bytes"], W["flops"])
 
+    comm = rank_comm(D) if W["reduce_view"] is not None else None
+    if comm is not None and W["reduce_view"].numel() > comm.max_floats:
+        comm = None                                   # prefill-sized sums stay with NCCL
+
     def step():
         plan.run(x, y)
         if W["reduce_view"] is not None:
-            dist.all_reduce(W["reduce_view"])
+            if comm is not None:
+                comm.all_reduce_(W["reduce_view"])    # one launch: stores into every rank's area, flags, fixed-order sum
+            else:
+                dist.all_reduce(W["reduce_view"])
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -354,6 +380,11 @@ def run_plan_bench(name, D: Dist, args, steps, tokens=None, layers=None, clocks=
         rec["clocks"] = clock_rec
     if checked:
         rec["tp_check"] = checked
+    if W["reduce_view"] is not None:
+        rec["rank_sum"] = ("glqb_comm_all_reduce (one launch, NVLink stores, fixed rank order)" if comm is not None
+                           else "ncclAllReduce" + (f" ({_COMM.get('why')})" if _COMM.get("why") else " (message larger than the communicator's area)"))
+        if comm is not None:
+            comm.check_status()
     plan.close()
     del W, plan, x, y
     torch.cuda.empty_cache()
@@ -500,6 +531,8 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
     norm1 = [torch.ones(hidden, device=dev, dtype=torch.bfloat16) for _ in Ls]
     norm2 = [torch.ones(hidden, device=dev, dtype=torch.bfloat16) for _ in Ls]
 
+    comm = rank_comm(D)
+
     def lin(L, x, **kw):
         return ops.fused_linear_trellis_3inst(x, L.sv, L.su, L.codes[0], None, None, None, None, L.wscale,
                                               L.n, L.m, L.n, L.m, **kw)
@@ -515,6 +548,8 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
             a = qkv[:, :d["q"].m]                                     # attention stand-in: a view, (1, 2048 / world)
             if world == 1:
                 lin(d["o"], a, accumulate_into=h)                     # o projection + residual add: one launch
+            elif comm is not None:
+                lin(d["o"], a, accumulate_into=h, reduce_over=comm)   # ... and the sum over ranks, same launch
             else:
                 o = lin(d["o"], a, out_dtype=torch.float32)
                 dist.all_reduce(o)
@@ -522,6 +557,8 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
             gu = shards(h, (d["gate"], d["up"]), w2)                  # RMSNorm + gate/up: one launch
             if world == 1:
                 lin(d["down"], gu, gated_act=0, accumulate_into=h)    # silu(gate) * up + down + residual: one launch
+            elif comm is not None:
+                lin(d["down"], gu, gated_act=0, accumulate_into=h, reduce_over=comm)
             else:
                 dn = lin(d["down"], gu, gated_act=0, out_dtype=torch.float32)
                 dist.all_reduce(dn)
@@ -532,7 +569,7 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
         out = forward(h0)
     D.sync()
     graph = None
-    if world == 1:
+    if world == 1 or comm is not None:
         try:
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):
@@ -560,7 +597,8 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
                      f"silu(gate) * up + down + residual as four calls (attention replaced by a view of the q output; "
                      f"{'one CUDA graph' if graph is not None else 'eager launches'}); "
                      f"{total_bytes / 1e6:.0f} MB of codes per step, larger than L2"
-                     + (f"; tp{world}: fp32 all-reduce after o and down" if world > 1 else ""),
+                     + ((f"; tp{world}: o and down summed over the ranks inside their decode kernels (glq_b200.comm)" if comm is not None
+                         else f"; tp{world}: fp32 NCCL all-reduce after o and down ({_COMM.get('why')})") if world > 1 else ""),
            "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h0.numel() * 2,
                    "d2h_bytes_per_step": out.numel() * 2},
            "gpu_launches": glq_launches * steps, "glq_launches_per_layer": glq_launches / n_layers,
@@ -568,6 +606,29 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
                                                   "activation and residual adds",
                         "achieved": gbs / world, "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s",
                         "frac": gbs / world / hbm, "kernel_ms": ms, "bytes_per_launch": code_bytes, "traffic": None}}
+    if world > 1:
+        # every rank must hold the same hidden state; and one o projection summed inside the kernel must equal the
+        # rank-ordered sum of the ranks' own fp32 outputs
+        outs = [torch.empty_like(out) for _ in range(world)]
+        dist.all_gather(outs, out)
+        same = all(torch.equal(outs[0], o) for o in outs) and bool(torch.isfinite(out.float()).all())
+        chk = {"chain_output_identical_on_all_ranks": same}
+        if comm is not None:
+            d0 = Ls[0]
+            a = h0[:, :d0["o"].n].contiguous()
+            mine = lin(d0["o"], a, out_dtype=torch.float32)
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            fixed = torch.zeros_like(mine)
+            for p_ in parts:
+                fixed += p_
+            got = lin(d0["o"], a, out_dtype=torch.float32, reduce_over=comm)
+            torch.cuda.synchronize()
+            chk["in_kernel_sum_max_rel_diff"] = ((got - fixed).abs().max() / fixed.abs().max().clamp_min(1e-30)).item()
+            same = same and chk["in_kernel_sum_max_rel_diff"] <= 2e-3
+            comm.check_status()
+        chk["result"] = "ok" if same else "FAILED"
+        rec["tp_check"] = chk
     del graph
     ops.clear_caches()
     torch.cuda.empty_cache()

@@ -26,6 +26,9 @@ EXPORTS = [
     "glqb_trellis_linear_noalloc", "glqb_noalloc_scratch_bytes",
     "glqb_moe_plan_create", "glqb_moe_plan_workspace_bytes", "glqb_moe_plan_code_bytes", "glqb_moe_plan_run",
     "glqb_moe_plan_status", "glqb_moe_plan_destroy", "glqb_moe_plan_set_timing", "glqb_moe_plan_kernel_ms",
+    "glqb_comm_create", "glqb_comm_handle", "glqb_comm_connect", "glqb_comm_connect_local", "glqb_comm_set_timeout_ms",
+    "glqb_comm_max_floats", "glqb_comm_all_reduce", "glqb_comm_status", "glqb_comm_epoch", "glqb_comm_destroy",
+    "glqb_plan_set_comm",
 ]
 
 
@@ -150,6 +153,28 @@ def load() -> C.CDLL:
     lib.glqb_moe_plan_kernel_ms.restype = C.c_int
     lib.glqb_moe_plan_destroy.argtypes = [vp]
     lib.glqb_moe_plan_destroy.restype = None
+    lib.glqb_comm_create.argtypes = [i32, i32, i64, C.POINTER(vp)]
+    lib.glqb_comm_create.restype = C.c_int
+    lib.glqb_comm_handle.argtypes = [vp, vp, i32]
+    lib.glqb_comm_handle.restype = C.c_int
+    lib.glqb_comm_connect.argtypes = [vp, C.c_char_p, i32]
+    lib.glqb_comm_connect.restype = C.c_int
+    lib.glqb_comm_connect_local.argtypes = [vp, C.POINTER(vp)]
+    lib.glqb_comm_connect_local.restype = C.c_int
+    lib.glqb_comm_set_timeout_ms.argtypes = [vp, i32]
+    lib.glqb_comm_set_timeout_ms.restype = C.c_int
+    lib.glqb_comm_max_floats.argtypes = [vp]
+    lib.glqb_comm_max_floats.restype = i64
+    lib.glqb_comm_all_reduce.argtypes = [vp, vp, i64, vp]
+    lib.glqb_comm_all_reduce.restype = C.c_int
+    lib.glqb_comm_status.argtypes = [vp, C.POINTER(i32), i32]
+    lib.glqb_comm_status.restype = C.c_int
+    lib.glqb_comm_epoch.argtypes = [vp, C.POINTER(i32)]
+    lib.glqb_comm_epoch.restype = C.c_int
+    lib.glqb_comm_destroy.argtypes = [vp]
+    lib.glqb_comm_destroy.restype = None
+    lib.glqb_plan_set_comm.argtypes = [vp, vp]
+    lib.glqb_plan_set_comm.restype = C.c_int
     lib.glqb_last_error.argtypes = []
     lib.glqb_last_error.restype = C.c_char_p
     lib.glqb_version.argtypes = []

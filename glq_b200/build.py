@@ -9,7 +9,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libglq_b200.so")
-SOURCES = ["glqb_api.cu", "glqb_gemm_inst.cu", "glqb_fused.cu", "glqb_noalloc.cu", "glqb_moe.cu"]
+SOURCES = ["glqb_api.cu", "glqb_gemm_inst.cu", "glqb_fused.cu", "glqb_noalloc.cu", "glqb_moe.cu", "glqb_comm.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "--expt-relaxed-constexpr"]
 

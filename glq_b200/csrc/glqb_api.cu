@@ -60,6 +60,7 @@ struct GlqbPlan {
   GemmItem* d_gemm_items = nullptr;
   int* d_status = nullptr;
   int* d_tickets = nullptr;      // completion tickets of the single-launch form, all zero between runs
+  const GlqbComm* comm = nullptr;  // tensor-parallel ranks whose outputs the single-launch kernel sums (glqb_plan_set_comm)
   int n_tickets = 0;
   int max_batch_gemm = 1;
   size_t ws_bytes = 0;
@@ -824,7 +825,7 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
   for (const Segment& s : P->segs) {
     if (s.fused) {
       fused_launch(s, P->dev.data() + s.first, reinterpret_cast<const uint8_t*>(x_base), reinterpret_cast<uint8_t*>(y_base),
-                   ws, P->d_tickets, stream);
+                   ws, P->d_tickets, P->comm ? comm_dev(P->comm) : nullptr, stream);
     } else if (s.tn) {
       gemm_launch(s, P->d_layers, P->d_gemm_items + s.item_first, ws, P->d_status, P->sm_count, stream);
     } else if (s.smem_table) {
@@ -864,6 +865,43 @@ int glqb_plan_run(GlqbPlan* P, const void* x_base, void* y_base, void* workspace
     CUDA_TRY(cudaLaunchKernelEx(&cfg, rht_out_kernel<false>, dl, di, cws, yb, none));
   }
   CUDA_TRY(cudaGetLastError());
+  return GLQB_OK;
+}
+
+int glqb_plan_set_comm(GlqbPlan* P, GlqbComm* comm) {
+  if (!P) return fail(GLQB_E_INVALID, "plan_set_comm: null plan");
+  if (!comm) {
+    for (DevLinear& L : P->dev) L.reduce = 0;
+    P->comm = nullptr;
+    return GLQB_OK;
+  }
+  const CommDev* C = comm_dev(comm);
+  if (!C) return fail(GLQB_E_INVALID, "plan_set_comm: the communicator is not connected");
+  // the sum runs where one CTA holds a whole output block: the single-launch form with every block inside the kernel
+  if (!P->items_out.empty()) return fail(GLQB_E_INVALID, "plan_set_comm: the plan transforms outputs in a kernel of its own");
+  long long floats = 0;
+  int units = 0;
+  for (const Segment& s : P->segs) {
+    if (!s.fused)
+      return fail(GLQB_E_INVALID, "plan_set_comm: only the single-launch decode form (trellis, at most %d tokens) sums over ranks",
+                  FUSED_MAX_TOKENS);
+    for (int i = s.first; i < s.first + s.count; ++i) {
+      DevLinear& L = P->dev[i];
+      if (L.stop_at_yrht) return fail(GLQB_E_INVALID, "plan_set_comm: layers that stop before the output transform have no sum");
+      L.comm_off = (int)floats;
+      L.comm_unit_base = units;
+      floats += (long long)L.m * L.batch;
+      units += L.nbm;
+    }
+    // every launch restarts at piece 0: launches of one stream follow one another, and areas alternate by epoch
+    if (floats > C->max_floats || units > COMM_MAX_UNITS)
+      return fail(GLQB_E_INVALID, "plan_set_comm: a launch exchanges %lld floats in %d pieces; the communicator holds %d and %d",
+                  floats, units, C->max_floats, COMM_MAX_UNITS);
+    floats = 0;
+    units = 0;
+  }
+  for (DevLinear& L : P->dev) L.reduce = 1;
+  P->comm = comm;
   return GLQB_OK;
 }
 

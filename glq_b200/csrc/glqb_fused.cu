@@ -7,7 +7,7 @@
 
 namespace glqb {
 
-typedef void (*FusedKernel)(const FusedLayers, int, int, int, const uint8_t*, uint8_t*, uint8_t*, int*);
+typedef void (*FusedKernel)(const FusedLayers, int, int, int, const uint8_t*, uint8_t*, uint8_t*, int*, const CommDev);
 static FusedKernel trellis_fused_pick(int k1, int k2) {
 #define F_CASE(A, B) if (k1 == A && k2 == B) return trellis_fused_kernel<A, B>;
 #ifdef GLQB_FAST_BUILD   /* developer builds for kernel experiments: the 4-bit single-stage rate only */
@@ -30,7 +30,7 @@ cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* r
 }
 
 void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_base, uint8_t* y_base, uint8_t* ws,
-                  int* tickets, cudaStream_t stream) {
+                  int* tickets, const CommDev* comm, cudaStream_t stream) {
   // Launched with programmatic stream serialization: when the previous kernel of the stream is another
   // single-launch decode kernel, this one's prologue (scheduling, table reads, the first weight loads) overlaps
   // its tail; the kernel itself waits (griddepcontrol.wait) before it reads activations or writes anything.
@@ -47,8 +47,11 @@ void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_ba
   cfg.numAttrs = pdl ? 1 : 0;
   FusedLayers T;
   memcpy(T.L, layers, sizeof(DevLinear) * (size_t)s.count);          // `layers`: the plan's HOST copy of the segment's entries
+  CommDev C;
+  memset(&C, 0, sizeof(C));                                           // world 0: no sum over ranks
+  if (comm) C = *comm;
   cudaLaunchKernelEx(&cfg, trellis_fused_pick(s.k1, s.k2), T, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
-                     tickets);
+                     tickets, C);
 }
 
 }  // namespace glqb

@@ -44,6 +44,9 @@ struct DevLinear {
   long long rstd_off;    // workspace bytes: 1 / rms of every token (fused RMSNorm applied to the output), written by the
                          // single-launch kernel for the output transforms that run as a kernel of their own
   int out_split_log;     // single-launch form: output blocks of at least 2^this rows are transformed by rht_out_kernel
+  int reduce;            // single-launch form, tensor-parallel ranks: the output is summed over the ranks in the kernel
+  int comm_off;          // ... first float of this layer's pieces in the receive areas, and its first piece number
+  int comm_unit_base;
   int nbn, nbm;
   int bn_off[GLQB_MAX_BLOCKS], bn_log[GLQB_MAX_BLOCKS];
   int bm_off[GLQB_MAX_BLOCKS], bm_log[GLQB_MAX_BLOCKS];
@@ -76,6 +79,7 @@ void set_error_message(const char* msg);
 
 // Status word of a plan: 0 = every kernel finished normally.  A role of the GEMM kernel whose bounded wait
 // ran out writes its code here (never a trap): 2 producers, 3 MMA issuer, 4 activation loader, 5 epilogue.
-enum : int { ST_OK = 0, ST_GAVE_UP_PRODUCER = 2, ST_GAVE_UP_MMA = 3, ST_GAVE_UP_LOADER = 4, ST_GAVE_UP_EPILOGUE = 5 };
+// 6: a wait for a tensor-parallel peer ran out (communicator status word, glqb_comm.cuh).
+enum : int { ST_OK = 0, ST_GAVE_UP_PRODUCER = 2, ST_GAVE_UP_MMA = 3, ST_GAVE_UP_LOADER = 4, ST_GAVE_UP_EPILOGUE = 5, ST_GAVE_UP_PEER = 6 };
 
 }  // namespace glqb

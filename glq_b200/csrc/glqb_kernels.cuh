@@ -4,6 +4,7 @@
 #include "glqb_internal.h"
 #include "glqb_decode.cuh"
 #include "glqb_fht.cuh"
+#include "glqb_comm.cuh"
 
 namespace glqb {
 
@@ -847,8 +848,12 @@ __host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, in
 constexpr int FUSED_IN_MAX_LOG = 13;             // longest input block of the in-kernel shuffle transform: 8192
 constexpr int FUSED_OUT_MAX_LOG = 13;            // longest output block the kernel can transform itself: 8192 (see out_split_log)
 
+// `C` (tensor-parallel ranks, row-parallel layer): instead of being written to y, the block's transformed values are
+// stored into every rank's receive area at float offset `piece` (this rank's source slot of epoch `comm_e`); the
+// caller exchanges flags and adds the ranks' blocks afterwards.
 __device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int tok, float in_scale,
-                                                const uint8_t* __restrict__ ws, uint8_t* __restrict__ y_base, float* fbuf) {
+                                                const uint8_t* __restrict__ ws, uint8_t* __restrict__ y_base, float* fbuf,
+                                                const CommDev* C = nullptr, int comm_e = 0, long long piece = 0) {
   const int logbs = L.bm_log[b], off = L.bm_off[b];
   const int m = L.m, cnt = L.fixed_slots, out_f = L.out_f, y_dtype = L.y_dtype;
   const long long slot_stride = (long long)L.batch * m;
@@ -864,6 +869,7 @@ __device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int t
   };
   auto load4 = [&](int i0, float (&q)[4]) {
     float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+
     for (int k = 0; k < cnt; ++k) {
       const float4 t = __ldcg(reinterpret_cast<const float4*>(part + i0 + k * slot_stride));
       s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
@@ -890,6 +896,20 @@ __device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int t
       store_act(y_base, yo + i, y_dtype, r);
     }
   };
+  if (C) {
+    float* dst[COMM_MAX_RANKS];
+#pragma unroll
+    for (int r = 0; r < COMM_MAX_RANKS; ++r) dst[r] = r < C->world ? comm_slot(*C, r, comm_e, C->rank) + piece : nullptr;
+    const int world = C->world;
+    auto push = [&](int i, float val, float sign) {                    // consecutive threads, consecutive i
+      const float r = val * rs * sign;
+#pragma unroll
+      for (int k = 0; k < COMM_MAX_RANKS; ++k)
+        if (k < world) dst[k][i] = r;
+    };
+    fht_fast<FUSED_OUT_MAX_LOG>(fbuf, logbs, load1, load4, pre, push);
+    return;
+  }
   fht_fast<FUSED_OUT_MAX_LOG>(fbuf, logbs, load1, load4, pre, store);
 }
 
@@ -907,7 +927,7 @@ template <int K1, int K2>
 __global__ void __launch_bounds__(MV_THREADS, GLQB_FUSED_MINB)
 trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int total_units, int scratch_elems,
                      const uint8_t* __restrict__ x_base, uint8_t* __restrict__ y_base, uint8_t* __restrict__ ws,
-                     int* __restrict__ tickets) {
+                     int* __restrict__ tickets, const __grid_constant__ CommDev C) {
   extern __shared__ __align__(16) uint8_t fsm[];
   const DevLinear* layers = T.L;
   const DevLinear& L0 = layers[0];
@@ -954,6 +974,8 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
   // plan's table.  Both are no-ops when the launch did not ask for the overlap.
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  // tensor-parallel ranks (C.world > 1): the outputs are summed over the ranks inside this kernel (phase 3)
+  const int comm_e = C.world > 1 ? comm_epoch(C) : 0;
 
   // ---- phase 1: the transformed activations of the shared input, in shared memory
   __shared__ float rstd_s[FUSED_MAX_TOKENS];                 // fused RMSNorm: 1 / rms per token, applied to the OUTPUT
@@ -1130,9 +1152,42 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
     const int li = todo[k] >> 8, b = todo[k] & 255;
     const DevLinear& L = layers[li];
     if (L.bm_log[b] <= FUSED_OUT_MAX_LOG) {
-      for (int tok = 0; tok < batch; ++tok) {
-        fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf);
+      if (C.world > 1 && L.reduce) {
+        // Row-parallel layer: every rank transforms its own partial result (its own signs), stores the block into
+        // all ranks' receive areas, and after the flag exchange adds the ranks' blocks in rank order: the same bits
+        // on every rank, residual add included.
+        const int logbs = L.bm_log[b], bs = 1 << logbs, off = L.bm_off[b];
+        const long long piece = (long long)L.comm_off + (long long)off * batch;            // floats; a multiple of 32
+        for (int tok = 0; tok < batch; ++tok) {
+          fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf, &C, comm_e, piece + ((long long)tok << logbs));
+          __syncthreads();
+        }
+        comm_signal_and_wait(C, comm_e, L.comm_unit_base + b);
+        const float* src = comm_slot(C, C.rank, comm_e, 0) + piece;
+        const bool accumulate = L.y_accumulate != 0;
+        for (int i = threadIdx.x * 4; i < bs * batch; i += blockDim.x * 4) {
+          float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int r = 0; r < C.world; ++r) {
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * C.max_floats + i));
+            a4.x += t.x; a4.y += t.y; a4.z += t.z; a4.w += t.w;
+          }
+          const float o[4] = {a4.x, a4.y, a4.z, a4.w};
+          const int tok = i >> logbs, j = i & (bs - 1);
+          const long long yo = L.y_off + (long long)tok * L.y_stride + off + j;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (off + j + c < L.out_f) {
+              float r = o[c];
+              if (accumulate) r += load_act(y_base, yo + c, L.y_dtype);
+              store_act(y_base, yo + c, L.y_dtype, r);
+            }
+        }
         __syncthreads();
+      } else {
+        for (int tok = 0; tok < batch; ++tok) {
+          fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf);
+          __syncthreads();
+        }
       }
     } else {   // not reached: blocks longer than the split threshold are transformed by rht_out_kernel
       const int bs = 1 << L.bm_log[b];
@@ -1143,6 +1198,7 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
       }
     }
   }
+  if (C.world > 1) comm_cta_done(C, comm_e);
 }
 
 // ---------------------------------------------------------------------------------------------

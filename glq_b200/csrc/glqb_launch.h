@@ -3,6 +3,7 @@
 // glqb_fused.cu: single-launch decode).  Splitting them keeps every unit's compile time in check.
 #pragma once
 #include "glqb_internal.h"
+#include "glqb_comm.cuh"
 
 namespace glqb {
 
@@ -46,7 +47,11 @@ void gemm_launch(const Segment& s, const DevLinear* layers, const GemmItem* item
 bool fused_available(int k1, int k2);
 cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* resident_ctas_out);
 // `layers`: HOST copy of the segment's table entries (they are passed to the kernel by value)
+// `comm`: null, or the communicator whose ranks' outputs are summed inside the kernel (layers with DevLinear::reduce)
 void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_base, uint8_t* y_base, uint8_t* ws,
-                  int* tickets, cudaStream_t stream);
+                  int* tickets, const CommDev* comm, cudaStream_t stream);
+
+// ---- glqb_comm.cu
+const CommDev* comm_dev(const GlqbComm* c);                  // null until the communicator is connected
 
 }  // namespace glqb

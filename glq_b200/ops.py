@@ -137,7 +137,7 @@ def clear_caches() -> None:
 
 
 def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_tokens=DECODE_MAX_TOKENS,
-                y_offset: int = 0, out_cols: Optional[int] = None, accumulate: bool = False) -> None:
+                y_offset: int = 0, out_cols: Optional[int] = None, accumulate: bool = False, comm=None) -> None:
     """Run a single-layer op over x2d (B, in) into out[:, y_offset : y_offset + out_cols].  Up to 64 tokens go
     through the streaming kernels in slices of <= max_tokens, more through one tensor-core plan; token counts
     are rounded up to ``token_bucket`` sizes (zero-padded copy in, extra rows dropped)."""
@@ -154,8 +154,15 @@ def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_t
             yout, yoff = torch.empty((bb, cols), dtype=out.dtype, device=out.device), 0
             if accumulate:
                 yout[:b] = dst_rows[:b, y_offset:y_offset + cols]
-        key = key_base + (bb, xin.dtype, yout.dtype, xin.stride(0), yout.stride(0), yoff)
+        key = key_base + (bb, xin.dtype, yout.dtype, xin.stride(0), yout.stride(0), yoff, id(comm) if comm is not None else 0)
+        fresh = key not in _PLAN_CACHE
         plan = _cached_plan(key, lambda: [make_spec(bb, xin.stride(0), yout.stride(0), yoff)])
+        if fresh and comm is not None:
+            try:
+                plan.set_comm(comm)
+            except RuntimeError:
+                _PLAN_CACHE.pop(key).close()
+                raise
         plan.run(xin, yout, workspace=shared_workspace(xin.device, plan.workspace_bytes))
         if bb != b:
             dst_rows[:b, y_offset:y_offset + cols] = yout[:b]
@@ -180,6 +187,14 @@ def _trellis_bits(packed: torch.Tensor) -> int:
 FUSED_MAX_TOKENS = 8        # the single-launch decode form, which also serves the fused norm / activation / residual
 
 
+class _InKernel:
+    """Marks a communicator whose sum the decode kernel itself performs (internal to _fused_trellis)."""
+
+    def __init__(self, comm):
+        self.comm = comm
+        self.world = comm.world
+
+
 def _apply_input_steps(x2d, in_features, in_norm_weight, in_norm_eps, gated_act):
     """The steps the single-launch form fuses, as separate torch kernels (more than 8 tokens)."""
     if gated_act is not None:
@@ -196,8 +211,41 @@ def _apply_input_steps(x2d, in_features, in_norm_weight, in_norm_eps, gated_act)
 
 def _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_rs2, in_features,
                    out_features, n_pad, m_pad, y_rht_out=None, col=0, out_dtype=None,
-                   in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None):
+                   in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None, reduce_over=None):
     _require_cuda(x, "x")
+    comm = None
+    if isinstance(reduce_over, _InKernel):
+        comm, reduce_over = reduce_over.comm, None
+    if reduce_over is not None and reduce_over.world == 1:
+        reduce_over = None
+    if reduce_over is not None:
+        if y_rht_out is not None:
+            raise RuntimeError("glq_b200: reduce_over applies to complete linears only")
+        ntok = x.reshape(-1, in_features * (2 if gated_act is not None else 1)).shape[0]
+        fits = ntok <= FUSED_MAX_TOKENS
+        if fits:
+            try:
+                return _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_rs2, in_features,
+                                      out_features, n_pad, m_pad, out_dtype=out_dtype, in_norm_weight=in_norm_weight,
+                                      in_norm_eps=in_norm_eps, gated_act=gated_act, accumulate_into=accumulate_into,
+                                      reduce_over=_InKernel(reduce_over))
+            except RuntimeError as e:
+                if "plan_set_comm" not in str(e) and "single-launch" not in str(e):
+                    raise
+        # the kernel cannot hold the sum (more than 8 tokens, or no single-launch form): fp32 partial result, then one
+        # launch of the stand-alone sum (or NCCL when it exceeds the communicator's area)
+        part = _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_rs2, in_features,
+                              out_features, n_pad, m_pad, out_dtype=torch.float32, in_norm_weight=in_norm_weight,
+                              in_norm_eps=in_norm_eps, gated_act=gated_act)
+        if part.numel() <= reduce_over.max_floats:
+            reduce_over.all_reduce_(part)
+        else:
+            import torch.distributed as dist
+            dist.all_reduce(part)
+        if accumulate_into is not None:
+            accumulate_into.add_(part.reshape(accumulate_into.shape).to(accumulate_into.dtype))
+            return accumulate_into
+        return part.to(out_dtype or x.dtype)
     x_cols = in_features * (2 if gated_act is not None else 1)
     x2d = x.reshape(-1, x_cols)
     if x2d.stride(-1) != 1:
@@ -245,9 +293,9 @@ def _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_r
     # two decoded stages keep two accumulator sets: 32 tokens per pass instead of 64
     try:
         _run_sliced(x2d, tgt, key, make_spec, 32 if has2 else DECODE_MAX_TOKENS, y_offset=yoff,
-                    out_cols=m_pad if stop else out_features, accumulate=accumulate_into is not None)
+                    out_cols=m_pad if stop else out_features, accumulate=accumulate_into is not None, comm=comm)
     except RuntimeError as e:
-        if not extras or "single-launch" not in str(e):
+        if comm is not None or not extras or "single-launch" not in str(e):
             raise
         # the single-launch form is unavailable for this layer (switched off, or the input does not fit in
         # shared memory): run the steps as their own kernels
@@ -264,16 +312,21 @@ def _fused_trellis(x, sv, su, packed, packed2, blocks_n, blocks_m, wscale, inv_r
 
 def fused_linear_trellis_3inst(x, sv, su, trellis_packed, blocks_n, blocks_m, blocks_n_meta, blocks_m_meta,
                                wscale, in_features, out_features, n_pad, m_pad, *, out_dtype=None,
-                               in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None):
+                               in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None,
+                               reduce_over=None):
     """input RHT -> 3INST decode + matmul -> x Wscale -> output RHT, (B, in) -> (B, out).
     Keyword arguments that are not in the reference: ``out_dtype`` selects the result dtype (default: that of
     x); ``in_norm_weight`` / ``in_norm_eps`` apply an RMSNorm to x first; ``gated_act`` (0 silu, 1 gelu-tanh,
     2 relu^2) takes x as [gate | up] of 2 * in_features values and feeds act(gate) * up; ``accumulate_into``
     adds the result to that (B, out) tensor in place (residual add) and returns it.  Up to 8 tokens these run
-    inside the one decode kernel, above that as separate torch kernels around the linear."""
+    inside the one decode kernel, above that as separate torch kernels around the linear.
+    ``reduce_over`` (a ``glq_b200.comm.Comm``): this rank holds a column shard of a row-parallel layer; the result
+    (and what is added to ``accumulate_into``) is the sum over the communicator's ranks, formed inside the decode
+    kernel up to 8 tokens, else by one extra launch."""
     return _fused_trellis(x, sv, su, trellis_packed, None, blocks_n, blocks_m, wscale, 0.0,
                           in_features, out_features, n_pad, m_pad, out_dtype=out_dtype, in_norm_weight=in_norm_weight,
-                          in_norm_eps=in_norm_eps, gated_act=gated_act, accumulate_into=accumulate_into)
+                          in_norm_eps=in_norm_eps, gated_act=gated_act, accumulate_into=accumulate_into,
+                          reduce_over=reduce_over)
 
 
 def fused_linear_trellis_3inst_rvq2(x, sv, su, trellis_packed, trellis_packed2, blocks_n, blocks_m,

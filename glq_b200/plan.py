@@ -160,6 +160,12 @@ class Plan:
         st = C.c_int32()
         _lib.check(self.lib.glqb_plan_status(self.handle, C.byref(st)), "plan_status")
 
+    def set_comm(self, comm) -> None:
+        """The outputs of all layers become sums over the ranks of ``comm`` (a ``glq_b200.comm.Comm``), computed
+        inside the single-launch decode kernel; raises RuntimeError for plans that do not take that form."""
+        self._comm = comm                       # keeps the communicator alive as long as the plan points at it
+        _lib.check(self.lib.glqb_plan_set_comm(self.handle, comm.handle if comm is not None else None), "plan_set_comm")
+
     def close(self) -> None:
         if getattr(self, "handle", None):
             self.lib.glqb_plan_destroy(self.handle)

@@ -118,6 +118,44 @@ int glqb_plan_status(GlqbPlan* plan, int32_t* status_out);
 void glqb_plan_destroy(GlqbPlan* plan);
 
 /*
+ * Sum over tensor-parallel ranks inside the kernels (one process per GPU, all on one node).  The reference leaves
+ * the sum of row-parallel partial outputs (o_proj, down_proj) to its host framework's NCCL all-reduce
+ * (glq_vllm/linear_method.py:1031-1102 runs under vLLM's RowParallelLinear); for decode-sized outputs that call is
+ * all latency.  A communicator owns one receive area per rank, mapped into every rank (CUDA IPC); a CTA stores its
+ * piece into all ranks' areas, raises a flag per peer, waits (bounded) for the peers' flags and adds the pieces in
+ * rank order 0..G-1, so every rank gets the same bits.  No loads from peer memory, no bulk-tensor copies.
+ *
+ * Set-up, once: every rank calls glqb_comm_create (allocates its area: the only allocation), exchanges the
+ * GLQB_COMM_HANDLE_BYTES handle of glqb_comm_handle with the other ranks by any host channel, and passes all ranks'
+ * handles (rank order, `handle_stride` bytes apart) to glqb_comm_connect.  glqb_comm_connect_local is the same for
+ * communicators that live in one process.  All ranks must then issue the same sequence of launches that use the
+ * communicator (the protocol counts them on the device, so CUDA-graph replays need no changing argument).
+ *
+ * max_floats: fp32 values one launch may exchange per rank.  A wait that exceeds the time limit (default 2 s) sets
+ * the status word instead of hanging: glqb_comm_status returns GLQB_E_DEVICE and the launch's results are invalid.
+ */
+typedef struct GlqbComm GlqbComm;
+#define GLQB_COMM_HANDLE_BYTES 64
+int glqb_comm_create(int32_t rank, int32_t world, int64_t max_floats, GlqbComm** out);
+int glqb_comm_handle(GlqbComm* comm, void* handle_out, int32_t handle_bytes);
+int glqb_comm_connect(GlqbComm* comm, const void* handles, int32_t handle_stride);
+int glqb_comm_connect_local(GlqbComm* comm, GlqbComm* const* comms_by_rank);
+int glqb_comm_set_timeout_ms(GlqbComm* comm, int32_t ms);
+int64_t glqb_comm_max_floats(const GlqbComm* comm);
+/* In-place sum of `count` fp32 values (count <= max_floats) over the ranks, one launch, no host synchronisation. */
+int glqb_comm_all_reduce(GlqbComm* comm, void* buf_f32, int64_t count, void* stream);
+/* Synchronising read of the status word; `reset` != 0 clears it afterwards. */
+int glqb_comm_status(GlqbComm* comm, int32_t* status_out, int32_t reset);
+/* launches that used the communicator so far (synchronising read; equal on all ranks between steps) */
+int glqb_comm_epoch(GlqbComm* comm, int32_t* epoch_out);
+void glqb_comm_destroy(GlqbComm* comm);
+/* The outputs of all layers of `plan` become sums over the communicator's ranks, computed inside the single-launch
+ * decode kernel right after the output transform (fp32, each rank with its own SU): every rank ends with the full
+ * result, the residual add (y_accumulate) included.  Plans that do not take the single-launch form are refused with
+ * GLQB_E_INVALID; sum their fp32 outputs with glqb_comm_all_reduce or NCCL instead.  comm = NULL detaches. */
+int glqb_plan_set_comm(GlqbPlan* plan, GlqbComm* comm);
+
+/*
  * MoE grouped expert matmul over trellis 3INST experts:
  *     out[t] = sum_j topk_weights[t,j] * W2_e( act( W13_e x_t ) ),  e = topk_ids[t,j]
  * Replaces glq_fused_moe_trellis_3inst_cuda (glq/csrc/glq_cuda.cu:5042; schema
