@@ -7,6 +7,14 @@ import types
 import pytest
 
 
+def _reference_dir() -> str:
+    """Where the reference project's sources are, if they are around: $GLQ_REFERENCE_DIR, else a folder named
+    ``reference`` beside this repository."""
+    import os
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    return os.environ.get("GLQ_REFERENCE_DIR") or os.path.join(os.path.dirname(here), "reference")
+
+
 def test_ops_module_exports_reference_names():
     from glq_b200 import dropin, ops
     for name in dropin.SERVED:
@@ -92,7 +100,7 @@ def test_schemas_equal_the_reference_strings_when_the_reference_is_importable(re
     itself needs vLLM's platform layer to import)."""
     import os
     import re
-    path = "/root/reference/glq_vllm/custom_ops.py"
+    path = os.path.join(_reference_dir(), "glq_vllm", "custom_ops.py")
     if not os.path.exists(path):
         pytest.skip("reference sources not present")
     from glq_b200 import dropin
@@ -184,11 +192,12 @@ def test_reference_callers_bind_to_our_operator_signatures():
     functions of glq_b200.ops.  In a child process, so that ops registered by other tests cannot take the call."""
     import os
     import subprocess
-    if not os.path.isdir("/root/reference/glq"):
+    ref = _reference_dir()
+    if not os.path.isdir(os.path.join(ref, "glq")):
         pytest.skip("reference sources not present")
     code = r"""
 import inspect, sys, types
-sys.path.insert(0, "/root/reference"); sys.path.insert(0, %r)
+sys.path.insert(0, %r); sys.path.insert(0, %r)
 import torch
 from glq import inference_kernel as ik
 from glq.quantized_linear import E8RHTLinear
@@ -218,7 +227,7 @@ for name, a in calls:
     assert b.arguments["wscale"] == 0.5
 assert inspect.signature(ops.glq_fused_linear_trellis_3inst_rvq2_cuda).bind(*calls[1][1]).arguments["inv_resid_scale2"] == 0.25
 print("bound", len(calls))
-""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+""" % (ref, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     env = dict(os.environ, TORCHDYNAMO_DISABLE="1")
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=600)
     assert res.returncode == 0 and "bound 2" in res.stdout, res.stdout + res.stderr

@@ -4,7 +4,7 @@ Two ranks of one communicator live in this process, both on cuda:0.  Kernels tha
 share a GPU, so the ranks run one after the other: the rank that goes first stores its pieces and raises its flags,
 then finds nothing from its peer and gives up after a few milliseconds (status 6, checked here: that is the
 bounded-wait test); the rank that goes second finds the first one's flags already raised, never waits, and must
-produce the exact fixed-order sum.  The order of the ranks alternates between rounds, which also exercises the
+produce the exact fixed-order sum.  The order of the ranks alternates between passes, which also exercises the
 double-buffered receive areas.  The real multi-GPU run of the same kernels is `bench.py --gpus N`.
 """
 from __future__ import annotations
@@ -98,7 +98,7 @@ def test_row_parallel_linear_summed_inside_the_decode_kernel(pair, B, m, n):
                                               n, m, n, m, reduce_over=pair[r], **kw)
 
     launches0 = pair[0].epoch()
-    # round 1: rank 1 first (gives up), rank 0 second (complete sum), fp32 output
+    # first pass: rank 1 first (gives up), rank 0 second (complete sum), fp32 output
     call(1, out_dtype=torch.float32)
     torch.cuda.synchronize()
     assert pair[1].status(reset=True) == 6
@@ -110,7 +110,7 @@ def test_row_parallel_linear_summed_inside_the_decode_kernel(pair, B, m, n):
     y_single = [ops.fused_linear_trellis_3inst(xs[r], sh[r]["sv"], sh[r]["su"], sh[r]["p"], None, None, None, None,
                                                sh[r]["ws"], n, m, n, m, out_dtype=torch.float32) for r in range(2)]
     assert torch.equal(y0, y_single[0] + y_single[1])
-    # round 2: rank 0 first, rank 1 second, with the residual add
+    # second pass: rank 0 first, rank 1 second, with the residual add
     h = [res.clone(), res.clone()]
     call(0, accumulate_into=h[0])
     torch.cuda.synchronize()

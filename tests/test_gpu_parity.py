@@ -535,7 +535,7 @@ def test_e8_gemm_vs_oracle(ops, e8_table, e8_cb, stages, T):
 
 
 # ---------------------------------------------------------------------------------------------
-# E8 decode with the codebook resident in shared memory (2-CTA cluster, distributed shared memory)
+# E8 decode with most of the codebook resident in the shared memory of one CTA per SM
 # ---------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("stages,small2", [(1, False), (2, False), (2, True), (4, False)])
 @pytest.mark.parametrize("B", [1, 9])
