@@ -394,7 +394,7 @@ def run_plan_bench(name, D: Dist, args, steps, tokens=None, layers=None, clocks=
 # --------------------------------------------------------------------------------------------------
 # MoE
 # --------------------------------------------------------------------------------------------------
-def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768, bits=(4,), world=1, rank=0):
+def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768, bits=(4,), world=1, rank=0, comm=None):
     """MoE step of the benchmark configuration: 128 experts, top-8, hidden 2048, expert intermediate 768 (gate/up
     fused 2048->1536, down 768->2048), trellis 4 bpw, gelu-tanh gating.  Router logits N(0,1) (near-uniform
     loads) or a Zipf(1.2) popularity over experts.  Expert parallel: fp32 partial results, one all-reduce."""
@@ -437,7 +437,7 @@ def build_moe(device, tokens, skew=None, E=128, top_k=8, hidden=2048, inter=768,
 
     def run(xin):
         # expert parallel: this rank's experts for all tokens, then one all-reduce of (tokens, hidden)
-        return tp.moe_expert_parallel(run_local, xin, topi, topw, E_all)
+        return tp.moe_expert_parallel(run_local, xin, topi, topw, E_all, comm=comm)
 
     code_bytes = (Wt["w13"].numel() * 2 + Wt["w2"].numel() * 2) * world     # all ranks together
     flops = 2 * tokens * top_k * (w13_out * hidden + hidden * inter)
@@ -449,7 +449,7 @@ def run_moe_bench(name, D: Dist, args, steps, tokens=None):
     from glq_b200 import ops
     skew = 1.2 if "zipf" in name else None
     T = tokens or 256
-    W = build_moe(D.device, T, skew, world=D.world, rank=D.rank)
+    W = build_moe(D.device, T, skew, world=D.world, rank=D.rank, comm=rank_comm(D))
     x = W["x"]
     for _ in range(max(args.warmup, 3)):
         y = W["run"](x)
@@ -478,7 +478,8 @@ def run_moe_bench(name, D: Dist, args, steps, tokens=None):
            "unit": "GB/s", "tflops": tf, "ms_per_step": ms, "n_gpus": D.world,
            "config": f"128 experts top-8, hidden 2048, expert intermediate 768, trellis 4 bpw, {T} tokens, "
                      f"{'Zipf(1.2) expert popularity' if skew else 'near-uniform routing'}; 302 MB of expert weights, larger than L2"
-                     + (f"; ep{D.world}: experts sharded over ranks, one fp32 all-reduce of (tokens, hidden)" if D.world > 1 else ""),
+                     + (f"; ep{D.world}: experts sharded over ranks, one fp32 sum of (tokens, hidden) over the ranks "
+                        f"({'glqb_comm_all_reduce' if (rank_comm(D) is not None and T * 2048 <= rank_comm(D).max_floats) else 'ncclAllReduce'})" if D.world > 1 else ""),
            "e2e": {"value": W["code_bytes"] / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                    "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": hy.numel() * hy.element_size()},
            "gpu_launches": (6 if T * 8 < 8192 else 8) * steps}

@@ -118,14 +118,20 @@ def localize_topk_ids(topk_ids: torch.Tensor, e0: int, e1: int) -> torch.Tensor:
 
 
 def moe_expert_parallel(run_local, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor,
-                        num_experts: int, group=None) -> torch.Tensor:
+                        num_experts: int, group=None, comm=None) -> torch.Tensor:
     """``run_local(x, local_ids, topk_weights) -> (tokens, hidden)`` computes this rank's experts; the result is
-    summed over ranks.  With one rank this is just ``run_local``."""
+    summed over ranks.  With one rank this is just ``run_local``.  ``comm`` (a ``glq_b200.comm.Comm`` over the same
+    ranks): fp32 results that fit its receive area are summed by the library's own one-launch kernel instead of
+    NCCL."""
     import torch.distributed as dist
     world = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
     rank = dist.get_rank(group) if world > 1 else 0
     e0, e1 = expert_range(num_experts, world, rank)
     y = run_local(x, localize_topk_ids(topk_ids, e0, e1), topk_weights)
     if world > 1:
-        dist.all_reduce(y, group=group)
+        if (comm is not None and y.dtype == torch.float32 and y.is_contiguous() and y.numel() <= comm.max_floats
+                and y.numel() % 4 == 0):
+            comm.all_reduce_(y)
+        else:
+            dist.all_reduce(y, group=group)
     return y

@@ -176,3 +176,32 @@ def test_checkpoint_folder_index_and_validation(tmp_path):
     with pytest.raises(ck.CheckpointError, match="bpw"):
         c.validate()
     c.close()
+
+
+def test_loader_takes_the_rank_s_own_shard_buffers_when_the_checkpoint_has_them():
+    """Host logic of the tensor-parallel loader (no GPU): with a communicator of G ranks the loader prefers the
+    buffers stored under <layer>.tp<G>.<rank>.<buffer>, and falls back to the whole layer otherwise."""
+    import types
+    from glq_b200.loader import LinearMethod, tp_buffer_key
+    rng = np.random.default_rng(6)
+    cfg = ck.QuantizeConfig.from_dict({"bpw": 4, "codebook": "trellis", "variant": "3inst", "trellis_layout": "kernel"})
+    whole = _trellis_layer(rng, 64, 128, 4)
+    shard1 = _trellis_layer(rng, 64, 64, 4)
+    tensors = {f"m.o_proj.{k}": v for k, v in whole.items()}
+    tensors.update({tp_buffer_key("m.o_proj", k, 2, 1): v for k, v in shard1.items()})
+    fake_comm = types.SimpleNamespace(world=2, rank=1)
+    layer = types.SimpleNamespace()
+    m = LinearMethod(cfg, comm=fake_comm)
+    m.create_weights(layer, 64, [64], 128, 64, torch.bfloat16, row_parallel=True)
+    m.load_from(layer, tensors, ["m.o_proj"])
+    assert layer.glq_tp_sharded and layer.glq_row_parallel
+    assert torch.equal(layer.glq_buffers["trellis_packed"].get_shard(0), shard1["trellis_packed"])
+    # rank 0 has no shard of its own in this checkpoint: the whole layer is taken
+    layer0 = types.SimpleNamespace()
+    m0 = LinearMethod(cfg, comm=types.SimpleNamespace(world=2, rank=0))
+    m0.create_weights(layer0, 128, [64], 128, 64, torch.bfloat16, row_parallel=True)
+    m0.load_from(layer0, tensors, ["m.o_proj"])
+    assert not layer0.glq_tp_sharded
+    assert torch.equal(layer0.glq_buffers["SV"].get_shard(0), whole["SV"])
+    with pytest.raises(ck.CheckpointError, match="shards"):
+        m0.load_from(layer0, tensors, ["a", "b"])
