@@ -657,10 +657,32 @@ def run_linear_latency(D: Dist, args, steps=200):
     g.replay()
     ms = timed(D, g.replay, steps) / 20
     ms_eager = timed(D, call, steps)
+    del g
+    # the same for an E8-shell layer of the reference's own CPU-runnable configuration (2048 x 2048, 2 stages), through
+    # a plan (the call underneath ops.fused_linear_block_diag)
+    from glq_b200.plan import Plan
+    E = synth.e8_layer("lat_e8", 2048, 2048, 2, synth.load_e8_table(dev), gen, dev)
+    y = torch.empty(1, 2048, device=dev, dtype=torch.bfloat16)
+    plan = Plan([E.spec(batch=1, x_stride=2048, y_stride=2048)])
+    call_e8 = lambda: plan.run(x, y)
+    for _ in range(5):
+        call_e8()
+    torch.cuda.synchronize()
+    g2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g2):
+        for _ in range(20):
+            call_e8()
+    g2.replay()
+    ms_e8 = timed(D, g2.replay, steps) / 20
+    e8_launches = plan.launches
+    del g2
+    plan.close()
     ops.clear_caches()
     return {"workload": "linear_call_latency", "metric": "time per call of one 2048x2048 trellis 4 bpw linear, batch 1",
             "value": ms * 1e3, "unit": "us", "higher_is_better": False, "eager_us": ms_eager * 1e3,
-            "config": "20 back-to-back calls in one CUDA graph (value) and eager Python calls (eager_us); weights L2-resident"}
+            "e8_2stage_us": ms_e8 * 1e3, "e8_launches_per_call": e8_launches,
+            "config": "20 back-to-back calls in one CUDA graph (value; e8_2stage_us: the same for a 2048x2048 two-stage E8-shell "
+                      "layer) and eager Python calls (eager_us); weights L2-resident"}
 
 
 # --------------------------------------------------------------------------------------------------

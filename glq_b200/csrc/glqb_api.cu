@@ -438,12 +438,22 @@ static int build_plan(GlqbPlan* P) {
   P->gemm_items.clear();
   P->n_tickets = 0;
   for (Segment& s : P->segs) {
-    if (!s.tn && s.format == GLQB_FMT_TRELLIS_3INST && s.nb == 1 && fused_enabled() && fused_available(s.k1, s.k2)) {
+    if (!s.tn && s.nb == 1 && fused_enabled() && fused_available(s)) {
       // single-launch form: every layer of the segment reads the same input, at most 8 tokens, and the
       // activations plus the transform scratch fit in shared memory
       const GlqbLinearDesc& d0 = P->descs[P->order[s.first]];
+      const bool e8 = s.format == GLQB_FMT_E8_SHELL;
       bool ok = !d0.x_is_rotated && d0.batch <= FUSED_MAX_TOKENS && s.count <= FUSED_MAX_LAYERS;
       for (int i = 1; i < s.count && ok; ++i) ok = same_input(d0, P->descs[P->order[s.first + i]]);
+      if (e8) {
+        // E8 strips are 16 rows: every output block must hold whole strips; the in-kernel input transform takes
+        // blocks of 32 values or more
+        for (int i = 0; i < s.count && ok; ++i) {
+          const GlqbLinearDesc& d = P->descs[P->order[s.first + i]];
+          for (int b = 0; b < d.n_blocks_m; ++b) ok = ok && d.blocks_m[b] >= 16;
+        }
+        for (int b = 0; b < d0.n_blocks_n; ++b) ok = ok && d0.blocks_n[b] >= 32;
+      }
       // wide inputs are transformed once by rht_in_kernel (every CTA recomputing them would cost more than
       // the extra launch); so is a fused RMSNorm whose output block is too long for the in-kernel transform
       static const int in_max_n = [] { const char* e = getenv("GLQB_FUSED_IN_MAX_N"); return e ? atoi(e) : 4096; }();
@@ -465,10 +475,10 @@ static int build_plan(GlqbPlan* P) {
       }
       if (!xr_global)
         for (int i = 0; i < d0.n_blocks_n; ++i) scratch = std::max(scratch, d0.blocks_n[i]);
-      const size_t smem = fused_smem_bytes(d0.n_pad, d0.batch, scratch);
+      const size_t smem = fused_smem_bytes(d0.n_pad, d0.batch, scratch, e8);
       if (ok && smem <= FUSED_SMEM_LIMIT) {
         int resident = 0;
-        CUDA_TRY(fused_prepare(s.k1, s.k2, FUSED_SMEM_LIMIT, smem, &resident));
+        CUDA_TRY(fused_prepare(s, FUSED_SMEM_LIMIT, smem, &resident));
         if (resident > 0) {
           // column groups per warp and unit: fewer for small layers, so that every SM gets work
           auto units_for = [&](int gpw) {
@@ -481,8 +491,8 @@ static int build_plan(GlqbPlan* P) {
           };
           // (every CTA repeats the input transform, so more CTAs than SMs only pays when there is more
           // streaming work than one CTA per SM can take)
-          int gpw = 8;
-          while (gpw > 2 && units_for(gpw) < (long long)cta_factor * P->sm_count) gpw >>= 1;
+          int gpw = e8 ? E8F_MAX_GPW : 8;                  // (an E8 group is 256 columns, a trellis group 32)
+          while (gpw > (e8 ? 1 : 2) && units_for(gpw) < (long long)cta_factor * P->sm_count) gpw >>= 1;
           long long units = units_for(gpw);
           if (units < (1ll << 30)) {
             units = 0;
@@ -641,7 +651,7 @@ static int build_plan(GlqbPlan* P) {
     if (!layer_fused[pos] && (d.in_norm_weight || d.in_gated_act || d.y_accumulate))
       return fail(GLQB_E_INVALID,
                   "layer %d: the fused norm / activation / residual steps are served by the single-launch decode form only "
-                  "(trellis, at most %d tokens, all layers of the call reading one input)", P->order[pos], FUSED_MAX_TOKENS);
+                  "(at most %d tokens, all layers of the call reading one input)", P->order[pos], FUSED_MAX_TOKENS);
   }
   // a call of a few layers is bound by the latency of one transform item, a sweep of many by their throughput
   const bool latency = n <= FUSED_MAX_LAYERS;

@@ -1,4 +1,5 @@
-// Instantiations and launches of the single-launch decode kernels (trellis_fused_kernel, glqb_kernels.cuh).
+// Instantiations and launches of the single-launch decode kernels (trellis_fused_kernel, e8_fused_kernel,
+// glqb_kernels.cuh).
 #include "glqb_kernels.cuh"
 #include <cstdlib>
 #include <cstring>
@@ -20,10 +21,25 @@ static FusedKernel trellis_fused_pick(int k1, int k2) {
   return nullptr;
 }
 
-bool fused_available(int k1, int k2) { return trellis_fused_pick(k1, k2) != nullptr; }
+static FusedKernel e8_fused_pick(int ns) {
+  switch (ns) {
+    case 1: return e8_fused_kernel<1>;
+    case 2: return e8_fused_kernel<2>;
+#ifndef GLQB_FAST_BUILD
+    case 3: return e8_fused_kernel<3>;
+    case 4: return e8_fused_kernel<4>;
+#endif
+  }
+  return nullptr;
+}
+static FusedKernel fused_pick(const Segment& s) {
+  return s.format == GLQB_FMT_E8_SHELL ? e8_fused_pick(s.ns) : trellis_fused_pick(s.k1, s.k2);
+}
 
-cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* resident_ctas_out) {
-  FusedKernel fk = trellis_fused_pick(k1, k2);
+bool fused_available(const Segment& s) { return fused_pick(s) != nullptr; }
+
+cudaError_t fused_prepare(const Segment& s, size_t smem_limit, size_t smem, int* resident_ctas_out) {
+  FusedKernel fk = fused_pick(s);
   cudaError_t e = cudaFuncSetAttribute(fk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
   if (e != cudaSuccess) return e;
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(resident_ctas_out, fk, MV_THREADS, smem);
@@ -50,7 +66,7 @@ void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_ba
   CommDev C;
   memset(&C, 0, sizeof(C));                                           // world 0: no sum over ranks
   if (comm) C = *comm;
-  cudaLaunchKernelEx(&cfg, trellis_fused_pick(s.k1, s.k2), T, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
+  cudaLaunchKernelEx(&cfg, fused_pick(s), T, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
                      tickets, C);
 }
 

@@ -836,10 +836,19 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
   return v;
 }
 
+// bytes of shared memory the transformed activations of a single-launch call take: trellis keeps (x, 0) half pairs
+// in fragment order; E8 keeps fp16 in the order of xr_index_e8 (several tokens: interleaved in groups of eight)
+template <bool E8FMT>
+__host__ __device__ __forceinline__ size_t fused_xs_bytes(int n, int batch) {
+  if (E8FMT) return (size_t)(batch == 1 ? 1 : 8) * n * 2;
+  return (size_t)batch * n * 4;
+}
+
 // shared-memory bytes of the fused kernel: activations (2 halfs per column and token), transform scratch
 // (the largest input block, or output tile, padded by one word per 32), the warps' partial sums
-__host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, int scratch_elems) {
-  return (size_t)batch * n * 4 + ((size_t)scratch_elems + scratch_elems / 32) * 4 + 8 * 256 * 4 + 64;
+__host__ __device__ __forceinline__ size_t fused_smem_bytes(int n, int batch, int scratch_elems, bool e8 = false) {
+  const size_t xs = e8 ? ((fused_xs_bytes<true>(n, batch) + 15) & ~(size_t)15) : fused_xs_bytes<false>(n, batch);
+  return xs + ((size_t)scratch_elems + scratch_elems / 32) * 4 + 8 * 256 * 4 + 64;
 }
 
 // Output transform of one (layer, Hadamard block, token) by the CTA that completed the block, with the
@@ -913,6 +922,164 @@ __device__ __forceinline__ void fused_out_block(const DevLinear& L, int b, int t
   fht_fast<FUSED_OUT_MAX_LOG>(fbuf, logbs, load1, load4, pre, store);
 }
 
+// Phase 1 of the single-launch decode kernels: the transformed activations of the shared input, in shared memory
+// (every CTA computes them itself; wide inputs are copied from the workspace, where rht_in_kernel left them).
+// Fused RMSNorm: rstd_s[token] receives 1 / rms, which the callers apply to the OUTPUT.
+template <bool E8FMT>
+__device__ __forceinline__ void fused_phase1(const DevLinear& L0, int batch, const uint8_t* __restrict__ x_base,
+                                             const uint8_t* __restrict__ ws, __half2* xs, float* fbuf, float* red,
+                                             float* rstd_s) {
+  const int n = L0.n;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (L0.xr_global) {
+    // wide inputs: rht_in_kernel transformed them once, just before this kernel; every CTA copies the result
+    const uint4* src = reinterpret_cast<const uint4*>(ws + L0.xr_off);
+    uint4* dst = reinterpret_cast<uint4*>(xs);
+    const int n16 = (int)(fused_xs_bytes<E8FMT>(n, batch) >> 4);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
+    __syncthreads();
+  } else {
+    const int x_dtype = L0.x_dtype;
+    const void* nw = L0.in_norm_w;
+    const int nw_dtype = L0.in_norm_dtype;
+    const bool gated = L0.in_gated_act != 0;
+    const bool vec_ok = !gated && act_rows_aligned4(x_base, L0.x_off, L0.x_stride, x_dtype) &&
+                        (nw == nullptr || (reinterpret_cast<uintptr_t>(nw) & 15) == 0);
+    const __half* sv = L0.sv;
+    for (int tok = 0; tok < batch; ++tok) {
+      const long long xt0 = L0.x_off + (long long)tok * L0.x_stride;
+      float ss = 0.f;                                        // this thread's share of sum(x^2) (fused RMSNorm)
+      // value of column i_abs fed to the transform: x (or act(gate) * up), times the norm weight, times the sign.
+      // The 1 / rms factor of the norm is a scalar per token and is applied to the output instead.
+      auto load1 = [&](int i_abs) -> float {
+        if (i_abs >= L0.in_f) return 0.f;                    // padded E8 layers
+        float v = input_value(L0, x_base, xt0, i_abs);
+        ss += v * v;
+        if (nw) v *= load_act(nw, i_abs, nw_dtype);
+        return v * __half2float(sv[i_abs]);
+      };
+      for (int b = 0; b < L0.nbn; ++b) {
+        const int off = L0.bn_off[b], logbs = L0.bn_log[b];
+        const float rs = rsqrtf((float)(1 << logbs));
+        const bool vok = vec_ok && (off & 3) == 0;
+        __half2* xt = xs + (size_t)tok * n;                  // trellis: n half2 per token, (x, 0) pairs in fragment order
+        auto put = [&](int i, float val) {
+          const int col = off + i;
+          if constexpr (E8FMT) {
+            reinterpret_cast<__half*>(xs)[xr_index_e8(tok, col, n, batch)] = __float2half_rn(val * rs);
+          } else {
+            xt[((col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31)) >> 1] =
+                __halves2half2(__float2half_rn(val * rs), __float2half_rn(0.f));
+          }
+        };
+        auto ld1 = [&](int i) -> float { return load1(off + i); };
+        auto none = [](int) -> float { return 0.f; };
+        auto put3 = [&](int i, float val, float) { put(i, val); };
+        if (logbs <= FUSED_IN_MAX_LOG) {
+          auto load4 = [&](int i0, float (&q)[4]) {
+            if (vok && off + i0 + 3 < L0.in_f) {             // (padded E8 layers: columns past in_features read as zero)
+              load_act4(x_base, xt0 + off + i0, x_dtype, q);
+              ss += q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3];
+              if (nw) {
+                float w4[4];
+                load_act4(nw, off + i0, nw_dtype, w4);
+                q[0] *= w4[0]; q[1] *= w4[1]; q[2] *= w4[2]; q[3] *= w4[3];
+              }
+              const uint2 s4 = *reinterpret_cast<const uint2*>(sv + off + i0);
+              const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
+              const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
+              q[0] *= a.x; q[1] *= a.y; q[2] *= c.x; q[3] *= c.y;
+            } else {
+#pragma unroll
+              for (int k = 0; k < 4; ++k) q[k] = load1(off + i0 + k);
+            }
+          };
+          fht_fast<FUSED_IN_MAX_LOG>(fbuf, logbs, ld1, load4, none, put3);
+        } else {
+          auto store1 = [&](int, int i, float val) { put(i, val); };
+          auto l1 = [&](int, int i) -> float { return load1(off + i); };
+          auto load32 = [&](int, int i0, float (&v)[32]) {
+#pragma unroll
+            for (int k = 0; k < 32; ++k) v[k] = load1(off + i0 + k);
+          };
+          fht_tile(fbuf, logbs, 1, load32, l1, store1);
+        }
+        __syncthreads();
+      }
+      if (nw) {                                              // every value of the token was loaded exactly once
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp] = ss;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+          float tot = 0.f;
+          for (int w = 0; w < MV_WARPS; ++w) tot += red[w];
+          rstd_s[tok] = rsqrtf(tot / (float)L0.in_f + L0.in_norm_eps);
+        }
+        __syncthreads();
+      }
+    }
+  }
+
+}
+
+// Phase 3 of the single-launch decode kernels: output transforms of the blocks this CTA completed (`todo` entries
+// are (layer << 8) | block), with the sum over tensor-parallel ranks when the layer asks for it.
+__device__ __forceinline__ void fused_phase3(const DevLinear* layers, const int* todo, int nt, int batch, const float* rstd_s,
+                                             const uint8_t* __restrict__ ws, uint8_t* __restrict__ y_base, float* fbuf,
+                                             int scratch_elems, const CommDev& C, int comm_e) {
+  for (int k = 0; k < nt; ++k) {
+    const int li = todo[k] >> 8, b = todo[k] & 255;
+    const DevLinear& L = layers[li];
+    if (L.bm_log[b] <= FUSED_OUT_MAX_LOG) {
+      if (C.world > 1 && L.reduce) {
+        // Row-parallel layer: every rank transforms its own partial result (its own signs), stores the block into
+        // all ranks' receive areas, and after the flag exchange adds the ranks' blocks in rank order: the same bits
+        // on every rank, residual add included.
+        const int logbs = L.bm_log[b], bs = 1 << logbs, off = L.bm_off[b];
+        const long long piece = (long long)L.comm_off + (long long)off * batch;            // floats; a multiple of 32
+        for (int tok = 0; tok < batch; ++tok) {
+          fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf, &C, comm_e, piece + ((long long)tok << logbs));
+          __syncthreads();
+        }
+        comm_signal_and_wait(C, comm_e, L.comm_unit_base + b);
+        const float* src = comm_slot(C, C.rank, comm_e, 0) + piece;
+        const bool accumulate = L.y_accumulate != 0;
+        for (int i = threadIdx.x * 4; i < bs * batch; i += blockDim.x * 4) {
+          float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int r = 0; r < C.world; ++r) {
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * C.max_floats + i));
+            a4.x += t.x; a4.y += t.y; a4.z += t.z; a4.w += t.w;
+          }
+          const float o[4] = {a4.x, a4.y, a4.z, a4.w};
+          const int tok = i >> logbs, j = i & (bs - 1);
+          const long long yo = L.y_off + (long long)tok * L.y_stride + off + j;
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (off + j + c < L.out_f) {
+              float r = o[c];
+              if (accumulate) r += load_act(y_base, yo + c, L.y_dtype);
+              store_act(y_base, yo + c, L.y_dtype, r);
+            }
+        }
+        __syncthreads();
+      } else {
+        for (int tok = 0; tok < batch; ++tok) {
+          fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf);
+          __syncthreads();
+        }
+      }
+    } else {   // not reached: blocks longer than the split threshold are transformed by rht_out_kernel
+      const int bs = 1 << L.bm_log[b];
+      const int tt = max(1, min(batch, scratch_elems / bs));
+      for (int t0 = 0; t0 < batch; t0 += tt) {
+        rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0), -1}, ws, y_base, nullptr, fbuf);
+        __syncthreads();
+      }
+    }
+  }
+}
+
 #ifndef GLQB_FUSED_MINB
 #define GLQB_FUSED_MINB 2
 #endif
@@ -980,91 +1147,7 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
   // ---- phase 1: the transformed activations of the shared input, in shared memory
   __shared__ float rstd_s[FUSED_MAX_TOKENS];                 // fused RMSNorm: 1 / rms per token, applied to the OUTPUT
   if (threadIdx.x < FUSED_MAX_TOKENS) rstd_s[threadIdx.x] = 1.f;
-  if (L0.xr_global) {
-    // wide inputs: rht_in_kernel transformed them once, just before this kernel; every CTA copies the result
-    const uint4* src = reinterpret_cast<const uint4*>(ws + L0.xr_off);
-    uint4* dst = reinterpret_cast<uint4*>(xs);
-    const int n16 = (int)(((size_t)batch * n * 4) >> 4);
-    for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldcg(src + i);
-    __syncthreads();
-  } else {
-    const int x_dtype = L0.x_dtype;
-    const void* nw = L0.in_norm_w;
-    const int nw_dtype = L0.in_norm_dtype;
-    const bool gated = L0.in_gated_act != 0;
-    const bool vec_ok = !gated && act_rows_aligned4(x_base, L0.x_off, L0.x_stride, x_dtype) &&
-                        (nw == nullptr || (reinterpret_cast<uintptr_t>(nw) & 15) == 0);
-    const __half* sv = L0.sv;
-    for (int tok = 0; tok < batch; ++tok) {
-      const long long xt0 = L0.x_off + (long long)tok * L0.x_stride;
-      float ss = 0.f;                                        // this thread's share of sum(x^2) (fused RMSNorm)
-      // value of column i_abs fed to the transform: x (or act(gate) * up), times the norm weight, times the sign.
-      // The 1 / rms factor of the norm is a scalar per token and is applied to the output instead.
-      auto load1 = [&](int i_abs) -> float {
-        float v = input_value(L0, x_base, xt0, i_abs);
-        ss += v * v;
-        if (nw) v *= load_act(nw, i_abs, nw_dtype);
-        return v * __half2float(sv[i_abs]);
-      };
-      for (int b = 0; b < L0.nbn; ++b) {
-        const int off = L0.bn_off[b], logbs = L0.bn_log[b];
-        const float rs = rsqrtf((float)(1 << logbs));
-        const bool vok = vec_ok && (off & 3) == 0;
-        __half2* xt = xs + (size_t)tok * n;                  // n half2 per token
-        auto put = [&](int i, float val) {
-          const int col = off + i;
-          xt[((col & ~31) * XR_TRELLIS_EXPAND + xr_pos_trellis(col & 31)) >> 1] =
-              __halves2half2(__float2half_rn(val * rs), __float2half_rn(0.f));
-        };
-        auto ld1 = [&](int i) -> float { return load1(off + i); };
-        auto none = [](int) -> float { return 0.f; };
-        auto put3 = [&](int i, float val, float) { put(i, val); };
-        if (logbs <= FUSED_IN_MAX_LOG) {
-          auto load4 = [&](int i0, float (&q)[4]) {
-            if (vok) {
-              load_act4(x_base, xt0 + off + i0, x_dtype, q);
-              ss += q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3];
-              if (nw) {
-                float w4[4];
-                load_act4(nw, off + i0, nw_dtype, w4);
-                q[0] *= w4[0]; q[1] *= w4[1]; q[2] *= w4[2]; q[3] *= w4[3];
-              }
-              const uint2 s4 = *reinterpret_cast<const uint2*>(sv + off + i0);
-              const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&s4.x));
-              const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&s4.y));
-              q[0] *= a.x; q[1] *= a.y; q[2] *= c.x; q[3] *= c.y;
-            } else {
-#pragma unroll
-              for (int k = 0; k < 4; ++k) q[k] = load1(off + i0 + k);
-            }
-          };
-          fht_fast<FUSED_IN_MAX_LOG>(fbuf, logbs, ld1, load4, none, put3);
-        } else {
-          auto store1 = [&](int, int i, float val) { put(i, val); };
-          auto l1 = [&](int, int i) -> float { return load1(off + i); };
-          auto load32 = [&](int, int i0, float (&v)[32]) {
-#pragma unroll
-            for (int k = 0; k < 32; ++k) v[k] = load1(off + i0 + k);
-          };
-          fht_tile(fbuf, logbs, 1, load32, l1, store1);
-        }
-        __syncthreads();
-      }
-      if (nw) {                                              // every value of the token was loaded exactly once
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp] = ss;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-          float tot = 0.f;
-          for (int w = 0; w < MV_WARPS; ++w) tot += red[w];
-          rstd_s[tok] = rsqrtf(tot / (float)L0.in_f + L0.in_norm_eps);
-        }
-        __syncthreads();
-      }
-    }
-  }
-
+  fused_phase1<false>(L0, batch, x_base, ws, xs, fbuf, red, rstd_s);
   if (blockIdx.x == 0 && threadIdx.x < batch && L0.in_norm_w && !L0.xr_global)      // for rht_out_kernel (long blocks)
     for (int li = 0; li < n_layers; ++li) reinterpret_cast<float*>(ws + layers[li].rstd_off)[threadIdx.x] = rstd_s[threadIdx.x];
 
@@ -1147,57 +1230,7 @@ trellis_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int to
   __syncthreads();
 
   // ---- phase 3: output transforms of the blocks this CTA completed
-  const int nt = n_todo;
-  for (int k = 0; k < nt; ++k) {
-    const int li = todo[k] >> 8, b = todo[k] & 255;
-    const DevLinear& L = layers[li];
-    if (L.bm_log[b] <= FUSED_OUT_MAX_LOG) {
-      if (C.world > 1 && L.reduce) {
-        // Row-parallel layer: every rank transforms its own partial result (its own signs), stores the block into
-        // all ranks' receive areas, and after the flag exchange adds the ranks' blocks in rank order: the same bits
-        // on every rank, residual add included.
-        const int logbs = L.bm_log[b], bs = 1 << logbs, off = L.bm_off[b];
-        const long long piece = (long long)L.comm_off + (long long)off * batch;            // floats; a multiple of 32
-        for (int tok = 0; tok < batch; ++tok) {
-          fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf, &C, comm_e, piece + ((long long)tok << logbs));
-          __syncthreads();
-        }
-        comm_signal_and_wait(C, comm_e, L.comm_unit_base + b);
-        const float* src = comm_slot(C, C.rank, comm_e, 0) + piece;
-        const bool accumulate = L.y_accumulate != 0;
-        for (int i = threadIdx.x * 4; i < bs * batch; i += blockDim.x * 4) {
-          float4 a4 = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (int r = 0; r < C.world; ++r) {
-            const float4 t = __ldcg(reinterpret_cast<const float4*>(src + (size_t)r * C.max_floats + i));
-            a4.x += t.x; a4.y += t.y; a4.z += t.z; a4.w += t.w;
-          }
-          const float o[4] = {a4.x, a4.y, a4.z, a4.w};
-          const int tok = i >> logbs, j = i & (bs - 1);
-          const long long yo = L.y_off + (long long)tok * L.y_stride + off + j;
-#pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (off + j + c < L.out_f) {
-              float r = o[c];
-              if (accumulate) r += load_act(y_base, yo + c, L.y_dtype);
-              store_act(y_base, yo + c, L.y_dtype, r);
-            }
-        }
-        __syncthreads();
-      } else {
-        for (int tok = 0; tok < batch; ++tok) {
-          fused_out_block(L, b, tok, rstd_s[tok], ws, y_base, fbuf);
-          __syncthreads();
-        }
-      }
-    } else {   // not reached: blocks longer than the split threshold are transformed by rht_out_kernel
-      const int bs = 1 << L.bm_log[b];
-      const int tt = max(1, min(batch, scratch_elems / bs));
-      for (int t0 = 0; t0 < batch; t0 += tt) {
-        rht_out_body<false>(L, RhtItem{li, b, t0, min(tt, batch - t0), -1}, ws, y_base, nullptr, fbuf);
-        __syncthreads();
-      }
-    }
-  }
+  fused_phase3(layers, todo, n_todo, batch, rstd_s, ws, y_base, fbuf, scratch_elems, C, comm_e);
   if (C.world > 1) comm_cta_done(C, comm_e);
 }
 
@@ -1466,6 +1499,192 @@ e8_mv_smem_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
   T.small_base = local + E8S_RESIDENT * 4;
   __syncthreads();
   e8_mv_body<NS, NB, 1>(layers, n_layers, total_groups, per_warp, ws, T, E8S_THREADS / 32);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Single-launch decode linear for E8-shell layers (at most 8 tokens, up to FUSED_MAX_LAYERS layers that read the
+// same input): the same three phases as trellis_fused_kernel with the E8 streaming arithmetic in the middle.
+// A work unit is (layer, 16-row strip, chunk of 8 warps x `per_warp` column groups of 256 columns); a lane (g, t)
+// holds 8 consecutive indices of rows g and g + 8 per group and stage, gathers their packed table entries from
+// global memory (L1 / L2: these launches are far too small to pay for a resident table), expands them with
+// e8_entry_to_half2 and multiplies against the activations kept in shared memory in the order of xr_index_e8.
+// Residual stages keep separate accumulators and are combined with fp32 multiply and add when the unit ends, as
+// in e8_mv_body.  Replaces the three launches (input transform, matvec, output transform) of the reference's E8
+// decode path (glq/csrc/glq_cuda.cu:2533, 3038) by one.
+// ---------------------------------------------------------------------------------------------
+constexpr int E8F_MAX_GPW = 4;                  // column groups per warp and unit (index registers: 8 per group)
+
+template <int NS>
+__global__ void __launch_bounds__(MV_THREADS, GLQB_FUSED_MINB)
+e8_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int total_units, int scratch_elems,
+                const uint8_t* __restrict__ x_base, uint8_t* __restrict__ y_base, uint8_t* __restrict__ ws,
+                int* __restrict__ tickets, const __grid_constant__ CommDev C) {
+  extern __shared__ __align__(16) uint8_t fsm[];
+  const DevLinear* layers = T.L;
+  const DevLinear& L0 = layers[0];
+  const int n = L0.n, batch = L0.batch;
+  __half2* xs = reinterpret_cast<__half2*>(fsm);
+  float* fbuf = reinterpret_cast<float*>(fsm + ((fused_xs_bytes<true>(n, batch) + 15) & ~(size_t)15));
+  float* red = fbuf + scratch_elems + scratch_elems / 32;                       // [8 warps][4 values][32 lanes]
+  __shared__ int todo[FUSED_MAX_TODO];
+  __shared__ int n_todo;
+  if (threadIdx.x == 0) n_todo = 0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, tq = lane & 3;
+
+  struct Unit { int li, strip, chunk, c0, ng; };
+  auto locate = [&](int u) -> Unit {
+    int li = 0;
+    while (li + 1 < n_layers && layers[li + 1].group_base <= u) ++li;
+    const DevLinear& L = layers[li];
+    const int kch = L.fixed_slots;
+    const int local = u - (int)L.group_base;
+    const int strip = local / kch, chunk = local - strip * kch;
+    const int gpw = L.per_warp;
+    const int c0 = (chunk * MV_WARPS + warp) * gpw;
+    return Unit{li, strip, chunk, c0, max(0, min(gpw, L.groups_per_strip - c0))};
+  };
+  // the indices of one stage of a unit: per group 8 of row g (qa) and 8 of row g + 8 (qb), 16 bytes each
+  auto fetch = [&](const Unit& U, int stage, uint4 (&qa)[E8F_MAX_GPW], uint4 (&qb)[E8F_MAX_GPW]) {
+    const DevLinear& L = layers[U.li];
+    const int nidx = L.n >> 3;
+    const uint16_t* q = reinterpret_cast<const uint16_t*>(L.codes[stage]);
+    const int rowA = U.strip * 16 + gq, rowB = rowA + 8;
+    const bool vec_ok = (nidx & 7) == 0 && (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+#pragma unroll
+    for (int i = 0; i < E8F_MAX_GPW; ++i) {
+      qa[i] = make_uint4(0u, 0u, 0u, 0u);
+      qb[i] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < U.ng) {
+        const int i0 = (U.c0 + i) * 32 + tq * 8;
+        const uint16_t* pa = q + (long long)rowA * nidx + i0;
+        const uint16_t* pb = q + (long long)rowB * nidx + i0;
+        if (vec_ok && i0 + 8 <= nidx) {
+          if (rowA < L.m) qa[i] = ld_stream_v4(pa);
+          if (rowB < L.m) qb[i] = ld_stream_v4(pb);
+        } else {
+          uint32_t wa[4] = {0u, 0u, 0u, 0u}, wb[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            if (i0 + k < nidx) {
+              if (rowA < L.m) wa[k >> 1] |= (uint32_t)pa[k] << ((k & 1) * 16);
+              if (rowB < L.m) wb[k >> 1] |= (uint32_t)pb[k] << ((k & 1) * 16);
+            }
+          qa[i] = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+          qb[i] = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+        }
+      }
+    }
+  };
+
+  // The indices do not depend on the activations: request the first unit's before the input transform.
+  int u = blockIdx.x;
+  Unit U = locate(min(u, total_units - 1));
+  uint4 qa0[E8F_MAX_GPW], qb0[E8F_MAX_GPW];
+  if (u < total_units) fetch(U, 0, qa0, qb0);
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const int comm_e = C.world > 1 ? comm_epoch(C) : 0;
+
+  // ---- phase 1: the transformed activations of the shared input, in shared memory
+  __shared__ float rstd_s[FUSED_MAX_TOKENS];
+  if (threadIdx.x < FUSED_MAX_TOKENS) rstd_s[threadIdx.x] = 1.f;
+  fused_phase1<true>(L0, batch, x_base, ws, xs, fbuf, red, rstd_s);
+  if (blockIdx.x == 0 && threadIdx.x < batch && L0.in_norm_w && !L0.xr_global)
+    for (int li = 0; li < n_layers; ++li) reinterpret_cast<float*>(ws + layers[li].rstd_off)[threadIdx.x] = rstd_s[threadIdx.x];
+
+  // ---- phase 2: work units
+  const uint32_t xs_addr = (uint32_t)__cvta_generic_to_shared(xs);
+  const int nidx = n >> 3;
+  // B fragments of one index (8-column block) for this lane's token: 16 bytes at block * xstep
+  const int token = min(gq, batch - 1);                     // columns past the batch repeat the last token
+  const uint32_t xa = xs_addr + (uint32_t)(batch == 1 ? 0 : (token & 7) * 16);
+  const uint32_t xstep = batch == 1 ? 16u : 128u;
+  while (u < total_units) {
+    const DevLinear& L = layers[U.li];
+    const int kch = L.fixed_slots, strip = U.strip, chunk = U.chunk, ng = U.ng, c0 = U.c0;
+    float acc[NS][4];
+#pragma unroll
+    for (int st = 0; st < NS; ++st)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[st][i] = 0.f;
+    if (ng > 0) {
+#pragma unroll
+      for (int st = 0; st < NS; ++st) {
+        uint4 qa[E8F_MAX_GPW], qb[E8F_MAX_GPW];
+        if (st > 0) fetch(U, st, qa, qb);
+        const uint32_t* table = L.table[st];
+        const uint32_t mask = (uint32_t)L.table_entries[st] - 1u;
+#pragma unroll
+        for (int i = 0; i < E8F_MAX_GPW; ++i) {
+          if (i < ng) {
+            const uint4 a4 = st == 0 ? qa0[i] : qa[i], b4 = st == 0 ? qb0[i] : qb[i];
+            const uint32_t wa[4] = {a4.x, a4.y, a4.z, a4.w}, wb[4] = {b4.x, b4.y, b4.z, b4.w};
+            uint32_t ea[8], eb[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {                   // all sixteen gathers of the group in flight
+              ea[k] = __ldg(table + ((wa[k >> 1] >> ((k & 1) * 16)) & mask));
+              eb[k] = __ldg(table + ((wb[k >> 1] >> ((k & 1) * 16)) & mask));
+            }
+            const int i0 = (c0 + i) * 32 + tq * 8;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int blk = min(i0 + k, nidx - 1);
+              uint4 xb = lds_v4(xa + (uint32_t)blk * xstep);
+              if (i0 + k >= nidx) xb = make_uint4(0u, 0u, 0u, 0u);     // past the row end: contributes nothing
+              uint32_t ha[4], hb[4];
+              e8_entry_to_half2(ea[k], ha);
+              e8_entry_to_half2(eb[k], hb);
+              const uint32_t a1[4] = {ha[0], hb[0], ha[1], hb[1]};
+              const uint32_t a2[4] = {ha[2], hb[2], ha[3], hb[3]};
+              mma16816(acc[st], a1, xb.x, xb.y);
+              mma16816(acc[st], a2, xb.z, xb.w);
+            }
+          }
+        }
+      }
+    }
+    // next unit of this CTA: its first-stage indices travel while this one is reduced
+    const int li_now = U.li;
+    u += gridDim.x;
+    if (u < total_units) { U = locate(u); fetch(U, 0, qa0, qb0); }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float v = acc[0][i];
+#pragma unroll
+      for (int st = 1; st < NS; ++st) v = __fadd_rn(v, __fmul_rn(L.stage_scale[st], acc[st][i]));
+      red[(warp * 4 + i) * 32 + lane] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
+      // thread (f, ln): fragment value f of lane ln, summed over the warps in warp order
+      const int f = threadIdx.x >> 5, ln = threadIdx.x & 31;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < MV_WARPS; ++w) sum += red[(w * 4 + f) * 32 + ln];
+      const int row = strip * 16 + (ln >> 2) + ((f >> 1) ? 8 : 0);
+      const int tk = (ln & 3) * 2 + (f & 1);
+      if (tk < batch && row < L.m) reinterpret_cast<float*>(ws + L.part_off)[((long long)chunk * batch + tk) * L.m + row] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int b = 0;
+      while (b + 1 < L.nbm && strip * 16 >= L.bm_off[b + 1]) ++b;
+      const int need = ((1 << L.bm_log[b]) >> 4) * kch;     // output blocks hold whole strips (16 rows or more)
+      int old = -2;
+      if (L.bm_log[b] < L.out_split_log || L.stop_at_yrht)
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(old) : "l"(tickets + L.ticket_base + b) : "memory");
+      if (old + 1 == need) {
+        tickets[L.ticket_base + b] = 0;
+        if (n_todo < FUSED_MAX_TODO) todo[n_todo++] = (li_now << 8) | b;
+      }
+    }
+  }
+  __syncthreads();
+
+  // ---- phase 3: output transforms of the blocks this CTA completed
+  fused_phase3(layers, todo, n_todo, batch, rstd_s, ws, y_base, fbuf, scratch_elems, C, comm_e);
+  if (C.world > 1) comm_cta_done(C, comm_e);
 }
 
 // ---------------------------------------------------------------------------------------------

@@ -44,8 +44,8 @@ void gemm_launch(const Segment& s, const DevLinear* layers, const GemmItem* item
                  int sm_count, cudaStream_t stream);
 
 // ---- glqb_fused.cu
-bool fused_available(int k1, int k2);
-cudaError_t fused_prepare(int k1, int k2, size_t smem_limit, size_t smem, int* resident_ctas_out);
+bool fused_available(const Segment& s);                      // is there a single-launch kernel for the segment's format / rates?
+cudaError_t fused_prepare(const Segment& s, size_t smem_limit, size_t smem, int* resident_ctas_out);
 // `layers`: HOST copy of the segment's table entries (they are passed to the kernel by value)
 // `comm`: null, or the communicator whose ranks' outputs are summed inside the kernel (layers with DevLinear::reduce)
 void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_base, uint8_t* y_base, uint8_t* ws,

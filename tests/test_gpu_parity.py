@@ -561,6 +561,7 @@ def test_e8_resident_table_path_matches_oracle_and_global_path(ops, e8_table, e8
     args = (x, cuda(sv), cuda(su), cuda(qs[0]), full, 0.02, n, m, n, m,
             torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m)), None, None, *tail)
     ops.clear_caches()
+    monkeypatch.setenv("GLQB_FUSED_DECODE", "0")               # the streaming kernels (not the single-launch form)
     monkeypatch.setenv("GLQB_E8_SMEM_MIN_BYTES", "0")          # force the shared-memory table path
     y_smem = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
     ops.clear_caches()
@@ -570,6 +571,50 @@ def test_e8_resident_table_path_matches_oracle_and_global_path(ops, e8_table, e8
     ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02)
     assert relerr(y_smem.cpu().numpy(), ref) <= TOL
     assert relerr(y_smem.cpu().numpy(), y_glob.cpu().numpy()) <= 1e-5
+
+
+@pytest.mark.parametrize("stages,small2", [(1, False), (2, False), (2, True), (3, False), (4, False)])
+@pytest.mark.parametrize("B", [1, 3, 8])
+def test_e8_single_launch_matches_three_launch_form(ops, e8_table, e8_cb, monkeypatch, stages, small2, B):
+    """Up to 8 tokens an E8 layer runs as ONE kernel too (input transform, gathers + matvec, output transform by the
+    CTA that completes a Hadamard block); the three-launch form stays selectable and the two agree far inside the
+    oracle tolerance.  A batch-1 case is wide enough (5376 columns) to have its input transformed by a kernel of
+    its own; n = 832 leaves a ragged last column group; m = 328 has an 8-row Hadamard block, shorter than a strip,
+    and must keep the three-launch form."""
+    full, small = e8_cb
+    rng = np.random.default_rng(900 + stages * 31 + B + int(small2))
+    m, n = (5376, 5376) if (B == 1 and stages == 2 and not small2) else (328 if B == 3 else 320, 832)
+    qs = [rng.integers(0, 65536, size=(m, n // 8), dtype=np.uint16).view(np.int16) for _ in range(stages)]
+    tabs = [e8_table] * stages
+    if small2:
+        qs[1] = rng.integers(0, 256, size=(m, n // 8), dtype=np.uint16).view(np.int16)
+        tabs[1] = e8_table[:256]
+    inv = [0.3, 0.09, 0.027][:stages - 1]
+    su, sv = signs(rng, m), signs(rng, n)
+    W = O.e8_decode_nstage(qs, tabs, inv)
+    x = cuda(rng.standard_normal((B, n)).astype(np.float32), torch.bfloat16)
+    empty_i = torch.empty(0, dtype=torch.int16, device="cuda")
+    empty_h = torch.empty(0, dtype=torch.float16, device="cuda")
+    tail = []
+    for s in range(1, 4):
+        cb = small if (s == 1 and small2) else full
+        tail += [cuda(qs[s]) if stages > s else empty_i, cb if stages > s else empty_h, inv[s - 1] if stages > s else 0.0]
+    args = (x, cuda(sv), cuda(su), cuda(qs[0]), full, 0.02, n, m, n, m,
+            torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m)), None, None, *tail)
+    ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02)
+    outs = {}
+    for form in ("1", "0"):
+        monkeypatch.setenv("GLQB_FUSED_DECODE", form)
+        ops.clear_caches()
+        y = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
+        assert relerr(y.cpu().numpy(), ref) <= TOL, form
+        plan = next(iter(ops._PLAN_CACHE.values()))
+        # 328 rows decompose into 256 + 64 + 8: a block shorter than a 16-row strip keeps the three-launch form
+        single = (1 if n <= 4096 else 2) if m != 328 else 3
+        assert plan.launches == (single if form == "1" else 3), (form, plan.launches)
+        outs[form] = y
+    assert relerr(outs["1"].cpu().numpy(), outs["0"].cpu().numpy()) <= 1e-5
+    ops.clear_caches()
 
 
 def test_glq_linear_module_matches_oracle(e8_table, e8_cb):
