@@ -455,26 +455,65 @@ def _e8_stages(qidxs, codebook, qidxs2, codebook2, inv_rs, qidxs3, codebook3, in
 
 
 def _fused_e8(x, sv, su, codes, tables, scales, wscale, in_features, out_features, n_pad, m_pad, bn, bm,
-              x_is_rotated=False, stop=False, out_dtype=None):
+              x_is_rotated=False, stop=False, out_dtype=None, in_norm_weight=None, in_norm_eps=1e-6, gated_act=None,
+              accumulate_into=None, reduce_over=None, _in_kernel=False):
     _require_cuda(x, "x")
+    comm = reduce_over if (reduce_over is not None and reduce_over.world > 1) else None
+    extras = in_norm_weight is not None or gated_act is not None or accumulate_into is not None
+    if (extras or comm is not None) and not _in_kernel:
+        if stop or x_is_rotated:
+            raise RuntimeError("glq_b200: fused norm / activation / residual / rank-sum steps apply to complete linears only")
+        x2 = x.reshape(-1, in_features * (2 if gated_act is not None else 1))
+        args = (sv, su, codes, tables, scales, wscale, in_features, out_features, n_pad, m_pad, bn, bm)
+        if x2.shape[0] <= FUSED_MAX_TOKENS:
+            try:                                             # all steps inside the one decode kernel
+                return _fused_e8(x2, *args, out_dtype=out_dtype, in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps,
+                                 gated_act=gated_act, accumulate_into=accumulate_into, reduce_over=comm, _in_kernel=True)
+            except RuntimeError as e:
+                if "single-launch" not in str(e) and "plan_set_comm" not in str(e):
+                    raise
+        # more than 8 tokens, or no single-launch form for this layer: the steps as kernels of their own
+        xin = _apply_input_steps(x2, in_features, in_norm_weight, in_norm_eps, gated_act)
+        y = _fused_e8(xin, *args, out_dtype=torch.float32 if comm is not None else out_dtype)
+        if comm is not None:
+            if y.numel() <= comm.max_floats:
+                comm.all_reduce_(y)
+            else:
+                import torch.distributed as dist
+                dist.all_reduce(y)
+        if accumulate_into is not None:
+            accumulate_into.add_(y.reshape(accumulate_into.shape).to(accumulate_into.dtype))
+            return accumulate_into
+        return y if comm is None else y.to(out_dtype or x.dtype)
     feat_in = n_pad if x_is_rotated else in_features
-    x2d = x.reshape(-1, feat_in)
+    x2d = x.reshape(-1, feat_in * (2 if gated_act is not None else 1))
     if x2d.stride(-1) != 1:
         x2d = x2d.contiguous()
     odt = torch.float32 if stop else (out_dtype or x2d.dtype)
-    out = torch.empty(x2d.shape[0], m_pad if stop else out_features, dtype=odt, device=x2d.device)
+    if accumulate_into is not None:
+        out = accumulate_into.reshape(-1, out_features)
+        if out.data_ptr() != accumulate_into.data_ptr() or out.stride(-1) != 1:
+            raise RuntimeError("glq_b200: accumulate_into must be a dense (tokens, out_features) tensor")
+        odt = out.dtype
+    else:
+        out = torch.empty(x2d.shape[0], m_pad if stop else out_features, dtype=odt, device=x2d.device)
 
     def make_spec(b, x_stride, y_stride, y_offset):
         return LinearSpec(format=_lib.FMT_E8_SHELL, m_pad=m_pad, n_pad=n_pad, in_features=feat_in,
                           out_features=m_pad if stop else out_features, codes=codes, tables=tables,
                           stage_scale=scales, su=su, sv=sv, wscale=float(wscale), blocks_n=bn, blocks_m=bm,
                           batch=b, x_dtype=x2d.dtype, y_dtype=odt, x_stride=x_stride, y_stride=y_stride,
-                          y_offset=y_offset, stop_at_yrht=stop, x_is_rotated=x_is_rotated)
+                          y_offset=y_offset, stop_at_yrht=stop, x_is_rotated=x_is_rotated,
+                          in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps, in_gated_act=gated_act,
+                          y_accumulate=accumulate_into is not None)
 
     key = ("e8", tuple(c.data_ptr() for c in codes), tuple(t.data_ptr() for t in tables), tuple(scales),
-           su.data_ptr(), sv.data_ptr(), float(wscale), m_pad, n_pad, in_features, out_features, stop, x_is_rotated)
-    _run_sliced(x2d, out, key, make_spec, 32 if len(codes) > 2 else DECODE_MAX_TOKENS)
-    return out
+           su.data_ptr(), sv.data_ptr(), float(wscale), m_pad, n_pad, in_features, out_features, stop, x_is_rotated,
+           in_norm_weight.data_ptr() if in_norm_weight is not None else 0, float(in_norm_eps), gated_act,
+           accumulate_into is not None)
+    _run_sliced(x2d, out, key, make_spec, 32 if len(codes) > 2 else DECODE_MAX_TOKENS,
+                accumulate=accumulate_into is not None, comm=comm)
+    return accumulate_into if accumulate_into is not None else out
 
 
 _EMPTY = None
@@ -482,24 +521,33 @@ _EMPTY = None
 
 def fused_linear(x, sv, su, qidxs, codebook, wscale, in_features, out_features, n_pad, m_pad, log_n, log_m,
                  qidxs2=_EMPTY, codebook2=_EMPTY, inv_resid_scale=0.0, qidxs3=_EMPTY, codebook3=_EMPTY,
-                 inv_resid_scale2=0.0, qidxs4=_EMPTY, codebook4=_EMPTY, inv_resid_scale3=0.0, out_dtype=None):
-    """Power-of-two padded E8 layer: whole-length Hadamard on both sides."""
+                 inv_resid_scale2=0.0, qidxs4=_EMPTY, codebook4=_EMPTY, inv_resid_scale3=0.0, out_dtype=None, *,
+                 in_norm_weight=None, in_norm_eps=1e-6, gated_act=None, accumulate_into=None, reduce_over=None):
+    """Power-of-two padded E8 layer: whole-length Hadamard on both sides.  The keyword-only arguments are those of
+    ``fused_linear_trellis_3inst`` (not in the reference)."""
     codes, tables, scales = _e8_stages(qidxs, codebook, qidxs2, codebook2, inv_resid_scale, qidxs3, codebook3,
                                        inv_resid_scale2, qidxs4, codebook4, inv_resid_scale3)
     return _fused_e8(x, sv, su, codes, tables, scales, wscale, in_features, out_features, n_pad, m_pad,
-                     [n_pad], [m_pad], out_dtype=out_dtype)
+                     [n_pad], [m_pad], out_dtype=out_dtype, in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps,
+                     gated_act=gated_act, accumulate_into=accumulate_into, reduce_over=reduce_over)
 
 
 def fused_linear_block_diag(x, sv, su, qidxs, codebook, wscale, in_features, out_features, n_pad, m_pad,
                             blocks_n, blocks_m, blocks_n_meta, blocks_m_meta,
                             qidxs2=_EMPTY, codebook2=_EMPTY, inv_resid_scale=0.0, qidxs3=_EMPTY, codebook3=_EMPTY,
                             inv_resid_scale2=0.0, qidxs4=_EMPTY, codebook4=_EMPTY, inv_resid_scale3=0.0,
-                            out_dtype=None):
-    """Unpadded E8 layer with block-diagonal Hadamards."""
+                            out_dtype=None, *, in_norm_weight=None, in_norm_eps=1e-6, gated_act=None,
+                            accumulate_into=None, reduce_over=None):
+    """Unpadded E8 layer with block-diagonal Hadamards.  Keyword-only arguments that are not in the reference, as
+    on ``fused_linear_trellis_3inst``: ``in_norm_weight`` / ``in_norm_eps`` (RMSNorm in front), ``gated_act``
+    (x holds [gate | up]), ``accumulate_into`` (residual add), ``reduce_over`` (sum over tensor-parallel ranks);
+    up to 8 tokens they run inside the one decode kernel."""
     codes, tables, scales = _e8_stages(qidxs, codebook, qidxs2, codebook2, inv_resid_scale, qidxs3, codebook3,
                                        inv_resid_scale2, qidxs4, codebook4, inv_resid_scale3)
     return _fused_e8(x, sv, su, codes, tables, scales, wscale, in_features, out_features, n_pad, m_pad,
-                     _blocks(blocks_n, n_pad), _blocks(blocks_m, m_pad), out_dtype=out_dtype)
+                     _blocks(blocks_n, n_pad), _blocks(blocks_m, m_pad), out_dtype=out_dtype,
+                     in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps, gated_act=gated_act,
+                     accumulate_into=accumulate_into, reduce_over=reduce_over)
 
 
 def dequant_matmul(x, qidxs, codebook, wscale, qidxs2=_EMPTY, codebook2=_EMPTY, inv_resid_scale=0.0,

@@ -124,6 +124,42 @@ def test_row_parallel_linear_summed_inside_the_decode_kernel(pair, B, m, n):
     ops.clear_caches()
 
 
+def test_row_parallel_e8_linear_summed_inside_the_decode_kernel(pair):
+    """The same sum inside the single-launch E8 kernel (two-stage shards of 320 x 576, 2 tokens)."""
+    import os
+    from glq_b200 import ops
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    table = np.load(os.path.join(root, "glq_b200", "data", "e8_shell_packed.npy"))
+    cb = cuda(O.e8_unpack_table(table).astype(np.float16))
+    rng = np.random.default_rng(77)
+    B, m, n = 2, 320, 576
+    ei = torch.empty(0, dtype=torch.int16, device="cuda")
+    eh = torch.empty(0, dtype=torch.float16, device="cuda")
+    bn, bm = torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m))
+    sh, refs, xs = [], [], []
+    for r in range(2):
+        qs = [rng.integers(0, 65536, size=(m, n // 8), dtype=np.uint16).view(np.int16) for _ in range(2)]
+        su = (rng.integers(0, 2, size=m) * 2 - 1).astype(np.float16)
+        sv = (rng.integers(0, 2, size=n) * 2 - 1).astype(np.float16)
+        W = CO.e8_decode(qs, [table, table], [0.1], m, n)
+        x = cuda(rng.standard_normal((B, n)).astype(np.float32), torch.bfloat16)
+        sh.append(dict(q=[cuda(q) for q in qs], su=cuda(su), sv=cuda(sv)))
+        xs.append(x)
+        refs.append(O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02))
+    call = lambda r: ops.fused_linear_block_diag(xs[r], sh[r]["sv"], sh[r]["su"], sh[r]["q"][0], cb, 0.02, n, m, n, m, bn, bm,
+                                                 None, None, sh[r]["q"][1], cb, 0.1, ei, eh, 0.0, ei, eh, 0.0,
+                                                 out_dtype=torch.float32, reduce_over=pair[r])
+    e0 = pair[0].epoch()
+    call(1)
+    torch.cuda.synchronize()
+    assert pair[1].status(reset=True) == 6
+    y = call(0)
+    torch.cuda.synchronize()
+    assert pair[0].status() == 0 and pair[0].epoch() == e0 + 1          # one launch, counted by the kernel itself
+    assert relerr(y.cpu().numpy(), refs[0].astype(np.float64) + refs[1]) <= TOL
+    ops.clear_caches()
+
+
 def test_more_tokens_than_the_kernel_holds_use_the_stand_alone_sum(pair):
     from glq_b200 import ops
     rng = np.random.default_rng(9)

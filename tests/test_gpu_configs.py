@@ -555,6 +555,42 @@ def test_fused_norm_activation_residual(ops, B):
     ops.clear_caches()
 
 
+@pytest.mark.parametrize("B", [1, 5, 20])
+def test_fused_norm_activation_residual_e8(ops, packed_table, cb16, B):
+    """The same three steps around an E8-shell layer (two stages, block-diagonal 320 x 576): inside the single-launch
+    E8 kernel up to 8 tokens, as torch kernels around the linear above that."""
+    rng = np.random.default_rng(7300 + B)
+    m, n = 320, 576
+    qs, inv, W, su, sv, ws = _e8_layer(rng, m, n, 2, packed_table)
+    t = dict(q=[cuda(q) for q in qs], su=cuda(su), sv=cuda(sv))
+    ei = torch.empty(0, dtype=torch.int16, device="cuda")
+    eh = torch.empty(0, dtype=torch.float16, device="cuda")
+    bn, bm = torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m))
+    call = lambda x, **kw: ops.fused_linear_block_diag(x, t["sv"], t["su"], t["q"][0], cb16, ws, n, m, n, m, bn, bm, None, None,
+                                                       t["q"][1], cb16, inv[0], ei, eh, 0.0, ei, eh, 0.0, **kw)
+    x = cuda(rng.standard_normal((B, n)).astype(np.float32) * 3.0, torch.bfloat16)
+    xf = x.float().cpu().numpy()
+    w = cuda(1.0 + 0.2 * rng.standard_normal(n).astype(np.float32), torch.bfloat16)
+    eps = 1e-5
+    y = call(x, in_norm_weight=w, in_norm_eps=eps, out_dtype=torch.float32)
+    xn = _bf16(xf / np.sqrt((xf.astype(np.float64) ** 2).mean(-1, keepdims=True) + eps))
+    xin = _bf16(w.float().cpu().numpy() * xn)
+    assert relerr(y.cpu().numpy(), O.linear_forward(xin, W, su, sv, ws)) <= TOL + 2.0 ** -8
+    xg = cuda(rng.standard_normal((B, 2 * n)).astype(np.float32), torch.bfloat16)
+    g, u = xg.float().cpu().numpy()[:, :n], xg.float().cpu().numpy()[:, n:]
+    res = cuda(rng.standard_normal((B, m)).astype(np.float32), torch.bfloat16)
+    h = res.clone()
+    out = call(xg, gated_act=0, accumulate_into=h)
+    assert out.data_ptr() == h.data_ptr()
+    xin = _bf16(_bf16(O._act("silu")(g)) * u)
+    ref = res.float().cpu().numpy() + O.linear_forward(xin, W, su, sv, ws)
+    assert relerr(h.float().cpu().numpy(), ref) <= TOL + 2.0 ** -7
+    if B <= 8:
+        plans = [p for p in ops._PLAN_CACHE.values() if hasattr(p, "launches")]
+        assert plans and all(p.launches == 1 for p in plans)
+    ops.clear_caches()
+
+
 def test_fused_norm_on_shards_in_one_launch(ops):
     rng = np.random.default_rng(7100)
     n, ms = 2048, [2048, 512, 512]
