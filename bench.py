@@ -504,7 +504,7 @@ def run_moe_bench(name, D: Dist, args, steps, tokens=None):
 # --------------------------------------------------------------------------------------------------
 # dependent chain through the operator layer, and the latency of one linear
 # --------------------------------------------------------------------------------------------------
-def run_chain_bench(D: Dist, args, steps, n_layers=36):
+def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
     """Batch-1 decode where every projection consumes the previous output, through glq_b200.ops (the calls a
     drop-in user makes), captured in one CUDA graph: per layer  qkv(h) -> o(attention stand-in) -> residual ->
     gate/up(h) -> silu(gate) * up -> down -> residual.  SmolLM3-3B shapes, trellis 4 bpw.  The attention itself
@@ -513,14 +513,25 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
     import torch
     import torch.distributed as dist
     from glq_b200 import ops, synth, tp
-    cfg = synth.SMOLLM3_3B
+    cfg = synth.LLAMA3_8B if e8 else synth.SMOLLM3_3B
     dev = D.device
     gen = torch.Generator(device=dev)
     gen.manual_seed(555 + D.rank)
-    shapes = {p: tp.shard_shape(p, m, n, D.world) for p, m, n in cfg["proj"]}
+    shapes = {p: tp.shard_shape(p, m, n, D.world, 16 if e8 else 32, 8 if e8 else 32) for p, m, n in cfg["proj"]}
     Ls = []
+    table = synth.load_e8_table(dev) if e8 else None
+    cb16 = None
+    if e8:
+        # the operator functions take the fp16 codebook the reference passes around; they pack it once
+        import numpy as np
+        nib = table.cpu().numpy().astype(np.uint32)
+        cb16 = torch.from_numpy((((nib[:, None] >> (4 * np.arange(8, dtype=np.uint32))) & 15).astype(np.float32) * 0.5 - 3.0)
+                                .astype(np.float16)).to(dev)
     for li in range(n_layers):
-        d = {p: synth.trellis_layer(f"L{li}.{p}", *shapes[p], [4], gen, dev) for p, _, _ in cfg["proj"]}
+        if e8:
+            d = {p: synth.e8_layer(f"L{li}.{p}", *shapes[p], 2, table, gen, dev) for p, _, _ in cfg["proj"]}
+        else:
+            d = {p: synth.trellis_layer(f"L{li}.{p}", *shapes[p], [4], gen, dev) for p, _, _ in cfg["proj"]}
         d["k"].sv = d["v"].sv = d["q"].sv
         d["up"].sv = d["gate"].sv
         Ls.append(d)
@@ -534,11 +545,20 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
 
     comm = rank_comm(D)
 
+    ei = torch.empty(0, dtype=torch.int16, device=dev)
+    eh = torch.empty(0, dtype=torch.float16, device=dev)
+
     def lin(L, x, **kw):
+        if e8:
+            return ops.fused_linear_block_diag(x, L.sv, L.su, L.codes[0], cb16, L.wscale, L.n, L.m, L.n, L.m, None, None, None, None,
+                                               L.codes[1], cb16, L.stage_scale[0], ei, eh, 0.0, ei, eh, 0.0, **kw)
         return ops.fused_linear_trellis_3inst(x, L.sv, L.su, L.codes[0], None, None, None, None, L.wscale,
                                               L.n, L.m, L.n, L.m, **kw)
 
     def shards(x, group, norm_w):
+        if e8:
+            return ops.fused_linear_e8_shards(x, group[0].sv, [(L.su, L.codes, L.stage_scale, L.wscale, L.m) for L in group], cb16,
+                                              in_norm_weight=norm_w, in_norm_eps=1e-6)
         return ops.fused_linear_trellis_3inst_shards(x, group[0].sv, [(L.su, L.codes[0], None, L.wscale, 0.0, L.m) for L in group],
                                                      in_norm_weight=norm_w, in_norm_eps=1e-6)
 
@@ -591,9 +611,10 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
     total_bytes = D.sum_int(code_bytes)[0]
     gbs = total_bytes / (ms * 1e-3) / 1e9
     glq_launches = sum(p.launches for p in ops._PLAN_CACHE.values() if hasattr(p, "launches"))
-    rec = {"workload": "decode_chain", "metric": METRIC, "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": world,
+    model = "Llama-3-8B decoder layers, E8 shell two-stage (4 bpw)" if e8 else "SmolLM3-3B decoder layers, trellis 4 bpw"
+    rec = {"workload": "decode_chain_e8" if e8 else "decode_chain", "metric": METRIC, "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": world,
            "us_per_layer": ms * 1e3 / n_layers, "us_per_linear": ms * 1e3 / (7 * n_layers),
-           "config": f"{n_layers} SmolLM3-3B decoder layers, trellis 4 bpw, batch 1, every projection consumes the previous "
+           "config": f"{n_layers} {model}, batch 1, every projection consumes the previous "
                      f"output through glq_b200.ops: per layer RMSNorm + q/k/v, o + residual, RMSNorm + gate/up, "
                      f"silu(gate) * up + down + residual as four calls (attention replaced by a view of the q output; "
                      f"{'one CUDA graph' if graph is not None else 'eager launches'}); "
@@ -603,8 +624,9 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36):
            "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h0.numel() * 2,
                    "d2h_bytes_per_step": out.numel() * 2},
            "gpu_launches": glq_launches * steps, "glq_launches_per_layer": glq_launches / n_layers,
-           "roofline": {"bound": "hbm", "kernel": "whole chain: 4 trellis_fused_kernel<4,0> launches per layer for its 7 linears, norms, "
-                                                  "activation and residual adds",
+           "roofline": {"bound": "hbm", "kernel": ("whole chain: 4 e8_fused_kernel<2> launches (+ 1 rht_in_kernel for down) per layer" if e8 else
+                                                  "whole chain: 4 trellis_fused_kernel<4,0> launches (+ 1 rht_in_kernel for down) per layer")
+                                                 + " for its 7 linears, norms, activation and residual adds",
                         "achieved": gbs / world, "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s",
                         "frac": gbs / world / hbm, "kernel_ms": ms, "bytes_per_launch": code_bytes, "traffic": None}}
     if world > 1:
@@ -805,7 +827,7 @@ DEFAULT_SUBS = [
     ("plan", "prefill_trellis", 2048, 4),
     ("plan", "decode_e8_62l", 1, 6), ("plan", "prefill_e8_62l", 2048, 3),
     ("moe", "moe", 256, None), ("moe", "moe", 4096, None), ("moe", "moe_zipf", 256, None), ("moe", "moe_zipf", 4096, None),
-    ("chain", "decode_chain", 1, 36), ("latency", "linear_call_latency", 1, None),
+    ("chain", "decode_chain", 1, 36), ("chain", "decode_chain_e8", 1, 32), ("latency", "linear_call_latency", 1, None),
 ]
 
 
@@ -820,7 +842,7 @@ def main():
     ap.add_argument("--no-subs", action="store_true", help="only the headline workload, no sub-records")
     ap.add_argument("--workload", default="decode_trellis_sweep",
                     help="decode_trellis_sweep (default, the headline with sub-records) or one of: "
-                         + ", ".join(list(WORKLOADS) + ["moe", "moe_zipf", "decode_chain", "linear_call_latency"]))
+                         + ", ".join(list(WORKLOADS) + ["moe", "moe_zipf", "decode_chain", "decode_chain_e8", "linear_call_latency"]))
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None,
                     help="decoder layers to build (default: per workload); smaller values are for profiler captures only")
@@ -850,11 +872,12 @@ def main():
         if kind == "moe":
             return run_moe_bench(name, D, args, n_steps, tokens)
         if kind == "chain":
-            return run_chain_bench(D, args, n_steps, layers or 36)
+            e8 = name == "decode_chain_e8"
+            return run_chain_bench(D, args, n_steps, layers or (32 if e8 else 36), e8=e8)
         return run_linear_latency(D, args)
 
     if args.workload != "decode_trellis_sweep":
-        kind = ("moe" if args.workload.startswith("moe") else "chain" if args.workload == "decode_chain"
+        kind = ("moe" if args.workload.startswith("moe") else "chain" if args.workload.startswith("decode_chain")
                 else "latency" if args.workload == "linear_call_latency" else "plan")
         rec = run_one(kind, args.workload, args.tokens, args.layers, clocks=True, check=True)
         if rank == 0:

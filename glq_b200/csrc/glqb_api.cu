@@ -305,6 +305,16 @@ static int validate(const GlqbLinearDesc& d, int idx) {
   return GLQB_OK;
 }
 
+// packed bytes of a layer's codes (what a decode launch must read once)
+static long long layer_code_bytes(const GlqbLinearDesc& d) {
+  if (d.format == GLQB_FMT_TRELLIS_3INST) {
+    long long b = 0;
+    for (int s = 0; s < d.n_stages; ++s) b += (long long)d.m_pad * d.n_pad * d.bits[s] / 8;
+    return b;
+  }
+  return (long long)d.n_stages * d.m_pad * (d.n_pad / 8) * 2;
+}
+
 // one thread per 32-value segment of the largest tile, between 64 and RHT_THREADS
 // ... except for decode-sized plans (at most 8 tokens), whose transforms use all 256 threads per array
 static int rht_threads(int max_elems, int max_batch = 1 << 30) {
@@ -444,6 +454,15 @@ static int build_plan(GlqbPlan* P) {
       const GlqbLinearDesc& d0 = P->descs[P->order[s.first]];
       const bool e8 = s.format == GLQB_FMT_E8_SHELL;
       bool ok = !d0.x_is_rotated && d0.batch <= FUSED_MAX_TOKENS && s.count <= FUSED_MAX_LAYERS;
+      {
+        // The single-launch form is built for latency: strip-sized work units with a CTA-wide reduction each.  Large
+        // launches are bound by streaming instead and keep the three-launch form (E8: with the resident table).
+        static const long long max_bytes_trellis = [] { const char* e = getenv("GLQB_FUSED_MAX_BYTES"); return e ? atoll(e) : (1ll << 40); }();
+        static const long long max_bytes_e8 = [] { const char* e = getenv("GLQB_FUSED_MAX_BYTES_E8"); return e ? atoll(e) : (32ll << 20); }();
+        long long bytes = 0;
+        for (int i = 0; i < s.count; ++i) bytes += layer_code_bytes(P->descs[P->order[s.first + i]]);
+        ok = ok && bytes <= (e8 ? max_bytes_e8 : max_bytes_trellis);
+      }
       for (int i = 1; i < s.count && ok; ++i) ok = same_input(d0, P->descs[P->order[s.first + i]]);
       if (e8) {
         // E8 strips are 16 rows: every output block must hold whole strips; the in-kernel input transform takes
@@ -648,7 +667,10 @@ static int build_plan(GlqbPlan* P) {
       for (int i = 0; i < s.count; ++i) layer_fused[s.first + i] = 1;
   for (int pos = 0; pos < n; ++pos) {
     const GlqbLinearDesc& d = P->descs[P->order[pos]];
-    if (!layer_fused[pos] && (d.in_norm_weight || d.in_gated_act || d.y_accumulate))
+    // outside the single-launch form the input transform kernel applies the norm / activation (one token per
+    // tile row, at most 8) and the output transform kernel the residual add: decode-sized layers only
+    if (!layer_fused[pos] && (d.in_norm_weight || d.in_gated_act || d.y_accumulate) &&
+        (d.batch > FUSED_MAX_TOKENS || P->dev[pos].gemm_tn))
       return fail(GLQB_E_INVALID,
                   "layer %d: the fused norm / activation / residual steps are served by the single-launch decode form only "
                   "(at most %d tokens, all layers of the call reading one input)", P->order[pos], FUSED_MAX_TOKENS);
@@ -688,10 +710,12 @@ static int build_plan(GlqbPlan* P) {
       if (Q.format == L.format && Q.gemm_tn == L.gemm_tn && Q.n == L.n && Q.in_f == L.in_f && Q.sv == L.sv &&
           Q.batch == L.batch &&
           Q.x_off == L.x_off && Q.x_stride == L.x_stride && Q.x_dtype == L.x_dtype && Q.nbn == L.nbn &&
-          Q.x_is_rotated == L.x_is_rotated &&
+          Q.x_is_rotated == L.x_is_rotated && Q.in_norm_w == L.in_norm_w && Q.in_norm_dtype == L.in_norm_dtype &&
+          Q.in_norm_eps == L.in_norm_eps && Q.in_gated_act == L.in_gated_act &&
           memcmp(e.blocks_n, d.blocks_n, sizeof(int32_t) * d.n_blocks_n) == 0)
         same = q;
     }
+    L.xr_global = 1;       // (three-launch form: a fused RMSNorm is complete in the transformed activations)
     if (same >= 0) {
       L.xr_off = P->dev[same].xr_off;
     } else {

@@ -397,6 +397,52 @@ def fused_linear_trellis_3inst_shards(x, sv, shards, blocks_n=None, out_dtype=No
     return out[:B]
 
 
+def fused_linear_e8_shards(x, sv, shards, codebook, codebook2=None, blocks_n=None, out_dtype=None, in_norm_weight=None,
+                           in_norm_eps=1e-6):
+    """Several unpadded (block-diagonal) E8-shell layers that read the same input — the q/k/v or gate/up parts of a
+    merged layer whose parts share SV — as ONE plan: one launch for up to 8 tokens.  ``shards`` is a sequence of
+    (su, [qidxs, qidxs2, ...], [inv_resid_scale, ...], wscale, m_pad); ``codebook`` the fp16 (65536, 8) table,
+    ``codebook2`` the table of the second stage when it differs (the 256-entry one).  Returns (B, sum of m_pad).
+    ``in_norm_weight`` applies an RMSNorm to x first.  Not in the reference."""
+    _require_cuda(x, "x")
+    n = sv.numel()
+    x2d = x.reshape(-1, n)
+    if x2d.stride(-1) != 1:
+        x2d = x2d.contiguous()
+    B = x2d.shape[0]
+    if in_norm_weight is not None and B > FUSED_MAX_TOKENS:
+        x2d, in_norm_weight = _apply_input_steps(x2d, n, in_norm_weight, in_norm_eps, None), None
+    total_m = sum(int(sh[4]) for sh in shards)
+    odt = out_dtype or x2d.dtype
+    bn = _blocks(blocks_n, n)
+    bb = token_bucket(B)
+    xin = x2d
+    if bb != B:
+        xin = x2d.new_zeros((bb, n))
+        xin[:B] = x2d
+    out = torch.empty((bb, total_m), dtype=odt, device=x2d.device)
+    t1 = e8_packed_table(codebook)
+    t2 = e8_packed_table(codebook2) if codebook2 is not None else t1
+    key = ("e8_shards", tuple(sh[1][0].data_ptr() for sh in shards), sv.data_ptr(), tuple(float(sh[3]) for sh in shards),
+           t1.data_ptr(), t2.data_ptr(), bb, xin.dtype, odt, xin.stride(0),
+           in_norm_weight.data_ptr() if in_norm_weight is not None else 0, float(in_norm_eps))
+
+    def make_specs():
+        specs, col = [], 0
+        for su, qs, inv, wscale, m in shards:
+            tables = [t1] + [t2 if k == 1 else t1 for k in range(1, len(qs))]
+            specs.append(LinearSpec(format=_lib.FMT_E8_SHELL, m_pad=int(m), n_pad=n, in_features=n, out_features=int(m),
+                                    codes=list(qs), tables=tables, stage_scale=[float(v) for v in inv], su=su, sv=sv,
+                                    wscale=float(wscale), blocks_n=bn, blocks_m=block_decompose(int(m)), batch=bb,
+                                    x_dtype=xin.dtype, y_dtype=odt, x_stride=xin.stride(0), y_stride=total_m, y_offset=col,
+                                    in_norm_weight=in_norm_weight, in_norm_eps=in_norm_eps))
+            col += int(m)
+        return specs
+    plan = _cached_plan(key, make_specs)
+    plan.run(xin, out, workspace=shared_workspace(xin.device, plan.workspace_bytes))
+    return out[:B]
+
+
 _ONES: dict = {}
 
 
