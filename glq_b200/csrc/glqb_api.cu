@@ -458,7 +458,7 @@ static int build_plan(GlqbPlan* P) {
         // The single-launch form is built for latency: strip-sized work units with a CTA-wide reduction each.  Large
         // launches are bound by streaming instead and keep the three-launch form (E8: with the resident table).
         static const long long max_bytes_trellis = [] { const char* e = getenv("GLQB_FUSED_MAX_BYTES"); return e ? atoll(e) : (1ll << 40); }();
-        static const long long max_bytes_e8 = [] { const char* e = getenv("GLQB_FUSED_MAX_BYTES_E8"); return e ? atoll(e) : (32ll << 20); }();
+        static const long long max_bytes_e8 = [] { const char* e = getenv("GLQB_FUSED_MAX_BYTES_E8"); return e ? atoll(e) : (16ll << 20); }();
         long long bytes = 0;
         for (int i = 0; i < s.count; ++i) bytes += layer_code_bytes(P->descs[P->order[s.first + i]]);
         ok = ok && bytes <= (e8 ? max_bytes_e8 : max_bytes_trellis);

@@ -555,6 +555,42 @@ def test_fused_norm_activation_residual(ops, B):
     ops.clear_caches()
 
 
+@pytest.mark.parametrize("B,n", [(1, 576), (5, 576), (2, 4672)])
+def test_fused_steps_in_the_three_launch_form(ops, monkeypatch, B, n):
+    """With the single-launch form switched off the same steps are applied by the transform kernels (norm and
+    activation by the input transform, the residual by the output transform); n = 4672 has a 4096-value Hadamard block,
+    which several CTAs share."""
+    monkeypatch.setenv("GLQB_FUSED_DECODE", "0")
+    ops.clear_caches()
+    rng = np.random.default_rng(7400 + B + n)
+    m = 4128                                                   # 4096 + 32: a long output block as well
+    packed = idx(rng, (m // 16) * (n // 16), 64)
+    W = CO.trellis_decode(packed, m, n, 4).astype(np.float32)
+    su, sv, ws = signs(rng, m), signs(rng, n), 0.02
+    t = dict(p=cuda(packed), su=cuda(su), sv=cuda(sv))
+    call = lambda x, **kw: ops.fused_linear_trellis_3inst(x, t["sv"], t["su"], t["p"], None, None, None, None, ws,
+                                                          n, m, n, m, **kw)
+    x = cuda(rng.standard_normal((B, n)).astype(np.float32) * 3.0, torch.bfloat16)
+    xf = x.float().cpu().numpy()
+    w = cuda(1.0 + 0.2 * rng.standard_normal(n).astype(np.float32), torch.bfloat16)
+    eps = 1e-5
+    res = cuda(rng.standard_normal((B, m)).astype(np.float32), torch.bfloat16)
+    h = res.clone()
+    call(x, in_norm_weight=w, in_norm_eps=eps, accumulate_into=h)
+    plans = [p for p in ops._PLAN_CACHE.values() if hasattr(p, "launches")]
+    assert plans and all(p.launches == 3 for p in plans)
+    xn = _bf16(xf / np.sqrt((xf.astype(np.float64) ** 2).mean(-1, keepdims=True) + eps))
+    xin = _bf16(w.float().cpu().numpy() * xn)
+    ref = res.float().cpu().numpy() + O.linear_forward(xin, W, su, sv, ws)
+    assert relerr(h.float().cpu().numpy(), ref) <= TOL + 2.0 ** -7
+    xg = cuda(rng.standard_normal((B, 2 * n)).astype(np.float32), torch.bfloat16)
+    g, u = xg.float().cpu().numpy()[:, :n], xg.float().cpu().numpy()[:, n:]
+    y = call(xg, gated_act=1, out_dtype=torch.float32)
+    xin = _bf16(_bf16(O._act(O.ACT_CODES[1])(g)) * u)
+    assert relerr(y.cpu().numpy(), O.linear_forward(xin, W, su, sv, ws)) <= TOL + 2.0 ** -8
+    ops.clear_caches()
+
+
 @pytest.mark.parametrize("B", [1, 5, 20])
 def test_fused_norm_activation_residual_e8(ops, packed_table, cb16, B):
     """The same three steps around an E8-shell layer (two stages, block-diagonal 320 x 576): inside the single-launch
