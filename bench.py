@@ -479,7 +479,7 @@ def run_moe_bench(name, D: Dist, args, steps, tokens=None):
            "config": f"128 experts top-8, hidden 2048, expert intermediate 768, trellis 4 bpw, {T} tokens, "
                      f"{'Zipf(1.2) expert popularity' if skew else 'near-uniform routing'}; 302 MB of expert weights, larger than L2"
                      + (f"; ep{D.world}: experts sharded over ranks, one fp32 sum of (tokens, hidden) over the ranks "
-                        f"({'glqb_comm_all_reduce' if (rank_comm(D) is not None and T * 2048 <= rank_comm(D).max_floats) else 'ncclAllReduce'})" if D.world > 1 else ""),
+                        f"({'glqb_comm_all_reduce' if (rank_comm(D) is not None and T * 2048 <= min(rank_comm(D).max_floats, 1 << 18)) else 'ncclAllReduce'})" if D.world > 1 else ""),
            "e2e": {"value": W["code_bytes"] / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                    "h2d_bytes_per_step": x.numel() * 2, "d2h_bytes_per_step": hy.numel() * hy.element_size()},
            "gpu_launches": (6 if T * 8 < 8192 else 8) * steps}

@@ -129,8 +129,10 @@ def moe_expert_parallel(run_local, x: torch.Tensor, topk_ids: torch.Tensor, topk
     e0, e1 = expert_range(num_experts, world, rank)
     y = run_local(x, localize_topk_ids(topk_ids, e0, e1), topk_weights)
     if world > 1:
-        if (comm is not None and y.dtype == torch.float32 and y.is_contiguous() and y.numel() <= comm.max_floats
-                and y.numel() % 4 == 0):
+        # (one-shot sums send every value to every peer: beyond about a megabyte NCCL's ring / in-switch sums win;
+        # measured at 8 GPUs: 0.6 MB 5 % faster than NCCL, 2 MB 6 % slower)
+        if (comm is not None and y.dtype == torch.float32 and y.is_contiguous()
+                and y.numel() <= min(comm.max_floats, 1 << 18)):
             comm.all_reduce_(y)
         else:
             dist.all_reduce(y, group=group)
