@@ -143,6 +143,7 @@ static MvKernel e8_kernel(int ns, int nb) {
 }
 
 constexpr size_t FUSED_SMEM_LIMIT = 200 * 1024;
+constexpr size_t FUSED_SMEM_MAX = 226 * 1024;       // one CTA per SM (the E8 form with a resident codebook); 1 KB left for static shared memory
 static bool fused_enabled() {
   const char* e = getenv("GLQB_FUSED_DECODE");
   return !e || atoi(e) != 0;
@@ -464,6 +465,7 @@ static int build_plan(GlqbPlan* P) {
         ok = ok && bytes <= (e8 ? max_bytes_e8 : max_bytes_trellis);
       }
       for (int i = 1; i < s.count && ok; ++i) ok = same_input(d0, P->descs[P->order[s.first + i]]);
+      if (!e8) ok = ok && d0.in_features == d0.n_pad;   // (trellis layers are never padded; the kernel's loads rely on it)
       if (e8) {
         // E8 strips are 16 rows: every output block must hold whole strips; the in-kernel input transform takes
         // blocks of 32 values or more
@@ -494,10 +496,35 @@ static int build_plan(GlqbPlan* P) {
       }
       if (!xr_global)
         for (int i = 0; i < d0.n_blocks_n; ++i) scratch = std::max(scratch, d0.blocks_n[i]);
-      const size_t smem = fused_smem_bytes(d0.n_pad, d0.batch, scratch, e8);
-      if (ok && smem <= FUSED_SMEM_LIMIT) {
+      size_t smem = fused_smem_bytes(d0.n_pad, d0.batch, scratch, e8);
+      size_t smem_limit = FUSED_SMEM_LIMIT;
+      s.res_entries = 0;
+      if (ok && e8 && smem <= FUSED_SMEM_LIMIT) {
+        // E8 launches of a few MB and more keep as much of the codebook in shared memory as fits beside the
+        // activations (one CTA per SM): otherwise every SM pulls most of the table through L2, one 32-byte sector
+        // per gather
+        const char* res_env = getenv("GLQB_E8_FUSED_RES_MIN_BYTES");          // (read per plan: the tests switch it)
+        const long long res_min = res_env ? atoll(res_env) : (3ll << 20);
+        long long bytes = 0;
+        const uint32_t* big = nullptr;
+        const uint32_t* small = nullptr;
+        int small_n = 0;
+        if (e8_uniform_tables(P->dev, s, &big, &small, &small_n, &bytes) && bytes >= res_min) {
+          const size_t room = FUSED_SMEM_MAX > smem + 1024 ? FUSED_SMEM_MAX - smem - 1024 : 0;
+          const int res = (int)std::min<size_t>(65536, room / 4 / 1024 * 1024);
+          if (res >= 32768) {
+            s.res_entries = res;
+            s.big_table = big;
+            s.small_table = small ? small : big;
+            s.small_entries = small_n;
+            smem += (size_t)res * 4 + 1024;
+            smem_limit = FUSED_SMEM_MAX;
+          }
+        }
+      }
+      if (ok && smem <= smem_limit) {
         int resident = 0;
-        CUDA_TRY(fused_prepare(s, FUSED_SMEM_LIMIT, smem, &resident));
+        CUDA_TRY(fused_prepare(s, smem_limit, smem, &resident));
         if (resident > 0) {
           // column groups per warp and unit: fewer for small layers, so that every SM gets work
           auto units_for = [&](int gpw) {
@@ -510,7 +537,11 @@ static int build_plan(GlqbPlan* P) {
           };
           // (every CTA repeats the input transform, so more CTAs than SMs only pays when there is more
           // streaming work than one CTA per SM can take)
-          int gpw = e8 ? E8F_MAX_GPW : 8;                  // (an E8 group is 256 columns, a trellis group 32)
+          // (an E8 group is 256 columns, a trellis group 32.)  No more groups per warp than keep all 8 warps of a
+          // unit busy on the narrowest layer: a 4096-wide E8 layer has 16 groups per strip, two per warp.
+          int gps_min = 1 << 30;
+          for (int i = 0; i < s.count; ++i) gps_min = std::min(gps_min, P->dev[s.first + i].groups_per_strip);
+          int gpw = std::min(e8 ? E8F_MAX_GPW : 8, std::max(1, (gps_min + MV_WARPS - 1) / MV_WARPS));
           while (gpw > (e8 ? 1 : 2) && units_for(gpw) < (long long)cta_factor * P->sm_count) gpw >>= 1;
           long long units = units_for(gpw);
           if (units < (1ll << 30)) {

@@ -21,25 +21,30 @@ static FusedKernel trellis_fused_pick(int k1, int k2) {
   return nullptr;
 }
 
-static FusedKernel e8_fused_pick(int ns) {
+typedef void (*E8FusedKernel)(const FusedLayers, int, int, int, const uint8_t*, uint8_t*, uint8_t*, int*, const CommDev,
+                              const uint32_t*, int, const uint32_t*, int);
+template <bool RES>
+static E8FusedKernel e8_fused_pick_r(int ns) {
   switch (ns) {
-    case 1: return e8_fused_kernel<1>;
-    case 2: return e8_fused_kernel<2>;
+    case 1: return e8_fused_kernel<1, RES>;
+    case 2: return e8_fused_kernel<2, RES>;
 #ifndef GLQB_FAST_BUILD
-    case 3: return e8_fused_kernel<3>;
-    case 4: return e8_fused_kernel<4>;
+    case 3: return e8_fused_kernel<3, RES>;
+    case 4: return e8_fused_kernel<4, RES>;
 #endif
   }
   return nullptr;
 }
-static FusedKernel fused_pick(const Segment& s) {
-  return s.format == GLQB_FMT_E8_SHELL ? e8_fused_pick(s.ns) : trellis_fused_pick(s.k1, s.k2);
+static E8FusedKernel e8_fused_pick(int ns, bool res) { return res ? e8_fused_pick_r<true>(ns) : e8_fused_pick_r<false>(ns); }
+static const void* fused_pick(const Segment& s) {
+  if (s.format == GLQB_FMT_E8_SHELL) return reinterpret_cast<const void*>(e8_fused_pick(s.ns, s.res_entries > 0));
+  return reinterpret_cast<const void*>(trellis_fused_pick(s.k1, s.k2));
 }
 
 bool fused_available(const Segment& s) { return fused_pick(s) != nullptr; }
 
 cudaError_t fused_prepare(const Segment& s, size_t smem_limit, size_t smem, int* resident_ctas_out) {
-  FusedKernel fk = fused_pick(s);
+  const void* fk = fused_pick(s);
   cudaError_t e = cudaFuncSetAttribute(fk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_limit);
   if (e != cudaSuccess) return e;
   return cudaOccupancyMaxActiveBlocksPerMultiprocessor(resident_ctas_out, fk, MV_THREADS, smem);
@@ -66,7 +71,12 @@ void fused_launch(const Segment& s, const DevLinear* layers, const uint8_t* x_ba
   CommDev C;
   memset(&C, 0, sizeof(C));                                           // world 0: no sum over ranks
   if (comm) C = *comm;
-  cudaLaunchKernelEx(&cfg, fused_pick(s), T, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
+  if (s.format == GLQB_FMT_E8_SHELL) {
+    cudaLaunchKernelEx(&cfg, e8_fused_pick(s.ns, s.res_entries > 0), T, s.count, s.total_units, s.scratch_elems, x_base, y_base,
+                       ws, tickets, C, s.big_table, s.res_entries, s.small_table, s.small_entries);
+    return;
+  }
+  cudaLaunchKernelEx(&cfg, trellis_fused_pick(s.k1, s.k2), T, s.count, s.total_units, s.scratch_elems, x_base, y_base, ws,
                      tickets, C);
 }
 

@@ -952,7 +952,7 @@ __device__ __forceinline__ void fused_phase1(const DevLinear& L0, int batch, con
       // value of column i_abs fed to the transform: x (or act(gate) * up), times the norm weight, times the sign.
       // The 1 / rms factor of the norm is a scalar per token and is applied to the output instead.
       auto load1 = [&](int i_abs) -> float {
-        if (i_abs >= L0.in_f) return 0.f;                    // padded E8 layers
+        if (E8FMT && i_abs >= L0.in_f) return 0.f;           // padded E8 layers (trellis layers are never padded)
         float v = input_value(L0, x_base, xt0, i_abs);
         ss += v * v;
         if (nw) v *= load_act(nw, i_abs, nw_dtype);
@@ -977,7 +977,7 @@ __device__ __forceinline__ void fused_phase1(const DevLinear& L0, int batch, con
         auto put3 = [&](int i, float val, float) { put(i, val); };
         if (logbs <= FUSED_IN_MAX_LOG) {
           auto load4 = [&](int i0, float (&q)[4]) {
-            if (vok && off + i0 + 3 < L0.in_f) {             // (padded E8 layers: columns past in_features read as zero)
+            if (vok && (!E8FMT || off + i0 + 3 < L0.in_f)) { // (padded E8 layers: columns past in_features read as zero)
               load_act4(x_base, xt0 + off + i0, x_dtype, q);
               ss += q[0] * q[0] + q[1] * q[1] + q[2] * q[2] + q[3] * q[3];
               if (nw) {
@@ -1514,12 +1514,27 @@ e8_mv_smem_kernel(const DevLinear* __restrict__ layers, int n_layers, long long 
 // ---------------------------------------------------------------------------------------------
 constexpr int E8F_MAX_GPW = 4;                  // column groups per warp and unit (index registers: 8 per group)
 
-template <int NS>
-__global__ void __launch_bounds__(MV_THREADS, GLQB_FUSED_MINB)
+// RES: the first `res_entries` entries of the 65,536-entry table (and a small second-stage table) are copied into
+// shared memory at the start of the kernel — before the wait for the previous kernel, so the copy overlaps its tail
+// — and one CTA runs per SM.  Used for launches of a few MB and more, where every SM would otherwise pull most of
+// the table through L2 one 32-byte sector per gather (the launch's shared memory leaves too little L1 to hold it).
+template <int NS, bool RES>
+__global__ void __launch_bounds__(MV_THREADS, RES ? 1 : GLQB_FUSED_MINB)
 e8_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int total_units, int scratch_elems,
                 const uint8_t* __restrict__ x_base, uint8_t* __restrict__ y_base, uint8_t* __restrict__ ws,
-                int* __restrict__ tickets, const __grid_constant__ CommDev C) {
-  extern __shared__ __align__(16) uint8_t fsm[];
+                int* __restrict__ tickets, const __grid_constant__ CommDev C, const uint32_t* __restrict__ big_table,
+                int res_entries, const uint32_t* __restrict__ small_table, int small_entries) {
+  extern __shared__ __align__(16) uint8_t fsm_all[];
+  uint8_t* fsm = fsm_all + (RES ? (size_t)res_entries * 4 + 1024 : 0);
+  const uint32_t table_smem = (uint32_t)__cvta_generic_to_shared(fsm_all);
+  const uint32_t small_smem = table_smem + (uint32_t)res_entries * 4u;
+  if constexpr (RES) {
+    const uint4* src = reinterpret_cast<const uint4*>(big_table);
+    uint4* dst = reinterpret_cast<uint4*>(fsm_all);
+    for (int i = threadIdx.x; i < res_entries / 4; i += blockDim.x) dst[i] = __ldg(src + i);
+    uint32_t* sm = reinterpret_cast<uint32_t*>(fsm_all + (size_t)res_entries * 4);
+    for (int i = threadIdx.x; i < small_entries && i < 256; i += blockDim.x) sm[i] = __ldg(small_table + i);
+  }
   const DevLinear* layers = T.L;
   const DevLinear& L0 = layers[0];
   const int n = L0.n, batch = L0.batch;
@@ -1615,6 +1630,24 @@ e8_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int total_u
         if (st > 0) fetch(U, st, qa, qb);
         const uint32_t* table = L.table[st];
         const uint32_t mask = (uint32_t)L.table_entries[st] - 1u;
+        // resident form: big-table entries below res_entries and every small-table entry come from shared memory
+        const bool is_big = L.table_entries[st] == 65536;
+        const uint32_t sbase = is_big ? table_smem : small_smem;
+        const uint32_t slimit = is_big ? (uint32_t)res_entries : 256u;
+        auto gather = [&](uint32_t idx) -> uint32_t {
+          if constexpr (RES) {
+            uint32_t v;
+            asm volatile("{\n\t.reg .pred p;\n\t"
+                         "setp.ge.u32 p, %1, %2;\n\t"
+                         "@!p ld.shared.u32 %0, [%3];\n\t"
+                         "@p ld.global.nc.u32 %0, [%4];\n\t}"
+                         : "=r"(v)
+                         : "r"(idx), "r"(slimit), "r"(sbase + (idx << 2)), "l"(table + idx));
+            return v;
+          } else {
+            return __ldg(table + idx);
+          }
+        };
 #pragma unroll
         for (int i = 0; i < E8F_MAX_GPW; ++i) {
           if (i < ng) {
@@ -1623,8 +1656,8 @@ e8_fused_kernel(const __grid_constant__ FusedLayers T, int n_layers, int total_u
             uint32_t ea[8], eb[8];
 #pragma unroll
             for (int k = 0; k < 8; ++k) {                   // all sixteen gathers of the group in flight
-              ea[k] = __ldg(table + ((wa[k >> 1] >> ((k & 1) * 16)) & mask));
-              eb[k] = __ldg(table + ((wb[k >> 1] >> ((k & 1) * 16)) & mask));
+              ea[k] = gather((wa[k >> 1] >> ((k & 1) * 16)) & mask);
+              eb[k] = gather((wb[k >> 1] >> ((k & 1) * 16)) & mask);
             }
             const int i0 = (c0 + i) * 32 + tq * 8;
 #pragma unroll

@@ -30,6 +30,7 @@ struct Segment {
   const uint32_t* big_table = nullptr;
   const uint32_t* small_table = nullptr;
   int small_entries = 0;
+  int res_entries = 0;       // single-launch E8 form: table entries kept in shared memory (0: all gathers go to L1 / L2)
 };
 
 

@@ -603,17 +603,21 @@ def test_e8_single_launch_matches_three_launch_form(ops, e8_table, e8_cb, monkey
             torch.tensor(O.block_decompose(n)), torch.tensor(O.block_decompose(m)), None, None, *tail)
     ref = O.linear_forward(x.float().cpu().numpy(), W, su, sv, 0.02)
     outs = {}
-    for form in ("1", "0"):
-        monkeypatch.setenv("GLQB_FUSED_DECODE", form)
+    # "1": gathers through L1 / L2 (small launches); "res": most of the codebook copied into shared memory first (what
+    # launches of a few MB do by themselves); "0": three launches
+    for form in ("1", "res", "0"):
+        monkeypatch.setenv("GLQB_FUSED_DECODE", "0" if form == "0" else "1")
+        monkeypatch.setenv("GLQB_E8_FUSED_RES_MIN_BYTES", "0" if form == "res" else str(1 << 40))
         ops.clear_caches()
         y = ops.fused_linear_block_diag(*args, out_dtype=torch.float32)
         assert relerr(y.cpu().numpy(), ref) <= TOL, form
         plan = next(iter(ops._PLAN_CACHE.values()))
         # 328 rows decompose into 256 + 64 + 8: a block shorter than a 16-row strip keeps the three-launch form
         single = (1 if n <= 4096 else 2) if m != 328 else 3
-        assert plan.launches == (single if form == "1" else 3), (form, plan.launches)
+        assert plan.launches == (single if form != "0" else 3), (form, plan.launches)
         outs[form] = y
     assert relerr(outs["1"].cpu().numpy(), outs["0"].cpu().numpy()) <= 1e-5
+    assert torch.equal(outs["1"], outs["res"])               # same arithmetic, only the source of the table entries differs
     ops.clear_caches()
 
 
