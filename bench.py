@@ -504,7 +504,7 @@ def run_moe_bench(name, D: Dist, args, steps, tokens=None):
 # --------------------------------------------------------------------------------------------------
 # dependent chain through the operator layer, and the latency of one linear
 # --------------------------------------------------------------------------------------------------
-def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
+def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False, dense62=False):
     """Batch-1 decode where every projection consumes the previous output, through glq_b200.ops (the calls a
     drop-in user makes), captured in one CUDA graph: per layer  qkv(h) -> o(attention stand-in) -> residual ->
     gate/up(h) -> silu(gate) * up -> down -> residual.  SmolLM3-3B shapes, trellis 4 bpw.  The attention itself
@@ -513,7 +513,8 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
     import torch
     import torch.distributed as dist
     from glq_b200 import ops, synth, tp
-    cfg = synth.LLAMA3_8B if e8 else synth.SMOLLM3_3B
+    cfg = synth.DENSE_62L if dense62 else synth.LLAMA3_8B if e8 else synth.SMOLLM3_3B
+    stage_cycle = [2, 3, 3] if dense62 else [2]          # nominal 4 / 5 / 6 bpw
     dev = D.device
     gen = torch.Generator(device=dev)
     gen.manual_seed(555 + D.rank)
@@ -529,7 +530,7 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
                                 .astype(np.float16)).to(dev)
     for li in range(n_layers):
         if e8:
-            d = {p: synth.e8_layer(f"L{li}.{p}", *shapes[p], 2, table, gen, dev) for p, _, _ in cfg["proj"]}
+            d = {p: synth.e8_layer(f"L{li}.{p}", *shapes[p], stage_cycle[li % len(stage_cycle)], table, gen, dev) for p, _, _ in cfg["proj"]}
         else:
             d = {p: synth.trellis_layer(f"L{li}.{p}", *shapes[p], [4], gen, dev) for p, _, _ in cfg["proj"]}
         d["k"].sv = d["v"].sv = d["q"].sv
@@ -550,8 +551,11 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
 
     def lin(L, x, **kw):
         if e8:
+            tail = []
+            for st in range(1, 4):
+                tail += [L.codes[st], cb16, L.stage_scale[st - 1]] if st < len(L.codes) else [ei, eh, 0.0]
             return ops.fused_linear_block_diag(x, L.sv, L.su, L.codes[0], cb16, L.wscale, L.n, L.m, L.n, L.m, None, None, None, None,
-                                               L.codes[1], cb16, L.stage_scale[0], ei, eh, 0.0, ei, eh, 0.0, **kw)
+                                               *tail, **kw)
         return ops.fused_linear_trellis_3inst(x, L.sv, L.su, L.codes[0], None, None, None, None, L.wscale,
                                               L.n, L.m, L.n, L.m, **kw)
 
@@ -611,8 +615,9 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
     total_bytes = D.sum_int(code_bytes)[0]
     gbs = total_bytes / (ms * 1e-3) / 1e9
     glq_launches = sum(p.launches for p in ops._PLAN_CACHE.values() if hasattr(p, "launches"))
-    model = "Llama-3-8B decoder layers, E8 shell two-stage (4 bpw)" if e8 else "SmolLM3-3B decoder layers, trellis 4 bpw"
-    rec = {"workload": "decode_chain_e8" if e8 else "decode_chain", "metric": METRIC, "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": world,
+    model = ("decoder layers of the 62-layer dense shape (hidden 5376, intermediate 21504), E8 shell 2 / 3 / 3 stages" if dense62 else
+             "Llama-3-8B decoder layers, E8 shell two-stage (4 bpw)" if e8 else "SmolLM3-3B decoder layers, trellis 4 bpw")
+    rec = {"workload": "decode_chain_62l" if dense62 else "decode_chain_e8" if e8 else "decode_chain", "metric": METRIC, "value": gbs, "unit": "GB/s", "ms_per_step": ms, "n_gpus": world,
            "us_per_layer": ms * 1e3 / n_layers, "us_per_linear": ms * 1e3 / (7 * n_layers),
            "config": f"{n_layers} {model}, batch 1, every projection consumes the previous "
                      f"output through glq_b200.ops: per layer RMSNorm + q/k/v, o + residual, RMSNorm + gate/up, "
@@ -624,7 +629,7 @@ def run_chain_bench(D: Dist, args, steps, n_layers=36, e8=False):
            "e2e": {"value": total_bytes / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h0.numel() * 2,
                    "d2h_bytes_per_step": out.numel() * 2},
            "gpu_launches": glq_launches * steps, "glq_launches_per_layer": glq_launches / n_layers,
-           "roofline": {"bound": "hbm", "kernel": ("whole chain: 4 e8_fused_kernel<2> launches (+ 1 rht_in_kernel for down) per layer" if e8 else
+           "roofline": {"bound": "hbm", "kernel": ("whole chain: e8_fused_kernel for the launches of up to 16 MB of indices, rht_in + e8_mv(_smem)_kernel + rht_out above" if e8 else
                                                   "whole chain: 4 trellis_fused_kernel<4,0> launches (+ 1 rht_in_kernel for down) per layer")
                                                  + " for its 7 linears, norms, activation and residual adds",
                         "achieved": gbs / world, "peak": hbm, "peak_kind": f"of {kind}", "unit": "GB/s",
@@ -827,7 +832,8 @@ DEFAULT_SUBS = [
     ("plan", "prefill_trellis", 2048, 4),
     ("plan", "decode_e8_62l", 1, 6), ("plan", "prefill_e8_62l", 2048, 3),
     ("moe", "moe", 256, None), ("moe", "moe", 4096, None), ("moe", "moe_zipf", 256, None), ("moe", "moe_zipf", 4096, None),
-    ("chain", "decode_chain", 1, 36), ("chain", "decode_chain_e8", 1, 32), ("latency", "linear_call_latency", 1, None),
+    ("chain", "decode_chain", 1, 36), ("chain", "decode_chain_e8", 1, 32), ("chain", "decode_chain_62l", 1, 62),
+    ("latency", "linear_call_latency", 1, None),
 ]
 
 
@@ -842,7 +848,7 @@ def main():
     ap.add_argument("--no-subs", action="store_true", help="only the headline workload, no sub-records")
     ap.add_argument("--workload", default="decode_trellis_sweep",
                     help="decode_trellis_sweep (default, the headline with sub-records) or one of: "
-                         + ", ".join(list(WORKLOADS) + ["moe", "moe_zipf", "decode_chain", "decode_chain_e8", "linear_call_latency"]))
+                         + ", ".join(list(WORKLOADS) + ["moe", "moe_zipf", "decode_chain", "decode_chain_e8", "decode_chain_62l", "linear_call_latency"]))
     ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--layers", type=int, default=None,
                     help="decoder layers to build (default: per workload); smaller values are for profiler captures only")
@@ -872,8 +878,9 @@ def main():
         if kind == "moe":
             return run_moe_bench(name, D, args, n_steps, tokens)
         if kind == "chain":
-            e8 = name == "decode_chain_e8"
-            return run_chain_bench(D, args, n_steps, layers or (32 if e8 else 36), e8=e8)
+            dense62 = name == "decode_chain_62l"
+            e8 = name == "decode_chain_e8" or dense62
+            return run_chain_bench(D, args, n_steps, layers or (62 if dense62 else 32 if e8 else 36), e8=e8, dense62=dense62)
         return run_linear_latency(D, args)
 
     if args.workload != "decode_trellis_sweep":
