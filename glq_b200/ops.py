@@ -30,6 +30,7 @@ DECODE_MAX_TOKENS = 64
 # create an unbounded number of plans per layer.
 PLAN_CACHE_MAX = int(os.environ.get("GLQB_PLAN_CACHE_MAX", "16384"))
 _PLAN_CACHE: "OrderedDict" = OrderedDict()
+_REFUSED: dict = {}                  # plan keys the library refused (form not available), with the message
 _TABLE_CACHE: dict = {}
 _WORKSPACES: dict = {}
 _RETIRED_WORKSPACES: list = []      # outgrown buffers stay alive: captured CUDA graphs may still point at them
@@ -130,6 +131,7 @@ def clear_caches() -> None:
     for p in _PLAN_CACHE.values():
         p.close()
     _PLAN_CACHE.clear()
+    _REFUSED.clear()
     _TABLE_CACHE.clear()
     _WORKSPACES.clear()
     _RETIRED_WORKSPACES.clear()
@@ -155,14 +157,24 @@ def _run_sliced(x2d: torch.Tensor, out: torch.Tensor, key_base, make_spec, max_t
             if accumulate:
                 yout[:b] = dst_rows[:b, y_offset:y_offset + cols]
         key = key_base + (bb, xin.dtype, yout.dtype, xin.stride(0), yout.stride(0), yoff, id(comm) if comm is not None else 0)
+        refused = _REFUSED.get(key)
+        if refused is not None:                       # the library refused this form before: do not build the plan again
+            raise RuntimeError(refused)
         fresh = key not in _PLAN_CACHE
-        plan = _cached_plan(key, lambda: [make_spec(bb, xin.stride(0), yout.stride(0), yoff)])
-        if fresh and comm is not None:
-            try:
-                plan.set_comm(comm)
-            except RuntimeError:
-                _PLAN_CACHE.pop(key).close()
-                raise
+        try:
+            plan = _cached_plan(key, lambda: [make_spec(bb, xin.stride(0), yout.stride(0), yoff)])
+            if fresh and comm is not None:
+                try:
+                    plan.set_comm(comm)
+                except RuntimeError:
+                    _PLAN_CACHE.pop(key).close()
+                    raise
+        except RuntimeError as e:
+            # callers fall back to another form on these two refusals, call after call (also inside graph capture,
+            # where building and freeing a plan is not allowed): remember them
+            if "single-launch" in str(e) or "plan_set_comm" in str(e):
+                _REFUSED[key] = str(e)
+            raise
         plan.run(xin, yout, workspace=shared_workspace(xin.device, plan.workspace_bytes))
         if bb != b:
             dst_rows[:b, y_offset:y_offset + cols] = yout[:b]

@@ -177,3 +177,33 @@ def test_more_tokens_than_the_kernel_holds_use_the_stand_alone_sum(pair):
     assert pair[1].status() == 0
     assert relerr(y.cpu().numpy(), refs[0].astype(np.float64) + refs[1]) <= TOL
     ops.clear_caches()
+
+
+def test_refused_in_kernel_sum_falls_back_without_rebuilding_plans(pair, monkeypatch):
+    """With the single-launch form switched off the plan cannot hold the sum: the operator computes this rank's fp32
+    result with the three-launch form and sums it with the stand-alone kernel.  The refusal is remembered, so later
+    calls (which may sit inside a CUDA graph capture, where building a plan is not allowed) build nothing."""
+    from glq_b200 import ops
+    monkeypatch.setenv("GLQB_FUSED_DECODE", "0")
+    ops.clear_caches()
+    rng = np.random.default_rng(31)
+    B, m, n = 2, 352, 576
+    sh = [_shard(rng, m, n), _shard(rng, m, n)]
+    xs = [cuda(rng.standard_normal((B, n)).astype(np.float32), torch.bfloat16) for _ in range(2)]
+    refs = [O.linear_forward(xs[r].float().cpu().numpy(), sh[r]["W"], sh[r]["su_h"], sh[r]["sv_h"], sh[r]["ws"]) for r in range(2)]
+    call = lambda r: ops.fused_linear_trellis_3inst(xs[r], sh[r]["sv"], sh[r]["su"], sh[r]["p"], None, None, None, None,
+                                                    sh[r]["ws"], n, m, n, m, reduce_over=pair[r], out_dtype=torch.float32)
+    call(0)
+    torch.cuda.synchronize()
+    assert pair[0].status(reset=True) == 6
+    y = call(1)
+    torch.cuda.synchronize()
+    assert pair[1].status() == 0
+    assert relerr(y.cpu().numpy(), refs[0].astype(np.float64) + refs[1]) <= TOL
+    assert len(ops._REFUSED) == 2                             # one refused form per rank's layer
+    plans = len(ops._PLAN_CACHE)
+    call(0)                                                   # (gives up again: nobody answers)
+    torch.cuda.synchronize()
+    assert pair[0].status(reset=True) == 6
+    assert len(ops._PLAN_CACHE) == plans and len(ops._REFUSED) == 2
+    ops.clear_caches()
