@@ -900,15 +900,28 @@ def main():
         subs = []
         if not args.no_subs and not args.layers:
             sub_steps = max(3, min(steps, 10))
+            failed = False
             for kind, name, tokens, layers in DEFAULT_SUBS:
                 if world > 1 and kind == "latency":
                     continue
+                if world > 1:
+                    # ranks agree before every sub-record: after a failure on any rank all of them stop here (a
+                    # sub-record must not take the headline down with it, nor leave ranks waiting for each other)
+                    flag = torch.tensor([1.0 if failed else 0.0], device=device)
+                    dist.all_reduce(flag)
+                    if flag.item() > 0:
+                        subs.append({"workload": name, "tokens": tokens, "error": "skipped after an earlier failure"})
+                        failed = True
+                        continue
                 try:
                     subs.append(run_one(kind, name, tokens, layers, check=(kind == "plan"), n_steps=sub_steps))
-                except Exception as e:      # a sub-record must not take the headline down with it
+                except Exception as e:
                     subs.append({"workload": name, "tokens": tokens, "error": f"{type(e).__name__}: {e}"})
-                    if world > 1:
-                        raise
+                    failed = True
+                    try:
+                        torch.cuda.synchronize()
+                    except Exception:
+                        pass
         if rank == 0:
             config = headline_config(args.gpus)
             if args.layers:
